@@ -1,0 +1,268 @@
+"""CPU oracle for the SAF mixed-attention hot path.  TEST INFRASTRUCTURE ONLY.
+
+This module restates, in plain torch CPU arithmetic (fp32 or fp64), what the
+reference computes on the path the CUDA library accelerates.  It is the checker
+for the parity tests, for ``__graft_entry__.smoke()`` and for the CPU-baseline
+leg of ``bench.py``; the product (the ``kernel`` package and the C-ABI library)
+never imports it and has no CPU fallback.
+
+Parity status: PINNED.  ``tests/golden/make_golden.py`` imports the reference
+itself (its eager ``CausalSelfAttention`` capture path, its cheap split path,
+``kernel/indexed_linear.py`` and the host helpers of ``kernel/fused_attn.py``,
+all of which run on CPU) and stores their outputs on seeded inputs under
+``tests/golden/``; ``tests/test_oracle_golden.py`` checks every function below
+against those vectors.  The GQA ``kvidx`` variant has no test in the reference;
+it is pinned against the reference's eager formula with repeated KV heads.
+
+Each function cites the reference file:line it follows (paths are relative to
+the reference project root).
+"""
+import math
+
+import torch
+
+BAND_ROWS = 64          # kernel/fused_attn.py:58
+
+
+# ---------------------------------------------------------------------------
+# error metrics used by every parity test
+# ---------------------------------------------------------------------------
+def max_abs(a, b):
+    return (a.double() - b.double()).abs().max().item() if a.numel() else 0.0
+
+
+def rel_l2(a, b):
+    """||a-b|| / ||b||  (supplement/test_controls.py:40-44 uses the same pair)."""
+    if a.numel() == 0:
+        return 0.0
+    d = (a.double() - b.double()).norm().item()
+    n = b.double().norm().item()
+    return d / max(n, 1e-30)
+
+
+# ---------------------------------------------------------------------------
+# RoPE                                                    nanogpt/model.py:57-99
+# ---------------------------------------------------------------------------
+def rope_cache(hd, T, base=10000.0, dtype=torch.float32):
+    """cos/sin tables (T, hd) = cat(freqs, freqs); nanogpt/model.py:73-83."""
+    inv_freq = 1.0 / (base ** (torch.arange(0, hd, 2, dtype=torch.float32) / hd))
+    pos = torch.arange(T, dtype=torch.float32)
+    freqs = torch.outer(pos, inv_freq)
+    emb = torch.cat((freqs, freqs), dim=-1)
+    return emb.cos().to(dtype), emb.sin().to(dtype)
+
+
+def rotate_half(x):
+    """nanogpt/model.py:57-60."""
+    x1, x2 = x.chunk(2, dim=-1)
+    return torch.cat((-x2, x1), dim=-1)
+
+
+def apply_rope(x, cos, sin):
+    """x: (..., T, hd); cos/sin: (T, hd).  nanogpt/model.py:63-68."""
+    return x * cos + rotate_half(x) * sin
+
+
+# ---------------------------------------------------------------------------
+# pattern builders
+# ---------------------------------------------------------------------------
+def sink_decay_pattern(alpha, rho, T, dtype=torch.float64):
+    """P[h,i,j] = a_h [j=0] + (1-a_h) rho_h^(i-j) / Z_i  for j<=i, else 0.
+
+    The structured pattern of the headline benchmark configuration (sink on
+    column 0 plus a geometric decay over distance); rows sum to one.  The
+    reference can only hold it as a dense state-1 buffer installed through
+    ``freeze_heads`` (nanogpt/model.py:705-733)."""
+    alpha = torch.as_tensor(alpha, dtype=dtype).reshape(-1)
+    rho = torch.as_tensor(rho, dtype=dtype).reshape(-1)
+    i = torch.arange(T, dtype=dtype)
+    dist = i[:, None] - i[None, :]
+    causal = dist >= 0
+    out = []
+    for a, r in zip(alpha.tolist(), rho.tolist()):
+        dec = torch.where(causal, torch.tensor(r, dtype=dtype) ** dist.clamp(min=0), torch.zeros((), dtype=dtype))
+        z = dec.sum(-1, keepdim=True)
+        p = (1.0 - a) * dec / z
+        p[:, 0] += a
+        out.append(p)
+    return torch.stack(out)
+
+
+def freeze_normalise(patterns):
+    """tril + row renormalisation applied at install time; nanogpt/model.py:716-719."""
+    patterns = patterns.tril()
+    return patterns / patterns.sum(-1, keepdim=True).clamp_min(1e-12)
+
+
+def decomp_logits(alpha, rho, rows=None):
+    """L[h,i,j] = alpha[h,j] + rho[h,i-j], -inf for j>i.  kernel/fused_attn.py:83-98."""
+    H, S = alpha.shape
+    r0, r1 = (0, S) if rows is None else rows
+    i = torch.arange(r0, r1)
+    j = torch.arange(S)
+    dist = i[:, None] - j[None, :]
+    lg = alpha[:, None, :] + rho[:, dist.clamp(min=0)]
+    return lg.masked_fill(dist < 0, float("-inf"))
+
+
+def decomposed_logz(alpha, rho, chunk=256):
+    """z[h,i] = logsumexp_{j<=i}(alpha[h,j] + rho[h,i-j]).  kernel/fused_attn.py:101-116."""
+    H, S = alpha.shape
+    z = torch.empty_like(alpha)
+    for i0 in range(0, S, chunk):
+        i1 = min(i0 + chunk, S)
+        z[:, i0:i1] = decomp_logits(alpha, rho, rows=(i0, i1)).logsumexp(-1)
+    return z
+
+
+def make_rho_band(rho):
+    """band[h,r,u] = rho[h, r-u+(S-64)], -inf outside [0,S).  kernel/fused_attn.py:65-80."""
+    H, S = rho.shape
+    assert S % BAND_ROWS == 0
+    r = torch.arange(BAND_ROWS)[:, None]
+    u = torch.arange(S)[None, :]
+    src = r - u + (S - BAND_ROWS)
+    band = rho[:, src.clamp(0, S - 1)]
+    ninf = torch.full((), float("-inf"), dtype=rho.dtype)
+    return torch.where((src >= 0) & (src < S), band, ninf).contiguous()
+
+
+def decomp_pattern(alpha, rho, z, T):
+    """exp(alpha[j] + rho[i-j] - z[i]) on the causal triangle; nanogpt/model.py:796-803,
+    kernel/test_fused_attn.py:40-50."""
+    lg = decomp_logits(alpha[:, :T], rho[:, :T])
+    return torch.exp(lg - z[:, :T, None])
+
+
+# ---------------------------------------------------------------------------
+# mixed attention                     nanogpt/model.py:824-844 (eager oracle),
+#                                     kernel/test_fused_attn.py:53-63 (ref())
+# ---------------------------------------------------------------------------
+def mixed_attn(q, k, v, patt, frozen, hidx=None, pidx=None, sm_scale=None,
+               alpha=None, rho=None, z=None, kvidx=None, dtype=torch.float32,
+               row_chunk=1024):
+    """Eager mixed attention, one (batch, head) and one row chunk at a time.
+
+    q, k: (B, U, T, hd) compact live heads (or (B, HKV, T, hd) k with kvidx);
+    v: (B, H, T, hd) (or (B, HKV, T, hd) with kvidx); frozen: (H,) ints with
+    0 = live softmax(q k^T * sm_scale) v, 1 = patt[pidx[h] or h, :T, :T] @ v,
+    2 = exp(alpha[j] + rho[i-j] - z[i]) @ v.  Returns (B, H, T, hd) in `dtype`.
+    Differentiable w.r.t. q, k, v (autograd gives the backward oracle).
+    """
+    frozen = [int(x) for x in torch.as_tensor(frozen).tolist()]
+    H = len(frozen)
+    B, T, hd = v.shape[0], v.shape[2], v.shape[3]
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(hd)
+    hidx = list(range(H)) if hidx is None else [int(x) for x in torch.as_tensor(hidx).tolist()]
+    pidx = list(range(H)) if pidx is None else [int(x) for x in torch.as_tensor(pidx).tolist()]
+    kv = None if kvidx is None else [int(x) for x in torch.as_tensor(kvidx).tolist()]
+    ar = torch.arange(T)
+    outs = []
+    for b in range(B):
+        per_head = []
+        for h in range(H):
+            vh = v[b, kv[h] if kv is not None else h].to(dtype)
+            rows = []
+            for i0 in range(0, T, row_chunk):
+                i1 = min(i0 + row_chunk, T)
+                if frozen[h] == 0:
+                    qh = q[b, hidx[h], i0:i1].to(dtype)
+                    kh = k[b, kv[h] if kv is not None else hidx[h], :i1].to(dtype)
+                    s = (qh @ kh.t()) * sm_scale
+                    mask = ar[i0:i1, None] >= ar[None, :i1]
+                    p = s.masked_fill(~mask, float("-inf")).softmax(-1)
+                elif frozen[h] == 1:
+                    p = patt[pidx[h], i0:i1, :i1].to(dtype)
+                else:
+                    lg = decomp_logits(alpha[h:h + 1, :T].to(dtype), rho[h:h + 1, :T].to(dtype),
+                                       rows=(i0, i1))[0, :, :i1]
+                    p = torch.exp(lg - z[h, i0:i1, None].to(dtype))
+                rows.append(p @ vh[:i1])
+            per_head.append(torch.cat(rows, 0))
+        outs.append(torch.stack(per_head))
+    return torch.stack(outs)
+
+
+def frozen_pv(patt, v, fz_idx, T, dtype=torch.float32):
+    """y[b,f] = patt[fz_idx[f], :T, :T] @ v[b,f].  kernel/test_frozen_attn.py:27-28."""
+    fz = torch.as_tensor(fz_idx).long()
+    return torch.matmul(patt[fz, :T, :T].to(dtype).unsqueeze(0), v.to(dtype))
+
+
+def sink_decay_scan(v, alpha, rho, dtype=torch.float64):
+    """O(T) form of sink_decay_pattern(alpha, rho) @ v for one head.
+
+    s_i = rho s_{i-1} + v_i ; Z_i = rho Z_{i-1} + 1 ; y_i = a v_0 + (1-a) s_i / Z_i.
+    v: (T, hd).  Used to check that the scan identity equals the dense product."""
+    T = v.shape[0]
+    y = torch.empty(T, v.shape[1], dtype=dtype)
+    s = torch.zeros(v.shape[1], dtype=dtype)
+    zn = 0.0
+    v = v.to(dtype)
+    for i in range(T):
+        s = rho * s + v[i]
+        zn = rho * zn + 1.0
+        y[i] = alpha * v[0] + (1.0 - alpha) * s / zn
+    return y
+
+
+# ---------------------------------------------------------------------------
+# indexed linear                                     kernel/indexed_linear.py
+# ---------------------------------------------------------------------------
+def linear_rows(x, weight, bias, rows):
+    """F.linear(x, weight[rows], bias[rows]).  kernel/indexed_linear.py:28-38."""
+    w = weight[rows]
+    b = None if bias is None else bias[rows]
+    return torch.nn.functional.linear(x, w, b)
+
+
+def linear_rows2(x, w1, w2, b1, b2, rows):
+    """[x@w1[rows]^T + b1[rows], x@w2[rows]^T + b2[rows]] on the feature dim.
+    kernel/indexed_linear.py:86-98."""
+    return torch.cat([linear_rows(x, w1, b1, rows), linear_rows(x, w2, b2, rows)], dim=-1)
+
+
+def linear_permuted_cols(y, weight, bias, cols):
+    """F.linear(y, weight[:, cols], bias).  kernel/indexed_linear.py:58-70."""
+    return torch.nn.functional.linear(y, weight[:, cols], bias)
+
+
+# ---------------------------------------------------------------------------
+# one attention layer (the module hook)     nanogpt/model.py:1063-1077, 824-844
+# ---------------------------------------------------------------------------
+def attention_layer(x, wq, wk, wv, wo, frozen, patt, n_head, rope=None, alpha=None, rho=None,
+                    z=None, dtype=torch.float32, row_chunk=1024):
+    """Eager capture path of the reference's CausalSelfAttention in dynamic mode:
+    full q/k/v projections, RoPE on q,k, softmax for live heads and stored pattern
+    for frozen ones, then c_proj.  x: (B,T,C); w*: (C,C) in F.linear layout.
+    `frozen`: (H,) ints 0/1/2; patt: (H,S,S) or None.  rope = (cos, sin) (T,hd)."""
+    B, T, C = x.shape
+    hd = C // n_head
+    x = x.to(dtype)
+    q = (x @ wq.to(dtype).t()).view(B, T, n_head, hd).transpose(1, 2)
+    k = (x @ wk.to(dtype).t()).view(B, T, n_head, hd).transpose(1, 2)
+    v = (x @ wv.to(dtype).t()).view(B, T, n_head, hd).transpose(1, 2)
+    if rope is not None:
+        cos, sin = rope[0].to(dtype), rope[1].to(dtype)
+        q, k = apply_rope(q, cos, sin), apply_rope(k, cos, sin)
+    y = mixed_attn(q, k, v, patt, frozen, alpha=alpha, rho=rho, z=z, dtype=dtype, row_chunk=row_chunk)
+    y = y.transpose(1, 2).reshape(B, T, C)
+    return y @ wo.to(dtype).t()
+
+
+# ---------------------------------------------------------------------------
+# seeded synthetic inputs of the benchmark configurations
+# ---------------------------------------------------------------------------
+def frozen_heads_for_layer(n_head, n_frozen, seed, layer):
+    """Seeded permutation choice of frozen heads (benchmark configurations 1-4)."""
+    g = torch.Generator().manual_seed(seed + layer)
+    return sorted(torch.randperm(n_head, generator=g)[:n_frozen].tolist())
+
+
+def sink_decay_params(n, seed):
+    """alpha ~ U(0.05, 0.3), rho ~ U(0.8, 0.99) per frozen head."""
+    g = torch.Generator().manual_seed(seed)
+    a = 0.05 + 0.25 * torch.rand(n, generator=g, dtype=torch.float64)
+    r = 0.8 + 0.19 * torch.rand(n, generator=g, dtype=torch.float64)
+    return a, r
