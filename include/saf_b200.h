@@ -1,0 +1,205 @@
+/* saf_b200 -- C ABI of the B200 (sm_100a) implementation of Selective Attention
+ * Freezing's mixed-attention hot path.
+ *
+ * The reference project has no native layer: its operator boundary is the Python
+ * import surface `from kernel import ...` (kernel/__init__.py:14-22).  Each entry
+ * point below sits underneath one of those Python operators and names the
+ * reference function it replaces.  All pointers are raw device pointers unless
+ * marked host; strides are in ELEMENTS; every call enqueues work on `stream`
+ * (a cudaStream_t passed as void*), never synchronises, never allocates device
+ * memory, and returns 0 or a negative SAF_ERR_* code before anything is
+ * launched when the arguments are invalid.  saf_last_error() gives the text.
+ */
+#ifndef SAF_B200_H
+#define SAF_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SAF_ABI_VERSION 1
+
+enum SafStatus {
+  SAF_OK = 0,
+  SAF_ERR_INVALID = -1,     /* bad shape / stride / null pointer / dtype        */
+  SAF_ERR_UNSUPPORTED = -2, /* valid request this build has no kernel for       */
+  SAF_ERR_CUDA = -3,        /* a CUDA runtime/driver call failed (launch, map)  */
+  SAF_ERR_LIMIT = -4        /* size beyond a stated fixed limit                 */
+};
+
+enum SafDType { SAF_F32 = 0, SAF_BF16 = 1, SAF_F16 = 2 };
+
+/* per-head state, the values of the `frozen` tensor
+ * (kernel/fused_attn.py:665-667 defines 0,1,2; 3 is this library's addition) */
+enum SafHeadState {
+  SAF_LIVE = 0,       /* causal softmax(q k^T * sm_scale) v                      */
+  SAF_DENSE = 1,      /* y_i = sum_{j<=i} patt[p, i, j] v_j                      */
+  SAF_DECOMP = 2,     /* y_i = sum_{j<=i} exp(alpha_j + rho_{i-j} - z_i) v_j     */
+  SAF_SINK_DECAY = 3  /* y_i = a v_0 + (1-a) sum_{j<=i} r^(i-j) v_j / Z_i  (scan) */
+};
+
+typedef struct SafTensor {
+  void* ptr;
+  int64_t stride[4]; /* elements; unused trailing entries ignored */
+} SafTensor;
+
+/* ---------------------------------------------------------------------------
+ * Mixed attention, all heads in one call.
+ * Replaces fused_mixed_attn / _fwd / _fwd_kernel (kernel/fused_attn.py:650-734,
+ * 572-591, 228-289) and, with `kvidx`, the GQA twin
+ * (qwen/kernel/fused_attn.py:667-768).
+ * ------------------------------------------------------------------------- */
+typedef struct SafMixedAttnArgs {
+  int32_t struct_size; /* sizeof(SafMixedAttnArgs), checked */
+  int32_t dtype;       /* SafDType of q, k, v, out                                  */
+  int32_t B, H, U, T, HD;
+  int32_t HKV;         /* 0: k has U heads, v has H heads.  >0: GQA, k and v have
+                          HKV heads and head h reads kv head kvidx[h]               */
+  int32_t S;           /* patt is (P, S, S); 0 when patt.ptr is null                */
+  int32_t SD;          /* alpha/rho/z are (H, SD); 0 when absent                    */
+  int32_t patt_dtype;  /* SafDType of patt                                          */
+  int32_t dec_dtype;   /* SafDType of alpha, rho, z                                 */
+  int32_t rope;        /* 0: q,k used as given.  1: rotate q,k while loading with
+                          the (T, HD) fp32 tables rope_cos / rope_sin
+                          (nanogpt/model.py:57-68 semantics)                        */
+  int32_t force_state; /* -1: use frozen[h].  0..3: every head has this state       */
+  float sm_scale;
+  SafTensor q, k;      /* (B, U, T, HD); GQA: k is (B, HKV, T, HD)                  */
+  SafTensor v;         /* (B, H, T, HD); GQA: (B, HKV, T, HD)                       */
+  SafTensor out;       /* (B, H, T, HD), any strides with unit last stride          */
+  SafTensor lse;       /* (B, H, T) fp32 or null; live rows get m + log2(l) in the
+                          log2 domain (kernel/fused_attn.py:223-225)                */
+  SafTensor patt;      /* (P, S, S)                                                 */
+  SafTensor alpha, rho, z; /* (H, SD)                                               */
+  const int32_t* frozen;   /* device (H,), SafHeadState per head                    */
+  const int32_t* hidx;     /* device (H,) head -> slot in q/k; null = identity      */
+  const int32_t* pidx;     /* device (H,) head -> pattern row; null = identity      */
+  const int32_t* kvidx;    /* device (H,) head -> kv head (GQA); null otherwise     */
+  const int32_t* frozen_host; /* HOST copy of frozen (optional scheduling hint)     */
+  const float* sd_alpha;   /* device (H,) sink weight a of SAF_SINK_DECAY heads     */
+  const float* sd_rho;     /* device (H,) decay r of SAF_SINK_DECAY heads           */
+  const float* rope_cos;   /* device (T, HD) fp32                                   */
+  const float* rope_sin;
+  int32_t* status;         /* optional device int32; a kernel that gave up on a
+                              bounded wait writes a non-zero code here              */
+} SafMixedAttnArgs;
+
+int saf_mixed_attn_fwd(const SafMixedAttnArgs* args, void* stream);
+
+/* Backward of the above.  Replaces _bwd / _bwd_preprocess / _bwd_dkdv / _bwd_dq
+ * (kernel/fused_attn.py:593-623, 291-540).  dq, dk must be zero-filled by the
+ * caller (frozen heads' slots are never written, kernel/fused_attn.py:597-598);
+ * delta is caller-provided (B, H, T) fp32 scratch. */
+typedef struct SafMixedAttnBwdArgs {
+  int32_t struct_size;
+  SafMixedAttnArgs fwd; /* same tensors as the forward call; out and lse filled   */
+  SafTensor dout;       /* (B, H, T, HD)                                          */
+  SafTensor dq, dk;     /* like q, k (own strides)                                */
+  SafTensor dv;         /* like v                                                 */
+  SafTensor delta;      /* (B, H, T) fp32 scratch                                 */
+} SafMixedAttnBwdArgs;
+
+int saf_mixed_attn_bwd(const SafMixedAttnBwdArgs* args, void* stream);
+
+/* ---------------------------------------------------------------------------
+ * Frozen heads only, compact values.
+ * Replaces frozen_pv / _pv_fwd_kernel / _pv_bwd_kernel
+ * (kernel/frozen_attn.py:185-192, 51-89, 91-128).
+ *   y[b,f] = patt[fz_idx[f], :T, :T] @ v[b,f]        dv[b,f] = patt^T @ dy[b,f]
+ * When sd_alpha/sd_rho are non-null the pattern is the structured sink+decay
+ * form and the O(T) scan is used instead of reading patt.
+ * ------------------------------------------------------------------------- */
+typedef struct SafFrozenPvArgs {
+  int32_t struct_size;
+  int32_t dtype, patt_dtype;
+  int32_t B, NF, T, HD, S;
+  SafTensor patt;          /* (n_head, S, S)               */
+  SafTensor v;             /* (B, NF, T, HD) fwd: values; bwd: dy */
+  SafTensor y;             /* (B, NF, T, HD) fwd: output;  bwd: dv */
+  const int32_t* fz_idx;   /* device (NF,) pattern row per compact head */
+  const float* sd_alpha;   /* device (NF,) or null */
+  const float* sd_rho;
+  int32_t* status;
+} SafFrozenPvArgs;
+
+int saf_frozen_pv_fwd(const SafFrozenPvArgs* args, void* stream);
+int saf_frozen_pv_bwd(const SafFrozenPvArgs* args, void* stream);
+
+/* ---------------------------------------------------------------------------
+ * Indexed linear: projections over head-sized row slabs of canonical weights,
+ * read in place (no gathered weight copy).
+ * Replaces linear_rows / linear_rows2 (kernel/indexed_linear.py:125-135, 28-55,
+ * 86-122) for row sets made of whole, aligned slabs of `slab` consecutive rows
+ * (the model passes every row of every live head, nanogpt/model.py:854-856).
+ *
+ *   out[m, g*slab + r] = sum_c x[m, c] * W_g[row0_g + r, c] (+ bias_g[row0_g + r])
+ *
+ * for slab-groups g = 0..n_slabs-1, each naming one weight matrix (by index
+ * into `weights`) and a first row.  With rope != 0 slab g with rope_flag[g] != 0
+ * is rotated in the epilogue (slab == head_dim, position = m % T).
+ * ------------------------------------------------------------------------- */
+#define SAF_MAX_WEIGHTS 4
+typedef struct SafIndexedLinearArgs {
+  int32_t struct_size;
+  int32_t dtype;            /* x, weights, out: SAF_BF16 (tensor cores) or SAF_F32 */
+  int32_t M, C;             /* x is (M, C) row-major with row stride ldx           */
+  int32_t n_weights;        /* <= SAF_MAX_WEIGHTS                                  */
+  int32_t n_slabs, slab;    /* output width = n_slabs * slab                       */
+  int32_t T;                /* sequence length (RoPE position = m % T); 0 = no RoPE */
+  const void* x;
+  int64_t ldx;
+  const void* weights[SAF_MAX_WEIGHTS]; /* each (rows_w, C) row-major, row stride ldw[w] */
+  const void* biases[SAF_MAX_WEIGHTS];  /* each (rows_w,) or null                     */
+  int64_t ldw[SAF_MAX_WEIGHTS];         /* row stride of each weight                  */
+  int64_t cdw[SAF_MAX_WEIGHTS];         /* column stride (0 or 1: row-major; ldw=1 with
+                                           cdw=row length addresses the transpose, which
+                                           is how linear_permuted_cols selects columns) */
+  int32_t rows_w[SAF_MAX_WEIGHTS];
+  const int32_t* slab_weight; /* HOST (n_slabs,) weight index of slab g            */
+  const int32_t* slab_row0;   /* HOST (n_slabs,) first weight row of slab g        */
+  const int32_t* slab_rope;   /* HOST (n_slabs,) or null: rotate this slab         */
+  const float* rope_cos;      /* device (T, slab) fp32                             */
+  const float* rope_sin;
+  void* out;                  /* (M, n_slabs*slab) row-major, row stride ldo       */
+  int64_t ldo;
+  int32_t* status;
+} SafIndexedLinearArgs;
+
+int saf_indexed_linear_fwd(const SafIndexedLinearArgs* args, void* stream);
+
+/* Backward pieces of the indexed linear (kernel/indexed_linear.py:100-122):
+ *   dx[m, c]  = sum_{g,r} dout[m, g*slab+r] * W_g[row0_g + r, c]  (+ bias[c])
+ *   dW_g[row0_g + r, c] = sum_m dout[m, g*slab+r] * x[m, c]; rows of no slab are
+ *   left untouched (the caller zero-fills dW, so they stay exactly zero).
+ * `weights` carry W for dx and receive dW (written) for dw; biases receive db.
+ * With transposed weight addressing (cdw) the dx product is also the forward of
+ * linear_permuted_cols (kernel/indexed_linear.py:58-70, 138-141); `bias` (C,)
+ * is added there and is null for a true backward. */
+int saf_indexed_linear_bwd_dx(const SafIndexedLinearArgs* args, const void* dout, int64_t lddo, void* dx,
+                              int64_t lddx, const void* bias, void* stream);
+int saf_indexed_linear_bwd_dw(const SafIndexedLinearArgs* args, const void* dout, int64_t lddo, void* stream);
+
+/* ---------------------------------------------------------------------------
+ * Freeze-time helper: z[h,i] = logsumexp_{j<=i}(alpha[h,j] + rho[h,i-j]).
+ * Replaces decomposed_logz (kernel/fused_attn.py:101-116).  fp32 in/out.
+ * ------------------------------------------------------------------------- */
+int saf_decomposed_logz(const float* alpha, const float* rho, float* z, int32_t H, int32_t S, void* stream);
+
+/* ---------------------------------------------------------------------------
+ * Library plumbing
+ * ------------------------------------------------------------------------- */
+int saf_abi_version(void);
+/* copies the calling thread's last error text (NUL-terminated); returns its length */
+int saf_last_error(char* buf, size_t n);
+/* number of kernel launches this library has enqueued in this process */
+int64_t saf_launch_count(void);
+/* 1 when the device under the current context is an sm_100 part, else 0 */
+int saf_device_supported(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SAF_B200_H */

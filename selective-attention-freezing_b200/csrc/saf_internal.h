@@ -1,0 +1,63 @@
+// Internal declarations shared by the translation units of libsaf_b200.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "../../include/saf_b200.h"
+
+namespace saf {
+
+// error text of the calling thread; returns `code` so call sites can `return fail(...)`
+int fail(int code, const char* fmt, ...);
+void count_launch(int n = 1);
+int check_launch(const char* what);   // cudaGetLastError -> SAF_ERR_CUDA
+
+// ---- element conversion -----------------------------------------------------
+template <typename T> __device__ __forceinline__ float to_f(T x);
+template <> __device__ __forceinline__ float to_f<float>(float x) { return x; }
+template <> __device__ __forceinline__ float to_f<__nv_bfloat16>(__nv_bfloat16 x) { return __bfloat162float(x); }
+template <> __device__ __forceinline__ float to_f<__half>(__half x) { return __half2float(x); }
+template <typename T> __device__ __forceinline__ T from_f(float x);
+template <> __device__ __forceinline__ float from_f<float>(float x) { return x; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
+template <> __device__ __forceinline__ __half from_f<__half>(float x) { return __float2half_rn(x); }
+
+// runtime-typed scalar load (pattern / decomposed buffers may differ from the activation type)
+__device__ __forceinline__ float load_rt(const void* base, int64_t idx, int dtype) {
+  if (dtype == SAF_F32) return reinterpret_cast<const float*>(base)[idx];
+  if (dtype == SAF_BF16) return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(base)[idx]);
+  return __half2float(reinterpret_cast<const __half*>(base)[idx]);
+}
+
+inline int dtype_size(int dt) { return dt == SAF_F32 ? 4 : 2; }
+
+// ---- kernels' host launchers (each returns SAF_OK or an error code) ----------
+// states_mask: bit s set -> heads in state s are processed by this launch
+int launch_generic_fwd(const SafMixedAttnArgs& a, uint32_t states_mask, cudaStream_t st);
+int launch_generic_bwd(const SafMixedAttnBwdArgs& a, uint32_t states_mask, cudaStream_t st);
+int launch_scan_fwd(const SafMixedAttnArgs& a, cudaStream_t st);                       // state 3 heads
+int launch_scan_bwd(const SafMixedAttnBwdArgs& a, cudaStream_t st);                    // state 3 heads: dv
+// tcgen05 fast path; returns SAF_ERR_UNSUPPORTED when the call does not qualify
+int launch_flash_fwd_sm100(const SafMixedAttnArgs& a, uint32_t* handled_states, cudaStream_t st);
+int launch_gemm_sm100(const SafIndexedLinearArgs& a, cudaStream_t st);
+int launch_gemm_generic(const SafIndexedLinearArgs& a, cudaStream_t st);
+int launch_gemm_bwd_dx(const SafIndexedLinearArgs& a, const void* dout, int64_t lddo, void* dx, int64_t lddx,
+                       const void* bias, cudaStream_t st);
+int launch_gemm_bwd_dw(const SafIndexedLinearArgs& a, const void* dout, int64_t lddo, cudaStream_t st);
+int launch_logz(const float* alpha, const float* rho, float* z, int H, int S, cudaStream_t st);
+
+// TMA descriptor encode through the driver entry point (no link-time libcuda dependency)
+typedef CUresult (*TensorMapEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                      const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                      CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                      CUtensorMapFloatOOBfill);
+TensorMapEncodeFn tensor_map_encoder();
+// rank-`rank` bf16 map, 128B swizzle; dims/strides innermost first, strides in BYTES for dims 1..rank-1
+int make_tensor_map_bf16(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
+                         const uint64_t* strides_bytes, const uint32_t* box, bool l2_256);
+
+}  // namespace saf

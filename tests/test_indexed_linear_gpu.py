@@ -1,0 +1,108 @@
+"""GPU parity of linear_rows / linear_rows2 / linear_permuted_cols (forward, dx, dW, db) against
+the CPU oracle, including the exact-zero gradient rows of unselected heads
+(kernel/indexed_linear.py:112-115, nanogpt/test_prior_decomposed.py:117-136)."""
+import pytest
+import torch
+
+from oracle import saf_oracle as O
+from tests.util import errs
+
+pytestmark = pytest.mark.gpu
+
+
+def head_rows(heads, hd):
+    return (torch.tensor(heads)[:, None] * hd + torch.arange(hd)).reshape(-1)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["fp32", "bf16"])
+@pytest.mark.parametrize("bias", [False, True], ids=["nobias", "bias"])
+@pytest.mark.parametrize("shape", [(2, 130, 256, 4, 64, [0, 2, 3]), (1, 515, 768, 12, 64, [0, 1, 3, 4, 6, 7, 9, 10, 11]),
+                                   (2, 64, 192, 2, 96, [1])], ids=lambda s: f"T{s[1]}C{s[2]}")
+def test_linear_rows2(shape, bias, dtype):
+    from kernel import linear_rows2, linear_rows
+    B, T, C, H, hd, live = shape
+    dev = "cuda"
+    g = torch.Generator().manual_seed(T + C)
+    x = torch.randn(B, T, C, generator=g).to(dtype)
+    w1 = (torch.randn(H * hd, C, generator=g) * 0.05).to(dtype)
+    w2 = (torch.randn(H * hd, C, generator=g) * 0.05).to(dtype)
+    b1 = (torch.randn(H * hd, generator=g) * 0.1).to(dtype) if bias else None
+    b2 = (torch.randn(H * hd, generator=g) * 0.1).to(dtype) if bias else None
+    rows = head_rows(live, hd)
+    ref_in = [t.float().clone().requires_grad_(True) if t is not None else None for t in (x, w1, w2, b1, b2)]
+    y_ref = O.linear_rows2(*ref_in, rows)
+    dev_in = [t.clone().to(dev).requires_grad_(True) if t is not None else None for t in (x, w1, w2, b1, b2)]
+    y = linear_rows2(*dev_in, rows.to(dev))
+    assert y.shape == y_ref.shape
+    tol = 2e-5 if dtype == torch.float32 else 2e-2
+    a, r = errs(y, y_ref)
+    assert a <= tol * max(1.0, y_ref.abs().max().item()), f"fwd {a}"
+    if dtype == torch.bfloat16:
+        assert r <= 1e-2
+    w = torch.randn(y_ref.shape, generator=g)
+    (y.float() * w.to(dev)).sum().backward()
+    (y_ref * w).sum().backward()
+    names = ("dx", "dw1", "dw2", "db1", "db2")
+    for n, d, rf in zip(names, dev_in, ref_in):
+        if d is None:
+            continue
+        a, r = errs(d.grad, rf.grad)
+        assert r <= (1e-5 if dtype == torch.float32 else 1.5e-2), f"{n} rel-l2 {r}"
+    # rows of frozen heads: exactly zero gradient
+    dead = [h for h in range(H) if h not in live]
+    if dead:
+        dr = head_rows(dead, hd).to(dev)
+        assert dev_in[1].grad[dr].abs().max().item() == 0.0
+        assert dev_in[2].grad[dr].abs().max().item() == 0.0
+    # single-weight variant, bit-identical to the matching half of the fused call
+    y1 = linear_rows(dev_in[0].detach(), dev_in[1].detach(), None if b1 is None else dev_in[3].detach(), rows.to(dev))
+    assert torch.equal(y1, y[..., : y.shape[-1] // 2])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["fp32", "bf16"])
+def test_linear_permuted_cols(dtype):
+    from kernel import linear_permuted_cols
+    dev = "cuda"
+    B, T, C, H, hd = 2, 77, 256, 4, 64
+    g = torch.Generator().manual_seed(11)
+    y_in = torch.randn(B, T, C, generator=g).to(dtype)
+    w = (torch.randn(C, C, generator=g) * 0.05).to(dtype)
+    b = (torch.randn(C, generator=g) * 0.1).to(dtype)
+    cols = torch.cat([head_rows([0, 2, 3], hd), head_rows([1], hd)])
+    ref_in = [t.float().clone().requires_grad_(True) for t in (y_in, w, b)]
+    o_ref = O.linear_permuted_cols(*ref_in, cols)
+    dev_in = [t.clone().to(dev).requires_grad_(True) for t in (y_in, w, b)]
+    o = linear_permuted_cols(*dev_in, cols.to(dev))
+    a, r = errs(o, o_ref)
+    assert r <= (1e-5 if dtype == torch.float32 else 1e-2), f"fwd {r}"
+    wgt = torch.randn(o_ref.shape, generator=g)
+    (o.float() * wgt.to(dev)).sum().backward()
+    (o_ref * wgt).sum().backward()
+    for n, d, rf in zip(("dy", "dw", "db"), dev_in, ref_in):
+        a, r = errs(d.grad, rf.grad)
+        assert r <= (1e-5 if dtype == torch.float32 else 1.5e-2), f"{n} rel-l2 {r}"
+
+
+def test_gather_is_bit_exact():
+    """Selecting rows must not change a single bit: the sliced product equals the same kernel
+    run over a physically gathered weight."""
+    from kernel import linear_rows
+    dev = "cuda"
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(300, 256, generator=g).bfloat16().to(dev)
+    w = (torch.randn(512, 256, generator=g) * 0.05).bfloat16().to(dev)
+    rows = head_rows([1, 4, 6], 64).to(dev)
+    y = linear_rows(x, w, None, rows)
+    wg = w[rows].contiguous()
+    y2 = linear_rows(x, wg, None, torch.arange(wg.shape[0], device=dev))
+    assert torch.equal(y, y2)
+
+
+def test_decomposed_logz_kernel():
+    from kernel import decomposed_logz
+    g = torch.Generator().manual_seed(9)
+    alpha = torch.randn(5, 320, generator=g) * 3
+    rho = torch.randn(5, 320, generator=g) * 3
+    z_ref = O.decomposed_logz(alpha.double(), rho.double())
+    z = decomposed_logz(alpha.cuda(), rho.cuda())
+    assert O.max_abs(z.cpu(), z_ref) <= 1e-5

@@ -1,0 +1,238 @@
+"""GPU parity of fused_mixed_attn (forward and backward) against the CPU oracle.
+
+Shapes, freeze sets and tolerances follow the reference's own kernel test
+(kernel/test_fused_attn.py:166-228): fp32 forward 2e-5 / grads 2e-4; bf16 forward
+6e-2 / grads 2e-1 there.  This build's bar for bf16 is tighter: forward
+max-abs <= 2e-2 and rel-L2 <= 1e-2 against the fp32 eager result.
+"""
+import pytest
+import torch
+
+from oracle import saf_oracle as O
+from tests.util import make_pattern, make_decomp, head_maps, errs
+
+pytestmark = pytest.mark.gpu
+
+FP32_FWD, FP32_BWD = 2e-5, 2e-4
+BF16_FWD_ABS, BF16_FWD_REL = 2e-2, 1e-2
+BF16_BWD_ABS, BF16_BWD_REL = 2e-1, 3.5e-2   # kernel/test_fused_attn.py:188-193, supplement/test_controls.py:188
+
+
+def run_case(B, H, T, hd, S, dense, dec=(), dtype=torch.float32, strided=False, no_patt=False, buf_bf16=False,
+             dec_scale=0.8, compact_patt=False, sink=(), backward=True, rope=False):
+    from kernel import fused_mixed_attn
+    dev = "cuda"
+    dense, dec, sink = list(dense), list(dec), list(sink)
+    states = [0] * H
+    for h in dense:
+        states[h] = 1
+    for h in dec:
+        states[h] = 2
+    for h in sink:
+        states[h] = 3
+    live, hidx = head_maps(H, states)
+    patt = make_pattern(H, S, seed=H * S + T)
+    alpha, rho, z = make_decomp(H, S, seed=H + S + T, scale=dec_scale)
+    if buf_bf16:
+        alpha, rho, z = alpha.bfloat16(), rho.bfloat16(), z.bfloat16()
+    sd_a, sd_r = O.sink_decay_params(H, seed=T + H)
+    sd_a, sd_r = sd_a.float().double(), sd_r.float().double()   # the kernel gets fp32 parameters
+    ref_patt = patt.clone().double()
+    if dec:
+        # fp32 with the reference's operation order, exp((alpha + rho) - z), as its own test does
+        # (kernel/test_fused_attn.py:40-50); at |logit| ~ 150 an fp64 pattern would differ by fp32 rounding alone
+        ref_patt[dec, :T, :T] = O.decomp_pattern(alpha[dec].float(), rho[dec].float(), z[dec].float(), T).double()
+    if sink:
+        ref_patt[sink, :T, :T] = O.sink_decay_pattern(sd_a[sink], sd_r[sink], T)
+    ref_states = [1 if s else 0 for s in states]
+
+    g = torch.Generator(device="cpu").manual_seed(T * hd + B)
+    base = [torch.randn(B, H, T, hd, generator=g).to(dtype) for _ in range(3)]
+    cos = sin = None
+    if rope:
+        cos, sin = O.rope_cache(hd, T)
+
+    # oracle, fp32 arithmetic on the (dtype-rounded) inputs
+    rq, rk, rv = [t.float().clone().requires_grad_(True) for t in base]
+    oq, ok = (O.apply_rope(rq, cos, sin), O.apply_rope(rk, cos, sin)) if rope else (rq, rk)
+    y_ref = O.mixed_attn(oq[:, live], ok[:, live], rv, ref_patt.float(), ref_states, hidx=hidx)
+
+    # device inputs: compact q/k (live heads only) + full v
+    if strided and live:
+        qk = torch.stack([base[0][:, live], base[1][:, live]], dim=2).transpose(1, 2).contiguous().transpose(1, 2)
+        qk = qk.to(dev).detach().requires_grad_(True)
+        dq_in, dk_in = qk[:, :, 0], qk[:, :, 1]
+    else:
+        dq_in = base[0][:, live].clone().to(dev).requires_grad_(True)
+        dk_in = base[1][:, live].clone().to(dev).requires_grad_(True)
+    dv_in = base[2].clone().to(dev).requires_grad_(True)
+    pidx = None
+    if compact_patt:
+        pidx = torch.zeros(H, dtype=torch.int32)
+        for slot, h in enumerate(dense):
+            pidx[h] = slot
+        pidx = pidx.to(dev)
+        kpatt = None if no_patt else patt[dense].contiguous().to(dev)
+    else:
+        kpatt = None if no_patt else patt.to(dev)
+    kw = {}
+    if dec:
+        kw.update(alpha=alpha.to(dev), rho=rho.to(dev), z=z.to(dev))
+    if sink:
+        kw.update(sink_decay=(sd_a.float().to(dev), sd_r.float().to(dev)))
+    if rope:
+        kw.update(rope=(cos.to(dev), sin.to(dev)))
+    frozen = torch.tensor(states, dtype=torch.int32, device=dev)
+    y = fused_mixed_attn(dq_in, dk_in, dv_in, kpatt, frozen, hidx.to(dev), pidx, **kw)
+    assert y.shape == (B, H, T, hd) and y.dtype == dtype
+    assert torch.isfinite(y.float()).all()
+    fa, fr = errs(y, y_ref)
+    if dtype == torch.float32:
+        assert fa <= FP32_FWD, f"fwd max-abs {fa}"
+    else:
+        assert fa <= BF16_FWD_ABS and fr <= BF16_FWD_REL, f"fwd max-abs {fa} rel-l2 {fr}"
+    if not backward:
+        return
+    gw = torch.Generator(device="cpu").manual_seed(7)
+    w = torch.randn(B, H, T, hd, generator=gw)
+    (y.float() * w.to(dev)).sum().backward()
+    (y_ref * w).sum().backward()
+    tol_abs = FP32_BWD if dtype == torch.float32 else BF16_BWD_ABS
+    a, r = errs(dv_in.grad, rv.grad)
+    assert a <= tol_abs, f"dv max-abs {a}"
+    if dtype != torch.float32:
+        assert r <= BF16_BWD_REL, f"dv rel-l2 {r}"
+    if live:
+        gq = qk.grad[:, :, 0] if (strided and live) else dq_in.grad
+        gk = qk.grad[:, :, 1] if (strided and live) else dk_in.grad
+        for name, got, want in (("dq", gq, rq.grad[:, live]), ("dk", gk, rk.grad[:, live])):
+            a, r = errs(got, want)
+            assert a <= tol_abs, f"{name} max-abs {a}"
+            if dtype != torch.float32 and want.abs().max().item() > 1e-3:   # T=1: the true gradient is zero
+                assert r <= BF16_BWD_REL, f"{name} rel-l2 {r}"
+    # frozen heads have no q/k slot: the oracle's gradient there is exactly zero too
+    fz = [h for h in range(H) if states[h]]
+    if fz and live:
+        assert rq.grad[:, fz].abs().max().item() == 0.0 and rk.grad[:, fz].abs().max().item() == 0.0
+
+
+BASE = [
+    (2, 12, 1024, 64, 1024, [0, 1, 2]),
+    (2, 12, 1024, 64, 1024, []),
+    (2, 12, 1024, 64, 1024, list(range(12))),
+    (2, 12, 1024, 64, 1024, [3, 7, 11]),
+    (2, 12, 700, 64, 1024, [0, 5, 11]),
+    (2, 12, 37, 64, 1024, [0, 5]),
+    (1, 16, 2048, 96, 2048, [0, 7, 8, 15]),
+    (4, 12, 2048, 64, 2048, [0, 1, 2]),
+]
+DEC = [
+    (2, 12, 1024, 64, 1024, [0, 1], [2, 3], False),
+    (2, 12, 1024, 64, 1024, [], [0, 5, 11], True),
+    (2, 12, 1024, 64, 1024, [], list(range(12)), True),
+    (2, 12, 700, 64, 1024, [3], [0, 7], False),
+    (2, 12, 37, 64, 1024, [5], [0, 2], False),
+    (1, 16, 2048, 96, 2048, [0, 8], [7, 15], False),
+    (4, 12, 2048, 64, 2048, [1], [0, 2], False),
+]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["fp32", "bf16"])
+@pytest.mark.parametrize("case", BASE[:6], ids=lambda c: f"B{c[0]}H{c[1]}T{c[2]}d{c[3]}nf{len(c[5])}")
+def test_dense_frozen(case, dtype):
+    run_case(*case, dtype=dtype)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["fp32", "bf16"])
+@pytest.mark.parametrize("case", BASE[6:], ids=lambda c: f"B{c[0]}H{c[1]}T{c[2]}d{c[3]}nf{len(c[5])}")
+def test_dense_frozen_long(case, dtype):
+    run_case(*case, dtype=dtype)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["fp32", "bf16"])
+@pytest.mark.parametrize("case", [BASE[0], BASE[4], BASE[5]], ids=lambda c: f"T{c[2]}")
+def test_strided_qk_views(case, dtype):
+    run_case(*case, dtype=dtype, strided=True)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["fp32", "bf16"])
+@pytest.mark.parametrize("case", DEC[:5], ids=lambda c: f"T{c[2]}nf{len(c[5])}nd{len(c[6])}")
+def test_decomposed(case, dtype):
+    B, H, T, hd, S, fz, dec, no_patt = case
+    run_case(B, H, T, hd, S, fz, dec, dtype=dtype, no_patt=no_patt)
+
+
+def test_decomposed_bf16_buffers():
+    B, H, T, hd, S, fz, dec, no_patt = DEC[0]
+    run_case(B, H, T, hd, S, fz, dec, dtype=torch.bfloat16, no_patt=no_patt, buf_bf16=True)
+
+
+@pytest.mark.parametrize("case", [(2, 12, 700, 64, 1024, [3], [0, 7], False), (2, 12, 37, 64, 1024, [], [0, 2, 5], True)],
+                         ids=["T700", "T37"])
+def test_decomposed_sharp_logits(case):
+    """logit scale 40: near one-hot rows, |logit| up to ~150 (kernel/test_fused_attn.py:213-223)."""
+    B, H, T, hd, S, fz, dec, no_patt = case
+    run_case(B, H, T, hd, S, fz, dec, dtype=torch.float32, no_patt=no_patt, dec_scale=40.0)
+
+
+def test_compact_pattern_rows():
+    """pidx maps heads to a compact pattern buffer (kernel/test_fused_attn.py:224-228)."""
+    run_case(2, 12, 700, 64, 1024, [3, 9], [0, 7], dtype=torch.float32, strided=True, compact_patt=True)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["fp32", "bf16"])
+@pytest.mark.parametrize("T", [1, 37, 700, 1024, 2048])
+def test_sink_decay_scan_heads(T, dtype):
+    """state 3: the scan must equal the dense product with the materialised pattern."""
+    run_case(2, 12, T, 64, max(T, 64), [1], [], dtype=dtype, sink=[2, 5, 8], no_patt=False)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["fp32", "bf16"])
+def test_rope_on_load(dtype):
+    run_case(2, 12, 700, 64, 1024, [2, 5, 8], dtype=dtype, rope=True)
+
+
+def test_head_dim_128():
+    run_case(2, 8, 512, 128, 512, [1, 6], dtype=torch.bfloat16)
+    run_case(1, 8, 300, 128, 512, [1, 6], dtype=torch.float32)
+
+
+def test_validate_messages():
+    from kernel import fused_mixed_attn
+    dev = "cuda"
+    q = torch.zeros(1, 2, 8, 64, device=dev)
+    v = torch.zeros(1, 3, 8, 64, device=dev)
+    frozen = torch.tensor([0, 1, 0], dtype=torch.int32, device=dev)
+    hidx = torch.tensor([0, 0, 1], dtype=torch.int32, device=dev)
+    with pytest.raises(AssertionError, match="dense-frozen heads require patt"):
+        fused_mixed_attn(q, q, v, None, frozen, hidx)
+    with pytest.raises(AssertionError, match="S >= T"):
+        fused_mixed_attn(q, q, v, torch.zeros(3, 4, 4, device=dev), frozen, hidx)
+    with pytest.raises(AssertionError, match="int32"):
+        fused_mixed_attn(q, q, v, torch.zeros(3, 8, 8, device=dev), frozen.long(), hidx)
+
+
+def test_gqa_forward_and_backward_error():
+    """kvidx variant (qwen/kernel/fused_attn.py:667-768): forward only."""
+    from kernel import fused_mixed_attn
+    dev = "cuda"
+    B, H, HKV, T, hd = 2, 6, 2, 300, 128
+    g = torch.Generator().manual_seed(5)
+    states = [0, 1, 0, 0, 1, 0]
+    live, hidx = head_maps(H, states)
+    kv = torch.tensor([0, 0, 0, 1, 1, 1], dtype=torch.int32)
+    q = torch.randn(B, len(live), T, hd, generator=g).bfloat16()
+    k = torch.randn(B, HKV, T, hd, generator=g).bfloat16()
+    v = torch.randn(B, HKV, T, hd, generator=g).bfloat16()
+    patt = make_pattern(2, 512, seed=3)
+    pidx = torch.tensor([0, 0, 0, 0, 1, 0], dtype=torch.int32)
+    y_ref = O.mixed_attn(q.float(), k.float(), v.float(), patt, states, hidx=hidx, pidx=pidx, kvidx=kv,
+                         sm_scale=0.11)
+    qd = q.to(dev).requires_grad_(True)
+    y = fused_mixed_attn(qd, k.to(dev), v.to(dev), patt.to(dev), torch.tensor(states, dtype=torch.int32, device=dev),
+                         hidx.to(dev), pidx.to(dev), sm_scale=0.11, kvidx=kv.to(dev))
+    assert y.is_contiguous()
+    a, r = errs(y, y_ref)
+    assert a <= BF16_FWD_ABS and r <= BF16_FWD_REL
+    with pytest.raises(NotImplementedError):
+        y.float().sum().backward()
