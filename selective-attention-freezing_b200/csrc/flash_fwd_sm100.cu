@@ -1,8 +1,405 @@
-// placeholder until the tcgen05 kernel lands
+// Live-head causal flash attention on tcgen05 / TMEM, fed by TMA.
+//
+// Replaces the live branch of the reference's fused forward (_acc_flash inside
+// _fwd_kernel, kernel/fused_attn.py:182-289: 64x64 Triton tiles, pointer loads,
+// 4 warps, no persistence).  One CTA owns TWO consecutive 128-row query tiles of one
+// (batch, head) and walks the causal range of 128-key tiles once for both:
+//
+//   warps 0-3   softmax of query tile 0 (one thread per row: TMEM lane == row)
+//   warps 4-7   softmax of query tile 1
+//   warp  8     TMA producer: Q tiles once, then K_j / V_j tiles through a ring of stages
+//   warp  9     MMA issuer:   S_t = Q_t K_j^T  (SS, 128x128xHD)  -> TMEM
+//                             O_t += P_t V_j   (TS: P read from TMEM, V MN-major in smem)
+//
+// TMEM columns: S0 [0,128) S1 [128,256) O0 [256,256+HD) O1 [256+HD,256+2HD).  P (bf16)
+// overwrites the first 64 columns of its S buffer, so scores never touch shared or
+// global memory.  The two query tiles alternate on the tensor core: while one tile's
+// scores are in the softmax warps the other tile's MMAs run.  The running output is
+// rescaled lazily: only when a row maximum grows by more than 2^8 (exact, because the
+// final normaliser l carries the same reference maximum).
+//
+// Head state is read per CTA from `frozen`; CTAs of heads in another state leave at
+// once (their work belongs to the scan / pattern kernels).
 #include "saf_internal.h"
+#include "sm100_prims.cuh"
+
 namespace saf {
-int launch_flash_fwd_sm100(const SafMixedAttnArgs&, uint32_t* handled, cudaStream_t) {
-  *handled = 0;
-  return SAF_ERR_UNSUPPORTED;
+namespace {
+
+constexpr int FM = 128;             // rows per query tile
+constexpr int FN = 128;             // keys per step
+constexpr int FLASH_THREADS = 320;
+constexpr float LOG2E_F = 1.4426950408889634f;
+constexpr float RESCALE_THRESHOLD = 8.0f;
+
+template <int HD>
+struct Cfg {
+  static constexpr int TILE_BYTES = 128 * HD * 2;
+  static constexpr int NSTAGE = (HD == 64) ? 6 : 4;
+  static constexpr int Q_BYTES = 2 * TILE_BYTES;
+  static constexpr int RING_BYTES = NSTAGE * TILE_BYTES;
+  static constexpr int SMEM_BYTES = 1024 + Q_BYTES + RING_BYTES + 512;
+  static constexpr int TMEM_COLS = 512;
+  static constexpr int O_COL = 256;
+};
+
+struct FlashParams {
+  int B, H, T, HKV, force_state, n_pairs;
+  float scale_log2;
+  const int32_t* frozen;
+  const int32_t* hidx;
+  const int32_t* kvidx;
+  float* lse;
+  int64_t lse_s[3];
+  int* status;
+};
+
+struct FlashBars {
+  uint64_t q_full;
+  uint64_t kv_full[6], kv_empty[6];
+  uint64_t s_full[2], p_full[2], o_done[2];
+  uint32_t tmem_base;
+};
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
+
+template <int HD>
+__device__ __forceinline__ void load_tile(uint8_t* dst, const CUtensorMap* m, uint64_t* bar, int row, int head, int b) {
+#pragma unroll
+  for (int hh = 0; hh < HD / 64; ++hh) tma_load_4d(dst + hh * 16384, m, bar, hh * 64, row, head, b);
+}
+
+template <int HD>
+__global__ void __launch_bounds__(FLASH_THREADS, 1)
+flash_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
+                 const __grid_constant__ CUtensorMap mapV, const __grid_constant__ CUtensorMap mapO,
+                 const __grid_constant__ FlashParams p) {
+  using C = Cfg<HD>;
+  // work item: heaviest row-tile pairs first
+  const int bh_count = p.B * p.H;
+  const int mp = p.n_pairs - 1 - (int)(blockIdx.x / bh_count);
+  const int bh = blockIdx.x % bh_count;
+  const int b = bh / p.H, h = bh % p.H;
+  const int state = p.force_state >= 0 ? p.force_state : p.frozen[h];
+  if (state != SAF_LIVE) return;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* sQ = smem;                       // 2 tiles
+  uint8_t* sRing = smem + C::Q_BYTES;       // NSTAGE tiles, K and V alternate
+  FlashBars* bars = reinterpret_cast<FlashBars*>(sRing + C::RING_BYTES);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int row0 = mp * 2 * FM;
+  const bool act1 = row0 + FM < p.T;
+  const int nkv0 = 2 * mp + 1;
+  const int nkv1 = act1 ? 2 * mp + 2 : 0;
+  const int nkv = act1 ? nkv1 : nkv0;
+  const int hq = p.hidx ? p.hidx[h] : h;
+  const int hk = (p.HKV > 0) ? p.kvidx[h] : hq;
+  const int hv = (p.HKV > 0) ? p.kvidx[h] : h;
+
+  if (tid == 0) {
+    mbar_init(&bars->q_full, 1);
+    for (int s = 0; s < C::NSTAGE; ++s) {
+      mbar_init(&bars->kv_full[s], 1);
+      mbar_init(&bars->kv_empty[s], 1);
+    }
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(&bars->s_full[t], 1);
+      mbar_init(&bars->p_full[t], 128);
+      mbar_init(&bars->o_done[t], 1);
+    }
+    fence_mbar_init();
+  }
+  if (warp == 9) {
+    tmem_alloc(&bars->tmem_base, C::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = bars->tmem_base;
+
+  if (warp == 8) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      tma_prefetch_desc(&mapQ);
+      tma_prefetch_desc(&mapK);
+      tma_prefetch_desc(&mapV);
+      mbar_expect_tx(&bars->q_full, (act1 ? 2 : 1) * C::TILE_BYTES);
+      load_tile<HD>(sQ, &mapQ, &bars->q_full, row0, hq, b);
+      if (act1) load_tile<HD>(sQ + C::TILE_BYTES, &mapQ, &bars->q_full, row0 + FM, hq, b);
+      for (int item = 0; item < 2 * nkv; ++item) {
+        const int s = item % C::NSTAGE;
+        if (!mbar_wait(&bars->kv_empty[s], ((item / C::NSTAGE) & 1) ^ 1)) {
+          dev_set_error(p.status, SAF_DEV_TIMEOUT_TMA, 20);
+          break;
+        }
+        mbar_expect_tx(&bars->kv_full[s], C::TILE_BYTES);
+        const int j = item >> 1;
+        if (item & 1) load_tile<HD>(sRing + s * C::TILE_BYTES, &mapV, &bars->kv_full[s], j * FN, hv, b);
+        else load_tile<HD>(sRing + s * C::TILE_BYTES, &mapK, &bars->kv_full[s], j * FN, hk, b);
+      }
+    }
+  } else if (warp == 9) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc_s = umma_idesc_bf16(FM, FN, 0, 0);   // Q K^T: both K-major
+      const uint32_t idesc_o = umma_idesc_bf16(FM, HD, 0, 1);   // P V  : V is MN-major
+      const uint32_t qaddr[2] = {smem_u32(sQ), smem_u32(sQ + C::TILE_BYTES)};
+      const uint32_t ring = smem_u32(sRing);
+      auto issue_s = [&](int t, uint32_t kaddr) {
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks) {
+          const uint32_t off = (ks >> 2) * 16384 + (ks & 3) * 32;
+          umma_ss(tmem + t * FN, umma_smem_desc_sw128(qaddr[t] + off, 16, 1024),
+                  umma_smem_desc_sw128(kaddr + off, 16, 1024), idesc_s, ks > 0);
+        }
+        umma_commit(&bars->s_full[t]);
+      };
+      bool ok = mbar_wait(&bars->q_full, 0);
+      if (!ok) dev_set_error(p.status, SAF_DEV_TIMEOUT_MMA, 21);
+      if (ok) {
+        // K_0
+        ok = mbar_wait(&bars->kv_full[0], 0);
+        if (!ok) dev_set_error(p.status, SAF_DEV_TIMEOUT_MMA, 22);
+      }
+      if (ok) {
+        tc_fence_after();
+        issue_s(0, ring);
+        if (act1) issue_s(1, ring);
+        umma_commit(&bars->kv_empty[0]);
+      }
+      for (int j = 0; j < nkv && ok; ++j) {
+        const int vitem = 2 * j + 1, vs = vitem % C::NSTAGE;
+        if (!mbar_wait(&bars->kv_full[vs], (vitem / C::NSTAGE) & 1)) {
+          dev_set_error(p.status, SAF_DEV_TIMEOUT_MMA, 23);
+          ok = false;
+          break;
+        }
+        const uint32_t vaddr = ring + vs * C::TILE_BYTES;
+        const int kitem = 2 * j + 2, ksn = kitem % C::NSTAGE;
+        const uint32_t kaddr = ring + ksn * C::TILE_BYTES;
+        bool k_ready = false;
+        for (int t = 0; t < 2 && ok; ++t) {
+          const int nk = t ? nkv1 : nkv0;
+          if (j >= nk) continue;
+          if (!mbar_wait(&bars->p_full[t], j & 1)) {
+            dev_set_error(p.status, SAF_DEV_TIMEOUT_MMA, 24);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+#pragma unroll
+          for (int ks = 0; ks < FN / 16; ++ks) {
+            umma_ts(tmem + C::O_COL + t * HD, tmem + t * FN + ks * 8,
+                    umma_smem_desc_sw128(vaddr + ks * 2048, 16384, 1024), idesc_o, (j > 0) || (ks > 0));
+          }
+          if (j == nk - 1) umma_commit(&bars->o_done[t]);
+          if (j + 1 < nk) {
+            if (!k_ready) {
+              if (!mbar_wait(&bars->kv_full[ksn], (kitem / C::NSTAGE) & 1)) {
+                dev_set_error(p.status, SAF_DEV_TIMEOUT_MMA, 25);
+                ok = false;
+                break;
+              }
+              tc_fence_after();
+              k_ready = true;
+            }
+            issue_s(t, kaddr);
+          }
+        }
+        if (!ok) break;
+        umma_commit(&bars->kv_empty[vs]);
+        if (j + 1 < nkv) umma_commit(&bars->kv_empty[ksn]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ softmax warpgroups
+    const int t = warp >> 2;
+    const int r = tid & 127;
+    const int nk = t ? nkv1 : nkv0;
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+    const uint32_t tS = tmem + lane_base + t * FN;
+    const uint32_t tO = tmem + lane_base + C::O_COL + t * HD;
+    float m_ref = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < nk; ++j) {
+      if (!mbar_wait(&bars->s_full[t], j & 1)) {
+        dev_set_error(p.status, SAF_DEV_TIMEOUT_SOFTMAX, 26);
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      uint32_t s[4][32];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) tmem_ld32(tS + q * 32, s[q]);
+      tmem_ld_wait();
+      if (j == nk - 1) {  // diagonal tile: keys after the row are masked
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (q * 32 + i > r) s[q][i] = 0xff800000u;  // -inf
+      }
+      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        mx0 = fmaxf(mx0, __uint_as_float(s[0][i]));
+        mx1 = fmaxf(mx1, __uint_as_float(s[1][i]));
+        mx2 = fmaxf(mx2, __uint_as_float(s[2][i]));
+        mx3 = fmaxf(mx3, __uint_as_float(s[3][i]));
+      }
+      const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2;
+      if (j == 0) {
+        m_ref = mx;
+      } else {
+        const bool need = mx > m_ref + RESCALE_THRESHOLD;
+        if (__any_sync(0xffffffffu, need)) {
+          const float f = need ? ex2(m_ref - mx) : 1.f;
+          if (need) m_ref = mx;
+          l *= f;
+#pragma unroll
+          for (int c0 = 0; c0 < HD; c0 += 32) {
+            uint32_t o[32];
+            tmem_ld32(tO + c0, o);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
+            tmem_st32(tO + c0, o);
+          }
+        }
+      }
+      float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const float p0 = ex2(fmaf(__uint_as_float(s[q][2 * i]), p.scale_log2, -m_ref));
+          const float p1 = ex2(fmaf(__uint_as_float(s[q][2 * i + 1]), p.scale_log2, -m_ref));
+          sum0 += p0;
+          sum1 += p1;
+          pk[i] = pack_bf16(p0, p1);
+        }
+        tmem_st16(tS + q * 16, pk);
+      }
+      l += sum0 + sum1;
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(&bars->p_full[t]);
+    }
+    if (nk > 0) {
+      if (ok && !mbar_wait(&bars->o_done[t], 0)) {
+        dev_set_error(p.status, SAF_DEV_TIMEOUT_SOFTMAX, 27);
+        ok = false;
+      }
+      tc_fence_after();
+      const float inv = 1.f / l;
+      uint8_t* stage = sQ + t * C::TILE_BYTES;   // this tile's Q is no longer read
+#pragma unroll
+      for (int c0 = 0; c0 < HD; c0 += 32) {
+        uint32_t o[32];
+        tmem_ld32(tO + c0, o);
+        tmem_ld_wait();
+        uint8_t* dst = stage + (c0 >> 6) * 16384 + r * 128;
+        const int cbase = (c0 & 63) >> 3;   // first 16-byte chunk of this group inside the 128-byte row
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint4 q;
+          q.x = pack_bf16(__uint_as_float(o[c * 8 + 0]) * inv, __uint_as_float(o[c * 8 + 1]) * inv);
+          q.y = pack_bf16(__uint_as_float(o[c * 8 + 2]) * inv, __uint_as_float(o[c * 8 + 3]) * inv);
+          q.z = pack_bf16(__uint_as_float(o[c * 8 + 4]) * inv, __uint_as_float(o[c * 8 + 5]) * inv);
+          q.w = pack_bf16(__uint_as_float(o[c * 8 + 6]) * inv, __uint_as_float(o[c * 8 + 7]) * inv);
+          *reinterpret_cast<uint4*>(dst + (((cbase + c) ^ (r & 7)) << 4)) = q;
+        }
+      }
+      fence_proxy_async_smem();
+      named_bar_sync(1 + t, 128);
+      const int trow = row0 + t * FM;
+      if (r == 0 && ok) {
+#pragma unroll
+        for (int hh = 0; hh < HD / 64; ++hh) tma_store_4d(&mapO, stage + hh * 16384, hh * 64, trow, h, b);
+        tma_store_commit();
+        tma_store_wait_all();
+      }
+      if (p.lse && trow + r < p.T)
+        p.lse[(int64_t)b * p.lse_s[0] + (int64_t)h * p.lse_s[1] + (int64_t)(trow + r) * p.lse_s[2]] = m_ref + log2f(l);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 9) tmem_dealloc(tmem, C::TMEM_COLS);
+}
+
+bool aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
+
+bool tma_ok(const SafTensor& t) {
+  if (!t.ptr || !aligned16(t.ptr) || t.stride[3] != 1) return false;
+  for (int i = 0; i < 3; ++i)
+    if (t.stride[i] % 8 || t.stride[i] <= 0) return false;
+  return true;
+}
+
+int make_map4(CUtensorMap* m, const SafTensor& t, int B, int Hn, int T, int HD) {
+  uint64_t dims[4] = {(uint64_t)HD, (uint64_t)T, (uint64_t)Hn, (uint64_t)B};
+  uint64_t strides[4] = {0, (uint64_t)t.stride[2] * 2, (uint64_t)t.stride[1] * 2, (uint64_t)t.stride[0] * 2};
+  uint32_t box[4] = {64, 128, 1, 1};
+  return make_tensor_map_bf16(m, t.ptr, 4, dims, strides, box, true);
+}
+
+template <int HD>
+int launch_typed(const SafMixedAttnArgs& a, cudaStream_t st) {
+  CUtensorMap mq, mk, mv, mo;
+  int rc;
+  const int Hkv = a.HKV > 0 ? a.HKV : 0;
+  if ((rc = make_map4(&mq, a.q, a.B, a.U, a.T, HD))) return rc;
+  if ((rc = make_map4(&mk, a.k, a.B, Hkv ? Hkv : a.U, a.T, HD))) return rc;
+  if ((rc = make_map4(&mv, a.v, a.B, Hkv ? Hkv : a.H, a.T, HD))) return rc;
+  if ((rc = make_map4(&mo, a.out, a.B, a.H, a.T, HD))) return rc;
+  FlashParams p;
+  memset(&p, 0, sizeof(p));
+  p.B = a.B; p.H = a.H; p.T = a.T; p.HKV = a.HKV; p.force_state = a.force_state;
+  p.n_pairs = (a.T + 2 * FM - 1) / (2 * FM);
+  p.scale_log2 = a.sm_scale * LOG2E_F;
+  p.frozen = a.frozen; p.hidx = a.hidx; p.kvidx = a.kvidx;
+  p.lse = reinterpret_cast<float*>(a.lse.ptr);
+  for (int i = 0; i < 3; ++i) p.lse_s[i] = a.lse.stride[i];
+  p.status = a.status;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(flash_fwd_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<HD>::SMEM_BYTES);
+    if (e != cudaSuccess) return fail(SAF_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    attr_set = true;
+  }
+  const unsigned grid = (unsigned)(p.n_pairs * a.B * a.H);
+  flash_fwd_kernel<HD><<<grid, FLASH_THREADS, Cfg<HD>::SMEM_BYTES, st>>>(mq, mk, mv, mo, p);
+  count_launch();
+  return check_launch("flash_fwd_kernel");
+}
+
+}  // namespace
+
+int launch_flash_fwd_sm100(const SafMixedAttnArgs& a, uint32_t* handled, cudaStream_t st) {
+  *handled = 0;
+  if (a.dtype != SAF_BF16 || (a.HD != 64 && a.HD != 128) || a.rope) return SAF_ERR_UNSUPPORTED;
+  if (a.U == 0 || (a.force_state >= 0 && a.force_state != SAF_LIVE)) return SAF_ERR_UNSUPPORTED;
+  if (a.frozen_host) {
+    bool any = false;
+    for (int h = 0; h < a.H; ++h) any |= a.frozen_host[h] == SAF_LIVE;
+    if (!any) return SAF_ERR_UNSUPPORTED;
+  }
+  if (a.sm_scale <= 0.f) return SAF_ERR_UNSUPPORTED;
+  if (!tma_ok(a.q) || !tma_ok(a.k) || !tma_ok(a.v) || !tma_ok(a.out)) return SAF_ERR_UNSUPPORTED;
+  if (!saf_device_supported()) return SAF_ERR_UNSUPPORTED;
+  const int rc = (a.HD == 64) ? launch_typed<64>(a, st) : launch_typed<128>(a, st);
+  if (rc == SAF_OK) *handled = 1u << SAF_LIVE;
+  return rc;
+}
+
 }  // namespace saf

@@ -1,5 +1,326 @@
-// placeholder until the tcgen05 kernel lands
+// Indexed linear on the 5th-generation tensor cores (tcgen05, TMEM accumulators).
+//
+//   out[m, g*slab + r] = sum_c x[m,c] * W_g[row0_g + r, c]  (+ bias)   [+ RoPE on chosen slabs]
+//
+// replaces the reference's gather-then-GEMM (kernel/indexed_linear.py:86-98: two
+// index_select + cat materialise a (2R, C) weight copy on every call, then cuBLAS;
+// RoPE afterwards as 3-4 elementwise kernels, nanogpt/model.py:1007-1008).  Here the
+// canonical weights are read in place: every 64-row block of output features has
+// its own TMA source (weight matrix, first row), so rows of frozen heads are never
+// touched, and the rotation is applied to the fp32 accumulator in the epilogue.
+//
+// Persistent, warp-specialised CTA (1 per SM):
+//   warp 0      TMA producer: x tile 128x64 and weight tile 128x64 per stage (128B swizzle)
+//   warp 1      MMA issuer: tcgen05.mma 128x128x16, bf16 -> fp32 in TMEM, 2 accumulator buffers
+//   warps 2..5  epilogue: TMEM -> registers (bias, RoPE) -> bf16 -> swizzled smem -> TMA store
+// All waits are bounded; a wait that runs out sets *status and the CTA drains.
 #include "saf_internal.h"
+#include "sm100_prims.cuh"
+
 namespace saf {
-int launch_gemm_sm100(const SafIndexedLinearArgs&, cudaStream_t) { return SAF_ERR_UNSUPPORTED; }
+namespace {
+
+constexpr int GM = 128, GN = 128, GK = 64;
+constexpr int STAGES = 5;
+constexpr int A_BYTES = GM * GK * 2;            // 16 KB
+constexpr int B_BYTES = GN * GK * 2;            // 16 KB
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;  // 32 KB
+constexpr int OUT_BYTES = GM * GN * 2;          // 32 KB staging for the TMA store
+constexpr int MAX_SUB = 160;                    // 64-row blocks of output features (N <= 10240)
+constexpr int GEMM_THREADS = 192;
+
+struct SubTable {
+  int32_t row0[MAX_SUB];
+  uint8_t weight[MAX_SUB];
+  uint8_t rope[MAX_SUB];     // 0: none, 1: this 64-block is the first half of a rotated slab... see kernel
+};
+
+struct GemmParams {
+  int M, N, K, T, slab;
+  int tiles_m, tiles_n;
+  const void* bias[SAF_MAX_WEIGHTS];
+  const float* cosT;
+  const float* sinT;
+  int* status;
+};
+
+struct SmemLayout {
+  uint64_t full[STAGES], empty[STAGES], acc_full[2], acc_empty[2];
+  uint32_t tmem_base;
+};
+
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+indexed_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant__ CUtensorMap mapW0,
+                    const __grid_constant__ CUtensorMap mapW1, const __grid_constant__ CUtensorMap mapW2,
+                    const __grid_constant__ CUtensorMap mapW3, const __grid_constant__ CUtensorMap mapO,
+                    const __grid_constant__ GemmParams p, const __grid_constant__ SubTable tb) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* stage_base = smem;
+  uint8_t* out_stage = smem + STAGES * STAGE_BYTES;
+  SmemLayout* sl = reinterpret_cast<SmemLayout*>(out_stage + OUT_BYTES);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int KB = (p.K + GK - 1) / GK;
+  const int total_tiles = p.tiles_m * p.tiles_n;
+
+  if (tid == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&sl->full[s], 1);
+      mbar_init(&sl->empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&sl->acc_full[b], 1);
+      mbar_init(&sl->acc_empty[b], 128);
+    }
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&sl->tmem_base, 256);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = sl->tmem_base;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      const CUtensorMap* wm[4] = {&mapW0, &mapW1, &mapW2, &mapW3};
+      tma_prefetch_desc(&mapX);
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        const int tm = tile / p.tiles_n, tn = tile - tm * p.tiles_n;
+        const int nsub = min(2, (p.N - tn * GN) / 64);
+        for (int kb = 0; kb < KB; ++kb, ++it) {
+          const int s = it % STAGES;
+          if (!mbar_wait(&sl->empty[s], ((it / STAGES) & 1) ^ 1)) {
+            dev_set_error(p.status, SAF_DEV_TIMEOUT_TMA, 10);
+            ok = false;
+            break;
+          }
+          uint8_t* a = stage_base + s * STAGE_BYTES;
+          uint8_t* b = a + A_BYTES;
+          mbar_expect_tx(&sl->full[s], A_BYTES + nsub * (B_BYTES / 2));
+          tma_load_2d(a, &mapX, &sl->full[s], kb * GK, tm * GM);
+          for (int u = 0; u < nsub; ++u) {
+            const int sb = tn * 2 + u;
+            tma_load_2d(b + u * (B_BYTES / 2), wm[tb.weight[sb]], &sl->full[s], kb * GK, tb.row0[sb]);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc_bf16(GM, GN, 0, 0);
+      uint32_t it = 0, lt = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++lt) {
+        const int buf = lt & 1;
+        if (!mbar_wait(&sl->acc_empty[buf], ((lt >> 1) & 1) ^ 1)) {
+          dev_set_error(p.status, SAF_DEV_TIMEOUT_MMA, 11);
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d = tmem + buf * GN;
+        for (int kb = 0; kb < KB; ++kb, ++it) {
+          const int s = it % STAGES;
+          if (!mbar_wait(&sl->full[s], (it / STAGES) & 1)) {
+            dev_set_error(p.status, SAF_DEV_TIMEOUT_MMA, 12);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a = smem_u32(stage_base + s * STAGE_BYTES);
+          const uint32_t b = a + A_BYTES;
+#pragma unroll
+          for (int k4 = 0; k4 < GK / 16; ++k4) {
+            umma_ss(d, umma_smem_desc_sw128(a + k4 * 32, 16, 1024), umma_smem_desc_sw128(b + k4 * 32, 16, 1024), idesc,
+                    (kb | k4) != 0);
+          }
+          umma_commit(&sl->empty[s]);
+        }
+        if (ok) umma_commit(&sl->acc_full[buf]);
+      }
+    }
+  } else {
+    // epilogue warps 2..5 -> TMEM lane quadrant (warp % 4)
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;           // row inside the tile
+    const int etid = tid - 64;                  // 0..127
+    const int half = p.slab >> 1;
+    uint32_t lt = 0;
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++lt) {
+      const int tm = tile / p.tiles_n, tn = tile - tm * p.tiles_n;
+      const int nsub = min(2, (p.N - tn * GN) / 64);
+      const int buf = lt & 1;
+      if (!mbar_wait(&sl->acc_full[buf], (lt >> 1) & 1)) {
+        dev_set_error(p.status, SAF_DEV_TIMEOUT_EPI, 13);
+        break;
+      }
+      tc_fence_after();
+      // staging buffer free? (previous tile's TMA store has read it)
+      if (etid == 0) tma_store_wait_read();
+      named_bar_sync(1, 128);
+      const int m = tm * GM + row;
+      const int t = (p.T > 0) ? (m % p.T) : 0;
+      const uint32_t tsrc = tmem + ((uint32_t)(quad * 32) << 16) + buf * GN;
+      for (int u = 0; u < nsub; ++u) {
+        const int sb = tn * 2 + u;
+        const int w = tb.weight[sb];
+        const int rp = tb.rope[sb];
+        // column offset of this 64-block inside its slab (slab = 64: 0; slab = 128: 0 or 64)
+        const int in_slab = (sb * 64) % p.slab;
+        float v[64];
+        {
+          uint32_t r0[32], r1[32];
+          tmem_ld32(tsrc + u * 64, r0);
+          tmem_ld32(tsrc + u * 64 + 32, r1);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            v[j] = __uint_as_float(r0[j]);
+            v[32 + j] = __uint_as_float(r1[j]);
+          }
+        }
+        if (p.bias[w]) {
+          const __nv_bfloat16* bp = reinterpret_cast<const __nv_bfloat16*>(p.bias[w]) + tb.row0[sb];
+#pragma unroll
+          for (int j = 0; j < 64; ++j) v[j] += __bfloat162float(bp[j]);
+        }
+        if (rp) {   // warp-uniform: rows past M are rotated too (t stays a valid table row) and clipped by the store
+          const float* cr = p.cosT + (int64_t)t * p.slab;
+          const float* sr = p.sinT + (int64_t)t * p.slab;
+          if (p.slab == 64) {
+            // pairs (d, d+32) live in this block
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const float c = cr[j], s = sr[j];
+              const float x1 = v[j], x2 = v[32 + j];
+              v[j] = x1 * c - x2 * s;
+              v[32 + j] = x2 * c + x1 * s;
+            }
+          } else {
+            // slab 128: partner block is the other 64-column block of the same tile
+            const int pu = u ^ 1;
+            uint32_t q0[32], q1[32];
+            tmem_ld32(tsrc + pu * 64, q0);
+            tmem_ld32(tsrc + pu * 64 + 32, q1);
+            tmem_ld_wait();
+            const __nv_bfloat16* bp = p.bias[w] ? reinterpret_cast<const __nv_bfloat16*>(p.bias[w]) + tb.row0[tn * 2 + pu] : nullptr;
+#pragma unroll
+            for (int j = 0; j < 64; ++j) {
+              float o = __uint_as_float(j < 32 ? q0[j] : q1[j - 32]);
+              if (bp) o += __bfloat162float(bp[j]);
+              const int d = in_slab + j;
+              const float c = cr[d], s = sr[d];
+              // first half: x1*c - x2*s ; second half: x2*c + x1*s
+              v[j] = (in_slab == 0) ? (v[j] * c - o * s) : (v[j] * c + o * s);
+            }
+          }
+        }
+        // bf16 pack -> swizzled staging: 16-byte chunk c of row r lands at chunk (c ^ (r & 7))
+        uint8_t* dst = out_stage + u * (OUT_BYTES / 2) + row * 128;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          uint4 q;
+          q.x = pack_bf16(v[c * 8 + 0], v[c * 8 + 1]);
+          q.y = pack_bf16(v[c * 8 + 2], v[c * 8 + 3]);
+          q.z = pack_bf16(v[c * 8 + 4], v[c * 8 + 5]);
+          q.w = pack_bf16(v[c * 8 + 6], v[c * 8 + 7]);
+          *reinterpret_cast<uint4*>(dst + ((c ^ (row & 7)) << 4)) = q;
+        }
+      }
+      // accumulator buffer can be overwritten by the MMA warp
+      tc_fence_before();
+      mbar_arrive(&sl->acc_empty[buf]);
+      fence_proxy_async_smem();
+      named_bar_sync(1, 128);
+      if (etid == 0) {
+        for (int u = 0; u < nsub; ++u) tma_store_2d(&mapO, out_stage + u * (OUT_BYTES / 2), tn * GN + u * 64, tm * GM);
+        tma_store_commit();
+      }
+    }
+    if (etid == 0) tma_store_wait_all();
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem, 256);
+}
+
+bool aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
+
+}  // namespace
+
+int launch_gemm_sm100(const SafIndexedLinearArgs& a, cudaStream_t st) {
+  if (a.dtype != SAF_BF16) return SAF_ERR_UNSUPPORTED;
+  if (a.slab != 64 && a.slab != 128) return SAF_ERR_UNSUPPORTED;
+  const int N = a.n_slabs * a.slab;
+  if (N / 64 > MAX_SUB) return SAF_ERR_UNSUPPORTED;
+  if (a.C % 8 || a.ldx % 8 || a.ldo % 8 || !aligned16(a.x) || !aligned16(a.out)) return SAF_ERR_UNSUPPORTED;
+  for (int w = 0; w < a.n_weights; ++w) {
+    if (!a.weights[w]) continue;
+    if (a.ldw[w] % 8 || (a.cdw[w] != 0 && a.cdw[w] != 1) || !aligned16(a.weights[w])) return SAF_ERR_UNSUPPORTED;
+  }
+  if (!saf_device_supported()) return SAF_ERR_UNSUPPORTED;
+
+  CUtensorMap mx, mw[4], mo;
+  int rc;
+  {
+    uint64_t dims[2] = {(uint64_t)a.C, (uint64_t)a.M};
+    uint64_t strides[2] = {0, (uint64_t)a.ldx * 2};
+    uint32_t box[2] = {GK, GM};
+    if ((rc = make_tensor_map_bf16(&mx, a.x, 2, dims, strides, box, true))) return rc;
+  }
+  for (int w = 0; w < 4; ++w) {
+    const int ww = (w < a.n_weights && a.weights[w]) ? w : 0;
+    uint64_t dims[2] = {(uint64_t)a.C, (uint64_t)a.rows_w[ww]};
+    uint64_t strides[2] = {0, (uint64_t)a.ldw[ww] * 2};
+    uint32_t box[2] = {GK, 64};
+    if ((rc = make_tensor_map_bf16(&mw[w], a.weights[ww], 2, dims, strides, box, true))) return rc;
+  }
+  {
+    uint64_t dims[2] = {(uint64_t)N, (uint64_t)a.M};
+    uint64_t strides[2] = {0, (uint64_t)a.ldo * 2};
+    uint32_t box[2] = {64, GM};
+    if ((rc = make_tensor_map_bf16(&mo, a.out, 2, dims, strides, box, false))) return rc;
+  }
+  SubTable tb;
+  memset(&tb, 0, sizeof(tb));
+  const int per = a.slab / 64;
+  for (int g = 0; g < a.n_slabs; ++g)
+    for (int u = 0; u < per; ++u) {
+      tb.row0[g * per + u] = a.slab_row0[g] + u * 64;
+      tb.weight[g * per + u] = (uint8_t)a.slab_weight[g];
+      tb.rope[g * per + u] = (uint8_t)(a.slab_rope ? (a.slab_rope[g] != 0) : 0);
+    }
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.M = a.M; p.N = N; p.K = a.C; p.T = a.T; p.slab = a.slab;
+  p.tiles_m = (a.M + GM - 1) / GM;
+  p.tiles_n = (N + GN - 1) / GN;
+  for (int w = 0; w < a.n_weights; ++w) p.bias[w] = a.biases[w];
+  p.cosT = a.rope_cos;
+  p.sinT = a.rope_sin;
+  p.status = a.status;
+
+  static int sm_count = 0;
+  if (!sm_count) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+  }
+  const size_t smem = 1024 + STAGES * STAGE_BYTES + OUT_BYTES + sizeof(SmemLayout);
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(indexed_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return fail(SAF_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    attr_set = true;
+  }
+  const int grid = std::min(sm_count, p.tiles_m * p.tiles_n);
+  indexed_gemm_kernel<<<grid, GEMM_THREADS, smem, st>>>(mx, mw[0], mw[1], mw[2], mw[3], mo, p, tb);
+  count_launch();
+  return check_launch("indexed_gemm_kernel");
+}
+
 }  // namespace saf

@@ -389,6 +389,8 @@ def _slabs_of(rows):
     for _, n in runs:
         slab = math.gcd(slab, n)
     slab = max(slab, 1)
+    if slab % 64 == 0:
+        slab = 64   # the tensor-core GEMM addresses weights in 64-row blocks
     row0 = []
     for first, n in runs:
         row0.extend(range(first, first + n, slab))

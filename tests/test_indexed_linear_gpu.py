@@ -106,3 +106,34 @@ def test_decomposed_logz_kernel():
     z_ref = O.decomposed_logz(alpha.double(), rho.double())
     z = decomposed_logz(alpha.cuda(), rho.cuda())
     assert O.max_abs(z.cpu(), z_ref) <= 1e-5
+
+
+@pytest.mark.parametrize("cfg", [(2, 9000, 768, 12, 64, [0, 1, 3, 4, 6, 7, 9, 10, 11], False),
+                                 (2, 1000, 768, 12, 64, [0, 1, 3, 4, 6, 7, 9, 10, 11], True),
+                                 (1, 700, 512, 4, 128, [0, 2, 3], False),
+                                 (3, 129, 256, 4, 64, [], False)],
+                         ids=["c2shape", "bias", "hd128", "allfrozen"])
+def test_qkv_projection_with_rope_epilogue(cfg):
+    """[Q(live) | K(live) | V(all)] in one tensor-core GEMM with the rotation in the epilogue equals
+    projection followed by the reference's apply_rotary_pos_emb (nanogpt/model.py:63-68)."""
+    from saf_b200 import qkv_projection
+    B, T, C, H, hd, live, bias = cfg
+    dev = "cuda"
+    g = torch.Generator().manual_seed(T + C + hd)
+    x = torch.randn(B, T, C, generator=g).bfloat16()
+    ws = [(torch.randn(H * hd, C, generator=g) * 0.05).bfloat16() for _ in range(3)]
+    bs = [(torch.randn(H * hd, generator=g) * 0.1).bfloat16() for _ in range(3)] if bias else None
+    cos, sin = O.rope_cache(hd, T)
+    rows = head_rows(live, hd) if live else torch.zeros(0, dtype=torch.long)
+    xf = x.float()
+    q = O.linear_rows(xf, ws[0].float(), None if bs is None else bs[0].float(), rows).view(B, T, len(live), hd)
+    k = O.linear_rows(xf, ws[1].float(), None if bs is None else bs[1].float(), rows).view(B, T, len(live), hd)
+    v = torch.nn.functional.linear(xf, ws[2].float(), None if bs is None else bs[2].float())
+    q = O.apply_rope(q.transpose(1, 2), cos, sin).transpose(1, 2).reshape(B * T, -1)
+    k = O.apply_rope(k.transpose(1, 2), cos, sin).transpose(1, 2).reshape(B * T, -1)
+    ref = torch.cat([q, k, v.reshape(B * T, -1)], dim=-1)
+    out = qkv_projection(x.to(dev), *[w.to(dev) for w in ws], live, hd, rope=(cos.to(dev), sin.to(dev)), T=T,
+                         biases=None if bs is None else [b.to(dev) for b in bs])
+    assert out.shape == ref.shape
+    a, r = errs(out, ref)
+    assert r <= 5e-3 and a <= 2e-2 * max(1.0, ref.abs().max().item()), f"{a} {r}"
