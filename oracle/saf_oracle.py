@@ -81,10 +81,10 @@ def sink_decay_pattern(alpha, rho, T, dtype=torch.float64):
     out = []
     for a, r in zip(alpha.tolist(), rho.tolist()):
         dec = torch.where(causal, torch.tensor(r, dtype=dtype) ** dist.clamp(min=0), torch.zeros((), dtype=dtype))
-        z = dec.sum(-1, keepdim=True)
-        p = (1.0 - a) * dec / z
-        p[:, 0] += a
-        out.append(p)
+        dec /= dec.sum(-1, keepdim=True)
+        dec *= (1.0 - a)
+        dec[:, 0] += a
+        out.append(dec)
     return torch.stack(out)
 
 
@@ -232,7 +232,7 @@ def linear_permuted_cols(y, weight, bias, cols):
 # one attention layer (the module hook)     nanogpt/model.py:1063-1077, 824-844
 # ---------------------------------------------------------------------------
 def attention_layer(x, wq, wk, wv, wo, frozen, patt, n_head, rope=None, alpha=None, rho=None,
-                    z=None, dtype=torch.float32, row_chunk=1024):
+                    z=None, dtype=torch.float32, row_chunk=1024, pidx=None):
     """Eager capture path of the reference's CausalSelfAttention in dynamic mode:
     full q/k/v projections, RoPE on q,k, softmax for live heads and stored pattern
     for frozen ones, then c_proj.  x: (B,T,C); w*: (C,C) in F.linear layout.
@@ -246,7 +246,7 @@ def attention_layer(x, wq, wk, wv, wo, frozen, patt, n_head, rope=None, alpha=No
     if rope is not None:
         cos, sin = rope[0].to(dtype), rope[1].to(dtype)
         q, k = apply_rope(q, cos, sin), apply_rope(k, cos, sin)
-    y = mixed_attn(q, k, v, patt, frozen, alpha=alpha, rho=rho, z=z, dtype=dtype, row_chunk=row_chunk)
+    y = mixed_attn(q, k, v, patt, frozen, pidx=pidx, alpha=alpha, rho=rho, z=z, dtype=dtype, row_chunk=row_chunk)
     y = y.transpose(1, 2).reshape(B, T, C)
     return y @ wo.to(dtype).t()
 

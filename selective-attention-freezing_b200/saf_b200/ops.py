@@ -53,6 +53,12 @@ def _require_cuda(t, name):
         raise RuntimeError("%s must be a CUDA tensor: this package has no CPU path" % name)
 
 
+def _ver(t):
+    """Version counter of a tensor; inference tensors have none (they cannot be modified in place
+    outside inference mode either), so they count as version 0."""
+    return 0 if t.is_inference() else t._version
+
+
 # host copies of small device index tensors, refreshed when the tensor changes
 _HOST_CACHE = {}
 
@@ -68,7 +74,7 @@ def host_ints(t):
     if t is None:
         return None
     hit = _HOST_CACHE.get(id(t))
-    if hit is not None and hit[0]() is t and hit[1] == t._version:
+    if hit is not None and hit[0]() is t and hit[1] == _ver(t):
         return hit[2]
     if t.is_cuda and torch.cuda.is_current_stream_capturing():
         return None
@@ -78,7 +84,7 @@ def host_ints(t):
             del _HOST_CACHE[k]
         if len(_HOST_CACHE) > 1024:
             _HOST_CACHE.clear()
-    _HOST_CACHE[id(t)] = (weakref.ref(t), t._version, vals)
+    _HOST_CACHE[id(t)] = (weakref.ref(t), _ver(t), vals)
     return vals
 
 
@@ -188,6 +194,19 @@ def _fill_mixed(a, q, k, v, out, lse, patt, alpha, rho, z, frozen, hidx, pidx, k
         a.rope_cos, a.rope_sin = _ptr(rope[0]), _ptr(rope[1])
 
 
+# attention-op timing probe: CUDA-event pairs around every forward attention launch, the same
+# protocol as the reference's AttnOpProbe (qwen/nanogpt/bench_qwen_prefill_triton.py:186-225)
+_ATTN_EVENTS = None
+
+
+def attention_timing(enable):
+    """Start (True) or stop (False) collecting event pairs; stopping returns the collected list."""
+    global _ATTN_EVENTS
+    got = _ATTN_EVENTS
+    _ATTN_EVENTS = [] if enable else None
+    return got
+
+
 class _FusedMixedAttn(torch.autograd.Function):
     """Mirror of kernel/fused_attn.py:626-647."""
 
@@ -205,7 +224,14 @@ class _FusedMixedAttn(torch.autograd.Function):
         a, keep = SafMixedAttnArgs(), []
         _fill_mixed(a, q, k, v, out, lse, patt, alpha, rho, z, frozen, hidx, pidx, kvidx, sm_scale, rope,
                     sink_decay, keep)
-        check(lib.saf_mixed_attn_fwd(C.byref(a), _stream(v)))
+        if _ATTN_EVENTS is not None:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            check(lib.saf_mixed_attn_fwd(C.byref(a), _stream(v)))
+            e1.record()
+            _ATTN_EVENTS.append((e0, e1))
+        else:
+            check(lib.saf_mixed_attn_fwd(C.byref(a), _stream(v)))
         ctx.save_for_backward(q, k, v, patt, alpha, rho, z, frozen, hidx, pidx, out, lse,
                               *(rope or ()), *(sink_decay or ()))
         ctx.sm_scale = sm_scale
@@ -375,7 +401,7 @@ def _slabs_of(rows):
     Returns (slab, [row0...]).  One device->host copy per distinct index tensor
     object and version."""
     hit = _SLAB_CACHE.get(id(rows))
-    if hit is not None and hit[0]() is rows and hit[1] == rows._version:
+    if hit is not None and hit[0]() is rows and hit[1] == _ver(rows):
         return hit[2]
     if rows.is_cuda and torch.cuda.is_current_stream_capturing():
         raise RuntimeError("index tensor not seen before CUDA graph capture: run one warm-up call first")
@@ -397,7 +423,7 @@ def _slabs_of(rows):
     out = (slab, row0)
     if len(_SLAB_CACHE) > 1024:
         _SLAB_CACHE.clear()
-    _SLAB_CACHE[id(rows)] = (weakref.ref(rows), rows._version, out)
+    _SLAB_CACHE[id(rows)] = (weakref.ref(rows), _ver(rows), out)
     return out
 
 

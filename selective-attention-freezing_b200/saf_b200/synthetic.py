@@ -1,0 +1,70 @@
+"""Seeded synthetic stand-ins for the benchmark configurations (no dataset or checkpoint is needed:
+the reference's own benches draw random token ids and uniform patterns too,
+nanogpt/bench_inference_triton.py:86-111,170-173)."""
+from types import SimpleNamespace
+
+import torch
+
+from .attention import SafCausalSelfAttention, rope_tables
+
+WORKLOADS = {
+    # name: layers, heads, head_dim, frozen heads per layer, sequence, batch per GPU
+    "c1": dict(n_layer=12, n_head=12, head_dim=64, n_frozen=3, T=4096, B=16, rope_base=10000.0),
+    "c2": dict(n_layer=12, n_head=12, head_dim=64, n_frozen=3, T=16384, B=4, rope_base=10000.0),
+    "c3": dict(n_layer=24, n_head=16, head_dim=128, n_frozen=4, T=8192, B=2, rope_base=10000.0),
+    "tiny": dict(n_layer=2, n_head=4, head_dim=64, n_frozen=1, T=512, B=2, rope_base=10000.0),
+}
+
+
+def frozen_heads_for_layer(n_head, n_frozen, seed, layer):
+    g = torch.Generator().manual_seed(seed + layer)
+    return sorted(torch.randperm(n_head, generator=g)[:n_frozen].tolist())
+
+
+def sink_decay_params(n, seed):
+    """a ~ U(0.05, 0.3), r ~ U(0.8, 0.99) per frozen head."""
+    g = torch.Generator().manual_seed(seed)
+    a = 0.05 + 0.25 * torch.rand(n, generator=g, dtype=torch.float64)
+    r = 0.8 + 0.19 * torch.rand(n, generator=g, dtype=torch.float64)
+    return a, r
+
+
+def build_attention_stack(name, device, dtype=torch.bfloat16, seed=1337):
+    """The attention+projection stack of a GPT-2-style model: one SafCausalSelfAttention per layer with
+    random-init N(0, 0.02^2) weights, 25 % of the heads of every layer frozen on seeded sink+decay patterns."""
+    w = WORKLOADS[name]
+    C = w["n_head"] * w["head_dim"]
+    cfg = SimpleNamespace(n_embd=C, n_head=w["n_head"], block_size=w["T"], bias=False, dropout=0.0,
+                          position_encoding="rope", rand_attn_prior_repr="dense", freeze_pattern_dtype="bfloat16")
+    g = torch.Generator().manual_seed(seed)
+    layers = []
+    for li in range(w["n_layer"]):
+        m = SafCausalSelfAttention(cfg, layer_idx=li)
+        with torch.no_grad():
+            for lin in (m.q_proj, m.k_proj, m.v_proj, m.c_proj):
+                lin.weight.copy_(torch.randn(C, C, generator=g) * 0.02)
+        fz = frozen_heads_for_layer(w["n_head"], w["n_frozen"], seed, li)
+        a, r = sink_decay_params(len(fz), seed + 1000 + li)
+        m.freeze_heads_sink_decay(fz, a.tolist(), r.tolist())
+        layers.append(m.to(device=device, dtype=dtype).eval())
+    cos, sin = rope_tables(w["head_dim"], w["T"], base=w["rope_base"], device=device)
+    rope = (cos.view(1, 1, w["T"], -1), sin.view(1, 1, w["T"], -1))
+    return layers, rope, w
+
+
+def stack_forward(layers, rope, x, probe=None):
+    """x -> layer_L(...layer_1(x)); `probe(i, fn)` may wrap each layer call (timing)."""
+    h = x
+    for i, m in enumerate(layers):
+        h = m(h, rope=rope) if probe is None else probe(i, m, h, rope)
+    return h
+
+
+def hot_stack_flops(w):
+    """Algorithmic FLOPs of one pass per sequence in the batch: live causal attention, indexed QKV GEMM, c_proj."""
+    H, hd, T, nf = w["n_head"], w["head_dim"], w["T"], w["n_frozen"]
+    U, C = H - nf, H * hd
+    live = 2 * U * T * T * hd                     # causal half of 4 T^2 hd
+    qkv = 2 * T * C * (2 * U + H) * hd
+    oproj = 2 * T * C * C
+    return dict(live=live * w["n_layer"], qkv=qkv * w["n_layer"], oproj=oproj * w["n_layer"])

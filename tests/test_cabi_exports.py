@@ -1,0 +1,107 @@
+"""CPU-side checks of the C ABI: the library loads without a GPU, exports every symbol the header
+declares, its structs have the size the ctypes mirror assumes, and bad arguments are refused with
+an error code and a message before anything touches a device."""
+import ctypes as C
+import os
+import re
+import subprocess
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+HEADER = os.path.join(ROOT, "include", "saf_b200.h")
+
+
+def declared_functions():
+    src = open(HEADER).read()
+    src = re.sub(r"/\*.*?\*/", "", src, flags=re.S)
+    return sorted(set(re.findall(r"\b(saf_[a-z0-9_]+)\s*\(", src)))
+
+
+def test_every_declared_symbol_is_exported():
+    from saf_b200 import _cabi
+    names = declared_functions()
+    assert len(names) >= 12
+    for n in names:
+        assert hasattr(_cabi.lib, n), f"{n} declared in include/saf_b200.h but not exported"
+    assert set(names) == set(_cabi.EXPORTS)
+
+
+def test_struct_sizes_match_the_header(tmp_path):
+    from saf_b200 import _cabi
+    prog = tmp_path / "sz.c"
+    prog.write_text('#include <stdio.h>\n#include "saf_b200.h"\nint main(){printf("%zu %zu %zu %zu %zu\\n",'
+                    "sizeof(SafTensor),sizeof(SafMixedAttnArgs),sizeof(SafMixedAttnBwdArgs),sizeof(SafFrozenPvArgs),"
+                    "sizeof(SafIndexedLinearArgs));return 0;}\n")
+    exe = tmp_path / "sz"
+    subprocess.check_call(["gcc", "-I", os.path.join(ROOT, "include"), str(prog), "-o", str(exe)])
+    got = [int(x) for x in subprocess.check_output([str(exe)]).split()]
+    want = [C.sizeof(t) for t in (_cabi.SafTensor, _cabi.SafMixedAttnArgs, _cabi.SafMixedAttnBwdArgs,
+                                  _cabi.SafFrozenPvArgs, _cabi.SafIndexedLinearArgs)]
+    assert got == want
+
+
+def test_invalid_arguments_are_refused_before_launch():
+    from saf_b200 import _cabi
+    a = _cabi.SafMixedAttnArgs()
+    a.struct_size = 12
+    assert _cabi.lib.saf_mixed_attn_fwd(C.byref(a), None) == _cabi.SAF_ERR_INVALID
+    assert "size mismatch" in _cabi.last_error()
+    a.struct_size = C.sizeof(_cabi.SafMixedAttnArgs)
+    a.dtype, a.B, a.H, a.T, a.HD, a.force_state = _cabi.SAF_BF16, 1, 2, 16, 256, -1
+    assert _cabi.lib.saf_mixed_attn_fwd(C.byref(a), None) == _cabi.SAF_ERR_UNSUPPORTED
+    assert "head_dim" in _cabi.last_error()
+    a.HD = 64
+    assert _cabi.lib.saf_mixed_attn_fwd(C.byref(a), None) == _cabi.SAF_ERR_INVALID   # null v / out
+    assert _cabi.lib.saf_mixed_attn_fwd(None, None) == _cabi.SAF_ERR_INVALID
+    p = _cabi.SafFrozenPvArgs()
+    assert _cabi.lib.saf_frozen_pv_fwd(C.byref(p), None) == _cabi.SAF_ERR_INVALID
+    ln = _cabi.SafIndexedLinearArgs()
+    ln.struct_size = C.sizeof(_cabi.SafIndexedLinearArgs)
+    ln.dtype, ln.M, ln.C, ln.n_weights, ln.n_slabs, ln.slab = _cabi.SAF_F16, 4, 8, 1, 1, 8
+    assert _cabi.lib.saf_indexed_linear_fwd(C.byref(ln), None) == _cabi.SAF_ERR_UNSUPPORTED
+    assert _cabi.lib.saf_decomposed_logz(None, None, None, 2, 8, None) == _cabi.SAF_ERR_INVALID
+    assert _cabi.lib.saf_decomposed_logz(None, None, None, 0, 8, None) == _cabi.SAF_OK
+
+
+def test_operators_refuse_cpu_tensors():
+    import torch
+    import kernel
+    v = torch.zeros(1, 2, 4, 8)
+    assert kernel.fused_attn_usable(v) is False and kernel.frozen_pv_usable(v) is False
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        kernel.fused_mixed_attn(v, v, v, None, torch.zeros(2, dtype=torch.int32))
+    assert kernel.HAVE_TRITON and kernel.BAND_ROWS == 64
+
+
+def test_host_helpers_match_oracle():
+    import torch
+    import kernel
+    from oracle import saf_oracle as O
+    g = torch.Generator().manual_seed(1)
+    al, rh = torch.randn(3, 128, generator=g), torch.randn(3, 128, generator=g)
+    assert torch.equal(kernel.make_rho_band(rh), O.make_rho_band(rh))
+    assert torch.equal(kernel.decomp_logits(al, rh, rows=(5, 9)), O.decomp_logits(al, rh, rows=(5, 9)))
+    assert O.max_abs(kernel.decomposed_logz(al, rh), O.decomposed_logz(al, rh)) <= 1e-6
+    with pytest.raises(AssertionError, match="multiple of 64"):
+        kernel.make_rho_band(torch.zeros(2, 100))
+
+
+def test_slab_decomposition_and_pattern_classifier():
+    import torch
+    from saf_b200.ops import _slabs_of
+    from saf_b200.attention import classify_sink_decay
+    from oracle import saf_oracle as O
+    rows = (torch.tensor([0, 1, 3, 6])[:, None] * 64 + torch.arange(64)).reshape(-1)
+    slab, row0 = _slabs_of(rows)
+    assert slab == 64 and row0 == [0, 64, 192, 384]
+    slab, row0 = _slabs_of(torch.tensor([5, 6, 7, 20, 21, 22, 40, 41, 42]))
+    assert slab == 3 and row0 == [5, 20, 40]
+    a, r = O.sink_decay_params(3, seed=2)
+    P = O.sink_decay_pattern(a, r, 200)
+    for i in range(3):
+        got = classify_sink_decay(P[i].float())
+        assert got is not None and abs(got[0] - a[i].item()) < 1e-5 and abs(got[1] - r[i].item()) < 1e-5
+    rnd = torch.rand(64, 64).tril()
+    assert classify_sink_decay(rnd / rnd.sum(-1, keepdim=True)) is None
