@@ -104,6 +104,25 @@ typedef struct SafMixedAttnBwdArgs {
 
 int saf_mixed_attn_bwd(const SafMixedAttnBwdArgs* args, void* stream);
 
+/* Same backward for callers that cannot supply scratch memory (no counterpart in the
+ * reference, which always allocates through torch).  Meant for hosts that planned
+ * their whole device arena ahead of time, plugin interfaces that pass only the
+ * operator's own tensors, or call sites where a device allocation is not allowed
+ * because it may synchronise the GPU.  `args->delta` is ignored: delta lives in a
+ * fixed array of SAF_STATIC_DELTA_FLOATS fp32 values (4 MiB) that every GPU loading
+ * this library holds until the process exits.
+ *   - B*H*T must not exceed SAF_STATIC_DELTA_FLOATS, else SAF_ERR_LIMIT (nothing runs).
+ *   - The call allocates nothing.  The first call on each device looks up the
+ *     array's device address (once per device, with that device current); make
+ *     that first call before starting any stream capture.
+ *   - All calls on a device share the array, which keeps the last call's values;
+ *     nothing in it needs clearing (rows are written before they are read), but
+ *     two calls that overlap on the GPU race on it -- keep them on one stream or
+ *     order them with events.
+ * Inputs, outputs and every other rule are those of saf_mixed_attn_bwd. */
+#define SAF_STATIC_DELTA_FLOATS (1 << 20)
+int saf_mixed_attn_bwd_static(const SafMixedAttnBwdArgs* args, void* stream);
+
 /* ---------------------------------------------------------------------------
  * Frozen heads only, compact values.
  * Replaces frozen_pv / _pv_fwd_kernel / _pv_bwd_kernel

@@ -13,6 +13,7 @@ SAF_OK, SAF_ERR_INVALID, SAF_ERR_UNSUPPORTED, SAF_ERR_CUDA, SAF_ERR_LIMIT = 0, -
 SAF_F32, SAF_BF16, SAF_F16 = 0, 1, 2
 LIVE, DENSE, DECOMP, SINK_DECAY = 0, 1, 2, 3
 MAX_WEIGHTS = 4
+STATIC_DELTA_FLOATS = 1 << 20
 
 
 class SafTensor(C.Structure):
@@ -67,7 +68,7 @@ class SafIndexedLinearArgs(C.Structure):
 
 EXPORTS = (
     "saf_abi_version", "saf_last_error", "saf_launch_count", "saf_device_supported",
-    "saf_mixed_attn_fwd", "saf_mixed_attn_bwd", "saf_frozen_pv_fwd", "saf_frozen_pv_bwd",
+    "saf_mixed_attn_fwd", "saf_mixed_attn_bwd", "saf_mixed_attn_bwd_static", "saf_frozen_pv_fwd", "saf_frozen_pv_bwd",
     "saf_indexed_linear_fwd", "saf_indexed_linear_bwd_dx", "saf_indexed_linear_bwd_dw",
     "saf_decomposed_logz",
 )
@@ -91,6 +92,7 @@ def _load():
     lib.saf_launch_count.restype = C.c_int64
     lib.saf_device_supported.restype = C.c_int
     for name, at in (("saf_mixed_attn_fwd", SafMixedAttnArgs), ("saf_mixed_attn_bwd", SafMixedAttnBwdArgs),
+                     ("saf_mixed_attn_bwd_static", SafMixedAttnBwdArgs),
                      ("saf_frozen_pv_fwd", SafFrozenPvArgs), ("saf_frozen_pv_bwd", SafFrozenPvArgs),
                      ("saf_indexed_linear_fwd", SafIndexedLinearArgs)):
         f = getattr(lib, name)
