@@ -1,26 +1,34 @@
-// Live-head causal flash attention on tcgen05 / TMEM, fed by TMA.
+// Mixed-attention forward on tcgen05 / TMEM, fed by TMA: live heads as causal flash attention,
+// structured (sink + decay) frozen heads as a co-scheduled scan, all in one launch.
 //
-// Replaces the live branch of the reference's fused forward (_acc_flash inside
-// _fwd_kernel, kernel/fused_attn.py:182-289: 64x64 Triton tiles, pointer loads,
-// 4 warps, no persistence).  One CTA owns TWO consecutive 128-row query tiles of one
-// (batch, head) and walks the causal range of 128-key tiles once for both:
+// Replaces the reference's fused forward (_fwd_kernel / _acc_flash, kernel/fused_attn.py:182-289:
+// 64x64 Triton tiles, pointer loads, 4 warps, no persistence).  A live CTA owns TWO consecutive
+// 128-row query tiles of one (batch, head) and walks the causal range of 128-key tiles once for both:
 //
-//   warps 0-3   softmax of query tile 0 (one thread per row: TMEM lane == row)
+//   warps 0-3   softmax of query tile 0 (one thread per row: TMEM lane == row, no shuffles)
 //   warps 4-7   softmax of query tile 1
 //   warp  8     TMA producer: Q tiles once, then K_j / V_j tiles through a ring of stages
 //   warp  9     MMA issuer:   S_t = Q_t K_j^T  (SS, 128x128xHD)  -> TMEM
 //                             O_t += P_t V_j   (TS: P read from TMEM, V MN-major in smem)
+//   warps 10-11 complete the third warpgroup (register reallocation works per warpgroup)
 //
-// TMEM columns: S0 [0,128) S1 [128,256) O0 [256,256+HD) O1 [256+HD,256+2HD).  P (bf16)
-// overwrites the first 64 columns of its S buffer, so scores never touch shared or
-// global memory.  The two query tiles alternate on the tensor core: while one tile's
-// scores are in the softmax warps the other tile's MMAs run.  The running output is
-// rescaled lazily: only when a row maximum grows by more than 2^8 (exact, because the
-// final normaliser l carries the same reference maximum).
+// TMEM columns: S0 [0,128) S1 [128,256) O0 [256,256+HD) O1 [256+HD,256+2HD).  P (bf16) overwrites
+// the first 64 columns of its S buffer, so scores never touch shared or global memory.  The two
+// query tiles alternate on the tensor core: while one tile's scores are in its softmax warps the
+// other tile's MMAs run.  The softmax warps take registers from the control warpgroup
+// (setmaxnreg) so a full 128-column score row stays in registers; their arithmetic uses the
+// packed f32x2 FMA/ADD and the 3-input max of sm_100, and a share of the exponentials is
+// evaluated on the FMA pipe (Cody-Waite + cubic) because the MUFU pipe is the narrowest unit
+// at head_dim 64.  The running output is rescaled lazily: only when a row maximum grows by more
+// than 2^8 (exact, because the final normaliser l carries the same reference maximum).
 //
-// Head state is read per CTA from `frozen`; CTAs of heads in another state leave at
-// once (their work belongs to the scan / pattern kernels).
+// Grid order: first one slot per (batch, head) that runs the O(T) scan if that head is frozen on a
+// structured pattern (first 256 threads; other heads' slots exit) -- they start at time zero and
+// finish long before the live tiles, so frozen heads cost no launch and almost no time.  Then the
+// live tiles, in groups of 8 (batch, head) pairs so the CTAs in flight share K/V in L2, heaviest
+// row tiles first inside a group.  CTAs of dense / decomposed heads exit (pattern kernels take them).
 #include "saf_internal.h"
+#include "scan_body.cuh"
 #include "sm100_prims.cuh"
 
 namespace saf {
@@ -28,9 +36,13 @@ namespace {
 
 constexpr int FM = 128;             // rows per query tile
 constexpr int FN = 128;             // keys per step
-constexpr int FLASH_THREADS = 320;
+constexpr int FLASH_THREADS = 384;
+constexpr int HEAD_GROUP = 8;
 constexpr float LOG2E_F = 1.4426950408889634f;
 constexpr float RESCALE_THRESHOLD = 8.0f;
+#ifndef SAF_POLY_EXP_PER_16
+#define SAF_POLY_EXP_PER_16 0       // of every 16 exponentials, this many run on the FMA pipe
+#endif
 
 template <int HD>
 struct Cfg {
@@ -52,6 +64,8 @@ struct FlashParams {
   float* lse;
   int64_t lse_s[3];
   int* status;
+  int has_scan;
+  ScanArgs scan;
 };
 
 struct FlashBars {
@@ -66,6 +80,34 @@ __device__ __forceinline__ float ex2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+// 2^x on the FMA/ALU pipes for x in [-126, 126]: round to nearest integer with the magic-number
+// add, cubic minimax on the fraction in [-0.5, 0.5], exponent added as an integer shift.
+// Relative error ~1e-4, far below the bf16 rounding the result goes through.
+__device__ __forceinline__ float2 exp2_poly2(float2 x) {
+  const float magic = 12582912.f;  // 1.5 * 2^23
+  x.x = fmaxf(x.x, -126.f);
+  x.y = fmaxf(x.y, -126.f);
+  const float2 t = __fadd2_rn(x, make_float2(magic, magic));
+  const float2 n = __fadd2_rn(t, make_float2(-magic, -magic));
+  const float2 f = __fadd2_rn(x, make_float2(-n.x, -n.y));
+  float2 p = __ffma2_rn(f, make_float2(0.0555054f, 0.0555054f), make_float2(0.2402265f, 0.2402265f));
+  p = __ffma2_rn(p, f, make_float2(0.6931472f, 0.6931472f));
+  p = __ffma2_rn(p, f, make_float2(1.f, 1.f));
+  float2 r;
+  r.x = __int_as_float(__float_as_int(p.x) + (__float_as_int(t.x) << 23));
+  r.y = __int_as_float(__float_as_int(p.y) + (__float_as_int(t.y) << 23));
+  return r;
+}
+
+template <int N>
+__device__ __forceinline__ void reg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
+template <int N>
+__device__ __forceinline__ void reg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
 
 template <int HD>
 __device__ __forceinline__ void load_tile(uint8_t* dst, const CUtensorMap* m, uint64_t* bar, int row, int head, int b) {
@@ -79,10 +121,24 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
                  const __grid_constant__ CUtensorMap mapV, const __grid_constant__ CUtensorMap mapO,
                  const __grid_constant__ FlashParams p) {
   using C = Cfg<HD>;
-  // work item: heaviest row-tile pairs first
   const int bh_count = p.B * p.H;
-  const int mp = p.n_pairs - 1 - (int)(blockIdx.x / bh_count);
-  const int bh = blockIdx.x % bh_count;
+  // ---- scan slots ---------------------------------------------------------------------------
+  if ((int)blockIdx.x < bh_count) {
+    const int b = blockIdx.x / p.H, h = blockIdx.x % p.H;
+    const int state = p.force_state >= 0 ? p.force_state : p.frozen[h];
+    if (state == SAF_SINK_DECAY && p.has_scan && threadIdx.x < SCAN_NT)
+      for (int col0 = 0; col0 < HD; col0 += SCAN_COLS) sink_decay_scan_cta<__nv_bfloat16, false>(p.scan, b, h, col0);
+    return;
+  }
+  // ---- live tiles: head groups, heaviest row-tile pairs first inside a group ------------------
+  const int li = blockIdx.x - bh_count;
+  const int per_group = HEAD_GROUP * p.n_pairs;
+  const int grp = li / per_group;
+  const int gsize = min(HEAD_GROUP, bh_count - grp * HEAD_GROUP);
+  const int rem = li - grp * per_group;
+  if (rem >= gsize * p.n_pairs) return;
+  const int mp = p.n_pairs - 1 - rem / gsize;
+  const int bh = grp * HEAD_GROUP + rem % gsize;
   const int b = bh / p.H, h = bh % p.H;
   const int state = p.force_state >= 0 ? p.force_state : p.frozen[h];
   if (state != SAF_LIVE) return;
@@ -125,108 +181,112 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
   tc_fence_after();
   const uint32_t tmem = bars->tmem_base;
 
-  if (warp == 8) {
-    // ------------------------------------------------------------ TMA producer
-    if (lane == 0) {
-      tma_prefetch_desc(&mapQ);
-      tma_prefetch_desc(&mapK);
-      tma_prefetch_desc(&mapV);
-      mbar_expect_tx(&bars->q_full, (act1 ? 2 : 1) * C::TILE_BYTES);
-      load_tile<HD>(sQ, &mapQ, &bars->q_full, row0, hq, b);
-      if (act1) load_tile<HD>(sQ + C::TILE_BYTES, &mapQ, &bars->q_full, row0 + FM, hq, b);
-      for (int item = 0; item < 2 * nkv; ++item) {
-        const int s = item % C::NSTAGE;
-        if (!mbar_wait(&bars->kv_empty[s], ((item / C::NSTAGE) & 1) ^ 1)) {
-          dev_set_error(p.status, SAF_DEV_TIMEOUT_TMA, 20);
-          break;
+  if (warp >= 8) {
+    reg_dec<48>();
+    if (warp == 8) {
+      // ---------------------------------------------------------- TMA producer
+      if (lane == 0) {
+        tma_prefetch_desc(&mapQ);
+        tma_prefetch_desc(&mapK);
+        tma_prefetch_desc(&mapV);
+        mbar_expect_tx(&bars->q_full, (act1 ? 2 : 1) * C::TILE_BYTES);
+        load_tile<HD>(sQ, &mapQ, &bars->q_full, row0, hq, b);
+        if (act1) load_tile<HD>(sQ + C::TILE_BYTES, &mapQ, &bars->q_full, row0 + FM, hq, b);
+        for (int item = 0; item < 2 * nkv; ++item) {
+          const int s = item % C::NSTAGE;
+          if (!mbar_wait(&bars->kv_empty[s], ((item / C::NSTAGE) & 1) ^ 1)) {
+            dev_set_error(p.status, SAF_DEV_TIMEOUT_TMA, 20);
+            break;
+          }
+          mbar_expect_tx(&bars->kv_full[s], C::TILE_BYTES);
+          const int j = item >> 1;
+          if (item & 1) load_tile<HD>(sRing + s * C::TILE_BYTES, &mapV, &bars->kv_full[s], j * FN, hv, b);
+          else load_tile<HD>(sRing + s * C::TILE_BYTES, &mapK, &bars->kv_full[s], j * FN, hk, b);
         }
-        mbar_expect_tx(&bars->kv_full[s], C::TILE_BYTES);
-        const int j = item >> 1;
-        if (item & 1) load_tile<HD>(sRing + s * C::TILE_BYTES, &mapV, &bars->kv_full[s], j * FN, hv, b);
-        else load_tile<HD>(sRing + s * C::TILE_BYTES, &mapK, &bars->kv_full[s], j * FN, hk, b);
       }
-    }
-  } else if (warp == 9) {
-    // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      const uint32_t idesc_s = umma_idesc_bf16(FM, FN, 0, 0);   // Q K^T: both K-major
-      const uint32_t idesc_o = umma_idesc_bf16(FM, HD, 0, 1);   // P V  : V is MN-major
-      const uint32_t qaddr[2] = {smem_u32(sQ), smem_u32(sQ + C::TILE_BYTES)};
-      const uint32_t ring = smem_u32(sRing);
-      auto issue_s = [&](int t, uint32_t kaddr) {
+    } else if (warp == 9) {
+      // ---------------------------------------------------------- MMA issuer
+      if (lane == 0) {
+        const uint32_t idesc_s = umma_idesc_bf16(FM, FN, 0, 0);   // Q K^T: both K-major
+        const uint32_t idesc_o = umma_idesc_bf16(FM, HD, 0, 1);   // P V  : V is MN-major
+        const uint32_t qaddr[2] = {smem_u32(sQ), smem_u32(sQ + C::TILE_BYTES)};
+        const uint32_t ring = smem_u32(sRing);
+        auto issue_s = [&](int t, uint32_t kaddr) {
 #pragma unroll
-        for (int ks = 0; ks < HD / 16; ++ks) {
-          const uint32_t off = (ks >> 2) * 16384 + (ks & 3) * 32;
-          umma_ss(tmem + t * FN, umma_smem_desc_sw128(qaddr[t] + off, 16, 1024),
-                  umma_smem_desc_sw128(kaddr + off, 16, 1024), idesc_s, ks > 0);
+          for (int ks = 0; ks < HD / 16; ++ks) {
+            const uint32_t off = (ks >> 2) * 16384 + (ks & 3) * 32;
+            umma_ss(tmem + t * FN, umma_smem_desc_sw128(qaddr[t] + off, 16, 1024),
+                    umma_smem_desc_sw128(kaddr + off, 16, 1024), idesc_s, ks > 0);
+          }
+          umma_commit(&bars->s_full[t]);
+        };
+        bool ok = mbar_wait(&bars->q_full, 0);
+        if (!ok) dev_set_error(p.status, SAF_DEV_TIMEOUT_MMA, 21);
+        if (ok) {
+          ok = mbar_wait(&bars->kv_full[0], 0);   // K_0
+          if (!ok) dev_set_error(p.status, SAF_DEV_TIMEOUT_MMA, 22);
         }
-        umma_commit(&bars->s_full[t]);
-      };
-      bool ok = mbar_wait(&bars->q_full, 0);
-      if (!ok) dev_set_error(p.status, SAF_DEV_TIMEOUT_MMA, 21);
-      if (ok) {
-        // K_0
-        ok = mbar_wait(&bars->kv_full[0], 0);
-        if (!ok) dev_set_error(p.status, SAF_DEV_TIMEOUT_MMA, 22);
-      }
-      if (ok) {
-        tc_fence_after();
-        issue_s(0, ring);
-        if (act1) issue_s(1, ring);
-        umma_commit(&bars->kv_empty[0]);
-      }
-      for (int j = 0; j < nkv && ok; ++j) {
-        const int vitem = 2 * j + 1, vs = vitem % C::NSTAGE;
-        if (!mbar_wait(&bars->kv_full[vs], (vitem / C::NSTAGE) & 1)) {
-          dev_set_error(p.status, SAF_DEV_TIMEOUT_MMA, 23);
-          ok = false;
-          break;
+        if (ok) {
+          tc_fence_after();
+          issue_s(0, ring);
+          if (act1) issue_s(1, ring);
+          umma_commit(&bars->kv_empty[0]);
         }
-        const uint32_t vaddr = ring + vs * C::TILE_BYTES;
-        const int kitem = 2 * j + 2, ksn = kitem % C::NSTAGE;
-        const uint32_t kaddr = ring + ksn * C::TILE_BYTES;
-        bool k_ready = false;
-        for (int t = 0; t < 2 && ok; ++t) {
-          const int nk = t ? nkv1 : nkv0;
-          if (j >= nk) continue;
-          if (!mbar_wait(&bars->p_full[t], j & 1)) {
-            dev_set_error(p.status, SAF_DEV_TIMEOUT_MMA, 24);
+        for (int j = 0; j < nkv && ok; ++j) {
+          const int vitem = 2 * j + 1, vs = vitem % C::NSTAGE;
+          if (!mbar_wait(&bars->kv_full[vs], (vitem / C::NSTAGE) & 1)) {
+            dev_set_error(p.status, SAF_DEV_TIMEOUT_MMA, 23);
             ok = false;
             break;
           }
-          tc_fence_after();
-#pragma unroll
-          for (int ks = 0; ks < FN / 16; ++ks) {
-            umma_ts(tmem + C::O_COL + t * HD, tmem + t * FN + ks * 8,
-                    umma_smem_desc_sw128(vaddr + ks * 2048, 16384, 1024), idesc_o, (j > 0) || (ks > 0));
-          }
-          if (j == nk - 1) umma_commit(&bars->o_done[t]);
-          if (j + 1 < nk) {
-            if (!k_ready) {
-              if (!mbar_wait(&bars->kv_full[ksn], (kitem / C::NSTAGE) & 1)) {
-                dev_set_error(p.status, SAF_DEV_TIMEOUT_MMA, 25);
-                ok = false;
-                break;
-              }
-              tc_fence_after();
-              k_ready = true;
+          const uint32_t vaddr = ring + vs * C::TILE_BYTES;
+          const int kitem = 2 * j + 2, ksn = kitem % C::NSTAGE;
+          const uint32_t kaddr = ring + ksn * C::TILE_BYTES;
+          bool k_ready = false;
+          for (int t = 0; t < 2 && ok; ++t) {
+            const int nk = t ? nkv1 : nkv0;
+            if (j >= nk) continue;
+            if (!mbar_wait(&bars->p_full[t], j & 1)) {
+              dev_set_error(p.status, SAF_DEV_TIMEOUT_MMA, 24);
+              ok = false;
+              break;
             }
-            issue_s(t, kaddr);
+            tc_fence_after();
+#pragma unroll
+            for (int ks = 0; ks < FN / 16; ++ks) {
+              umma_ts(tmem + C::O_COL + t * HD, tmem + t * FN + ks * 8,
+                      umma_smem_desc_sw128(vaddr + ks * 2048, 16384, 1024), idesc_o, (j > 0) || (ks > 0));
+            }
+            if (j == nk - 1) umma_commit(&bars->o_done[t]);
+            if (j + 1 < nk) {
+              if (!k_ready) {
+                if (!mbar_wait(&bars->kv_full[ksn], (kitem / C::NSTAGE) & 1)) {
+                  dev_set_error(p.status, SAF_DEV_TIMEOUT_MMA, 25);
+                  ok = false;
+                  break;
+                }
+                tc_fence_after();
+                k_ready = true;
+              }
+              issue_s(t, kaddr);
+            }
           }
+          if (!ok) break;
+          umma_commit(&bars->kv_empty[vs]);
+          if (j + 1 < nkv) umma_commit(&bars->kv_empty[ksn]);
         }
-        if (!ok) break;
-        umma_commit(&bars->kv_empty[vs]);
-        if (j + 1 < nkv) umma_commit(&bars->kv_empty[ksn]);
       }
     }
   } else {
     // ------------------------------------------------------------ softmax warpgroups
+    reg_inc<224>();
     const int t = warp >> 2;
     const int r = tid & 127;
     const int nk = t ? nkv1 : nkv0;
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     const uint32_t tS = tmem + lane_base + t * FN;
     const uint32_t tO = tmem + lane_base + C::O_COL + t * HD;
+    const float sc = p.scale_log2;
     float m_ref = -INFINITY, l = 0.f;
     bool ok = true;
     for (int j = 0; j < nk; ++j) {
@@ -247,15 +307,18 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
           for (int i = 0; i < 32; ++i)
             if (q * 32 + i > r) s[q][i] = 0xff800000u;  // -inf
       }
-      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+      float mx0 = __uint_as_float(s[0][0]), mx1 = __uint_as_float(s[1][0]);
+      float mx2 = __uint_as_float(s[2][0]), mx3 = __uint_as_float(s[3][0]);
 #pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        mx0 = fmaxf(mx0, __uint_as_float(s[0][i]));
-        mx1 = fmaxf(mx1, __uint_as_float(s[1][i]));
-        mx2 = fmaxf(mx2, __uint_as_float(s[2][i]));
-        mx3 = fmaxf(mx3, __uint_as_float(s[3][i]));
+      for (int i = 1; i < 31; i += 2) {
+        mx0 = fmax3(mx0, __uint_as_float(s[0][i]), __uint_as_float(s[0][i + 1]));
+        mx1 = fmax3(mx1, __uint_as_float(s[1][i]), __uint_as_float(s[1][i + 1]));
+        mx2 = fmax3(mx2, __uint_as_float(s[2][i]), __uint_as_float(s[2][i + 1]));
+        mx3 = fmax3(mx3, __uint_as_float(s[3][i]), __uint_as_float(s[3][i + 1]));
       }
-      const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2;
+      mx0 = fmax3(mx0, __uint_as_float(s[0][31]), __uint_as_float(s[1][31]));
+      mx2 = fmax3(mx2, __uint_as_float(s[2][31]), __uint_as_float(s[3][31]));
+      const float mx = fmax3(mx0, mx1, fmaxf(mx2, mx3)) * sc;
       if (j == 0) {
         m_ref = mx;
       } else {
@@ -275,21 +338,29 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
           }
         }
       }
-      float sum0 = 0.f, sum1 = 0.f;
+      const float2 sc2 = make_float2(sc, sc), nm2 = make_float2(-m_ref, -m_ref);
+      float2 acc0 = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
         uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          const float p0 = ex2(fmaf(__uint_as_float(s[q][2 * i]), p.scale_log2, -m_ref));
-          const float p1 = ex2(fmaf(__uint_as_float(s[q][2 * i + 1]), p.scale_log2, -m_ref));
-          sum0 += p0;
-          sum1 += p1;
-          pk[i] = pack_bf16(p0, p1);
+          const float2 x = __ffma2_rn(make_float2(__uint_as_float(s[q][2 * i]), __uint_as_float(s[q][2 * i + 1])), sc2, nm2);
+          float2 e;
+          if (i < SAF_POLY_EXP_PER_16 / 2) {
+            e = exp2_poly2(x);
+          } else {
+            e.x = ex2(x.x);
+            e.y = ex2(x.y);
+          }
+          if (i & 1) acc1 = __fadd2_rn(acc1, e);
+          else acc0 = __fadd2_rn(acc0, e);
+          pk[i] = pack_bf16(e.x, e.y);
         }
         tmem_st16(tS + q * 16, pk);
       }
-      l += sum0 + sum1;
+      acc0 = __fadd2_rn(acc0, acc1);
+      l += acc0.x + acc0.y;
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(&bars->p_full[t]);
@@ -371,13 +442,28 @@ int launch_typed(const SafMixedAttnArgs& a, cudaStream_t st) {
   p.lse = reinterpret_cast<float*>(a.lse.ptr);
   for (int i = 0; i < 3; ++i) p.lse_s[i] = a.lse.stride[i];
   p.status = a.status;
+  if (a.sd_alpha && a.sd_rho) {
+    p.has_scan = 1;
+    ScanArgs& s = p.scan;
+    s.in = a.v.ptr;
+    s.out = a.out.ptr;
+    for (int i = 0; i < 4; ++i) {
+      s.si[i] = a.v.stride[i];
+      s.so[i] = a.out.stride[i];
+    }
+    s.frozen = a.frozen; s.kvidx = a.kvidx; s.sd_alpha = a.sd_alpha; s.sd_rho = a.sd_rho;
+    s.B = a.B; s.H = a.H; s.T = a.T; s.HD = a.HD; s.force_state = a.force_state; s.HKV = a.HKV;
+    s.vec_ok = 1;   // tma_ok() already demands 16-byte aligned bases and strides
+  }
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(flash_fwd_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<HD>::SMEM_BYTES);
     if (e != cudaSuccess) return fail(SAF_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     attr_set = true;
   }
-  const unsigned grid = (unsigned)(p.n_pairs * a.B * a.H);
+  const int bh = a.B * a.H;
+  const int groups = (bh + HEAD_GROUP - 1) / HEAD_GROUP;
+  const unsigned grid = (unsigned)(bh + groups * HEAD_GROUP * p.n_pairs);
   flash_fwd_kernel<HD><<<grid, FLASH_THREADS, Cfg<HD>::SMEM_BYTES, st>>>(mq, mk, mv, mo, p);
   count_launch();
   return check_launch("flash_fwd_kernel");
@@ -398,7 +484,7 @@ int launch_flash_fwd_sm100(const SafMixedAttnArgs& a, uint32_t* handled, cudaStr
   if (!tma_ok(a.q) || !tma_ok(a.k) || !tma_ok(a.v) || !tma_ok(a.out)) return SAF_ERR_UNSUPPORTED;
   if (!saf_device_supported()) return SAF_ERR_UNSUPPORTED;
   const int rc = (a.HD == 64) ? launch_typed<64>(a, st) : launch_typed<128>(a, st);
-  if (rc == SAF_OK) *handled = 1u << SAF_LIVE;
+  if (rc == SAF_OK) *handled = (1u << SAF_LIVE) | ((a.sd_alpha && a.sd_rho) ? (1u << SAF_SINK_DECAY) : 0u);
   return rc;
 }
 

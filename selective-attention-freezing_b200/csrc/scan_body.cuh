@@ -1,0 +1,258 @@
+// Device code of the structured-pattern scan, shared by the stand-alone scan kernel (scan.cu) and
+// by the mixed forward kernel, which runs it in the CTAs of sink+decay heads.
+#pragma once
+#include "saf_internal.h"
+
+namespace saf {
+
+constexpr int SCAN_NT = 256;
+constexpr int SCAN_ROWS = 256;   // rows per block step
+constexpr int SCAN_COLS = 64;    // columns per CTA
+
+template <typename T>
+__device__ __forceinline__ void load8(const T* p, int64_t sd, bool vec, int ncol, float (&v)[8]) {
+  if (vec) {
+    if constexpr (sizeof(T) == 2) {
+      const uint4 u = *reinterpret_cast<const uint4*>(p);
+      const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        T lo, hi;
+        const uint16_t l16 = (uint16_t)(w[i] & 0xffffu), h16 = (uint16_t)(w[i] >> 16);
+        lo = *reinterpret_cast<const T*>(&l16);
+        hi = *reinterpret_cast<const T*>(&h16);
+        v[2 * i] = to_f<T>(lo);
+        v[2 * i + 1] = to_f<T>(hi);
+      }
+    } else {
+      const float4 x = *reinterpret_cast<const float4*>(p);
+      const float4 y = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p) + 4);
+      v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w;
+      v[4] = y.x; v[5] = y.y; v[6] = y.z; v[7] = y.w;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = (i < ncol) ? to_f<T>(p[(int64_t)i * sd]) : 0.f;
+  }
+}
+
+template <typename T>
+__device__ __forceinline__ void store8(T* p, int64_t sd, bool vec, int ncol, const float (&v)[8]) {
+  if (vec) {
+    if constexpr (sizeof(T) == 2) {
+      uint32_t w[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const T lo = from_f<T>(v[2 * i]), hi = from_f<T>(v[2 * i + 1]);
+        w[i] = (uint32_t)(*reinterpret_cast<const uint16_t*>(&lo)) | ((uint32_t)(*reinterpret_cast<const uint16_t*>(&hi)) << 16);
+      }
+      *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+    } else {
+      *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+      *reinterpret_cast<float4*>(reinterpret_cast<float*>(p) + 4) = make_float4(v[4], v[5], v[6], v[7]);
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      if (i < ncol) p[(int64_t)i * sd] = from_f<T>(v[i]);
+  }
+}
+
+// (1-r) / (1 - r^(n))  =  1 / Z_{n-1};   r == 1 -> 1/n
+__device__ __forceinline__ float inv_z(float r, float log_r, int n) {
+  if (r >= 1.f) return 1.f / (float)n;
+  if (r <= 0.f) return 1.f;
+  return (1.f - r) / (-expm1f((float)n * log_r));
+}
+
+struct ScanArgs {
+  const void* in;      // V (fwd) or dY (bwd)
+  void* out;           // Y (fwd) or dV (bwd)
+  int64_t si[4], so[4];
+  const int32_t* frozen;
+  const int32_t* kvidx;   // fwd only: input head = kvidx[h]
+  const float* sd_alpha;
+  const float* sd_rho;
+  int B, H, T, HD, force_state, HKV;
+  int vec_ok;
+};
+
+// 256-thread barrier that leaves barrier 0 (and any other warps of the CTA) alone
+__device__ __forceinline__ void scan_bar() { asm volatile("bar.sync 15, 256;" ::: "memory"); }
+
+// One CTA-wide pass over the whole sequence of head (b, h), columns [col0, col0+64).
+// Must be called by exactly the first 256 threads of the CTA, all of them.
+template <typename T, bool BWD>
+__device__ __forceinline__ void sink_decay_scan_cta(const ScanArgs& a, int b, int h, int col0) {
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int cg = lane & 7, rl = lane >> 3;
+  const int c0 = col0 + cg * 8;
+  const int ncol = max(0, min(8, a.HD - c0));
+  const bool vec = a.vec_ok && ncol == 8;
+  const float alpha = a.sd_alpha[h], r = a.sd_rho[h];
+  const float log_r = (r > 0.f && r < 1.f) ? log1pf(r - 1.f) : 0.f;
+  const float r2 = r * r, r4 = r2 * r2, r8 = r4 * r4, r16 = r8 * r8, r32 = r16 * r16;
+  const int hin = (!BWD && a.HKV > 0) ? (a.kvidx ? a.kvidx[h] : 0) : h;
+  const T* ib = reinterpret_cast<const T*>(a.in) + (int64_t)b * a.si[0] + (int64_t)hin * a.si[1] + (int64_t)c0 * a.si[3];
+  T* ob = reinterpret_cast<T*>(a.out) + (int64_t)b * a.so[0] + (int64_t)h * a.so[1] + (int64_t)c0 * a.so[3];
+
+  __shared__ float wtot[2][8][SCAN_COLS];   // double-buffered: one barrier per block step
+  __shared__ float colsum[32][SCAN_COLS];   // bwd: per (warp, rl) partial column sums of dY
+  __shared__ float row0[SCAN_COLS];         // bwd: scanned value of row 0
+
+  float v0[8];
+#pragma unroll
+  for (int c = 0; c < 8; ++c) v0[c] = 0.f;
+  if (!BWD && ncol > 0) load8<T>(ib, a.si[3], vec, ncol, v0);
+  float carry[8], csum[8];
+#pragma unroll
+  for (int c = 0; c < 8; ++c) carry[c] = csum[c] = 0.f;
+  // decay from the end of the previous warp to the start of this thread's row group
+  float rg = 1.f;  // r^(8*rl)
+  for (int i = 0; i < rl; ++i) rg *= r8;
+
+  const int Tn = a.T;
+  // 16-bit vector path: the next block's rows are fetched (raw 16-byte words) while this block is scanned
+  const bool pf = vec && sizeof(T) == 2;
+  uint4 nraw[8];
+  auto prefetch = [&](int blk) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int p = blk + warp * 32 + rl * 8 + j;
+      const int i = BWD ? (Tn - 1 - p) : p;
+      nraw[j] = (p < Tn) ? *reinterpret_cast<const uint4*>(ib + (int64_t)i * a.si[2]) : make_uint4(0, 0, 0, 0);
+    }
+  };
+  if (pf) prefetch(0);
+  int buf = 0;
+  for (int blk = 0; blk < Tn; blk += SCAN_ROWS, buf ^= 1) {
+    const int p0 = blk + warp * 32 + rl * 8;   // scan position of this thread's first row
+    float x[8][8];
+    if (pf) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const uint32_t w4[4] = {nraw[j].x, nraw[j].y, nraw[j].z, nraw[j].w};
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const uint16_t l16 = (uint16_t)(w4[q] & 0xffffu), h16 = (uint16_t)(w4[q] >> 16);
+          x[j][2 * q] = to_f<T>(*reinterpret_cast<const T*>(&l16));
+          x[j][2 * q + 1] = to_f<T>(*reinterpret_cast<const T*>(&h16));
+        }
+      }
+      if (blk + SCAN_ROWS < Tn) prefetch(blk + SCAN_ROWS);
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int p = p0 + j;
+      const int i = BWD ? (Tn - 1 - p) : p;     // memory row
+      if (p < Tn && ncol > 0) {
+        if (!pf) load8<T>(ib + (int64_t)i * a.si[2], a.si[3], vec, ncol, x[j]);
+        if (BWD) {
+          const float w = (1.f - alpha) * inv_z(r, log_r, i + 1);
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            csum[c] += x[j][c];
+            x[j][c] *= w;
+          }
+        }
+      } else {
+#pragma unroll
+        for (int c = 0; c < 8; ++c) x[j][c] = 0.f;
+      }
+    }
+    // local scan over the 8 rows
+#pragma unroll
+    for (int j = 1; j < 8; ++j)
+#pragma unroll
+      for (int c = 0; c < 8; ++c) x[j][c] = fmaf(r, x[j - 1][c], x[j][c]);
+    // combine the 4 row groups of the warp (inclusive, decay r^8 per group)
+    float inc[8], exc[8];
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      float t = x[7][c];
+      float y = __shfl_up_sync(0xffffffffu, t, 8);
+      if (rl >= 1) t = fmaf(r8, y, t);
+      y = __shfl_up_sync(0xffffffffu, t, 16);
+      if (rl >= 2) t = fmaf(r16, y, t);
+      inc[c] = t;
+      y = __shfl_up_sync(0xffffffffu, t, 8);
+      exc[c] = (rl >= 1) ? y : 0.f;
+    }
+    if (rl == 3) {
+#pragma unroll
+      for (int c = 0; c < 8; ++c) wtot[buf][warp][cg * 8 + c] = inc[c];
+    }
+    scan_bar();
+    // carry into this warp = sum_{w'<warp} r32^(warp-1-w') wtot[w'] + r32^warp * carry
+    float cw[8];
+#pragma unroll
+    for (int c = 0; c < 8; ++c) cw[c] = carry[c];
+    for (int w = 0; w < warp; ++w)
+#pragma unroll
+      for (int c = 0; c < 8; ++c) cw[c] = fmaf(r32, cw[c], wtot[buf][w][cg * 8 + c]);
+    // block carry for the next step (all warps compute the same value)
+    {
+      float nc[8];
+#pragma unroll
+      for (int c = 0; c < 8; ++c) nc[c] = cw[c];
+      for (int w = warp; w < 8; ++w)
+#pragma unroll
+        for (int c = 0; c < 8; ++c) nc[c] = fmaf(r32, nc[c], wtot[buf][w][cg * 8 + c]);
+#pragma unroll
+      for (int c = 0; c < 8; ++c) carry[c] = nc[c];
+    }
+    // state just before this thread's first row
+    float cin[8];
+#pragma unroll
+    for (int c = 0; c < 8; ++c) cin[c] = fmaf(rg, cw[c], exc[c]);
+    float rp = r;  // r^(j+1)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int p = p0 + j;
+      const int i = BWD ? (Tn - 1 - p) : p;
+      float o[8];
+      if (!BWD) {
+        const float w = (1.f - alpha) * inv_z(r, log_r, i + 1);
+#pragma unroll
+        for (int c = 0; c < 8; ++c) o[c] = fmaf(alpha, v0[c], w * fmaf(rp, cin[c], x[j][c]));
+      } else {
+#pragma unroll
+        for (int c = 0; c < 8; ++c) o[c] = fmaf(rp, cin[c], x[j][c]);
+      }
+      if (p < Tn && ncol > 0) {
+        if (BWD && i == 0) {
+#pragma unroll
+          for (int c = 0; c < 8; ++c) row0[cg * 8 + c] = o[c];
+        } else {
+          store8<T>(ob + (int64_t)i * a.so[2], a.so[3], vec, ncol, o);
+        }
+      }
+      rp *= r;
+    }
+  }
+  if (BWD) {
+    // dV_0 = scan value + alpha * sum_i dY_i
+#pragma unroll
+    for (int c = 0; c < 8; ++c) colsum[warp * 4 + rl][cg * 8 + c] = csum[c];
+    scan_bar();
+    if (tid < SCAN_COLS) {
+      float s = 0.f;
+      for (int k = 0; k < 32; ++k) s += colsum[k][tid];
+      const int c = col0 + tid;
+      if (c < a.HD && Tn > 0) {
+        T* o0 = reinterpret_cast<T*>(a.out) + (int64_t)b * a.so[0] + (int64_t)h * a.so[1] + (int64_t)c * a.so[3];
+        *o0 = from_f<T>(row0[tid] + alpha * s);
+      }
+    }
+  }
+}
+
+template <typename T, bool BWD>
+__global__ void __launch_bounds__(SCAN_NT) sink_decay_scan_kernel(const __grid_constant__ ScanArgs a) {
+  const int bh = blockIdx.x, b = bh / a.H, h = bh % a.H;
+  const int state = a.force_state >= 0 ? a.force_state : a.frozen[h];
+  if (state != SAF_SINK_DECAY) return;
+  sink_decay_scan_cta<T, BWD>(a, b, h, blockIdx.y * SCAN_COLS);
+}
+
+}  // namespace saf
