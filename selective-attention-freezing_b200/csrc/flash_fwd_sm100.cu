@@ -7,20 +7,23 @@
 //
 //   warps 0-3   softmax of query tile 0 (one thread per row: TMEM lane == row, no shuffles)
 //   warps 4-7   softmax of query tile 1
-//   warp  8     TMA producer: Q tiles once, then K_j / V_j tiles through a ring of stages
-//   warp  9     MMA issuer:   S_t = Q_t K_j^T  (SS, 128x128xHD)  -> TMEM
-//                             O_t += P_t V_j   (TS: P read from TMEM, V MN-major in smem)
-//   warps 10-11 complete the third warpgroup (register reallocation works per warpgroup)
+//   warp  8     TMA producer: Q tiles once, then K_j and V_j tiles through two rings of stages
+//   warp  9     score MMA issuer:  S_t(j) = Q_t K_j^T   (SS, 128x128xHD)  -> TMEM score buffer
+//   warp  10    output MMA issuer: O_t += P_t(j) V_j     (TS: P read from TMEM, V MN-major in smem)
+//   warp  11    completes the third warpgroup (register reallocation works per warpgroup)
 //
-// TMEM columns: S0 [0,128) S1 [128,256) O0 [256,256+HD) O1 [256+HD,256+2HD).  P (bf16) overwrites
-// the first 64 columns of its S buffer, so scores never touch shared or global memory.  The two
-// query tiles alternate on the tensor core: while one tile's scores are in its softmax warps the
-// other tile's MMAs run.  The softmax warps take registers from the control warpgroup
-// (setmaxnreg) so a full 128-column score row stays in registers; their arithmetic uses the
-// packed f32x2 FMA/ADD and the 3-input max of sm_100, and a share of the exponentials is
-// evaluated on the FMA pipe (Cody-Waite + cubic) because the MUFU pipe is the narrowest unit
-// at head_dim 64.  The running output is rescaled lazily: only when a row maximum grows by more
-// than 2^8 (exact, because the final normaliser l carries the same reference maximum).
+// TMEM (512 columns): score buffers of 128 columns each, then O0, O1 (HD columns each).  P (bf16)
+// overwrites the first 64 columns of its score buffer, so scores never touch shared or global memory.
+// head_dim 64 leaves room for THREE score buffers shared by the two query tiles in rotation (the k-th
+// score tile, k = 2j + t, lives in buffer k mod 3), so S_t(j+1) is computed while P_t(j) is still being
+// made and a softmax warpgroup finds its next scores ready when it finishes a tile; head_dim 128 fills
+// TMEM with two score buffers, one per tile.  Two issuing warps split the per-tile bookkeeping
+// (barrier waits, descriptor updates, commits), which otherwise costs more than the MMAs themselves;
+// the whole warp walks the schedule so addresses stay in uniform registers and one elected lane issues.
+// The softmax warps take registers from the control warpgroup (setmaxnreg) so a full 128-column score
+// row stays in registers; their arithmetic uses the packed f32x2 FMA/ADD and the 3-input max of sm_100.
+// The running output is rescaled lazily: only when a row maximum grows by more than 2^8 (exact, because
+// the final normaliser l carries the same reference maximum).
 //
 // Grid order: first one slot per (batch, head) that runs the O(T) scan if that head is frozen on a
 // structured pattern (first 256 threads; other heads' slots exit) -- they start at time zero and
@@ -41,18 +44,19 @@ constexpr int HEAD_GROUP = 8;
 constexpr float LOG2E_F = 1.4426950408889634f;
 constexpr float RESCALE_THRESHOLD = 8.0f;
 #ifndef SAF_POLY_EXP_PER_16
-#define SAF_POLY_EXP_PER_16 0       // of every 16 exponentials, this many run on the FMA pipe
+#define SAF_POLY_EXP_PER_16 4       // of every 16 exponentials, this many run on the FMA pipe
 #endif
 
 template <int HD>
 struct Cfg {
   static constexpr int TILE_BYTES = 128 * HD * 2;
-  static constexpr int NSTAGE = (HD == 64) ? 6 : 4;
+  static constexpr int KSTAGE = (HD == 64) ? 4 : 2;    // K ring and V ring, powers of two
   static constexpr int Q_BYTES = 2 * TILE_BYTES;
-  static constexpr int RING_BYTES = NSTAGE * TILE_BYTES;
+  static constexpr int RING_BYTES = 2 * KSTAGE * TILE_BYTES;
   static constexpr int SMEM_BYTES = 1024 + Q_BYTES + RING_BYTES + 512;
   static constexpr int TMEM_COLS = 512;
-  static constexpr int O_COL = 256;
+  static constexpr int NBUF = (HD == 64) ? 3 : 2;      // score buffers
+  static constexpr int O_COL = NBUF * 128;
 };
 
 struct FlashParams {
@@ -70,8 +74,10 @@ struct FlashParams {
 
 struct FlashBars {
   uint64_t q_full;
-  uint64_t kv_full[6], kv_empty[6];
-  uint64_t s_full[2], p_full[2], o_done[2];
+  uint64_t k_full[4], k_empty[4], v_full[4], v_empty[4];
+  uint64_t s_full[3];     // score buffer written by the score MMAs
+  uint64_t p_full[3];     // P written by the softmax warpgroup (128 arrivals)
+  uint64_t buf_free[3];   // PV product that read P from this buffer has finished
   uint32_t tmem_base;
 };
 
@@ -146,10 +152,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* sQ = smem;                       // 2 tiles
-  uint8_t* sRing = smem + C::Q_BYTES;       // NSTAGE tiles, K and V alternate
-  FlashBars* bars = reinterpret_cast<FlashBars*>(sRing + C::RING_BYTES);
+  uint8_t* sK = smem + C::Q_BYTES;                          // KSTAGE key tiles
+  uint8_t* sV = sK + C::KSTAGE * C::TILE_BYTES;             // KSTAGE value tiles
+  FlashBars* bars = reinterpret_cast<FlashBars*>(sK + C::RING_BYTES);
 
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int tid = threadIdx.x, warp = tid >> 5;
   const int row0 = mp * 2 * FM;
   const bool act1 = row0 + FM < p.T;
   const int nkv0 = 2 * mp + 1;
@@ -161,14 +168,16 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
 
   if (tid == 0) {
     mbar_init(&bars->q_full, 1);
-    for (int s = 0; s < C::NSTAGE; ++s) {
-      mbar_init(&bars->kv_full[s], 1);
-      mbar_init(&bars->kv_empty[s], 1);
+    for (int s = 0; s < C::KSTAGE; ++s) {
+      mbar_init(&bars->k_full[s], 1);
+      mbar_init(&bars->k_empty[s], 1);
+      mbar_init(&bars->v_full[s], 1);
+      mbar_init(&bars->v_empty[s], 1);
     }
-    for (int t = 0; t < 2; ++t) {
-      mbar_init(&bars->s_full[t], 1);
-      mbar_init(&bars->p_full[t], 128);
-      mbar_init(&bars->o_done[t], 1);
+    for (int i = 0; i < 3; ++i) {
+      mbar_init(&bars->s_full[i], 1);
+      mbar_init(&bars->p_full[i], 128);
+      mbar_init(&bars->buf_free[i], 1);
     }
     fence_mbar_init();
   }
@@ -182,98 +191,125 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
   const uint32_t tmem = bars->tmem_base;
 
   if (warp >= 8) {
-    reg_dec<48>();
+    reg_dec<56>();
+    // score tiles in production order: k -> (tile t, key step j); with one active tile k = j
+    const int n_prod = act1 ? 2 * nkv1 : nkv0;
+    const bool leader = elect_one();
     if (warp == 8) {
       // ---------------------------------------------------------- TMA producer
-      if (lane == 0) {
+      if (leader) {
         tma_prefetch_desc(&mapQ);
         tma_prefetch_desc(&mapK);
         tma_prefetch_desc(&mapV);
         mbar_expect_tx(&bars->q_full, (act1 ? 2 : 1) * C::TILE_BYTES);
         load_tile<HD>(sQ, &mapQ, &bars->q_full, row0, hq, b);
         if (act1) load_tile<HD>(sQ + C::TILE_BYTES, &mapQ, &bars->q_full, row0 + FM, hq, b);
-        for (int item = 0; item < 2 * nkv; ++item) {
-          const int s = item % C::NSTAGE;
-          if (!mbar_wait(&bars->kv_empty[s], ((item / C::NSTAGE) & 1) ^ 1)) {
+        // order of first use: K0, then (K_{j+1}, V_j) -- scores run one key tile ahead of the outputs
+        bool ok = true;
+        auto load_k = [&](int j) {
+          const int s = j & (C::KSTAGE - 1);
+          if (!mbar_wait(&bars->k_empty[s], ((j / C::KSTAGE) & 1) ^ 1)) {
             dev_set_error(p.status, SAF_DEV_TIMEOUT_TMA, 20);
-            break;
+            ok = false;
+            return;
           }
-          mbar_expect_tx(&bars->kv_full[s], C::TILE_BYTES);
-          const int j = item >> 1;
-          if (item & 1) load_tile<HD>(sRing + s * C::TILE_BYTES, &mapV, &bars->kv_full[s], j * FN, hv, b);
-          else load_tile<HD>(sRing + s * C::TILE_BYTES, &mapK, &bars->kv_full[s], j * FN, hk, b);
+          mbar_expect_tx(&bars->k_full[s], C::TILE_BYTES);
+          load_tile<HD>(sK + s * C::TILE_BYTES, &mapK, &bars->k_full[s], j * FN, hk, b);
+        };
+        auto load_v = [&](int j) {
+          const int s = j & (C::KSTAGE - 1);
+          if (!mbar_wait(&bars->v_empty[s], ((j / C::KSTAGE) & 1) ^ 1)) {
+            dev_set_error(p.status, SAF_DEV_TIMEOUT_TMA, 21);
+            ok = false;
+            return;
+          }
+          mbar_expect_tx(&bars->v_full[s], C::TILE_BYTES);
+          load_tile<HD>(sV + s * C::TILE_BYTES, &mapV, &bars->v_full[s], j * FN, hv, b);
+        };
+        load_k(0);
+        for (int j = 0; j < nkv && ok; ++j) {
+          if (j + 1 < nkv) load_k(j + 1);
+          if (ok) load_v(j);
         }
       }
     } else if (warp == 9) {
-      // ---------------------------------------------------------- MMA issuer
-      if (lane == 0) {
-        const uint32_t idesc_s = umma_idesc_bf16(FM, FN, 0, 0);   // Q K^T: both K-major
-        const uint32_t idesc_o = umma_idesc_bf16(FM, HD, 0, 1);   // P V  : V is MN-major
-        const uint32_t qaddr[2] = {smem_u32(sQ), smem_u32(sQ + C::TILE_BYTES)};
-        const uint32_t ring = smem_u32(sRing);
-        auto issue_s = [&](int t, uint32_t kaddr) {
-#pragma unroll
-          for (int ks = 0; ks < HD / 16; ++ks) {
-            const uint32_t off = (ks >> 2) * 16384 + (ks & 3) * 32;
-            umma_ss(tmem + t * FN, umma_smem_desc_sw128(qaddr[t] + off, 16, 1024),
-                    umma_smem_desc_sw128(kaddr + off, 16, 1024), idesc_s, ks > 0);
-          }
-          umma_commit(&bars->s_full[t]);
-        };
-        bool ok = mbar_wait(&bars->q_full, 0);
-        if (!ok) dev_set_error(p.status, SAF_DEV_TIMEOUT_MMA, 21);
-        if (ok) {
-          ok = mbar_wait(&bars->kv_full[0], 0);   // K_0
-          if (!ok) dev_set_error(p.status, SAF_DEV_TIMEOUT_MMA, 22);
-        }
-        if (ok) {
-          tc_fence_after();
-          issue_s(0, ring);
-          if (act1) issue_s(1, ring);
-          umma_commit(&bars->kv_empty[0]);
-        }
-        for (int j = 0; j < nkv && ok; ++j) {
-          const int vitem = 2 * j + 1, vs = vitem % C::NSTAGE;
-          if (!mbar_wait(&bars->kv_full[vs], (vitem / C::NSTAGE) & 1)) {
-            dev_set_error(p.status, SAF_DEV_TIMEOUT_MMA, 23);
-            ok = false;
-            break;
-          }
-          const uint32_t vaddr = ring + vs * C::TILE_BYTES;
-          const int kitem = 2 * j + 2, ksn = kitem % C::NSTAGE;
-          const uint32_t kaddr = ring + ksn * C::TILE_BYTES;
-          bool k_ready = false;
-          for (int t = 0; t < 2 && ok; ++t) {
-            const int nk = t ? nkv1 : nkv0;
-            if (j >= nk) continue;
-            if (!mbar_wait(&bars->p_full[t], j & 1)) {
-              dev_set_error(p.status, SAF_DEV_TIMEOUT_MMA, 24);
-              ok = false;
+      // ---------------------------------------------------------- score MMA issuer
+      const uint32_t idesc_s = umma_idesc_bf16(FM, FN, 0, 0);   // Q K^T: both operands K-major
+      const uint32_t qaddr0 = smem_u32(sQ), kbase = smem_u32(sK);
+      bool ok = mbar_wait(&bars->q_full, 0);
+      if (!ok) dev_set_error(p.status, SAF_DEV_TIMEOUT_MMA, 22);
+      int buf = 0, bph = 0, k_waited = -1;
+      for (int k = 0; k < n_prod && ok; ++k) {
+        const int t = act1 ? (k & 1) : 0, j = act1 ? (k >> 1) : k;
+        if (j < (t ? nkv1 : nkv0)) {
+          const int ks_ = j & (C::KSTAGE - 1);
+          if (j > k_waited) {
+            if (!mbar_wait(&bars->k_full[ks_], (j / C::KSTAGE) & 1)) {
+              dev_set_error(p.status, SAF_DEV_TIMEOUT_MMA, 23);
               break;
             }
-            tc_fence_after();
-#pragma unroll
-            for (int ks = 0; ks < FN / 16; ++ks) {
-              umma_ts(tmem + C::O_COL + t * HD, tmem + t * FN + ks * 8,
-                      umma_smem_desc_sw128(vaddr + ks * 2048, 16384, 1024), idesc_o, (j > 0) || (ks > 0));
-            }
-            if (j == nk - 1) umma_commit(&bars->o_done[t]);
-            if (j + 1 < nk) {
-              if (!k_ready) {
-                if (!mbar_wait(&bars->kv_full[ksn], (kitem / C::NSTAGE) & 1)) {
-                  dev_set_error(p.status, SAF_DEV_TIMEOUT_MMA, 25);
-                  ok = false;
-                  break;
-                }
-                tc_fence_after();
-                k_ready = true;
-              }
-              issue_s(t, kaddr);
-            }
+            k_waited = j;
           }
-          if (!ok) break;
-          umma_commit(&bars->kv_empty[vs]);
-          if (j + 1 < nkv) umma_commit(&bars->kv_empty[ksn]);
+          // the PV product that read P from this buffer (its previous use) must have finished
+          if (k >= C::NBUF && !mbar_wait(&bars->buf_free[buf], bph ^ 1)) {
+            dev_set_error(p.status, SAF_DEV_TIMEOUT_MMA, 24);
+            break;
+          }
+          tc_fence_after();
+          const uint32_t qa = qaddr0 + t * C::TILE_BYTES, ka = kbase + ks_ * C::TILE_BYTES;
+          const uint32_t d = tmem + buf * FN;
+          if (leader) {
+#pragma unroll
+            for (int ks = 0; ks < HD / 16; ++ks) {
+              const uint32_t off = (ks >> 2) * 16384 + (ks & 3) * 32;
+              umma_ss(d, umma_smem_desc_sw128(qa + off, 16, 1024), umma_smem_desc_sw128(ka + off, 16, 1024), idesc_s,
+                      ks > 0);
+            }
+            umma_commit(&bars->s_full[buf]);
+            if (t == 1 || !act1) umma_commit(&bars->k_empty[ks_]);   // last reader of K_j
+          }
+          __syncwarp();
+        }
+        if (++buf == C::NBUF) {
+          buf = 0;
+          bph ^= 1;
+        }
+      }
+    } else if (warp == 10) {
+      // ---------------------------------------------------------- output MMA issuer
+      const uint32_t idesc_o = umma_idesc_bf16(FM, HD, 0, 1);   // P V: V is MN-major
+      const uint32_t vbase = smem_u32(sV);
+      int buf = 0, bph = 0, v_waited = -1;
+      for (int c = 0; c < n_prod; ++c) {
+        const int t = act1 ? (c & 1) : 0, j = act1 ? (c >> 1) : c;
+        if (j < (t ? nkv1 : nkv0)) {
+          const int vs_ = j & (C::KSTAGE - 1);
+          if (j > v_waited) {
+            if (!mbar_wait(&bars->v_full[vs_], (j / C::KSTAGE) & 1)) {
+              dev_set_error(p.status, SAF_DEV_TIMEOUT_MMA, 25);
+              break;
+            }
+            v_waited = j;
+          }
+          if (!mbar_wait(&bars->p_full[buf], bph)) {
+            dev_set_error(p.status, SAF_DEV_TIMEOUT_MMA, 26);
+            break;
+          }
+          tc_fence_after();
+          const uint32_t va = vbase + vs_ * C::TILE_BYTES;
+          const uint32_t dO = tmem + C::O_COL + t * HD, aP = tmem + buf * FN;
+          if (leader) {
+#pragma unroll
+            for (int ks = 0; ks < FN / 16; ++ks)
+              umma_ts(dO, aP + ks * 8, umma_smem_desc_sw128(va + ks * 2048, 16384, 1024), idesc_o, (j > 0) || (ks > 0));
+            umma_commit(&bars->buf_free[buf]);
+            if (t == 1 || !act1) umma_commit(&bars->v_empty[vs_]);   // last reader of V_j
+          }
+          __syncwarp();
+        }
+        if (++buf == C::NBUF) {
+          buf = 0;
+          bph ^= 1;
         }
       }
     }
@@ -284,14 +320,17 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
     const int r = tid & 127;
     const int nk = t ? nkv1 : nkv0;
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-    const uint32_t tS = tmem + lane_base + t * FN;
     const uint32_t tO = tmem + lane_base + C::O_COL + t * HD;
+    // score buffer of this tile's step j: production index k = 2j + t (k = j with one active tile)
+    const int kstep = act1 ? 2 : 1;
+    int buf = act1 ? t : 0, bph = 0, pbuf = 0, pph = 0;
     const float sc = p.scale_log2;
     float m_ref = -INFINITY, l = 0.f;
     bool ok = true;
     for (int j = 0; j < nk; ++j) {
-      if (!mbar_wait(&bars->s_full[t], j & 1)) {
-        dev_set_error(p.status, SAF_DEV_TIMEOUT_SOFTMAX, 26);
+      const uint32_t tS = tmem + lane_base + buf * FN;
+      if (!mbar_wait(&bars->s_full[buf], bph)) {
+        dev_set_error(p.status, SAF_DEV_TIMEOUT_SOFTMAX, 27);
         ok = false;
         break;
       }
@@ -324,6 +363,13 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
       } else {
         const bool need = mx > m_ref + RESCALE_THRESHOLD;
         if (__any_sync(0xffffffffu, need)) {
+          // O_t must hold the finished P_t(j-1) V_{j-1} before it is rescaled
+          if (!mbar_wait(&bars->buf_free[pbuf], pph)) {
+            dev_set_error(p.status, SAF_DEV_TIMEOUT_SOFTMAX, 28);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
           const float f = need ? ex2(m_ref - mx) : 1.f;
           if (need) m_ref = mx;
           l *= f;
@@ -363,11 +409,19 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
       l += acc0.x + acc0.y;
       tmem_st_wait();
       tc_fence_before();
-      mbar_arrive(&bars->p_full[t]);
+      mbar_arrive(&bars->p_full[buf]);
+      pbuf = buf;
+      pph = bph;
+      buf += kstep;
+      if (buf >= C::NBUF) {
+        buf -= C::NBUF;
+        bph ^= 1;
+      }
     }
     if (nk > 0) {
-      if (ok && !mbar_wait(&bars->o_done[t], 0)) {
-        dev_set_error(p.status, SAF_DEV_TIMEOUT_SOFTMAX, 27);
+      // the last PV product of this tile
+      if (ok && !mbar_wait(&bars->buf_free[pbuf], pph)) {
+        dev_set_error(p.status, SAF_DEV_TIMEOUT_SOFTMAX, 29);
         ok = false;
       }
       tc_fence_after();

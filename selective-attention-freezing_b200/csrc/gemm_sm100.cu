@@ -111,37 +111,41 @@ indexed_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_const
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      const uint32_t idesc = umma_idesc_bf16(GM, GN, 0, 0);
-      uint32_t it = 0, lt = 0;
-      bool ok = true;
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++lt) {
-        const int buf = lt & 1;
-        if (!mbar_wait(&sl->acc_empty[buf], ((lt >> 1) & 1) ^ 1)) {
-          dev_set_error(p.status, SAF_DEV_TIMEOUT_MMA, 11);
+    // the whole warp walks the schedule (uniform addresses); one elected lane issues
+    const bool leader = elect_one();
+    const uint32_t idesc = umma_idesc_bf16(GM, GN, 0, 0);
+    const uint32_t sbase = smem_u32(stage_base);
+    uint32_t it = 0, lt = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++lt) {
+      const int buf = lt & 1;
+      if (!mbar_wait(&sl->acc_empty[buf], ((lt >> 1) & 1) ^ 1)) {
+        dev_set_error(p.status, SAF_DEV_TIMEOUT_MMA, 11);
+        break;
+      }
+      tc_fence_after();
+      const uint32_t d = tmem + buf * GN;
+      for (int kb = 0; kb < KB; ++kb, ++it) {
+        const int s = it % STAGES;
+        if (!mbar_wait(&sl->full[s], (it / STAGES) & 1)) {
+          dev_set_error(p.status, SAF_DEV_TIMEOUT_MMA, 12);
+          ok = false;
           break;
         }
         tc_fence_after();
-        const uint32_t d = tmem + buf * GN;
-        for (int kb = 0; kb < KB; ++kb, ++it) {
-          const int s = it % STAGES;
-          if (!mbar_wait(&sl->full[s], (it / STAGES) & 1)) {
-            dev_set_error(p.status, SAF_DEV_TIMEOUT_MMA, 12);
-            ok = false;
-            break;
-          }
-          tc_fence_after();
-          const uint32_t a = smem_u32(stage_base + s * STAGE_BYTES);
-          const uint32_t b = a + A_BYTES;
+        const uint32_t a = sbase + s * STAGE_BYTES;
+        const uint32_t b = a + A_BYTES;
+        if (leader) {
 #pragma unroll
-          for (int k4 = 0; k4 < GK / 16; ++k4) {
+          for (int k4 = 0; k4 < GK / 16; ++k4)
             umma_ss(d, umma_smem_desc_sw128(a + k4 * 32, 16, 1024), umma_smem_desc_sw128(b + k4 * 32, 16, 1024), idesc,
                     (kb | k4) != 0);
-          }
           umma_commit(&sl->empty[s]);
         }
-        if (ok) umma_commit(&sl->acc_full[buf]);
+        __syncwarp();
       }
+      if (ok && leader) umma_commit(&sl->acc_full[buf]);
+      __syncwarp();
     }
   } else {
     // epilogue warps 2..5 -> TMEM lane quadrant (warp % 4)

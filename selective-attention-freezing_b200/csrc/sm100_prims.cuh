@@ -70,12 +70,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // Bounded wait.  Returns false when the budget ran out (caller must bail out:
 // record the error, stop issuing work and fall through to the teardown).
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-  if (mbar_try_wait(bar, parity)) return true;
-  uint64_t t0 = globaltimer_ns();
+  // the clock is read only after many failed polls: a healthy wait never pays for it
+  uint64_t t0 = 0;
   uint32_t it = 0;
   while (!mbar_try_wait(bar, parity)) {
-    if ((++it & 0x3ff) == 0) {
-      if (globaltimer_ns() - t0 > SAF_WAIT_LIMIT_NS) return false;
+    if ((++it & 0xfff) == 0) {
+      const uint64_t now = globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > SAF_WAIT_LIMIT_NS) return false;
     }
   }
   return true;

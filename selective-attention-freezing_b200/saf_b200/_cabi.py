@@ -7,7 +7,7 @@ import ctypes as C
 import os
 
 _ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-LIB_PATH = os.path.join(_ROOT, "lib", "libsaf_b200.so")
+LIB_PATH = os.environ.get("SAF_B200_LIB") or os.path.join(_ROOT, "lib", "libsaf_b200.so")
 
 SAF_OK, SAF_ERR_INVALID, SAF_ERR_UNSUPPORTED, SAF_ERR_CUDA, SAF_ERR_LIMIT = 0, -1, -2, -3, -4
 SAF_F32, SAF_BF16, SAF_F16 = 0, 1, 2
