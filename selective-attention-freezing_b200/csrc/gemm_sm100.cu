@@ -197,12 +197,19 @@ indexed_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_const
           const float* sr = p.sinT + (int64_t)t * p.slab;
           if (p.slab == 64) {
             // pairs (d, d+32) live in this block
+            // each thread reads its own table row: 16-byte loads (a row is 256 B, 16-byte aligned)
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const float c = cr[j], s = sr[j];
-              const float x1 = v[j], x2 = v[32 + j];
-              v[j] = x1 * c - x2 * s;
-              v[32 + j] = x2 * c + x1 * s;
+            for (int j4 = 0; j4 < 8; ++j4) {
+              const float4 c4 = reinterpret_cast<const float4*>(cr)[j4];
+              const float4 s4 = reinterpret_cast<const float4*>(sr)[j4];
+              const float cc[4] = {c4.x, c4.y, c4.z, c4.w}, ss[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const int j = j4 * 4 + e;
+                const float x1 = v[j], x2 = v[32 + j];
+                v[j] = x1 * cc[e] - x2 * ss[e];
+                v[32 + j] = x2 * cc[e] + x1 * ss[e];
+              }
             }
           } else {
             // slab 128: partner block is the other 64-column block of the same tile
@@ -213,13 +220,18 @@ indexed_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_const
             tmem_ld_wait();
             const __nv_bfloat16* bp = p.bias[w] ? reinterpret_cast<const __nv_bfloat16*>(p.bias[w]) + tb.row0[tn * 2 + pu] : nullptr;
 #pragma unroll
-            for (int j = 0; j < 64; ++j) {
-              float o = __uint_as_float(j < 32 ? q0[j] : q1[j - 32]);
-              if (bp) o += __bfloat162float(bp[j]);
-              const int d = in_slab + j;
-              const float c = cr[d], s = sr[d];
-              // first half: x1*c - x2*s ; second half: x2*c + x1*s
-              v[j] = (in_slab == 0) ? (v[j] * c - o * s) : (v[j] * c + o * s);
+            for (int j4 = 0; j4 < 16; ++j4) {
+              const float4 c4 = reinterpret_cast<const float4*>(cr + in_slab)[j4];
+              const float4 s4 = reinterpret_cast<const float4*>(sr + in_slab)[j4];
+              const float cc[4] = {c4.x, c4.y, c4.z, c4.w}, ss[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const int j = j4 * 4 + e;
+                float o = __uint_as_float(j < 32 ? q0[j] : q1[j - 32]);
+                if (bp) o += __bfloat162float(bp[j]);
+                // first half: x1*c - x2*s ; second half: x2*c + x1*s
+                v[j] = (in_slab == 0) ? (v[j] * cc[e] - o * ss[e]) : (v[j] * cc[e] + o * ss[e]);
+              }
             }
           }
         }
@@ -262,6 +274,7 @@ int launch_gemm_sm100(const SafIndexedLinearArgs& a, cudaStream_t st) {
   const int N = a.n_slabs * a.slab;
   if (N / 64 > MAX_SUB) return SAF_ERR_UNSUPPORTED;
   if (a.C % 8 || a.ldx % 8 || a.ldo % 8 || !aligned16(a.x) || !aligned16(a.out)) return SAF_ERR_UNSUPPORTED;
+  if ((a.rope_cos && !aligned16(a.rope_cos)) || (a.rope_sin && !aligned16(a.rope_sin))) return SAF_ERR_UNSUPPORTED;
   for (int w = 0; w < a.n_weights; ++w) {
     if (!a.weights[w]) continue;
     if (a.ldw[w] % 8 || (a.cdw[w] != 0 && a.cdw[w] != 1) || !aligned16(a.weights[w])) return SAF_ERR_UNSUPPORTED;
