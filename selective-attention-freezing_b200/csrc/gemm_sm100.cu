@@ -10,9 +10,11 @@
 // touched, and the rotation is applied to the fp32 accumulator in the epilogue.
 //
 // Persistent, warp-specialised CTA (1 per SM):
-//   warp 0      TMA producer: x tile 128x64 and weight tile 128x64 per stage (128B swizzle)
-//   warp 1      MMA issuer: tcgen05.mma 128x128x16, bf16 -> fp32 in TMEM, 2 accumulator buffers
-//   warps 2..5  epilogue: TMEM -> registers (bias, RoPE) -> bf16 -> swizzled smem -> TMA store
+//   warp 0      TMA producer: x tile 128x64 and four 64x64 weight blocks per stage (128B swizzle)
+//   warp 1      MMA issuer: tcgen05.mma 128x256x16, bf16 -> fp32 in TMEM, 2 accumulator buffers (512 columns)
+//   warps 2..5  epilogue, 64 columns at a time: TMEM -> registers (bias, RoPE) -> bf16 -> swizzled smem
+//               -> TMA store (two staging blocks in flight).  The row's cos/sin values are fetched once
+//               per tile, before the accumulator is waited for, so their latency hides behind the MMAs.
 // All waits are bounded; a wait that runs out sets *status and the CTA drains.
 #include "saf_internal.h"
 #include "sm100_prims.cuh"
@@ -20,14 +22,16 @@
 namespace saf {
 namespace {
 
-constexpr int GM = 128, GN = 128, GK = 64;
-constexpr int STAGES = 5;
+constexpr int GM = 128, GN = 256, GK = 64;   // 128x256 tiles: 96 B/clk/SM of operand traffic at full MMA rate
+constexpr int SUBS = GN / 64;                // 64-column blocks per tile
+constexpr int STAGES = 4;
 constexpr int A_BYTES = GM * GK * 2;            // 16 KB
-constexpr int B_BYTES = GN * GK * 2;            // 16 KB
-constexpr int STAGE_BYTES = A_BYTES + B_BYTES;  // 32 KB
-constexpr int OUT_BYTES = GM * GN * 2;          // 32 KB staging for the TMA store
+constexpr int B_BYTES = GN * GK * 2;            // 32 KB
+constexpr int SUB_BYTES = 64 * GK * 2;          // 8 KB: one 64-row block of weights
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;  // 48 KB
+constexpr int OUT_BYTES = 2 * GM * 64 * 2;      // two 16 KB staging blocks for the TMA stores
 constexpr int MAX_SUB = 160;                    // 64-row blocks of output features (N <= 10240)
-constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_THREADS = 192;   // TMA warp, MMA warp, one epilogue warpgroup
 
 struct SubTable {
   int32_t row0[MAX_SUB];
@@ -70,12 +74,12 @@ indexed_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_const
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&sl->acc_full[b], 1);
-      mbar_init(&sl->acc_empty[b], 128);
+      mbar_init(&sl->acc_empty[b], 4);      // one arrival per epilogue warp
     }
     fence_mbar_init();
   }
   if (warp == 1) {
-    tmem_alloc(&sl->tmem_base, 256);
+    tmem_alloc(&sl->tmem_base, 512);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -91,7 +95,7 @@ indexed_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_const
       bool ok = true;
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
         const int tm = tile / p.tiles_n, tn = tile - tm * p.tiles_n;
-        const int nsub = min(2, (p.N - tn * GN) / 64);
+        const int nsub = min(SUBS, (p.N - tn * GN) / 64);
         for (int kb = 0; kb < KB; ++kb, ++it) {
           const int s = it % STAGES;
           if (!mbar_wait(&sl->empty[s], ((it / STAGES) & 1) ^ 1)) {
@@ -101,11 +105,11 @@ indexed_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_const
           }
           uint8_t* a = stage_base + s * STAGE_BYTES;
           uint8_t* b = a + A_BYTES;
-          mbar_expect_tx(&sl->full[s], A_BYTES + nsub * (B_BYTES / 2));
+          mbar_expect_tx(&sl->full[s], A_BYTES + nsub * SUB_BYTES);
           tma_load_2d(a, &mapX, &sl->full[s], kb * GK, tm * GM);
           for (int u = 0; u < nsub; ++u) {
-            const int sb = tn * 2 + u;
-            tma_load_2d(b + u * (B_BYTES / 2), wm[tb.weight[sb]], &sl->full[s], kb * GK, tb.row0[sb]);
+            const int sb = tn * SUBS + u;
+            tma_load_2d(b + u * SUB_BYTES, wm[tb.weight[sb]], &sl->full[s], kb * GK, tb.row0[sb]);
           }
         }
       }
@@ -152,25 +156,35 @@ indexed_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_const
     const int quad = warp & 3;
     const int row = quad * 32 + lane;           // row inside the tile
     const int etid = tid - 64;                  // 0..127
-    const int half = p.slab >> 1;
     uint32_t lt = 0;
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++lt) {
       const int tm = tile / p.tiles_n, tn = tile - tm * p.tiles_n;
-      const int nsub = min(2, (p.N - tn * GN) / 64);
+      const int nsub = min(SUBS, (p.N - tn * GN) / 64);
       const int buf = lt & 1;
+      const int m = tm * GM + row;
+      const int t = (p.T > 0) ? (m % p.T) : 0;
+      // head_dim 64: this row's 32 cos and 32 sin values, shared by every rotated block of the tile
+      float4 cs4[8], sn4[8];
+      if (p.slab == 64 && p.cosT) {
+        const float4* cr4 = reinterpret_cast<const float4*>(p.cosT + (int64_t)t * 64);
+        const float4* sr4 = reinterpret_cast<const float4*>(p.sinT + (int64_t)t * 64);
+#pragma unroll
+        for (int j4 = 0; j4 < 8; ++j4) {
+          cs4[j4] = cr4[j4];
+          sn4[j4] = sr4[j4];
+        }
+      }
       if (!mbar_wait(&sl->acc_full[buf], (lt >> 1) & 1)) {
         dev_set_error(p.status, SAF_DEV_TIMEOUT_EPI, 13);
         break;
       }
       tc_fence_after();
-      // staging buffer free? (previous tile's TMA store has read it)
-      if (etid == 0) tma_store_wait_read();
-      named_bar_sync(1, 128);
-      const int m = tm * GM + row;
-      const int t = (p.T > 0) ? (m % p.T) : 0;
       const uint32_t tsrc = tmem + ((uint32_t)(quad * 32) << 16) + buf * GN;
       for (int u = 0; u < nsub; ++u) {
-        const int sb = tn * 2 + u;
+        // staging block (u & 1) is free once the store issued two blocks ago has read it
+        if (etid == 0) tma_store_wait_read1();
+        named_bar_sync(1, 128);
+        const int sb = tn * SUBS + u;
         const int w = tb.weight[sb];
         const int rp = tb.rope[sb];
         // column offset of this 64-block inside its slab (slab = 64: 0; slab = 128: 0 or 64)
@@ -200,8 +214,8 @@ indexed_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_const
             // each thread reads its own table row: 16-byte loads (a row is 256 B, 16-byte aligned)
 #pragma unroll
             for (int j4 = 0; j4 < 8; ++j4) {
-              const float4 c4 = reinterpret_cast<const float4*>(cr)[j4];
-              const float4 s4 = reinterpret_cast<const float4*>(sr)[j4];
+              const float4 c4 = cs4[j4];
+              const float4 s4 = sn4[j4];
               const float cc[4] = {c4.x, c4.y, c4.z, c4.w}, ss[4] = {s4.x, s4.y, s4.z, s4.w};
 #pragma unroll
               for (int e = 0; e < 4; ++e) {
@@ -218,7 +232,7 @@ indexed_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_const
             tmem_ld32(tsrc + pu * 64, q0);
             tmem_ld32(tsrc + pu * 64 + 32, q1);
             tmem_ld_wait();
-            const __nv_bfloat16* bp = p.bias[w] ? reinterpret_cast<const __nv_bfloat16*>(p.bias[w]) + tb.row0[tn * 2 + pu] : nullptr;
+            const __nv_bfloat16* bp = p.bias[w] ? reinterpret_cast<const __nv_bfloat16*>(p.bias[w]) + tb.row0[tn * SUBS + pu] : nullptr;
 #pragma unroll
             for (int j4 = 0; j4 < 16; ++j4) {
               const float4 c4 = reinterpret_cast<const float4*>(cr + in_slab)[j4];
@@ -236,7 +250,7 @@ indexed_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_const
           }
         }
         // bf16 pack -> swizzled staging: 16-byte chunk c of row r lands at chunk (c ^ (r & 7))
-        uint8_t* dst = out_stage + u * (OUT_BYTES / 2) + row * 128;
+        uint8_t* dst = out_stage + (u & 1) * (OUT_BYTES / 2) + row * 128;
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
           uint4 q;
@@ -246,22 +260,23 @@ indexed_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_const
           q.w = pack_bf16(v[c * 8 + 6], v[c * 8 + 7]);
           *reinterpret_cast<uint4*>(dst + ((c ^ (row & 7)) << 4)) = q;
         }
+        fence_proxy_async_smem();
+        named_bar_sync(1, 128);
+        if (etid == 0) {
+          tma_store_2d(&mapO, out_stage + (u & 1) * (OUT_BYTES / 2), tn * GN + u * 64, tm * GM);
+          tma_store_commit();
+        }
       }
       // accumulator buffer can be overwritten by the MMA warp
       tc_fence_before();
-      mbar_arrive(&sl->acc_empty[buf]);
-      fence_proxy_async_smem();
-      named_bar_sync(1, 128);
-      if (etid == 0) {
-        for (int u = 0; u < nsub; ++u) tma_store_2d(&mapO, out_stage + u * (OUT_BYTES / 2), tn * GN + u * 64, tm * GM);
-        tma_store_commit();
-      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sl->acc_empty[buf]);
     }
     if (etid == 0) tma_store_wait_all();
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem, 256);
+  if (warp == 1) tmem_dealloc(tmem, 512);
 }
 
 bool aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
