@@ -231,6 +231,7 @@ def main():
     total_ms = parallel.max_over_ranks(total_ms, dev)
     e2e_ms = parallel.max_over_ranks(e2e_ms, dev)
     tokens = parallel.sum_over_ranks(B * T, dev)
+    parallel.finalize()
     if rank != 0:
         return
 

@@ -51,3 +51,9 @@ def sum_over_ranks(value, device="cpu"):
     t = torch.tensor([float(value)], dtype=torch.float64, device=device)
     dist.all_reduce(t, op=dist.ReduceOp.SUM)
     return t.item()
+
+
+def finalize():
+    """Tear the process group down (quietens NCCL's exit warning)."""
+    if dist.is_initialized():
+        dist.destroy_process_group()
