@@ -33,9 +33,9 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.join(ROOT, "selective-attention-freezing_b200"))
 
 METRIC = "prefill tokens/s, SAF-25% 124M @16K ctx (attention+projection stack)"
-# DRAM bytes per launch of the mixed-attention kernel from the ncu capture summarised under profiles/
-# (None until a capture of the current kernel exists)
-ATTN_TRAFFIC_BYTES = None
+# DRAM bytes per launch of the mixed-attention kernel at the c2 shape (dram__bytes_read.sum + dram__bytes_write.sum
+# of the ncu capture summarised in profiles/flash_fwd_hd64_c2.md); other workloads report null
+ATTN_TRAFFIC_BYTES = {"c2": 279262208 + 86932736}
 
 
 def measured_peaks():
@@ -255,9 +255,9 @@ def main():
         "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": x_host.numel() * 2,
                 "d2h_bytes_per_step": last_host.numel() * 2},
         "gpu_launches": launches,
-        "roofline": {"bound": "tensor", "kernel": "mixed-attention launch (flash_fwd_kernel<64> + frozen-head scan)",
+        "roofline": {"bound": "tensor", "kernel": "flash_fwd_kernel (live heads on tcgen05 + co-scheduled frozen-head scan, one launch per layer)",
                      "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s", "frac": achieved / peak_tf,
-                     "peak_kind": f"{peak_kind} sustained dense bf16", "traffic": ATTN_TRAFFIC_BYTES,
+                     "peak_kind": f"{peak_kind} sustained dense bf16", "traffic": ATTN_TRAFFIC_BYTES.get(args.workload),
                      "flops_per_launch": live_flops_per_launch, "ms_per_launch": attn_mean_ms,
                      "launches_timed": len(attn_ms)},
         "stack": {"tflops": stack_flops / (ms_per_step * 1e-3) / 1e12, "frac_of_peak": stack_flops / (ms_per_step * 1e-3) / 1e12 / peak_tf,
