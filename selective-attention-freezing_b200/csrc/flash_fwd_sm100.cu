@@ -53,7 +53,7 @@ struct Cfg {
   static constexpr int KSTAGE = (HD == 64) ? 4 : 2;    // K ring and V ring, powers of two
   static constexpr int Q_BYTES = 2 * TILE_BYTES;
   static constexpr int RING_BYTES = 2 * KSTAGE * TILE_BYTES;
-  static constexpr int SMEM_BYTES = 1024 + Q_BYTES + RING_BYTES + 512;
+  static constexpr int SMEM_BYTES = 1024 + Q_BYTES + RING_BYTES + 4096;
   static constexpr int TMEM_COLS = 512;
   static constexpr int NBUF = (HD == 64) ? 3 : 2;      // score buffers
   static constexpr int O_COL = NBUF * 128;
@@ -70,6 +70,14 @@ struct FlashParams {
   int* status;
   int has_scan;
   ScanArgs scan;
+  // frozen heads whose pattern is produced by the softmax warps (P -> TMEM -> P V on the tensor core)
+  const void* patt;          // dense (P, S, S), state 1
+  int64_t patt_s[3];
+  int patt_dtype;
+  const int32_t* pidx;
+  const void *alpha, *rho, *z;   // decomposed (H, S), state 2
+  int64_t alpha_s[2], rho_s[2], z_s[2];
+  int dec_dtype;
 };
 
 struct FlashBars {
@@ -79,6 +87,8 @@ struct FlashBars {
   uint64_t p_full[3];     // P written by the softmax warpgroup (128 arrivals)
   uint64_t buf_free[3];   // PV product that read P from this buffer has finished
   uint32_t tmem_base;
+  float dec_alpha[2][128];   // decomposed heads: alpha of the current key tile, per query tile
+  float dec_rho[2][256];     // and the rho values its distances can take
 };
 
 __device__ __forceinline__ float ex2(float x) {
@@ -147,7 +157,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
   const int bh = grp * HEAD_GROUP + rem % gsize;
   const int b = bh / p.H, h = bh % p.H;
   const int state = p.force_state >= 0 ? p.force_state : p.frozen[h];
-  if (state != SAF_LIVE) return;
+  // live heads: flash attention.  Dense / decomposed frozen heads: same pipeline without Q K^T -- the
+  // softmax warps write the pattern tile P into TMEM and the tensor core does P V.
+  const bool live = state == SAF_LIVE;
+  if (!live && !((state == SAF_DENSE && p.patt) || (state == SAF_DECOMP && p.alpha))) return;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -201,9 +214,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
         tma_prefetch_desc(&mapQ);
         tma_prefetch_desc(&mapK);
         tma_prefetch_desc(&mapV);
-        mbar_expect_tx(&bars->q_full, (act1 ? 2 : 1) * C::TILE_BYTES);
-        load_tile<HD>(sQ, &mapQ, &bars->q_full, row0, hq, b);
-        if (act1) load_tile<HD>(sQ + C::TILE_BYTES, &mapQ, &bars->q_full, row0 + FM, hq, b);
+        if (live) {
+          mbar_expect_tx(&bars->q_full, (act1 ? 2 : 1) * C::TILE_BYTES);
+          load_tile<HD>(sQ, &mapQ, &bars->q_full, row0, hq, b);
+          if (act1) load_tile<HD>(sQ + C::TILE_BYTES, &mapQ, &bars->q_full, row0 + FM, hq, b);
+        }
         // order of first use: K0, then (K_{j+1}, V_j) -- scores run one key tile ahead of the outputs
         bool ok = true;
         auto load_k = [&](int j) {
@@ -226,13 +241,13 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
           mbar_expect_tx(&bars->v_full[s], C::TILE_BYTES);
           load_tile<HD>(sV + s * C::TILE_BYTES, &mapV, &bars->v_full[s], j * FN, hv, b);
         };
-        load_k(0);
+        if (live) load_k(0);
         for (int j = 0; j < nkv && ok; ++j) {
-          if (j + 1 < nkv) load_k(j + 1);
+          if (live && j + 1 < nkv) load_k(j + 1);
           if (ok) load_v(j);
         }
       }
-    } else if (warp == 9) {
+    } else if (warp == 9 && live) {
       // ---------------------------------------------------------- score MMA issuer
       const uint32_t idesc_s = umma_idesc_bf16(FM, FN, 0, 0);   // Q K^T: both operands K-major
       const uint32_t qaddr0 = smem_u32(sQ), kbase = smem_u32(sK);
@@ -327,6 +342,102 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
     const float sc = p.scale_log2;
     float m_ref = -INFINITY, l = 0.f;
     bool ok = true;
+    if (!live) {
+      // ---- frozen head: this thread produces row r of the pattern tile, P_t(j) = pattern[i0 + r, 128 j ...]
+      const int i_row = row0 + t * FM + r;                 // absolute query row
+      const bool row_ok = i_row < p.T;
+      const int hp = p.pidx ? p.pidx[h] : h;
+      float zrow = INFINITY;                               // rows past T give exact zeros (decomposed)
+      if (state == SAF_DECOMP && row_ok)
+        zrow = load_rt(p.z, (int64_t)h * p.z_s[0] + (int64_t)i_row * p.z_s[1], p.dec_dtype);
+      float* al_s = bars->dec_alpha[t];                    // alpha of the tile's 128 keys
+      float* rh_s = bars->dec_rho[t];                      // rho[(i0 - j0 - 127) + x], x in [0, 255)
+      for (int j = 0; j < nk; ++j) {
+        const uint32_t tS = tmem + lane_base + buf * FN;
+        const int j0 = j * FN;
+        // the P V product that read this buffer (three score tiles ago) must have finished
+        if ((act1 ? 2 * j + t : j) >= C::NBUF && !mbar_wait(&bars->buf_free[buf], bph ^ 1)) {
+          dev_set_error(p.status, SAF_DEV_TIMEOUT_SOFTMAX, 31);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const bool diag = (j == nk - 1);
+        if (state == SAF_DECOMP) {
+          named_bar_sync(1 + t, 128);                      // previous step's readers are done with the vectors
+          const int key = j0 + r;
+          al_s[r] = (key < p.T) ? load_rt(p.alpha, (int64_t)h * p.alpha_s[0] + (int64_t)key * p.alpha_s[1], p.dec_dtype) : 0.f;
+          const int d0 = row0 + t * FM - j0 - 127;         // distance of rh_s[0]
+#pragma unroll
+          for (int x = r; x < 255; x += 128) {
+            const int d = d0 + x;
+            rh_s[x] = (d >= 0 && d < p.T) ? load_rt(p.rho, (int64_t)h * p.rho_s[0] + (int64_t)d * p.rho_s[1], p.dec_dtype) : 0.f;
+          }
+          named_bar_sync(1 + t, 128);
+        }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          float pv[32];
+          if (state == SAF_DENSE) {
+            const int64_t base = (int64_t)hp * p.patt_s[0] + (int64_t)i_row * p.patt_s[1] + (int64_t)(j0 + q * 32) * p.patt_s[2];
+            if (row_ok && p.patt_s[2] == 1 && p.patt_dtype == SAF_BF16) {
+              const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.patt) + base);
+              const bool vec = ((reinterpret_cast<uintptr_t>(src) & 15) == 0) && (j0 + q * 32 + 32 <= p.T);
+#pragma unroll
+              for (int v8 = 0; v8 < 4; ++v8) {
+                if (vec) {
+                  const uint4 u4 = src[v8];
+                  const uint32_t w4[4] = {u4.x, u4.y, u4.z, u4.w};
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) {
+                    pv[v8 * 8 + 2 * e] = __uint_as_float(w4[e] << 16);
+                    pv[v8 * 8 + 2 * e + 1] = __uint_as_float(w4[e] & 0xffff0000u);
+                  }
+                } else {
+#pragma unroll
+                  for (int e = 0; e < 8; ++e) {
+                    const int c = q * 32 + v8 * 8 + e;
+                    pv[v8 * 8 + e] = (j0 + c < p.T) ? load_rt(p.patt, base + v8 * 8 + e, SAF_BF16) : 0.f;
+                  }
+                }
+              }
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) {
+                const int c = q * 32 + i;
+                pv[i] = (row_ok && j0 + c < p.T) ? load_rt(p.patt, base + (int64_t)i * p.patt_s[2], p.patt_dtype) : 0.f;
+              }
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const int c = q * 32 + i;
+              pv[i] = ex2((al_s[c] + rh_s[r - c + 127] - zrow) * LOG2E_F);
+            }
+          }
+          if (diag) {   // keys after the row do not count (a stored pattern is lower-triangular anyway)
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (q * 32 + i > r) pv[i] = 0.f;
+          }
+          uint32_t pk[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) pk[i] = pack_bf16(pv[2 * i], pv[2 * i + 1]);
+          tmem_st16(tS + q * 16, pk);
+        }
+        tmem_st_wait();
+        tc_fence_before();
+        mbar_arrive(&bars->p_full[buf]);
+        pbuf = buf;
+        pph = bph;
+        buf += kstep;
+        if (buf >= C::NBUF) {
+          buf -= C::NBUF;
+          bph ^= 1;
+        }
+      }
+      l = 1.f;
+    } else
     for (int j = 0; j < nk; ++j) {
       const uint32_t tS = tmem + lane_base + buf * FN;
       if (!mbar_wait(&bars->s_full[buf], bph)) {
@@ -453,7 +564,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
         tma_store_commit();
         tma_store_wait_all();
       }
-      if (p.lse && trow + r < p.T)
+      if (live && p.lse && trow + r < p.T)
         p.lse[(int64_t)b * p.lse_s[0] + (int64_t)h * p.lse_s[1] + (int64_t)(trow + r) * p.lse_s[2]] = m_ref + log2f(l);
     }
   }
@@ -483,8 +594,9 @@ int launch_typed(const SafMixedAttnArgs& a, cudaStream_t st) {
   CUtensorMap mq, mk, mv, mo;
   int rc;
   const int Hkv = a.HKV > 0 ? a.HKV : 0;
-  if ((rc = make_map4(&mq, a.q, a.B, a.U, a.T, HD))) return rc;
-  if ((rc = make_map4(&mk, a.k, a.B, Hkv ? Hkv : a.U, a.T, HD))) return rc;
+  const bool any_live = a.U > 0 && a.q.ptr && a.k.ptr;     // an all-frozen layer has no q/k: the maps are never used
+  if ((rc = make_map4(&mq, any_live ? a.q : a.v, a.B, any_live ? a.U : (Hkv ? Hkv : a.H), a.T, HD))) return rc;
+  if ((rc = make_map4(&mk, any_live ? a.k : a.v, a.B, any_live ? (Hkv ? Hkv : a.U) : (Hkv ? Hkv : a.H), a.T, HD))) return rc;
   if ((rc = make_map4(&mv, a.v, a.B, Hkv ? Hkv : a.H, a.T, HD))) return rc;
   if ((rc = make_map4(&mo, a.out, a.B, a.H, a.T, HD))) return rc;
   FlashParams p;
@@ -496,6 +608,17 @@ int launch_typed(const SafMixedAttnArgs& a, cudaStream_t st) {
   p.lse = reinterpret_cast<float*>(a.lse.ptr);
   for (int i = 0; i < 3; ++i) p.lse_s[i] = a.lse.stride[i];
   p.status = a.status;
+  p.patt = a.patt.ptr;
+  for (int i = 0; i < 3; ++i) p.patt_s[i] = a.patt.stride[i];
+  p.patt_dtype = a.patt_dtype;
+  p.pidx = a.pidx;
+  p.alpha = a.alpha.ptr; p.rho = a.rho.ptr; p.z = a.z.ptr;
+  for (int i = 0; i < 2; ++i) {
+    p.alpha_s[i] = a.alpha.stride[i];
+    p.rho_s[i] = a.rho.stride[i];
+    p.z_s[i] = a.z.stride[i];
+  }
+  p.dec_dtype = a.dec_dtype;
   if (a.sd_alpha && a.sd_rho) {
     p.has_scan = 1;
     ScanArgs& s = p.scan;
@@ -528,17 +651,26 @@ int launch_typed(const SafMixedAttnArgs& a, cudaStream_t st) {
 int launch_flash_fwd_sm100(const SafMixedAttnArgs& a, uint32_t* handled, cudaStream_t st) {
   *handled = 0;
   if (a.dtype != SAF_BF16 || (a.HD != 64 && a.HD != 128) || a.rope) return SAF_ERR_UNSUPPORTED;
-  if (a.U == 0 || (a.force_state >= 0 && a.force_state != SAF_LIVE)) return SAF_ERR_UNSUPPORTED;
-  if (a.frozen_host) {
-    bool any = false;
-    for (int h = 0; h < a.H; ++h) any |= a.frozen_host[h] == SAF_LIVE;
-    if (!any) return SAF_ERR_UNSUPPORTED;
-  }
   if (a.sm_scale <= 0.f) return SAF_ERR_UNSUPPORTED;
-  if (!tma_ok(a.q) || !tma_ok(a.k) || !tma_ok(a.v) || !tma_ok(a.out)) return SAF_ERR_UNSUPPORTED;
+  const bool q_ok = a.U > 0 && a.q.ptr && a.k.ptr;
+  if (q_ok && (!tma_ok(a.q) || !tma_ok(a.k))) return SAF_ERR_UNSUPPORTED;
+  if (!tma_ok(a.v) || !tma_ok(a.out)) return SAF_ERR_UNSUPPORTED;
   if (!saf_device_supported()) return SAF_ERR_UNSUPPORTED;
+  // states this launch serves
+  uint32_t can = 0;
+  if (q_ok) can |= 1u << SAF_LIVE;
+  if (a.patt.ptr) can |= 1u << SAF_DENSE;
+  if (a.alpha.ptr && a.rho.ptr && a.z.ptr) can |= 1u << SAF_DECOMP;
+  if (a.sd_alpha && a.sd_rho) can |= 1u << SAF_SINK_DECAY;
+  uint32_t present = can;
+  if (a.force_state >= 0) present = 1u << a.force_state;
+  else if (a.frozen_host) {
+    present = 0;
+    for (int h = 0; h < a.H; ++h) present |= 1u << a.frozen_host[h];
+  }
+  if (!(present & can)) return SAF_ERR_UNSUPPORTED;
   const int rc = (a.HD == 64) ? launch_typed<64>(a, st) : launch_typed<128>(a, st);
-  if (rc == SAF_OK) *handled = (1u << SAF_LIVE) | ((a.sd_alpha && a.sd_rho) ? (1u << SAF_SINK_DECAY) : 0u);
+  if (rc == SAF_OK) *handled = can;
   return rc;
 }
 
