@@ -207,6 +207,13 @@ int saf_mixed_attn_bwd(const SafMixedAttnBwdArgs* args, void* stream) {
       return fail(SAF_ERR_INVALID, "live heads need dq, dk, delta and lse");
   }
   cudaStream_t st = (cudaStream_t)stream;
+  if (todo & 1u) {
+    // tensor-core path for the live heads; it reports what it covered
+    uint32_t handled = 0;
+    rc = launch_flash_bwd_sm100(*args, &handled, st);
+    if (rc == SAF_OK) todo &= ~handled;
+    else if (rc != SAF_ERR_UNSUPPORTED) return rc;
+  }
   if (todo & (1u << SAF_SINK_DECAY)) {
     if ((rc = launch_scan_bwd(*args, st))) return rc;
     todo &= ~(1u << SAF_SINK_DECAY);

@@ -1,0 +1,725 @@
+// Backward of the live (flash) heads on tcgen05 / TMEM, fed by TMA.
+//
+// Same split as the reference (kernel/fused_attn.py:291-540, 593-623: _bwd_preprocess, _bwd_dkdv, _bwd_dq):
+// no atomics, deterministic, dq/dk/dv written once.
+//
+//   delta kernel   delta_i = sum_d O_id dO_id                                   (HBM-bound, 16-byte loads)
+//   dK/dV kernel   one CTA per 128-key tile j; walks the query tiles i >= j:
+//                    S^T  = K_j Q_i^T            SS MMA 128x128xHD -> TMEM   (keys on lanes, queries on columns)
+//                    dP^T = V_j dO_i^T           SS MMA 128x128xHD -> TMEM
+//                    P^T  = exp2(S^T scale - lse_i)   , bf16 back into the S^T columns
+//                    dS^T = P^T (dP^T - delta_i)      , bf16 back into the dP^T columns
+//                    dV_j += P^T  dO_i           TS MMA (A from TMEM, dO_i MN-major from the same smem tile)
+//                    dK_j += dS^T Q_i            TS MMA
+//                  computing the transposed tiles directly puts P^T / dS^T in the layout the TS MMA wants,
+//                  so nothing is transposed through shared memory.
+//   dQ kernel      one CTA per 128-row query tile i; walks the key tiles j <= i:
+//                    S = Q_i K_j^T, dP = dO_i V_j^T, dS = P (dP - delta), dQ_i += dS K_j   (TS MMA)
+//
+// CTA = 384 threads: warps 0-3 and 4-7 are two compute warpgroups that split the 128 columns of a tile in
+// halves (TMEM lane = row = thread; both groups cover all 128 lanes), warp 8 TMA producer, warp 9 MMA
+// issuer (whole warp walks the schedule, one elected lane issues), warps 10-11 complete the third
+// warpgroup for the register reallocation.  The bf16 operand a compute warpgroup writes lands in the
+// first half of ITS OWN 64 score columns (half 0: columns 0-31, half 1: columns 64-95), so the other
+// group's unread scores are never overwritten; the TS MMA takes each 16-row k-step from its own address.
+// The sm_scale factor of dS is applied once to the finished dK / dQ accumulators.
+// Every wait is bounded; on expiry the kernel records a code in *status and falls through.
+#include "saf_internal.h"
+#include "sm100_prims.cuh"
+
+namespace saf {
+namespace {
+
+constexpr int BWD_THREADS = 384;
+constexpr int BWD_HEAD_GROUP = 8;
+constexpr float LOG2E_B = 1.4426950408889634f;
+
+template <int HD>
+struct BwdCfg {
+  static constexpr int TILE_BYTES = 128 * HD * 2;
+  static constexpr int NSTAGE = (HD == 64) ? 3 : 2;   // ring of streamed tile pairs
+  static constexpr int SMEM_BYTES = 1024 + 2 * TILE_BYTES + NSTAGE * 2 * TILE_BYTES + 4096;
+  static constexpr int TMEM_COLS = 512;
+};
+
+struct BwdParams {
+  int B, H, T, n_tiles, force_state;
+  float scale_log2, sm_scale;
+  const int32_t* frozen;
+  const int32_t* hidx;
+  const float* lse;
+  int64_t lse_s[3];
+  float* delta;
+  int64_t delta_s[3];
+  int* status;
+};
+
+struct BwdBars {
+  uint64_t res_full;                    // the two resident tiles
+  uint64_t ring_full[3], ring_empty[3];
+  uint64_t s_full[2], dp_full, p_full, ds_full, acc_full;
+  uint32_t tmem_base;
+  alignas(16) float lse[2][128];        // dK/dV kernel: lse and delta of the current query tile (read as float4)
+  alignas(16) float dl[2][128];
+};
+
+__device__ __forceinline__ float ex2b(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+template <int N>
+__device__ __forceinline__ void breg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
+template <int N>
+__device__ __forceinline__ void breg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
+
+template <int HD>
+__device__ __forceinline__ void bload_tile(uint8_t* dst, const CUtensorMap* m, uint64_t* bar, int row, int head, int b) {
+#pragma unroll
+  for (int hh = 0; hh < HD / 64; ++hh) tma_load_4d(dst + hh * 16384, m, bar, hh * 64, row, head, b);
+}
+
+// D[128 x 128] = A[128 x HD] B[128 x HD]^T, both operands K-major tiles in shared memory
+template <int HD>
+__device__ __forceinline__ void issue_ss(uint32_t d, uint32_t a_smem, uint32_t b_smem, uint32_t idesc) {
+#pragma unroll
+  for (int ks = 0; ks < HD / 16; ++ks) {
+    const uint32_t off = (ks >> 2) * 16384 + (ks & 3) * 32;
+    umma_ss(d, umma_smem_desc_sw128(a_smem + off, 16, 1024), umma_smem_desc_sw128(b_smem + off, 16, 1024), idesc, ks > 0);
+  }
+}
+// D[128 x HD] (+)= A[128 x 128] B[128 x HD]; A = bf16 in TMEM in the split layout described above,
+// B = a [128 rows x HD] tile read MN-major
+__device__ __forceinline__ void issue_ts(uint32_t d, uint32_t a_tmem, uint32_t b_smem, uint32_t idesc, bool accumulate) {
+#pragma unroll
+  for (int ks = 0; ks < 8; ++ks)
+    umma_ts(d, a_tmem + (ks >> 2) * 64 + (ks & 3) * 8, umma_smem_desc_sw128(b_smem + ks * 2048, 16384, 1024), idesc,
+            accumulate || ks > 0);
+}
+
+// 32 fp32 accumulator columns [c0, c0+32) of row r -> bf16 -> 128-byte-swizzled staging tile
+__device__ __forceinline__ void stage_cols(uint8_t* stage, const uint32_t (&o)[32], int c0, int r, float f) {
+  uint8_t* dst = stage + (c0 >> 6) * 16384 + r * 128;
+  const int cbase = (c0 & 63) >> 3;
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    uint4 q;
+    q.x = pack_bf16(__uint_as_float(o[c * 8 + 0]) * f, __uint_as_float(o[c * 8 + 1]) * f);
+    q.y = pack_bf16(__uint_as_float(o[c * 8 + 2]) * f, __uint_as_float(o[c * 8 + 3]) * f);
+    q.z = pack_bf16(__uint_as_float(o[c * 8 + 4]) * f, __uint_as_float(o[c * 8 + 5]) * f);
+    q.w = pack_bf16(__uint_as_float(o[c * 8 + 6]) * f, __uint_as_float(o[c * 8 + 7]) * f);
+    *reinterpret_cast<uint4*>(dst + (((cbase + c) ^ (r & 7)) << 4)) = q;
+  }
+}
+
+// CTA -> (batch, head, tile), heads in groups so CTAs in flight share their streamed tiles in L2,
+// heaviest tiles first inside a group.  Returns false when the CTA has nothing to do.
+__device__ __forceinline__ bool bwd_cta_coords(const BwdParams& p, bool heavy_is_low, int& b, int& h, int& tile) {
+  const int bh_count = p.B * p.H;
+  const int per_group = BWD_HEAD_GROUP * p.n_tiles;
+  const int grp = blockIdx.x / per_group;
+  const int gsize = min(BWD_HEAD_GROUP, bh_count - grp * BWD_HEAD_GROUP);
+  const int rem = blockIdx.x - grp * per_group;
+  if (rem >= gsize * p.n_tiles) return false;
+  const int t = rem / gsize;
+  tile = heavy_is_low ? t : p.n_tiles - 1 - t;
+  const int bh = grp * BWD_HEAD_GROUP + rem % gsize;
+  b = bh / p.H;
+  h = bh % p.H;
+  const int state = p.force_state >= 0 ? p.force_state : p.frozen[h];
+  return state == SAF_LIVE;
+}
+
+template <int HD>
+__device__ __forceinline__ void bwd_setup(BwdBars* bars, int tid, int warp) {
+  if (tid == 0) {
+    mbar_init(&bars->res_full, 1);
+    for (int s = 0; s < 3; ++s) {
+      mbar_init(&bars->ring_full[s], 1);
+      mbar_init(&bars->ring_empty[s], 1);
+    }
+    mbar_init(&bars->s_full[0], 1);
+    mbar_init(&bars->s_full[1], 1);
+    mbar_init(&bars->dp_full, 1);
+    mbar_init(&bars->p_full, 256);
+    mbar_init(&bars->ds_full, 256);
+    mbar_init(&bars->acc_full, 1);
+    fence_mbar_init();
+  }
+  if (warp == 9) {
+    tmem_alloc(&bars->tmem_base, BwdCfg<HD>::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+}
+
+// ---------------------------------------------------------------------------------------------
+// dK_j, dV_j
+// ---------------------------------------------------------------------------------------------
+template <int HD>
+__global__ void __launch_bounds__(BWD_THREADS, 1)
+flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
+                      const __grid_constant__ CUtensorMap mapV, const __grid_constant__ CUtensorMap mapdO,
+                      const __grid_constant__ CUtensorMap mapdK, const __grid_constant__ CUtensorMap mapdV,
+                      const __grid_constant__ BwdParams p) {
+  using C = BwdCfg<HD>;
+  int b, h, jt;
+  if (!bwd_cta_coords(p, true, b, h, jt)) return;
+  const int hq = p.hidx ? p.hidx[h] : h;
+  const int n = p.n_tiles - jt;            // query tiles jt .. n_tiles-1
+  const int j0 = jt * 128;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* sK = smem;
+  uint8_t* sV = smem + C::TILE_BYTES;
+  uint8_t* ring = smem + 2 * C::TILE_BYTES;           // stage s: [Q_i | dO_i]
+  BwdBars* bars = reinterpret_cast<BwdBars*>(ring + C::NSTAGE * 2 * C::TILE_BYTES);
+  const int tid = threadIdx.x, warp = tid >> 5;
+  bwd_setup<HD>(bars, tid, warp);
+  const uint32_t tmem = bars->tmem_base;
+  constexpr uint32_t COL_S = 0, COL_DP = 128, COL_DV = 256, COL_DK = 256 + HD;
+
+  if (warp >= 8) {
+    breg_dec<56>();
+    const bool leader = elect_one();
+    if (warp == 8) {
+      // ------------------------------------------------------------ TMA producer
+      if (leader) {
+        tma_prefetch_desc(&mapQ);
+        tma_prefetch_desc(&mapK);
+        tma_prefetch_desc(&mapV);
+        tma_prefetch_desc(&mapdO);
+        mbar_expect_tx(&bars->res_full, 2 * C::TILE_BYTES);
+        bload_tile<HD>(sK, &mapK, &bars->res_full, j0, hq, b);
+        bload_tile<HD>(sV, &mapV, &bars->res_full, j0, h, b);
+        for (int i = 0; i < n; ++i) {
+          const int s = i % C::NSTAGE;
+          if (!mbar_wait(&bars->ring_empty[s], ((i / C::NSTAGE) & 1) ^ 1)) {
+            dev_set_error(p.status, SAF_DEV_TIMEOUT_TMA, 40);
+            break;
+          }
+          uint8_t* dst = ring + s * 2 * C::TILE_BYTES;
+          mbar_expect_tx(&bars->ring_full[s], 2 * C::TILE_BYTES);
+          bload_tile<HD>(dst, &mapQ, &bars->ring_full[s], (jt + i) * 128, hq, b);
+          bload_tile<HD>(dst + C::TILE_BYTES, &mapdO, &bars->ring_full[s], (jt + i) * 128, h, b);
+        }
+      }
+    } else if (warp == 9) {
+      // ------------------------------------------------------------ MMA issuer
+      const uint32_t idesc_s = umma_idesc_bf16(128, 128, 0, 0);
+      const uint32_t idesc_o = umma_idesc_bf16(128, HD, 0, 1);
+      const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aR = smem_u32(ring);
+      bool ok = mbar_wait(&bars->res_full, 0);
+      if (!ok) dev_set_error(p.status, SAF_DEV_TIMEOUT_MMA, 41);
+      for (int i = 0; i < n && ok; ++i) {
+        const int s = i % C::NSTAGE;
+        const uint32_t aQ = aR + s * 2 * C::TILE_BYTES, adO = aQ + C::TILE_BYTES;
+        if (i == 0) {
+          if (!mbar_wait(&bars->ring_full[0], 0)) {
+            dev_set_error(p.status, SAF_DEV_TIMEOUT_MMA, 42);
+            break;
+          }
+          tc_fence_after();
+          if (leader) {
+            issue_ss<HD>(tmem + COL_S, aK, aQ, idesc_s);
+            umma_commit(&bars->s_full[0]);
+            issue_ss<HD>(tmem + COL_DP, aV, adO, idesc_s);
+            umma_commit(&bars->dp_full);
+          }
+          __syncwarp();
+        }
+        if (!mbar_wait(&bars->p_full, i & 1)) {
+          dev_set_error(p.status, SAF_DEV_TIMEOUT_MMA, 43);
+          break;
+        }
+        tc_fence_after();
+        if (leader) issue_ts(tmem + COL_DV, tmem + COL_S, adO, idesc_o, i > 0);
+        __syncwarp();
+        const int s2 = (i + 1) % C::NSTAGE;
+        const uint32_t aQ2 = aR + s2 * 2 * C::TILE_BYTES, adO2 = aQ2 + C::TILE_BYTES;
+        if (i + 1 < n) {
+          if (!mbar_wait(&bars->ring_full[s2], ((i + 1) / C::NSTAGE) & 1)) {
+            dev_set_error(p.status, SAF_DEV_TIMEOUT_MMA, 44);
+            break;
+          }
+          tc_fence_after();
+          if (leader) {
+            issue_ss<HD>(tmem + COL_S, aK, aQ2, idesc_s);   // ordered behind the dV product that read P^T
+            umma_commit(&bars->s_full[0]);
+          }
+          __syncwarp();
+        }
+        if (!mbar_wait(&bars->ds_full, i & 1)) {
+          dev_set_error(p.status, SAF_DEV_TIMEOUT_MMA, 45);
+          break;
+        }
+        tc_fence_after();
+        if (leader) {
+          issue_ts(tmem + COL_DK, tmem + COL_DP, aQ, idesc_o, i > 0);
+          umma_commit(&bars->ring_empty[s]);
+          if (i + 1 < n) {
+            issue_ss<HD>(tmem + COL_DP, aV, adO2, idesc_s);  // ordered behind the dK product that read dS^T
+            umma_commit(&bars->dp_full);
+          }
+        }
+        __syncwarp();
+      }
+      if (leader) umma_commit(&bars->acc_full);
+      __syncwarp();
+    }
+  } else {
+    // -------------------------------------------------------------- compute warpgroups
+    breg_inc<224>();
+    const int half = warp >> 2;
+    const int r = tid & 127;                       // key row of the tile
+    const int cb = half * 64;                      // first query column of this group
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+    const uint32_t tS = tmem + lane_base + COL_S, tdP = tmem + lane_base + COL_DP;
+    const float sc = p.scale_log2;
+    const float* lse_g = p.lse + (int64_t)b * p.lse_s[0] + (int64_t)h * p.lse_s[1];
+    const float* dl_g = p.delta + (int64_t)b * p.delta_s[0] + (int64_t)h * p.delta_s[1];
+    auto fetch = [&](int qt) -> float {
+      const int row = qt * 128 + r;
+      if (tid < 128) return row < p.T ? lse_g[(int64_t)row * p.lse_s[2]] : INFINITY;   // +inf: P = 0 past T
+      return row < p.T ? dl_g[(int64_t)row * p.delta_s[2]] : 0.f;
+    };
+    float nxt = fetch(jt);
+    bool ok = true;
+    for (int i = 0; i < n; ++i) {
+      const int st = i & 1;
+      if (tid < 128) bars->lse[st][r] = nxt;
+      else bars->dl[st][r] = nxt;
+      named_bar_sync(1, 256);
+      if (i + 1 < n) nxt = fetch(jt + i + 1);
+      // ---- P^T
+      if (!mbar_wait(&bars->s_full[0], i & 1)) {
+        dev_set_error(p.status, SAF_DEV_TIMEOUT_SOFTMAX, 46);
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      float pf[64];
+#pragma unroll
+      for (int ch = 0; ch < 2; ++ch) {
+        uint32_t s[32];
+        tmem_ld32(tS + cb + ch * 32, s);
+        tmem_ld_wait();
+        const float4* L4 = reinterpret_cast<const float4*>(&bars->lse[st][cb + ch * 32]);
+#pragma unroll
+        for (int x = 0; x < 8; ++x) {
+          const float4 L = L4[x];
+          pf[ch * 32 + x * 4 + 0] = ex2b(fmaf(__uint_as_float(s[x * 4 + 0]), sc, -L.x));
+          pf[ch * 32 + x * 4 + 1] = ex2b(fmaf(__uint_as_float(s[x * 4 + 1]), sc, -L.y));
+          pf[ch * 32 + x * 4 + 2] = ex2b(fmaf(__uint_as_float(s[x * 4 + 2]), sc, -L.z));
+          pf[ch * 32 + x * 4 + 3] = ex2b(fmaf(__uint_as_float(s[x * 4 + 3]), sc, -L.w));
+        }
+        if (i == 0) {   // diagonal tile: query c sees key r only if c >= r
+#pragma unroll
+          for (int x = 0; x < 32; ++x)
+            if (cb + ch * 32 + x < r) pf[ch * 32 + x] = 0.f;
+        }
+        uint32_t pk[16];
+#pragma unroll
+        for (int x = 0; x < 16; ++x) pk[x] = pack_bf16(pf[ch * 32 + 2 * x], pf[ch * 32 + 2 * x + 1]);
+        tmem_st16(tS + cb + ch * 16, pk);
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(&bars->p_full);
+      // ---- dS^T
+      if (!mbar_wait(&bars->dp_full, i & 1)) {
+        dev_set_error(p.status, SAF_DEV_TIMEOUT_SOFTMAX, 47);
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+#pragma unroll
+      for (int ch = 0; ch < 2; ++ch) {
+        uint32_t d[32];
+        tmem_ld32(tdP + cb + ch * 32, d);
+        tmem_ld_wait();
+        const float4* D4 = reinterpret_cast<const float4*>(&bars->dl[st][cb + ch * 32]);
+        uint32_t pk[16];
+#pragma unroll
+        for (int x = 0; x < 8; ++x) {
+          const float4 D = D4[x];
+          const float d0 = pf[ch * 32 + x * 4 + 0] * (__uint_as_float(d[x * 4 + 0]) - D.x);
+          const float d1 = pf[ch * 32 + x * 4 + 1] * (__uint_as_float(d[x * 4 + 1]) - D.y);
+          const float d2 = pf[ch * 32 + x * 4 + 2] * (__uint_as_float(d[x * 4 + 2]) - D.z);
+          const float d3 = pf[ch * 32 + x * 4 + 3] * (__uint_as_float(d[x * 4 + 3]) - D.w);
+          pk[2 * x] = pack_bf16(d0, d1);
+          pk[2 * x + 1] = pack_bf16(d2, d3);
+        }
+        tmem_st16(tdP + cb + ch * 16, pk);
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(&bars->ds_full);
+    }
+    // ---- epilogue: dV_j, dK_j -> bf16 -> swizzled staging (the K / V tiles are no longer read) -> TMA store
+    if (ok && !mbar_wait(&bars->acc_full, 0)) {
+      dev_set_error(p.status, SAF_DEV_TIMEOUT_SOFTMAX, 48);
+      ok = false;
+    }
+    tc_fence_after();
+#pragma unroll
+    for (int c0 = half * (HD / 2); c0 < (half + 1) * (HD / 2); c0 += 32) {
+      uint32_t o[32];
+      tmem_ld32(tmem + lane_base + COL_DV + c0, o);
+      tmem_ld_wait();
+      stage_cols(sV, o, c0, r, 1.f);
+      tmem_ld32(tmem + lane_base + COL_DK + c0, o);
+      tmem_ld_wait();
+      stage_cols(sK, o, c0, r, p.sm_scale);
+    }
+    fence_proxy_async_smem();
+    named_bar_sync(1, 256);
+    if (tid == 0 && ok) {
+#pragma unroll
+      for (int hh = 0; hh < HD / 64; ++hh) {
+        tma_store_4d(&mapdV, sV + hh * 16384, hh * 64, j0, h, b);
+        tma_store_4d(&mapdK, sK + hh * 16384, hh * 64, j0, hq, b);
+      }
+      tma_store_commit();
+      tma_store_wait_all();
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 9) tmem_dealloc(tmem, C::TMEM_COLS);
+}
+
+// ---------------------------------------------------------------------------------------------
+// dQ_i
+// ---------------------------------------------------------------------------------------------
+template <int HD>
+__global__ void __launch_bounds__(BWD_THREADS, 1)
+flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
+                    const __grid_constant__ CUtensorMap mapV, const __grid_constant__ CUtensorMap mapdO,
+                    const __grid_constant__ CUtensorMap mapdQ, const __grid_constant__ BwdParams p) {
+  using C = BwdCfg<HD>;
+  int b, h, it;
+  if (!bwd_cta_coords(p, false, b, h, it)) return;
+  const int hq = p.hidx ? p.hidx[h] : h;
+  const int n = it + 1;                    // key tiles 0 .. it
+  const int i0 = it * 128;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* sQ = smem;
+  uint8_t* sdO = smem + C::TILE_BYTES;
+  uint8_t* ring = smem + 2 * C::TILE_BYTES;           // stage s: [K_j | V_j]
+  BwdBars* bars = reinterpret_cast<BwdBars*>(ring + C::NSTAGE * 2 * C::TILE_BYTES);
+  const int tid = threadIdx.x, warp = tid >> 5;
+  bwd_setup<HD>(bars, tid, warp);
+  const uint32_t tmem = bars->tmem_base;
+  constexpr uint32_t COL_S = 0 /* two buffers */, COL_DP = 256, COL_DQ = 384;
+
+  if (warp >= 8) {
+    breg_dec<56>();
+    const bool leader = elect_one();
+    if (warp == 8) {
+      // ------------------------------------------------------------ TMA producer
+      if (leader) {
+        tma_prefetch_desc(&mapQ);
+        tma_prefetch_desc(&mapK);
+        tma_prefetch_desc(&mapV);
+        tma_prefetch_desc(&mapdO);
+        mbar_expect_tx(&bars->res_full, 2 * C::TILE_BYTES);
+        bload_tile<HD>(sQ, &mapQ, &bars->res_full, i0, hq, b);
+        bload_tile<HD>(sdO, &mapdO, &bars->res_full, i0, h, b);
+        for (int j = 0; j < n; ++j) {
+          const int s = j % C::NSTAGE;
+          if (!mbar_wait(&bars->ring_empty[s], ((j / C::NSTAGE) & 1) ^ 1)) {
+            dev_set_error(p.status, SAF_DEV_TIMEOUT_TMA, 50);
+            break;
+          }
+          uint8_t* dst = ring + s * 2 * C::TILE_BYTES;
+          mbar_expect_tx(&bars->ring_full[s], 2 * C::TILE_BYTES);
+          bload_tile<HD>(dst, &mapK, &bars->ring_full[s], j * 128, hq, b);
+          bload_tile<HD>(dst + C::TILE_BYTES, &mapV, &bars->ring_full[s], j * 128, h, b);
+        }
+      }
+    } else if (warp == 9) {
+      // ------------------------------------------------------------ MMA issuer
+      const uint32_t idesc_s = umma_idesc_bf16(128, 128, 0, 0);
+      const uint32_t idesc_o = umma_idesc_bf16(128, HD, 0, 1);
+      const uint32_t aQ = smem_u32(sQ), adO = smem_u32(sdO), aR = smem_u32(ring);
+      bool ok = mbar_wait(&bars->res_full, 0);
+      if (!ok) dev_set_error(p.status, SAF_DEV_TIMEOUT_MMA, 51);
+      // scores run up to two key tiles ahead (two score buffers), dP one ahead
+      auto issue_scores = [&](int j) -> bool {
+        const int s = j % C::NSTAGE;
+        if (!mbar_wait(&bars->ring_full[s], (j / C::NSTAGE) & 1)) {
+          dev_set_error(p.status, SAF_DEV_TIMEOUT_MMA, 52);
+          return false;
+        }
+        tc_fence_after();
+        if (leader) {
+          issue_ss<HD>(tmem + COL_S + (j & 1) * 128, aQ, aR + s * 2 * C::TILE_BYTES, idesc_s);
+          umma_commit(&bars->s_full[j & 1]);
+        }
+        __syncwarp();
+        return true;
+      };
+      auto issue_dp = [&](int j) {   // its ring stage was waited for by issue_scores(j)
+        const int s = j % C::NSTAGE;
+        if (leader) {
+          issue_ss<HD>(tmem + COL_DP, adO, aR + s * 2 * C::TILE_BYTES + C::TILE_BYTES, idesc_s);
+          umma_commit(&bars->dp_full);
+        }
+        __syncwarp();
+      };
+      if (ok) ok = issue_scores(0);
+      if (ok) issue_dp(0);
+      if (ok && n > 1) ok = issue_scores(1);
+      for (int j = 0; j < n && ok; ++j) {
+        const int s = j % C::NSTAGE;
+        if (!mbar_wait(&bars->ds_full, j & 1)) {
+          dev_set_error(p.status, SAF_DEV_TIMEOUT_MMA, 53);
+          break;
+        }
+        tc_fence_after();
+        if (leader) {
+          issue_ts(tmem + COL_DQ, tmem + COL_DP, aR + s * 2 * C::TILE_BYTES, idesc_o, j > 0);
+          umma_commit(&bars->ring_empty[s]);
+        }
+        __syncwarp();
+        if (j + 1 < n) issue_dp(j + 1);               // ordered behind the dQ product that read dS
+        if (j + 2 < n) ok = issue_scores(j + 2);      // score buffer j & 1 was read before ds_full(j)
+      }
+      if (leader) umma_commit(&bars->acc_full);
+      __syncwarp();
+    }
+  } else {
+    // -------------------------------------------------------------- compute warpgroups
+    breg_inc<224>();
+    const int half = warp >> 2;
+    const int r = tid & 127;                       // query row of the tile
+    const int cb = half * 64;                      // first key column of this group
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+    const uint32_t tdP = tmem + lane_base + COL_DP;
+    const float sc = p.scale_log2;
+    const int row = i0 + r;
+    float lse_r = INFINITY, dl_r = 0.f;            // +inf: P = 0 for rows past T
+    if (row < p.T) {
+      lse_r = p.lse[(int64_t)b * p.lse_s[0] + (int64_t)h * p.lse_s[1] + (int64_t)row * p.lse_s[2]];
+      dl_r = p.delta[(int64_t)b * p.delta_s[0] + (int64_t)h * p.delta_s[1] + (int64_t)row * p.delta_s[2]];
+    }
+    bool ok = true;
+    for (int j = 0; j < n; ++j) {
+      const uint32_t tS = tmem + lane_base + COL_S + (j & 1) * 128;
+      if (!mbar_wait(&bars->s_full[j & 1], (j >> 1) & 1)) {
+        dev_set_error(p.status, SAF_DEV_TIMEOUT_SOFTMAX, 54);
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      float pf[64];
+#pragma unroll
+      for (int ch = 0; ch < 2; ++ch) {
+        uint32_t s[32];
+        tmem_ld32(tS + cb + ch * 32, s);
+        tmem_ld_wait();
+#pragma unroll
+        for (int x = 0; x < 32; ++x) pf[ch * 32 + x] = ex2b(fmaf(__uint_as_float(s[x]), sc, -lse_r));
+        if (j == n - 1) {   // diagonal tile: keys after the row do not count
+#pragma unroll
+          for (int x = 0; x < 32; ++x)
+            if (cb + ch * 32 + x > r) pf[ch * 32 + x] = 0.f;
+        }
+      }
+      if (!mbar_wait(&bars->dp_full, j & 1)) {
+        dev_set_error(p.status, SAF_DEV_TIMEOUT_SOFTMAX, 55);
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+#pragma unroll
+      for (int ch = 0; ch < 2; ++ch) {
+        uint32_t d[32];
+        tmem_ld32(tdP + cb + ch * 32, d);
+        tmem_ld_wait();
+        uint32_t pk[16];
+#pragma unroll
+        for (int x = 0; x < 16; ++x)
+          pk[x] = pack_bf16(pf[ch * 32 + 2 * x] * (__uint_as_float(d[2 * x]) - dl_r),
+                            pf[ch * 32 + 2 * x + 1] * (__uint_as_float(d[2 * x + 1]) - dl_r));
+        tmem_st16(tdP + cb + ch * 16, pk);
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(&bars->ds_full);
+    }
+    if (ok && !mbar_wait(&bars->acc_full, 0)) {
+      dev_set_error(p.status, SAF_DEV_TIMEOUT_SOFTMAX, 56);
+      ok = false;
+    }
+    tc_fence_after();
+#pragma unroll
+    for (int c0 = half * (HD / 2); c0 < (half + 1) * (HD / 2); c0 += 32) {
+      uint32_t o[32];
+      tmem_ld32(tmem + lane_base + COL_DQ + c0, o);
+      tmem_ld_wait();
+      stage_cols(sQ, o, c0, r, p.sm_scale);
+    }
+    fence_proxy_async_smem();
+    named_bar_sync(1, 256);
+    if (tid == 0 && ok) {
+#pragma unroll
+      for (int hh = 0; hh < HD / 64; ++hh) tma_store_4d(&mapdQ, sQ + hh * 16384, hh * 64, i0, hq, b);
+      tma_store_commit();
+      tma_store_wait_all();
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 9) tmem_dealloc(tmem, C::TMEM_COLS);
+}
+
+// ---------------------------------------------------------------------------------------------
+// delta_i = sum_d O_id dO_id for the live heads (kernel/fused_attn.py:291-310)
+// ---------------------------------------------------------------------------------------------
+struct DeltaParams {
+  const __nv_bfloat16* o;
+  const __nv_bfloat16* dout;
+  int64_t o_s[3], do_s[3];
+  float* delta;
+  int64_t delta_s[3];
+  const int32_t* frozen;
+  int B, H, T, force_state;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(256) flash_bwd_delta_kernel(const __grid_constant__ DeltaParams p) {
+  constexpr int TPR = HD / 8;              // threads per row, 16 bytes each
+  constexpr int ROWS = 256 / TPR;
+  const int bh = blockIdx.y, b = bh / p.H, h = bh % p.H;
+  const int state = p.force_state >= 0 ? p.force_state : p.frozen[h];
+  if (state != SAF_LIVE) return;
+  const int row = blockIdx.x * ROWS + threadIdx.x / TPR;
+  const int c = (threadIdx.x % TPR) * 8;
+  float s = 0.f;
+  if (row < p.T) {
+    const uint4 a = *reinterpret_cast<const uint4*>(p.o + (int64_t)b * p.o_s[0] + (int64_t)h * p.o_s[1] + (int64_t)row * p.o_s[2] + c);
+    const uint4 d = *reinterpret_cast<const uint4*>(p.dout + (int64_t)b * p.do_s[0] + (int64_t)h * p.do_s[1] + (int64_t)row * p.do_s[2] + c);
+    const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, dw[4] = {d.x, d.y, d.z, d.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      s = fmaf(__uint_as_float(aw[e] << 16), __uint_as_float(dw[e] << 16), s);
+      s = fmaf(__uint_as_float(aw[e] & 0xffff0000u), __uint_as_float(dw[e] & 0xffff0000u), s);
+    }
+  }
+#pragma unroll
+  for (int off = TPR / 2; off; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+  if (row < p.T && (threadIdx.x % TPR) == 0)
+    p.delta[(int64_t)b * p.delta_s[0] + (int64_t)h * p.delta_s[1] + (int64_t)row * p.delta_s[2]] = s;
+}
+
+bool bwd_aligned16(const void* q) { return ((uintptr_t)q & 15) == 0; }
+
+bool bwd_tma_ok(const SafTensor& t) {
+  if (!t.ptr || !bwd_aligned16(t.ptr) || t.stride[3] != 1) return false;
+  for (int i = 0; i < 3; ++i)
+    if (t.stride[i] % 8 || t.stride[i] <= 0) return false;
+  return true;
+}
+
+int bwd_map4(CUtensorMap* m, const SafTensor& t, int B, int Hn, int T, int HD) {
+  uint64_t dims[4] = {(uint64_t)HD, (uint64_t)T, (uint64_t)Hn, (uint64_t)B};
+  uint64_t strides[4] = {0, (uint64_t)t.stride[2] * 2, (uint64_t)t.stride[1] * 2, (uint64_t)t.stride[0] * 2};
+  uint32_t box[4] = {64, 128, 1, 1};
+  return make_tensor_map_bf16(m, t.ptr, 4, dims, strides, box, true);
+}
+
+template <int HD>
+int bwd_launch_typed(const SafMixedAttnBwdArgs& g, cudaStream_t st) {
+  const SafMixedAttnArgs& a = g.fwd;
+  CUtensorMap mq, mk, mv, mdo, mdq, mdk, mdv;
+  int rc;
+  if ((rc = bwd_map4(&mq, a.q, a.B, a.U, a.T, HD))) return rc;
+  if ((rc = bwd_map4(&mk, a.k, a.B, a.U, a.T, HD))) return rc;
+  if ((rc = bwd_map4(&mv, a.v, a.B, a.H, a.T, HD))) return rc;
+  if ((rc = bwd_map4(&mdo, g.dout, a.B, a.H, a.T, HD))) return rc;
+  if ((rc = bwd_map4(&mdq, g.dq, a.B, a.U, a.T, HD))) return rc;
+  if ((rc = bwd_map4(&mdk, g.dk, a.B, a.U, a.T, HD))) return rc;
+  if ((rc = bwd_map4(&mdv, g.dv, a.B, a.H, a.T, HD))) return rc;
+
+  DeltaParams d;
+  d.o = reinterpret_cast<const __nv_bfloat16*>(a.out.ptr);
+  d.dout = reinterpret_cast<const __nv_bfloat16*>(g.dout.ptr);
+  for (int i = 0; i < 3; ++i) {
+    d.o_s[i] = a.out.stride[i];
+    d.do_s[i] = g.dout.stride[i];
+    d.delta_s[i] = g.delta.stride[i];
+  }
+  d.delta = reinterpret_cast<float*>(g.delta.ptr);
+  d.frozen = a.frozen;
+  d.B = a.B; d.H = a.H; d.T = a.T; d.force_state = a.force_state;
+  constexpr int ROWS = 256 / (HD / 8);
+  flash_bwd_delta_kernel<HD><<<dim3((a.T + ROWS - 1) / ROWS, a.B * a.H), 256, 0, st>>>(d);
+  count_launch();
+  if ((rc = check_launch("flash_bwd_delta_kernel"))) return rc;
+
+  BwdParams p;
+  memset(&p, 0, sizeof(p));
+  p.B = a.B; p.H = a.H; p.T = a.T; p.force_state = a.force_state;
+  p.n_tiles = (a.T + 127) / 128;
+  p.sm_scale = a.sm_scale;
+  p.scale_log2 = a.sm_scale * LOG2E_B;
+  p.frozen = a.frozen; p.hidx = a.hidx;
+  p.lse = reinterpret_cast<const float*>(a.lse.ptr);
+  p.delta = d.delta;
+  for (int i = 0; i < 3; ++i) {
+    p.lse_s[i] = a.lse.stride[i];
+    p.delta_s[i] = g.delta.stride[i];
+  }
+  p.status = a.status;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(flash_bwd_dkdv_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdCfg<HD>::SMEM_BYTES);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(flash_bwd_dq_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdCfg<HD>::SMEM_BYTES);
+    if (e != cudaSuccess) return fail(SAF_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    attr_set = true;
+  }
+  const int bh = a.B * a.H;
+  const int groups = (bh + BWD_HEAD_GROUP - 1) / BWD_HEAD_GROUP;
+  const unsigned grid = (unsigned)(groups * BWD_HEAD_GROUP * p.n_tiles);
+  flash_bwd_dkdv_kernel<HD><<<grid, BWD_THREADS, BwdCfg<HD>::SMEM_BYTES, st>>>(mq, mk, mv, mdo, mdk, mdv, p);
+  count_launch();
+  if ((rc = check_launch("flash_bwd_dkdv_kernel"))) return rc;
+  flash_bwd_dq_kernel<HD><<<grid, BWD_THREADS, BwdCfg<HD>::SMEM_BYTES, st>>>(mq, mk, mv, mdo, mdq, p);
+  count_launch();
+  return check_launch("flash_bwd_dq_kernel");
+}
+
+}  // namespace
+
+// Live heads of a bf16 backward at head_dim 64 / 128 without in-kernel RoPE or GQA; everything else
+// stays with the generic kernels.
+int launch_flash_bwd_sm100(const SafMixedAttnBwdArgs& g, uint32_t* handled, cudaStream_t st) {
+  *handled = 0;
+  const SafMixedAttnArgs& a = g.fwd;
+  if (a.dtype != SAF_BF16 || (a.HD != 64 && a.HD != 128) || a.rope || a.HKV > 0) return SAF_ERR_UNSUPPORTED;
+  if (a.U <= 0 || a.sm_scale <= 0.f) return SAF_ERR_UNSUPPORTED;
+  if (!bwd_tma_ok(a.q) || !bwd_tma_ok(a.k) || !bwd_tma_ok(a.v) || !bwd_tma_ok(g.dout) || !bwd_tma_ok(g.dq) ||
+      !bwd_tma_ok(g.dk) || !bwd_tma_ok(g.dv) || !bwd_tma_ok(a.out))
+    return SAF_ERR_UNSUPPORTED;
+  if (!a.lse.ptr || !g.delta.ptr) return SAF_ERR_UNSUPPORTED;
+  if (!saf_device_supported()) return SAF_ERR_UNSUPPORTED;
+  if (a.force_state >= 0 && a.force_state != SAF_LIVE) return SAF_ERR_UNSUPPORTED;
+  if (a.frozen_host) {
+    bool any = false;
+    for (int h = 0; h < a.H; ++h) any |= a.frozen_host[h] == SAF_LIVE;
+    if (!any) return SAF_ERR_UNSUPPORTED;
+  }
+  const int rc = (a.HD == 64) ? bwd_launch_typed<64>(g, st) : bwd_launch_typed<128>(g, st);
+  if (rc == SAF_OK) *handled = 1u << SAF_LIVE;
+  return rc;
+}
+
+}  // namespace saf

@@ -43,6 +43,7 @@ int launch_scan_fwd(const SafMixedAttnArgs& a, cudaStream_t st);                
 int launch_scan_bwd(const SafMixedAttnBwdArgs& a, cudaStream_t st);                    // state 3 heads: dv
 // tcgen05 fast path; returns SAF_ERR_UNSUPPORTED when the call does not qualify
 int launch_flash_fwd_sm100(const SafMixedAttnArgs& a, uint32_t* handled_states, cudaStream_t st);
+int launch_flash_bwd_sm100(const SafMixedAttnBwdArgs& a, uint32_t* handled_states, cudaStream_t st);
 int launch_gemm_sm100(const SafIndexedLinearArgs& a, cudaStream_t st);
 int launch_gemm_generic(const SafIndexedLinearArgs& a, cudaStream_t st);
 int launch_gemm_bwd_dx(const SafIndexedLinearArgs& a, const void* dout, int64_t lddo, void* dx, int64_t lddx,
