@@ -202,6 +202,18 @@ int saf_indexed_linear_bwd_dx(const SafIndexedLinearArgs* args, const void* dout
 int saf_indexed_linear_bwd_dw(const SafIndexedLinearArgs* args, const void* dout, int64_t lddo, void* stream);
 
 /* ---------------------------------------------------------------------------
+ * In-place rotary embedding of chosen `slab`-wide column slabs of x (M, n_slabs*slab):
+ * row m uses table row m % T of rope_cos / rope_sin (fp32 (T, slab), halves repeated).
+ * Replaces apply_rotary_pos_emb / rotate_half on the compact q,k (nanogpt/model.py:57-99);
+ * inverse != 0 applies the adjoint rotation, which is what the backward of a projection
+ * with the rotation fused into its epilogue needs for the incoming gradient.
+ * slab_rope: HOST array (n_slabs) of flags, or null = rotate every slab.
+ * ------------------------------------------------------------------------- */
+int saf_rope_slabs(void* x, int64_t ld, int32_t M, int32_t n_slabs, int32_t slab, int32_t T,
+                   const int32_t* slab_rope, const float* rope_cos, const float* rope_sin, int32_t dtype,
+                   int32_t inverse, void* stream);
+
+/* ---------------------------------------------------------------------------
  * Freeze-time helper: z[h,i] = logsumexp_{j<=i}(alpha[h,j] + rho[h,i-j]).
  * Replaces decomposed_logz (kernel/fused_attn.py:101-116).  fp32 in/out.
  * ------------------------------------------------------------------------- */

@@ -314,6 +314,8 @@ int saf_indexed_linear_bwd_dx(const SafIndexedLinearArgs* args, const void* dout
   if (rc) return rc;
   if (args->M == 0) return SAF_OK;
   if (!dout || !dx) return fail(SAF_ERR_INVALID, "dout and dx must be non-null");
+  rc = launch_gemm_bwd_dx_sm100(*args, dout, lddo, dx, lddx, bias, (cudaStream_t)stream);
+  if (rc != SAF_ERR_UNSUPPORTED) return rc;
   return launch_gemm_bwd_dx(*args, dout, lddo, dx, lddx, bias, (cudaStream_t)stream);
 }
 
@@ -322,7 +324,20 @@ int saf_indexed_linear_bwd_dw(const SafIndexedLinearArgs* args, const void* dout
   if (rc) return rc;
   if (args->n_slabs == 0) return SAF_OK;
   if (!dout) return fail(SAF_ERR_INVALID, "dout must be non-null");
+  rc = launch_gemm_bwd_dw_sm100(*args, dout, lddo, (cudaStream_t)stream);
+  if (rc != SAF_ERR_UNSUPPORTED) return rc;
   return launch_gemm_bwd_dw(*args, dout, lddo, (cudaStream_t)stream);
+}
+
+int saf_rope_slabs(void* x, int64_t ld, int32_t M, int32_t n_slabs, int32_t slab, int32_t T,
+                   const int32_t* slab_rope, const float* rope_cos, const float* rope_sin, int32_t dtype,
+                   int32_t inverse, void* stream) {
+  if (M < 0 || n_slabs < 0 || slab <= 0 || T <= 0) return fail(SAF_ERR_INVALID, "bad dimensions");
+  if (slab % 2) return fail(SAF_ERR_INVALID, "RoPE requires an even head dimension");
+  if (dtype != SAF_F32 && dtype != SAF_BF16) return fail(SAF_ERR_UNSUPPORTED, "rope_slabs takes fp32 or bf16");
+  if (M == 0 || n_slabs == 0) return SAF_OK;
+  if (!x || !rope_cos || !rope_sin) return fail(SAF_ERR_INVALID, "null pointer");
+  return launch_rope_slabs(x, ld, M, n_slabs, slab, T, slab_rope, rope_cos, rope_sin, dtype, inverse, (cudaStream_t)stream);
 }
 
 int saf_decomposed_logz(const float* alpha, const float* rho, float* z, int32_t H, int32_t S, void* stream) {

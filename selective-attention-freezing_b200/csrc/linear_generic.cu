@@ -154,7 +154,7 @@ __global__ void bias_grad_kernel(const T* __restrict__ dout, int64_t lddo, int M
 template <typename T>
 __global__ void rope_slabs_kernel(T* __restrict__ out, int64_t ldo, int M, int n_slabs, int slab, int Tlen,
                                   const float* __restrict__ cosT, const float* __restrict__ sinT,
-                                  const __grid_constant__ SlabTable tb) {
+                                  const __grid_constant__ SlabTable tb, float sgn) {
   const int half = slab >> 1;
   const int64_t total = (int64_t)M * n_slabs * half;
   for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
@@ -165,8 +165,9 @@ __global__ void rope_slabs_kernel(T* __restrict__ out, int64_t ldo, int M, int n
     const int t = (int)(m % Tlen);
     T* p = out + m * ldo + (int64_t)g * slab;
     const float x1 = to_f<T>(p[d]), x2 = to_f<T>(p[d + half]);
-    const float c1 = cosT[(int64_t)t * slab + d], s1 = sinT[(int64_t)t * slab + d];
-    const float c2 = cosT[(int64_t)t * slab + d + half], s2 = sinT[(int64_t)t * slab + d + half];
+    // sgn = -1 gives the adjoint (inverse) rotation; the tables repeat per half
+    const float c1 = cosT[(int64_t)t * slab + d], s1 = sgn * sinT[(int64_t)t * slab + d];
+    const float c2 = cosT[(int64_t)t * slab + d + half], s2 = sgn * sinT[(int64_t)t * slab + d + half];
     p[d] = from_f<T>(x1 * c1 - x2 * s1);
     p[d + half] = from_f<T>(x2 * c2 + x1 * s2);
   }
@@ -210,7 +211,7 @@ int gemm_generic_typed(const SafIndexedLinearArgs& a, int mode, const void* dout
       const int64_t total = (int64_t)a.M * a.n_slabs * (a.slab / 2);
       const int blocks = (int)std::min<int64_t>((total + 255) / 256, 148 * 16);
       rope_slabs_kernel<T><<<blocks, 256, 0, st>>>(reinterpret_cast<T*>(a.out), a.ldo, a.M, a.n_slabs, a.slab, a.T,
-                                                  a.rope_cos, a.rope_sin, tb);
+                                                  a.rope_cos, a.rope_sin, tb, 1.f);
       count_launch();
       if ((rc = check_launch("rope_slabs_kernel"))) return rc;
     }
@@ -285,6 +286,23 @@ int launch_gemm_bwd_dx(const SafIndexedLinearArgs& a, const void* dout, int64_t 
 int launch_gemm_bwd_dw(const SafIndexedLinearArgs& a, const void* dout, int64_t lddo, cudaStream_t st) {
   if (a.dtype == SAF_F32) return gemm_generic_typed<float>(a, 2, dout, lddo, nullptr, 0, nullptr, st);
   return gemm_generic_typed<__nv_bfloat16>(a, 2, dout, lddo, nullptr, 0, nullptr, st);
+}
+int launch_rope_slabs(void* x, int64_t ld, int M, int n_slabs, int slab, int T, const int32_t* slab_rope,
+                      const float* cosT, const float* sinT, int dtype, int inverse, cudaStream_t st) {
+  if (n_slabs > MAX_SLABS) return fail(SAF_ERR_LIMIT, "n_slabs %d exceeds the limit of %d", n_slabs, MAX_SLABS);
+  SlabTable tb;
+  memset(&tb, 0, sizeof(tb));
+  for (int g = 0; g < n_slabs; ++g) tb.rope[g] = (uint8_t)(slab_rope ? (slab_rope[g] != 0) : 1);
+  const int64_t total = (int64_t)M * n_slabs * (slab / 2);
+  const int blocks = (int)std::min<int64_t>((total + 255) / 256, 148 * 16);
+  const float sgn = inverse ? -1.f : 1.f;
+  if (dtype == SAF_F32)
+    rope_slabs_kernel<float><<<blocks, 256, 0, st>>>(reinterpret_cast<float*>(x), ld, M, n_slabs, slab, T, cosT, sinT, tb, sgn);
+  else
+    rope_slabs_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(reinterpret_cast<__nv_bfloat16*>(x), ld, M, n_slabs, slab, T,
+                                                            cosT, sinT, tb, sgn);
+  count_launch();
+  return check_launch("rope_slabs_kernel");
 }
 int launch_logz(const float* alpha, const float* rho, float* z, int H, int S, cudaStream_t st) {
   const int64_t warps = (int64_t)H * S;

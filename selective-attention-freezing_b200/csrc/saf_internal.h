@@ -49,6 +49,12 @@ int launch_gemm_generic(const SafIndexedLinearArgs& a, cudaStream_t st);
 int launch_gemm_bwd_dx(const SafIndexedLinearArgs& a, const void* dout, int64_t lddo, void* dx, int64_t lddx,
                        const void* bias, cudaStream_t st);
 int launch_gemm_bwd_dw(const SafIndexedLinearArgs& a, const void* dout, int64_t lddo, cudaStream_t st);
+// tcgen05 versions of the two backward products; SAF_ERR_UNSUPPORTED when the call does not qualify
+int launch_gemm_bwd_dx_sm100(const SafIndexedLinearArgs& a, const void* dout, int64_t lddo, void* dx, int64_t lddx,
+                             const void* bias, cudaStream_t st);
+int launch_gemm_bwd_dw_sm100(const SafIndexedLinearArgs& a, const void* dout, int64_t lddo, cudaStream_t st);
+int launch_rope_slabs(void* x, int64_t ld, int M, int n_slabs, int slab, int T, const int32_t* slab_rope,
+                      const float* cosT, const float* sinT, int dtype, int inverse, cudaStream_t st);
 int launch_logz(const float* alpha, const float* rho, float* z, int H, int S, cudaStream_t st);
 
 // TMA descriptor encode through the driver entry point (no link-time libcuda dependency)

@@ -348,12 +348,13 @@ class SafCausalSelfAttention(nn.Module):
         if nuf == 0:
             qu = ku = v[:, :0]
         else:
+            # rotation fused into the projection's epilogue (adjoint rotation in its backward), so the
+            # attention kernels get rotated q, k and take the tensor-core path
             qk = ops.linear_rows2(x, self.q_proj.weight, self.k_proj.weight, self.q_proj.bias, self.k_proj.bias,
-                                  self._uf_cols).view(B, T, 2, nuf, hd)
+                                  self._uf_cols, rope=rp, head_dim=hd).view(B, T, 2, nuf, hd)
             qu, ku = qk[:, :, 0].transpose(1, 2), qk[:, :, 1].transpose(1, 2)
         y = ops.fused_mixed_attn(qu, ku, v, patt, self._fz_mask_i32, self._hidx_i32,
-                                 alpha=dec[0], rho=dec[1], z=dec[2], validate=False, sink_decay=self._sd,
-                                 rope=rp if nuf > 0 else None)
+                                 alpha=dec[0], rho=dec[1], z=dec[2], validate=False, sink_decay=self._sd)
         y = y.transpose(1, 2).reshape(B, T, nh * hd)
         return self.c_proj(y)
 

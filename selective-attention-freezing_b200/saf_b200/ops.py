@@ -395,11 +395,25 @@ def frozen_pv(patt, v, fz_idx, T, *, sink_decay=None):
 _SLAB_CACHE = {}
 
 
-def _slabs_of(rows):
+def _slabs_of(rows, want=None):
     """Decompose a unique-row index tensor into equal runs of consecutive rows.
 
-    Returns (slab, [row0...]).  One device->host copy per distinct index tensor
-    object and version."""
+    Returns (slab, [row0...]); `want` forces the slab width (every run must be a
+    multiple of it).  One device->host copy per distinct index tensor object and version."""
+    if want is not None:
+        slab, row0 = _slabs_of(rows)
+        if slab % want and want % slab:
+            raise ValueError("rows do not form runs of %d consecutive rows" % want)
+        if slab == want:
+            return slab, row0
+        if slab > want:
+            return want, [r + o for r in row0 for o in range(0, slab, want)]
+        step = want // slab   # merge consecutive blocks of one run
+        merged = row0[::step]
+        for i, r in enumerate(merged):
+            if row0[i * step:(i + 1) * step] != list(range(r, r + want, slab)):
+                raise ValueError("rows do not form runs of %d consecutive rows" % want)
+        return want, merged
     hit = _SLAB_CACHE.get(id(rows))
     if hit is not None and hit[0]() is rows and hit[1] == _ver(rows):
         return hit[2]
@@ -487,35 +501,46 @@ class _RowSlicedLinearN(torch.autograd.Function):
     Mirror of kernel/indexed_linear.py:28-55 (one weight) and :86-122 (two weights)."""
 
     @staticmethod
-    def forward(ctx, x, rows, nw, *wb):
+    def forward(ctx, x, rows, nw, rope, *wb):
+        # rope = None or (cos, sin, T, head_dim): every slab is one head and is rotated in the epilogue
         weights, biases = list(wb[:nw]), list(wb[nw:])
         _check_lin(x, *weights)
-        slab, row0 = _slabs_of(rows)
+        slab, row0 = _slabs_of(rows, want=rope[3] if rope is not None else None)
         x2 = _as_2d(x)
         n_per = len(row0)
         sw = [i for i in range(nw) for _ in range(n_per)]
         sr = row0 * nw
         keep = []
-        a = _lin_args(x2, weights, biases, slab, sw, sr, keep)
+        if rope is not None:
+            a = _lin_args(x2, weights, biases, slab, sw, sr, keep, rope=rope[:2], T=rope[2], slab_rope=[1] * len(sr))
+        else:
+            a = _lin_args(x2, weights, biases, slab, sw, sr, keep)
         out = torch.empty((x2.shape[0], nw * n_per * slab), device=x.device, dtype=x.dtype)
         a.out, a.ldo = out.data_ptr(), out.stride(0)
         check(lib.saf_indexed_linear_fwd(C.byref(a), _stream(x)))
-        ctx.save_for_backward(x, rows, *weights)
+        ctx.save_for_backward(x, rows, *weights, *(rope[:2] if rope is not None else ()))
         ctx.nw = nw
+        ctx.rope = None if rope is None else (rope[2], rope[3])
         ctx.has_bias = [b is not None for b in biases]
         return out.view(*x.shape[:-1], out.shape[-1])
 
     @staticmethod
     def backward(ctx, dout):
         x, rows = ctx.saved_tensors[:2]
-        weights = list(ctx.saved_tensors[2:])
         nw = ctx.nw
-        slab, row0 = _slabs_of(rows)
+        weights = list(ctx.saved_tensors[2:2 + nw])
+        slab, row0 = _slabs_of(rows, want=ctx.rope[1] if ctx.rope is not None else None)
         n_per = len(row0)
         sw = [i for i in range(nw) for _ in range(n_per)]
         sr = row0 * nw
         dout2 = _as_2d(dout)
         x2 = _as_2d(x)
+        if ctx.rope is not None:
+            # gradient w.r.t. the un-rotated projection: adjoint rotation of a private copy
+            cos, sin = ctx.saved_tensors[2 + nw:4 + nw]
+            dout2 = dout2.clone() if dout2.data_ptr() == dout.data_ptr() else dout2
+            check(lib.saf_rope_slabs(dout2.data_ptr(), dout2.stride(0), dout2.shape[0], len(sr), slab, ctx.rope[0],
+                                     None, cos.data_ptr(), sin.data_ptr(), _dt(dout2), 1, _stream(x)))
         dx = None
         grads_w = [None] * nw
         grads_b = [None] * nw
@@ -537,7 +562,7 @@ class _RowSlicedLinearN(torch.autograd.Function):
             a = _lin_args(x2, dws, dbs, slab, sw, sr, keep)
             check(lib.saf_indexed_linear_bwd_dw(C.byref(a), dout2.data_ptr(), dout2.stride(0), _stream(x)))
             grads_w, grads_b = dws, dbs
-        return (dx, None, None, *grads_w, *grads_b)
+        return (dx, None, None, None, *grads_w, *grads_b)
 
 
 class _ColPermutedLinear(torch.autograd.Function):
@@ -587,13 +612,22 @@ class _ColPermutedLinear(torch.autograd.Function):
 def linear_rows(x, weight, bias, rows):
     """Linear over a unique-row slice of `weight` (kernel/indexed_linear.py:125-128)."""
     x, weight, bias = _autocast_args(x, weight, bias)
-    return _RowSlicedLinearN.apply(x, rows, 1, weight, bias)
+    return _RowSlicedLinearN.apply(x, rows, 1, None, weight, bias)
 
 
-def linear_rows2(x, w1, w2, b1, b2, rows):
-    """(..., 2R) = [x @ w1[rows]^T + b1[rows], x @ w2[rows]^T + b2[rows]] (kernel/indexed_linear.py:131-135)."""
+def linear_rows2(x, w1, w2, b1, b2, rows, *, rope=None, head_dim=None):
+    """(..., 2R) = [x @ w1[rows]^T + b1[rows], x @ w2[rows]^T + b2[rows]] (kernel/indexed_linear.py:131-135).
+
+    Addition (keyword-only, default off): rope=(cos, sin) fp32 (T, head_dim) tables with `rows` made of whole
+    heads of `head_dim` rows: every head of the result is rotated (nanogpt/model.py:57-99) in the GEMM
+    epilogue; the backward applies the adjoint rotation to the incoming gradient first."""
     x, w1, w2, b1, b2 = _autocast_args(x, w1, w2, b1, b2)
-    return _RowSlicedLinearN.apply(x, rows, 2, w1, w2, b1, b2)
+    rp = None
+    if rope is not None:
+        if head_dim is None:
+            head_dim = rope[0].shape[-1]
+        rp = (rope[0], rope[1], x.shape[-2], head_dim)
+    return _RowSlicedLinearN.apply(x, rows, 2, rp, w1, w2, b1, b2)
 
 
 def linear_permuted_cols(y, weight, bias, cols):

@@ -137,3 +137,66 @@ def test_qkv_projection_with_rope_epilogue(cfg):
     assert out.shape == ref.shape
     a, r = errs(out, ref)
     assert r <= 5e-3 and a <= 2e-2 * max(1.0, ref.abs().max().item()), f"{a} {r}"
+
+
+@pytest.mark.parametrize("cfg", [(2, 300, 256, 4, 64, [0, 2, 3], torch.float32), (2, 300, 256, 4, 64, [0, 2, 3], torch.bfloat16),
+                                 (1, 1100, 1024, 8, 128, [0, 1, 2, 4, 5, 7], torch.bfloat16),
+                                 (2, 40, 96, 3, 32, [0, 2], torch.float32)],
+                         ids=lambda c: f"T{c[1]}C{c[2]}hd{c[4]}{'bf16' if c[6] == torch.bfloat16 else 'fp32'}")
+def test_linear_rows2_with_fused_rope(cfg):
+    """Rotation in the projection's epilogue, adjoint rotation in its backward (training path of the hook)."""
+    from kernel import linear_rows2
+    B, T, C, H, hd, live, dtype = cfg
+    dev = "cuda"
+    g = torch.Generator().manual_seed(T + C + hd)
+    x = torch.randn(B, T, C, generator=g).to(dtype)
+    w1 = (torch.randn(H * hd, C, generator=g) * 0.05).to(dtype)
+    w2 = (torch.randn(H * hd, C, generator=g) * 0.05).to(dtype)
+    rows = head_rows(live, hd)
+    cos, sin = O.rope_cache(hd, T)
+    ref_in = [t.float().clone().requires_grad_(True) for t in (x, w1, w2)]
+    U = len(live)
+    y_lin = O.linear_rows2(ref_in[0], ref_in[1], ref_in[2], None, None, rows).view(B, T, 2 * U, hd)
+    y_ref = O.apply_rope(y_lin.transpose(1, 2), cos, sin).transpose(1, 2).reshape(B, T, 2 * U * hd)
+    dev_in = [t.clone().to(dev).requires_grad_(True) for t in (x, w1, w2)]
+    y = linear_rows2(dev_in[0], dev_in[1], dev_in[2], None, None, rows.to(dev), rope=(cos.to(dev), sin.to(dev)), head_dim=hd)
+    a, r = errs(y, y_ref)
+    if dtype == torch.float32:
+        assert a <= 2e-5 * max(1.0, y_ref.abs().max().item()), f"fwd {a}"
+    else:
+        assert r <= 1e-2, f"fwd rel-l2 {r}"
+    w = torch.randn(y_ref.shape, generator=g)
+    (y.float() * w.to(dev)).sum().backward()
+    (y_ref * w).sum().backward()
+    for n, d, rf in zip(("dx", "dw1", "dw2"), dev_in, ref_in):
+        a, r = errs(d.grad, rf.grad)
+        assert r <= (1e-5 if dtype == torch.float32 else 1.5e-2), f"{n} rel-l2 {r}"
+    dead = [h for h in range(H) if h not in live]
+    dr = head_rows(dead, hd).to(dev)
+    assert dev_in[1].grad[dr].abs().max().item() == 0.0 and dev_in[2].grad[dr].abs().max().item() == 0.0
+
+
+def test_backward_products_many_tiles_bf16():
+    """dx and dW on the tensor-core kernels across several persistent tiles and ragged edges."""
+    from kernel import linear_rows2
+    B, T, C, H, hd = 3, 1500, 1096, 16, 128
+    live = [0, 1, 2, 3, 5, 6, 7, 8, 10, 11, 13, 14, 15]
+    dev = "cuda"
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(B, T, C, generator=g).bfloat16()
+    w1 = (torch.randn(H * hd, C, generator=g) * 0.05).bfloat16()
+    w2 = (torch.randn(H * hd, C, generator=g) * 0.05).bfloat16()
+    rows = head_rows(live, hd)
+    ref_in = [t.float().clone().requires_grad_(True) for t in (x, w1, w2)]
+    y_ref = O.linear_rows2(ref_in[0], ref_in[1], ref_in[2], None, None, rows)
+    dev_in = [t.clone().to(dev).requires_grad_(True) for t in (x, w1, w2)]
+    y = linear_rows2(dev_in[0], dev_in[1], dev_in[2], None, None, rows.to(dev))
+    w = torch.randn(y_ref.shape, generator=g).bfloat16().float()
+    (y.float() * w.to(dev)).sum().backward()
+    (y_ref * w).sum().backward()
+    for n, d, rf in zip(("dx", "dw1", "dw2"), dev_in, ref_in):
+        a, r = errs(d.grad, rf.grad)
+        assert r <= 1.5e-2, f"{n} rel-l2 {r}"
+    dead = [h for h in range(H) if h not in live]
+    dr = head_rows(dead, hd).to(dev)
+    assert dev_in[1].grad[dr].abs().max().item() == 0.0 and dev_in[2].grad[dr].abs().max().item() == 0.0
