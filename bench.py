@@ -228,6 +228,9 @@ def main():
         parallel.barrier()
         e2e_ms = e0.elapsed_time(e1)
 
+        # per-layer split (outside the timed regions): each piece launched alone on layer 0's tensors
+        split = synthetic.per_layer_split(layers[0], rope, x_dev) if rank == 0 else None
+
     total_ms = parallel.max_over_ranks(total_ms, dev)
     e2e_ms = parallel.max_over_ranks(e2e_ms, dev)
     tokens = parallel.sum_over_ranks(B * T, dev)
@@ -262,6 +265,7 @@ def main():
                      "launches_timed": len(attn_ms)},
         "stack": {"tflops": stack_flops / (ms_per_step * 1e-3) / 1e12, "frac_of_peak": stack_flops / (ms_per_step * 1e-3) / 1e12 / peak_tf,
                   "attention_share_of_step": sum(attn_ms) / total_ms},
+        "per_layer_ms": split,
     }
     if world == 1 and not args.no_cpu_baseline:
         tok_s, t_layer, cores, sample = cpu_reference_sample(w, 2, 1)

@@ -68,6 +68,54 @@ __device__ __forceinline__ float ex2b(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+#ifndef SAF_BWD_POLY_PER_8
+#define SAF_BWD_POLY_PER_8 0        // of every 8 exponentials, this many run on the FMA pipe
+#endif
+// 2^x on the FMA/ALU pipes for x <= 0 (clamped at -126): round to nearest integer with the magic-number
+// add, cubic minimax on the fraction, exponent added as an integer shift.  Relative error ~1e-4.
+__device__ __forceinline__ float2 exp2_poly2b(float2 x) {
+  const float magic = 12582912.f;  // 1.5 * 2^23
+  x.x = fmaxf(x.x, -126.f);
+  x.y = fmaxf(x.y, -126.f);
+  const float2 t = __fadd2_rn(x, make_float2(magic, magic));
+  const float2 n = __fadd2_rn(t, make_float2(-magic, -magic));
+  const float2 f = __fadd2_rn(x, make_float2(-n.x, -n.y));
+  float2 q = __ffma2_rn(f, make_float2(0.0555054f, 0.0555054f), make_float2(0.2402265f, 0.2402265f));
+  q = __ffma2_rn(q, f, make_float2(0.6931472f, 0.6931472f));
+  q = __ffma2_rn(q, f, make_float2(1.f, 1.f));
+  float2 r;
+  r.x = __int_as_float(__float_as_int(q.x) + (__float_as_int(t.x) << 23));
+  r.y = __int_as_float(__float_as_int(q.y) + (__float_as_int(t.y) << 23));
+  return r;
+}
+// p = 2^(s*sc - l) for four neighbouring columns; the first SAF_BWD_POLY_PER_8/2 of every four column pairs
+// (counted by `pair`) use the polynomial
+__device__ __forceinline__ void exp4(float (&o)[4], const uint32_t (&s)[4], float sc, const float4& L, int pair) {
+  const float x0 = fmaf(__uint_as_float(s[0]), sc, -L.x), x1 = fmaf(__uint_as_float(s[1]), sc, -L.y);
+  const float x2 = fmaf(__uint_as_float(s[2]), sc, -L.z), x3 = fmaf(__uint_as_float(s[3]), sc, -L.w);
+  if ((pair & 3) < SAF_BWD_POLY_PER_8 / 2) {
+    const float2 e = exp2_poly2b(make_float2(x0, x1));
+    o[0] = e.x; o[1] = e.y;
+  } else {
+    o[0] = ex2b(x0); o[1] = ex2b(x1);
+  }
+  if (((pair + 1) & 3) < SAF_BWD_POLY_PER_8 / 2) {
+    const float2 e = exp2_poly2b(make_float2(x2, x3));
+    o[2] = e.x; o[3] = e.y;
+  } else {
+    o[2] = ex2b(x2); o[3] = ex2b(x3);
+  }
+}
+// two fp32 -> packed bf16x2
+__device__ __forceinline__ uint32_t bpack(float lo, float hi) {
+#ifdef SAF_BWD_PACK_INT
+  // round half up on the integer pipe instead of the conversion unit
+  const uint32_t a = __float_as_uint(lo) + 0x8000u, b = __float_as_uint(hi) + 0x8000u;
+  return __byte_perm(a, b, 0x7632);
+#else
+  return pack_bf16(lo, hi);
+#endif
+}
 template <int N>
 __device__ __forceinline__ void breg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
 template <int N>
@@ -310,11 +358,13 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         const float4* L4 = reinterpret_cast<const float4*>(&bars->lse[st][cb + ch * 32]);
 #pragma unroll
         for (int x = 0; x < 8; ++x) {
-          const float4 L = L4[x];
-          pf[ch * 32 + x * 4 + 0] = ex2b(fmaf(__uint_as_float(s[x * 4 + 0]), sc, -L.x));
-          pf[ch * 32 + x * 4 + 1] = ex2b(fmaf(__uint_as_float(s[x * 4 + 1]), sc, -L.y));
-          pf[ch * 32 + x * 4 + 2] = ex2b(fmaf(__uint_as_float(s[x * 4 + 2]), sc, -L.z));
-          pf[ch * 32 + x * 4 + 3] = ex2b(fmaf(__uint_as_float(s[x * 4 + 3]), sc, -L.w));
+          const uint32_t s4[4] = {s[x * 4 + 0], s[x * 4 + 1], s[x * 4 + 2], s[x * 4 + 3]};
+          float o4[4];
+          exp4(o4, s4, sc, L4[x], 2 * x);
+          pf[ch * 32 + x * 4 + 0] = o4[0];
+          pf[ch * 32 + x * 4 + 1] = o4[1];
+          pf[ch * 32 + x * 4 + 2] = o4[2];
+          pf[ch * 32 + x * 4 + 3] = o4[3];
         }
         if (i == 0) {   // diagonal tile: query c sees key r only if c >= r
 #pragma unroll
@@ -323,7 +373,7 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         }
         uint32_t pk[16];
 #pragma unroll
-        for (int x = 0; x < 16; ++x) pk[x] = pack_bf16(pf[ch * 32 + 2 * x], pf[ch * 32 + 2 * x + 1]);
+        for (int x = 0; x < 16; ++x) pk[x] = bpack(pf[ch * 32 + 2 * x], pf[ch * 32 + 2 * x + 1]);
         tmem_st16(tS + cb + ch * 16, pk);
       }
       tmem_st_wait();
@@ -350,8 +400,8 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
           const float d1 = pf[ch * 32 + x * 4 + 1] * (__uint_as_float(d[x * 4 + 1]) - D.y);
           const float d2 = pf[ch * 32 + x * 4 + 2] * (__uint_as_float(d[x * 4 + 2]) - D.z);
           const float d3 = pf[ch * 32 + x * 4 + 3] * (__uint_as_float(d[x * 4 + 3]) - D.w);
-          pk[2 * x] = pack_bf16(d0, d1);
-          pk[2 * x + 1] = pack_bf16(d2, d3);
+          pk[2 * x] = bpack(d0, d1);
+          pk[2 * x + 1] = bpack(d2, d3);
         }
         tmem_st16(tdP + cb + ch * 16, pk);
       }
@@ -525,7 +575,15 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_const
         tmem_ld32(tS + cb + ch * 32, s);
         tmem_ld_wait();
 #pragma unroll
-        for (int x = 0; x < 32; ++x) pf[ch * 32 + x] = ex2b(fmaf(__uint_as_float(s[x]), sc, -lse_r));
+        for (int x = 0; x < 8; ++x) {
+          const uint32_t s4[4] = {s[x * 4 + 0], s[x * 4 + 1], s[x * 4 + 2], s[x * 4 + 3]};
+          float o4[4];
+          exp4(o4, s4, sc, make_float4(lse_r, lse_r, lse_r, lse_r), 2 * x);
+          pf[ch * 32 + x * 4 + 0] = o4[0];
+          pf[ch * 32 + x * 4 + 1] = o4[1];
+          pf[ch * 32 + x * 4 + 2] = o4[2];
+          pf[ch * 32 + x * 4 + 3] = o4[3];
+        }
         if (j == n - 1) {   // diagonal tile: keys after the row do not count
 #pragma unroll
           for (int x = 0; x < 32; ++x)
@@ -546,8 +604,8 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_const
         uint32_t pk[16];
 #pragma unroll
         for (int x = 0; x < 16; ++x)
-          pk[x] = pack_bf16(pf[ch * 32 + 2 * x] * (__uint_as_float(d[2 * x]) - dl_r),
-                            pf[ch * 32 + 2 * x + 1] * (__uint_as_float(d[2 * x + 1]) - dl_r));
+          pk[x] = bpack(pf[ch * 32 + 2 * x] * (__uint_as_float(d[2 * x]) - dl_r),
+                        pf[ch * 32 + 2 * x + 1] * (__uint_as_float(d[2 * x + 1]) - dl_r));
         tmem_st16(tdP + cb + ch * 16, pk);
       }
       tmem_st_wait();

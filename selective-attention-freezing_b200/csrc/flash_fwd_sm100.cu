@@ -44,7 +44,7 @@ constexpr int HEAD_GROUP = 8;
 constexpr float LOG2E_F = 1.4426950408889634f;
 constexpr float RESCALE_THRESHOLD = 8.0f;
 #ifndef SAF_POLY_EXP_PER_16
-#define SAF_POLY_EXP_PER_16 4       // of every 16 exponentials, this many run on the FMA pipe
+#define SAF_POLY_EXP_PER_16 8       // of every 16 exponentials, this many run on the FMA pipe
 #endif
 
 template <int HD>

@@ -173,6 +173,42 @@ __global__ void rope_slabs_kernel(T* __restrict__ out, int64_t ldo, int M, int n
   }
 }
 
+// bf16, 16-byte accesses: one thread rotates 8 pairs (d .. d+7, d+half .. d+half+7) of one slab of one row
+__global__ void __launch_bounds__(256) rope_slabs_vec_kernel(__nv_bfloat16* __restrict__ out, int64_t ldo, int M, int n_slabs,
+                                                             int slab, int Tlen, const float* __restrict__ cosT,
+                                                             const float* __restrict__ sinT,
+                                                             const __grid_constant__ SlabTable tb, float sgn) {
+  const int half = slab >> 1, per_slab = half >> 3;
+  const int64_t total = (int64_t)M * n_slabs * per_slab;
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
+    const int d = (int)(idx % per_slab) * 8;
+    const int g = (int)((idx / per_slab) % n_slabs);
+    const int64_t m = idx / ((int64_t)per_slab * n_slabs);
+    if (!tb.rope[g]) continue;
+    const int t = (int)(m % Tlen);
+    __nv_bfloat16* p = out + m * ldo + (int64_t)g * slab + d;
+    uint4 lo = *reinterpret_cast<const uint4*>(p), hi = *reinterpret_cast<const uint4*>(p + half);
+    const float4* c4 = reinterpret_cast<const float4*>(cosT + (int64_t)t * slab + d);
+    const float4* s4 = reinterpret_cast<const float4*>(sinT + (int64_t)t * slab + d);
+    const float4 ca = c4[0], cb = c4[1], sa = s4[0], sb = s4[1];
+    const float cc[8] = {ca.x, ca.y, ca.z, ca.w, cb.x, cb.y, cb.z, cb.w};
+    const float ss[8] = {sa.x, sa.y, sa.z, sa.w, sb.x, sb.y, sb.z, sb.w};
+    uint32_t lw[4] = {lo.x, lo.y, lo.z, lo.w}, hw[4] = {hi.x, hi.y, hi.z, hi.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float x1a = __uint_as_float(lw[e] << 16), x1b = __uint_as_float(lw[e] & 0xffff0000u);
+      const float x2a = __uint_as_float(hw[e] << 16), x2b = __uint_as_float(hw[e] & 0xffff0000u);
+      const float sA = sgn * ss[2 * e], sB = sgn * ss[2 * e + 1];   // the tables repeat per half
+      const __nv_bfloat162 l2 = __floats2bfloat162_rn(x1a * cc[2 * e] - x2a * sA, x1b * cc[2 * e + 1] - x2b * sB);
+      const __nv_bfloat162 h2 = __floats2bfloat162_rn(x2a * cc[2 * e] + x1a * sA, x2b * cc[2 * e + 1] + x1b * sB);
+      lw[e] = *reinterpret_cast<const uint32_t*>(&l2);
+      hw[e] = *reinterpret_cast<const uint32_t*>(&h2);
+    }
+    *reinterpret_cast<uint4*>(p) = make_uint4(lw[0], lw[1], lw[2], lw[3]);
+    *reinterpret_cast<uint4*>(p + half) = make_uint4(hw[0], hw[1], hw[2], hw[3]);
+  }
+}
+
 int fill_tables(const SafIndexedLinearArgs& a, WeightSet* ws, SlabTable* tb) {
   if (a.n_slabs > MAX_SLABS) return fail(SAF_ERR_LIMIT, "n_slabs %d exceeds the limit of %d", a.n_slabs, MAX_SLABS);
   memset(ws, 0, sizeof(*ws));
@@ -296,7 +332,13 @@ int launch_rope_slabs(void* x, int64_t ld, int M, int n_slabs, int slab, int T, 
   const int64_t total = (int64_t)M * n_slabs * (slab / 2);
   const int blocks = (int)std::min<int64_t>((total + 255) / 256, 148 * 16);
   const float sgn = inverse ? -1.f : 1.f;
-  if (dtype == SAF_F32)
+  const bool vec = dtype == SAF_BF16 && slab % 16 == 0 && ld % 8 == 0 && ((uintptr_t)x & 15) == 0 &&
+                   ((uintptr_t)cosT & 15) == 0 && ((uintptr_t)sinT & 15) == 0;
+  if (vec) {
+    const int64_t tv = (int64_t)M * n_slabs * (slab / 16);
+    const int bv = (int)std::min<int64_t>((tv + 255) / 256, 148 * 32);
+    rope_slabs_vec_kernel<<<bv, 256, 0, st>>>(reinterpret_cast<__nv_bfloat16*>(x), ld, M, n_slabs, slab, T, cosT, sinT, tb, sgn);
+  } else if (dtype == SAF_F32)
     rope_slabs_kernel<float><<<blocks, 256, 0, st>>>(reinterpret_cast<float*>(x), ld, M, n_slabs, slab, T, cosT, sinT, tb, sgn);
   else
     rope_slabs_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(reinterpret_cast<__nv_bfloat16*>(x), ld, M, n_slabs, slab, T,

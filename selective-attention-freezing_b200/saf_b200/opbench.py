@@ -1,0 +1,142 @@
+"""Operator timings on the benchmark shapes: each operator of the hot path, forward and backward, launched
+alone on seeded synthetic tensors and timed with CUDA events (median).  The counterpart of the reference's
+per-operator probes (qwen/nanogpt/bench_qwen_prefill_triton.py:186-225); also the command the ncu captures
+of single kernels are taken from.
+
+    python -m saf_b200.opbench --workload c3 --ops attn_fwd,attn_bwd,qk_fwd,qk_bwd [--B 2 --T 8192] [--reps 5]
+
+Prints one JSON line per operator: ms, algorithmic TFLOP/s (backward counted as 2.5x / 2x the forward
+FLOPs, as the reference's roofline does) and the library launches of one call.
+"""
+import argparse
+import json
+import os
+import sys
+
+import torch
+
+if __package__ in (None, ""):
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from saf_b200 import ops, synthetic  # noqa: E402
+
+
+def _timed(fn, reps):
+    for _ in range(2):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(reps):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        ts.append(a.elapsed_time(b))
+    return sorted(ts)[len(ts) // 2]
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--workload", default="c3")
+    ap.add_argument("--ops", default="attn_fwd,attn_bwd,qk_fwd,qk_bwd")
+    ap.add_argument("--B", type=int, default=None)
+    ap.add_argument("--T", type=int, default=None)
+    ap.add_argument("--reps", type=int, default=5)
+    ap.add_argument("--frozen", default="sink_decay", choices=["sink_decay", "dense", "none"])
+    args = ap.parse_args()
+    w = dict(synthetic.WORKLOADS[args.workload])
+    if args.B:
+        w["B"] = args.B
+    if args.T:
+        w["T"] = args.T
+    dev = torch.device("cuda")
+    B, T, H, hd, nf = w["B"], w["T"], w["n_head"], w["head_dim"], w["n_frozen"]
+    if args.frozen == "none":
+        nf = 0
+    C, U = H * hd, H - nf
+    fz = synthetic.frozen_heads_for_layer(H, nf, 1337, 0) if nf else []
+    live = [h for h in range(H) if h not in fz]
+    g = torch.Generator().manual_seed(7)
+    state = 3 if args.frozen == "sink_decay" else 1
+    frozen = torch.tensor([state if h in fz else 0 for h in range(H)], dtype=torch.int32, device=dev)
+    hidx = torch.zeros(H, dtype=torch.int32)
+    for s, h in enumerate(live):
+        hidx[h] = s
+    hidx = hidx.to(dev)
+    q = torch.randn(B, U, T, hd, generator=g).bfloat16().to(dev).requires_grad_(True)
+    k = torch.randn(B, U, T, hd, generator=g).bfloat16().to(dev).requires_grad_(True)
+    v = torch.randn(B, H, T, hd, generator=g).bfloat16().to(dev).requires_grad_(True)
+    dy = torch.randn(B, H, T, hd, generator=g).bfloat16().to(dev)
+    kw, patt = {}, None
+    if nf and args.frozen == "sink_decay":
+        a, r = synthetic.sink_decay_params(H, 2337)
+        kw["sink_decay"] = (a.float().to(dev), r.float().to(dev))
+    elif nf:
+        p = torch.rand(nf, T, T, generator=g).tril_()
+        patt = (p / p.sum(-1, keepdim=True)).bfloat16().to(dev)
+        pidx = torch.zeros(H, dtype=torch.int32)
+        for s, h in enumerate(fz):
+            pidx[h] = s
+        kw["pidx"] = pidx.to(dev)
+    x = torch.randn(B, T, C, generator=g).bfloat16().to(dev).requires_grad_(True)
+    w1 = (torch.randn(C, C, generator=g) * 0.02).bfloat16().to(dev).requires_grad_(True)
+    w2 = (torch.randn(C, C, generator=g) * 0.02).bfloat16().to(dev).requires_grad_(True)
+    rows = (torch.tensor(live)[:, None] * hd + torch.arange(hd)).reshape(-1).to(dev)
+    cos, sin = synthetic.rope_tables(hd, T, base=w["rope_base"], device=dev)
+    dqk = torch.randn(B, T, 2 * U * hd, generator=g).bfloat16().to(dev)
+
+    def attn():
+        return ops.fused_mixed_attn(q, k, v, patt, frozen, hidx, validate=False, **kw)
+
+    def qk():
+        return ops.linear_rows2(x, w1, w2, None, None, rows, rope=(cos, sin), head_dim=hd)
+
+    fl_attn = 2.0 * B * U * T * T * hd
+    fl_qk = 2.0 * B * T * C * 2 * U * hd
+    shape = f"B{B} T{T} H{H} hd{hd} live{U} frozen{nf}({args.frozen})"
+    for op in args.ops.split(","):
+        if op == "attn_fwd":
+            with torch.no_grad():
+                n0 = ops.launch_count()
+                attn()
+                n = ops.launch_count() - n0
+                ms = _timed(attn, args.reps)
+            fl = fl_attn
+        elif op == "attn_bwd":
+            y = attn()
+            n0 = ops.launch_count()
+            y.backward(dy, retain_graph=True)
+            n = ops.launch_count() - n0
+
+            def run():
+                q.grad = k.grad = v.grad = None
+                y.backward(dy, retain_graph=True)
+            ms = _timed(run, args.reps)
+            fl = 2.5 * fl_attn
+        elif op == "qk_fwd":
+            with torch.no_grad():
+                n0 = ops.launch_count()
+                qk()
+                n = ops.launch_count() - n0
+                ms = _timed(qk, args.reps)
+            fl = fl_qk
+        elif op == "qk_bwd":
+            y = qk()
+            n0 = ops.launch_count()
+            y.backward(dqk, retain_graph=True)
+            n = ops.launch_count() - n0
+
+            def run():
+                x.grad = w1.grad = w2.grad = None
+                y.backward(dqk, retain_graph=True)
+            ms = _timed(run, args.reps)
+            fl = 2.0 * fl_qk
+        else:
+            raise SystemExit("unknown op %r" % op)
+        print(json.dumps({"op": op, "shape": shape, "ms": round(ms, 4), "tflops": round(fl / ms / 1e9, 1),
+                          "launches": n}), flush=True)
+
+
+if __name__ == "__main__":
+    main()

@@ -68,3 +68,55 @@ def hot_stack_flops(w):
     qkv = 2 * T * C * (2 * U + H) * hd
     oproj = 2 * T * C * C
     return dict(live=live * w["n_layer"], qkv=qkv * w["n_layer"], oproj=oproj * w["n_layer"])
+
+
+def per_layer_split(m, rope, x, reps=5):
+    """Device time (ms, median of `reps`, CUDA events) of the pieces of one layer's hot path on input x:
+    the fused projection, the mixed-attention launch, and -- each launched alone on the same tensors --
+    the live heads only and the frozen heads only, then c_proj.  bf16 inference path."""
+    from . import ops
+    B, T, C = x.shape
+    nh, hd = m.n_head, m.head_dim
+    if m._fz_dirty:
+        m._refresh_freeze_cache()
+    live = list(m._live)
+    nuf = len(live)
+    fz = [h for h in range(nh) if h not in live]
+    rp = m._rope_f32(rope, T, x.device)
+
+    def timed(fn):
+        for _ in range(2):
+            out = fn()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(reps):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            out = fn()
+            b.record()
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b))
+        return sorted(ts)[len(ts) // 2], out
+
+    with torch.inference_mode():
+        w = [m.q_proj.weight, m.k_proj.weight, m.v_proj.weight]
+        t_qkv, qkv = timed(lambda: ops.qkv_projection(x, w[0], w[1], w[2], live, hd, rope=rp, T=T))
+        qkv = qkv.view(B, T, 2 * nuf + nh, hd)
+        qu, ku = qkv[:, :, :nuf].transpose(1, 2), qkv[:, :, nuf:2 * nuf].transpose(1, 2)
+        v = qkv[:, :, 2 * nuf:].transpose(1, 2)
+        t_mixed, y = timed(lambda: ops.fused_mixed_attn(qu, ku, v, None, m._fz_mask_i32, m._hidx_i32, validate=False,
+                                                        sink_decay=m._sd))
+        out = {"qkv_rope_gemm": t_qkv, "mixed_attention": t_mixed}
+        if nuf:
+            zeros = torch.zeros(nuf, dtype=torch.int32, device=x.device)
+            v_live = qkv[:, :, [2 * nuf + h for h in live]].transpose(1, 2)
+            out["live_heads_alone"], _ = timed(lambda: ops.fused_mixed_attn(qu, ku, v_live, None, zeros, validate=False))
+        if fz:
+            sd = m._sd
+            idx = torch.tensor(fz, device=x.device)
+            v_fz = qkv[:, :, [2 * nuf + h for h in fz]].transpose(1, 2)
+            a_fz, r_fz = sd[0][idx].contiguous(), sd[1][idx].contiguous()
+            out["frozen_heads_alone"], _ = timed(lambda: ops.frozen_pv(None, v_fz, None, T, sink_decay=(a_fz, r_fz)))
+        y2 = y.transpose(1, 2).reshape(B, T, nh * hd)
+        out["c_proj_gemm"], _ = timed(lambda: ops.linear_rows(y2, m.c_proj.weight, None, m._all_rows))
+    return out
