@@ -25,6 +25,7 @@
 // The sm_scale factor of dS is applied once to the finished dK / dQ accumulators.
 // Every wait is bounded; on expiry the kernel records a code in *status and falls through.
 #include "saf_internal.h"
+#include "scan_body.cuh"
 #include "sm100_prims.cuh"
 
 namespace saf {
@@ -34,11 +35,22 @@ constexpr int BWD_THREADS = 384;
 constexpr int BWD_HEAD_GROUP = 8;
 constexpr float LOG2E_B = 1.4426950408889634f;
 
+#ifdef SAF_BWD_TRACE
+// timing probe (only in specially built libraries): clock64 stamps of one CTA's pipeline events
+__device__ long long g_trace[2][8][64];   // [kernel][event][tile]
+#define TRACE(kern, evt, tile) do { if (trace_on && (tile) < 64) g_trace[kern][evt][tile] = clock64(); } while (0)
+#else
+#define TRACE(kern, evt, tile) do { } while (0)
+#endif
+
 template <int HD>
 struct BwdCfg {
   static constexpr int TILE_BYTES = 128 * HD * 2;
-  static constexpr int NSTAGE = (HD == 64) ? 3 : 2;   // ring of streamed tile pairs
+  static constexpr int NSTAGE = (HD == 64) ? 3 : 2;   // dK/dV kernel: ring of streamed (Q_i, dO_i) pairs
+  static constexpr int KS = 3;                        // dQ kernel: K ring (a K tile lives until its dQ product)
+  static constexpr int VS = (HD == 64) ? 3 : 2;       // dQ kernel: V ring (a V tile is done after its dP product)
   static constexpr int SMEM_BYTES = 1024 + 2 * TILE_BYTES + NSTAGE * 2 * TILE_BYTES + 4096;
+  static constexpr int SMEM_BYTES_DQ = 1024 + 2 * TILE_BYTES + (KS + VS) * TILE_BYTES + 512;
   static constexpr int TMEM_COLS = 512;
 };
 
@@ -52,14 +64,22 @@ struct BwdParams {
   float* delta;
   int64_t delta_s[3];
   int* status;
+  // structured frozen heads: their reverse scan (dV = P^T dO) runs in the leading CTAs of the dK/dV launch
+  int scan_slots;
+  ScanArgs scan;
 };
 
 struct BwdBars {
   uint64_t res_full;                    // the two resident tiles
   uint64_t ring_full[3], ring_empty[3];
+  uint64_t v_full[3], v_empty[3];       // dQ kernel: the V ring (ring_* is its K ring)
   uint64_t s_full[2], dp_full, p_full, ds_full, acc_full;
   uint32_t tmem_base;
-  alignas(16) float lse[2][128];        // dK/dV kernel: lse and delta of the current query tile (read as float4)
+};
+static_assert(sizeof(BwdBars) <= 256, "barrier block");
+// dK/dV kernel only, placed 256 bytes after the barriers: lse and delta of the current query tile (read as float4)
+struct BwdVectors {
+  alignas(16) float lse[2][128];
   alignas(16) float dl[2][128];
 };
 
@@ -69,7 +89,7 @@ __device__ __forceinline__ float ex2b(float x) {
   return y;
 }
 #ifndef SAF_BWD_POLY_PER_8
-#define SAF_BWD_POLY_PER_8 0        // of every 8 exponentials, this many run on the FMA pipe
+#define SAF_BWD_POLY_PER_8 4        // of every 8 exponentials, this many run on the FMA pipe
 #endif
 // 2^x on the FMA/ALU pipes for x <= 0 (clamped at -126): round to nearest integer with the magic-number
 // add, cubic minimax on the fraction, exponent added as an integer shift.  Relative error ~1e-4.
@@ -162,12 +182,12 @@ __device__ __forceinline__ void stage_cols(uint8_t* stage, const uint32_t (&o)[3
 
 // CTA -> (batch, head, tile), heads in groups so CTAs in flight share their streamed tiles in L2,
 // heaviest tiles first inside a group.  Returns false when the CTA has nothing to do.
-__device__ __forceinline__ bool bwd_cta_coords(const BwdParams& p, bool heavy_is_low, int& b, int& h, int& tile) {
+__device__ __forceinline__ bool bwd_cta_coords(const BwdParams& p, int cta, bool heavy_is_low, int& b, int& h, int& tile) {
   const int bh_count = p.B * p.H;
   const int per_group = BWD_HEAD_GROUP * p.n_tiles;
-  const int grp = blockIdx.x / per_group;
+  const int grp = cta / per_group;
   const int gsize = min(BWD_HEAD_GROUP, bh_count - grp * BWD_HEAD_GROUP);
-  const int rem = blockIdx.x - grp * per_group;
+  const int rem = cta - grp * per_group;
   if (rem >= gsize * p.n_tiles) return false;
   const int t = rem / gsize;
   tile = heavy_is_low ? t : p.n_tiles - 1 - t;
@@ -185,6 +205,8 @@ __device__ __forceinline__ void bwd_setup(BwdBars* bars, int tid, int warp) {
     for (int s = 0; s < 3; ++s) {
       mbar_init(&bars->ring_full[s], 1);
       mbar_init(&bars->ring_empty[s], 1);
+      mbar_init(&bars->v_full[s], 1);
+      mbar_init(&bars->v_empty[s], 1);
     }
     mbar_init(&bars->s_full[0], 1);
     mbar_init(&bars->s_full[1], 1);
@@ -213,8 +235,17 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
                       const __grid_constant__ CUtensorMap mapdK, const __grid_constant__ CUtensorMap mapdV,
                       const __grid_constant__ BwdParams p) {
   using C = BwdCfg<HD>;
+  if ((int)blockIdx.x < p.scan_slots) {
+    // ---- reverse scan of a structured frozen head: one slot per (batch, head, 64-column slice)
+    constexpr int PER = HD / SCAN_COLS;
+    const int bh = blockIdx.x / PER, col0 = (blockIdx.x % PER) * SCAN_COLS;
+    const int sb = bh / p.H, sh = bh % p.H;
+    const int state = p.force_state >= 0 ? p.force_state : p.frozen[sh];
+    if (state == SAF_SINK_DECAY && threadIdx.x < SCAN_NT) sink_decay_scan_cta<__nv_bfloat16, true>(p.scan, sb, sh, col0);
+    return;
+  }
   int b, h, jt;
-  if (!bwd_cta_coords(p, true, b, h, jt)) return;
+  if (!bwd_cta_coords(p, (int)blockIdx.x - p.scan_slots, true, b, h, jt)) return;
   const int hq = p.hidx ? p.hidx[h] : h;
   const int n = p.n_tiles - jt;            // query tiles jt .. n_tiles-1
   const int j0 = jt * 128;
@@ -225,10 +256,14 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
   uint8_t* sV = smem + C::TILE_BYTES;
   uint8_t* ring = smem + 2 * C::TILE_BYTES;           // stage s: [Q_i | dO_i]
   BwdBars* bars = reinterpret_cast<BwdBars*>(ring + C::NSTAGE * 2 * C::TILE_BYTES);
+  BwdVectors* vec = reinterpret_cast<BwdVectors*>(reinterpret_cast<uint8_t*>(bars) + 256);
   const int tid = threadIdx.x, warp = tid >> 5;
   bwd_setup<HD>(bars, tid, warp);
   const uint32_t tmem = bars->tmem_base;
   constexpr uint32_t COL_S = 0, COL_DP = 128, COL_DV = 256, COL_DK = 256 + HD;
+#ifdef SAF_BWD_TRACE
+  const bool trace_on = (b == 0 && h == 0 && jt == 0) && (tid == 0 || tid == 9 * 32);
+#endif
 
   if (warp >= 8) {
     breg_dec<56>();
@@ -243,16 +278,24 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         mbar_expect_tx(&bars->res_full, 2 * C::TILE_BYTES);
         bload_tile<HD>(sK, &mapK, &bars->res_full, j0, hq, b);
         bload_tile<HD>(sV, &mapV, &bars->res_full, j0, h, b);
+        // stage s holds [Q_i | dO_i]; the two halves are loaded and released separately: dO_i is done after
+        // the dV product, Q_i only after the dK product, and S(i+1) must not wait for dO_{i+1}
         for (int i = 0; i < n; ++i) {
           const int s = i % C::NSTAGE;
-          if (!mbar_wait(&bars->ring_empty[s], ((i / C::NSTAGE) & 1) ^ 1)) {
+          const uint32_t ph = ((i / C::NSTAGE) & 1) ^ 1;
+          uint8_t* dst = ring + s * 2 * C::TILE_BYTES;
+          if (!mbar_wait(&bars->v_empty[s], ph)) {
             dev_set_error(p.status, SAF_DEV_TIMEOUT_TMA, 40);
             break;
           }
-          uint8_t* dst = ring + s * 2 * C::TILE_BYTES;
-          mbar_expect_tx(&bars->ring_full[s], 2 * C::TILE_BYTES);
+          mbar_expect_tx(&bars->v_full[s], C::TILE_BYTES);
+          bload_tile<HD>(dst + C::TILE_BYTES, &mapdO, &bars->v_full[s], (jt + i) * 128, h, b);
+          if (!mbar_wait(&bars->ring_empty[s], ph)) {
+            dev_set_error(p.status, SAF_DEV_TIMEOUT_TMA, 49);
+            break;
+          }
+          mbar_expect_tx(&bars->ring_full[s], C::TILE_BYTES);
           bload_tile<HD>(dst, &mapQ, &bars->ring_full[s], (jt + i) * 128, hq, b);
-          bload_tile<HD>(dst + C::TILE_BYTES, &mapdO, &bars->ring_full[s], (jt + i) * 128, h, b);
         }
       }
     } else if (warp == 9) {
@@ -266,7 +309,7 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         const int s = i % C::NSTAGE;
         const uint32_t aQ = aR + s * 2 * C::TILE_BYTES, adO = aQ + C::TILE_BYTES;
         if (i == 0) {
-          if (!mbar_wait(&bars->ring_full[0], 0)) {
+          if (!mbar_wait(&bars->ring_full[0], 0) || !mbar_wait(&bars->v_full[0], 0)) {
             dev_set_error(p.status, SAF_DEV_TIMEOUT_MMA, 42);
             break;
           }
@@ -284,7 +327,11 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
           break;
         }
         tc_fence_after();
-        if (leader) issue_ts(tmem + COL_DV, tmem + COL_S, adO, idesc_o, i > 0);
+        TRACE(0, 4, i);   // issuer saw p_full
+        if (leader) {
+          issue_ts(tmem + COL_DV, tmem + COL_S, adO, idesc_o, i > 0);
+          umma_commit(&bars->v_empty[s]);                 // dO_i is not read again
+        }
         __syncwarp();
         const int s2 = (i + 1) % C::NSTAGE;
         const uint32_t aQ2 = aR + s2 * 2 * C::TILE_BYTES, adO2 = aQ2 + C::TILE_BYTES;
@@ -305,15 +352,24 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
           break;
         }
         tc_fence_after();
+        TRACE(0, 5, i);   // issuer saw ds_full
         if (leader) {
           issue_ts(tmem + COL_DK, tmem + COL_DP, aQ, idesc_o, i > 0);
-          umma_commit(&bars->ring_empty[s]);
-          if (i + 1 < n) {
+          umma_commit(&bars->ring_empty[s]);              // Q_i is not read again
+        }
+        __syncwarp();
+        if (i + 1 < n) {
+          if (!mbar_wait(&bars->v_full[s2], ((i + 1) / C::NSTAGE) & 1)) {
+            dev_set_error(p.status, SAF_DEV_TIMEOUT_MMA, 59);
+            break;
+          }
+          tc_fence_after();
+          if (leader) {
             issue_ss<HD>(tmem + COL_DP, aV, adO2, idesc_s);  // ordered behind the dK product that read dS^T
             umma_commit(&bars->dp_full);
           }
+          __syncwarp();
         }
-        __syncwarp();
       }
       if (leader) umma_commit(&bars->acc_full);
       __syncwarp();
@@ -338,8 +394,8 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
     bool ok = true;
     for (int i = 0; i < n; ++i) {
       const int st = i & 1;
-      if (tid < 128) bars->lse[st][r] = nxt;
-      else bars->dl[st][r] = nxt;
+      if (tid < 128) vec->lse[st][r] = nxt;
+      else vec->dl[st][r] = nxt;
       named_bar_sync(1, 256);
       if (i + 1 < n) nxt = fetch(jt + i + 1);
       // ---- P^T
@@ -349,36 +405,42 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         break;
       }
       tc_fence_after();
+      TRACE(0, 0, i);   // scores visible
       float pf[64];
-#pragma unroll
-      for (int ch = 0; ch < 2; ++ch) {
-        uint32_t s[32];
-        tmem_ld32(tS + cb + ch * 32, s);
+      {
+        // both 32-column halves are requested before the single wait: one TMEM round trip per phase
+        uint32_t s[2][32];
+        tmem_ld32(tS + cb, s[0]);
+        tmem_ld32(tS + cb + 32, s[1]);
         tmem_ld_wait();
-        const float4* L4 = reinterpret_cast<const float4*>(&bars->lse[st][cb + ch * 32]);
 #pragma unroll
-        for (int x = 0; x < 8; ++x) {
-          const uint32_t s4[4] = {s[x * 4 + 0], s[x * 4 + 1], s[x * 4 + 2], s[x * 4 + 3]};
-          float o4[4];
-          exp4(o4, s4, sc, L4[x], 2 * x);
-          pf[ch * 32 + x * 4 + 0] = o4[0];
-          pf[ch * 32 + x * 4 + 1] = o4[1];
-          pf[ch * 32 + x * 4 + 2] = o4[2];
-          pf[ch * 32 + x * 4 + 3] = o4[3];
+        for (int ch = 0; ch < 2; ++ch) {
+          const float4* L4 = reinterpret_cast<const float4*>(&vec->lse[st][cb + ch * 32]);
+#pragma unroll
+          for (int x = 0; x < 8; ++x) {
+            const uint32_t s4[4] = {s[ch][x * 4 + 0], s[ch][x * 4 + 1], s[ch][x * 4 + 2], s[ch][x * 4 + 3]};
+            float o4[4];
+            exp4(o4, s4, sc, L4[x], 2 * x);
+            pf[ch * 32 + x * 4 + 0] = o4[0];
+            pf[ch * 32 + x * 4 + 1] = o4[1];
+            pf[ch * 32 + x * 4 + 2] = o4[2];
+            pf[ch * 32 + x * 4 + 3] = o4[3];
+          }
+          if (i == 0) {   // diagonal tile: query c sees key r only if c >= r
+#pragma unroll
+            for (int x = 0; x < 32; ++x)
+              if (cb + ch * 32 + x < r) pf[ch * 32 + x] = 0.f;
+          }
+          uint32_t pk[16];
+#pragma unroll
+          for (int x = 0; x < 16; ++x) pk[x] = bpack(pf[ch * 32 + 2 * x], pf[ch * 32 + 2 * x + 1]);
+          tmem_st16(tS + cb + ch * 16, pk);
         }
-        if (i == 0) {   // diagonal tile: query c sees key r only if c >= r
-#pragma unroll
-          for (int x = 0; x < 32; ++x)
-            if (cb + ch * 32 + x < r) pf[ch * 32 + x] = 0.f;
-        }
-        uint32_t pk[16];
-#pragma unroll
-        for (int x = 0; x < 16; ++x) pk[x] = bpack(pf[ch * 32 + 2 * x], pf[ch * 32 + 2 * x + 1]);
-        tmem_st16(tS + cb + ch * 16, pk);
       }
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(&bars->p_full);
+      TRACE(0, 1, i);   // P^T handed over
       // ---- dS^T
       if (!mbar_wait(&bars->dp_full, i & 1)) {
         dev_set_error(p.status, SAF_DEV_TIMEOUT_SOFTMAX, 47);
@@ -386,28 +448,33 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         break;
       }
       tc_fence_after();
-#pragma unroll
-      for (int ch = 0; ch < 2; ++ch) {
-        uint32_t d[32];
-        tmem_ld32(tdP + cb + ch * 32, d);
+      TRACE(0, 2, i);   // dP^T visible
+      {
+        uint32_t d[2][32];
+        tmem_ld32(tdP + cb, d[0]);
+        tmem_ld32(tdP + cb + 32, d[1]);
         tmem_ld_wait();
-        const float4* D4 = reinterpret_cast<const float4*>(&bars->dl[st][cb + ch * 32]);
-        uint32_t pk[16];
 #pragma unroll
-        for (int x = 0; x < 8; ++x) {
-          const float4 D = D4[x];
-          const float d0 = pf[ch * 32 + x * 4 + 0] * (__uint_as_float(d[x * 4 + 0]) - D.x);
-          const float d1 = pf[ch * 32 + x * 4 + 1] * (__uint_as_float(d[x * 4 + 1]) - D.y);
-          const float d2 = pf[ch * 32 + x * 4 + 2] * (__uint_as_float(d[x * 4 + 2]) - D.z);
-          const float d3 = pf[ch * 32 + x * 4 + 3] * (__uint_as_float(d[x * 4 + 3]) - D.w);
-          pk[2 * x] = bpack(d0, d1);
-          pk[2 * x + 1] = bpack(d2, d3);
+        for (int ch = 0; ch < 2; ++ch) {
+          const float4* D4 = reinterpret_cast<const float4*>(&vec->dl[st][cb + ch * 32]);
+          uint32_t pk[16];
+#pragma unroll
+          for (int x = 0; x < 8; ++x) {
+            const float4 D = D4[x];
+            const float d0 = pf[ch * 32 + x * 4 + 0] * (__uint_as_float(d[ch][x * 4 + 0]) - D.x);
+            const float d1 = pf[ch * 32 + x * 4 + 1] * (__uint_as_float(d[ch][x * 4 + 1]) - D.y);
+            const float d2 = pf[ch * 32 + x * 4 + 2] * (__uint_as_float(d[ch][x * 4 + 2]) - D.z);
+            const float d3 = pf[ch * 32 + x * 4 + 3] * (__uint_as_float(d[ch][x * 4 + 3]) - D.w);
+            pk[2 * x] = bpack(d0, d1);
+            pk[2 * x + 1] = bpack(d2, d3);
+          }
+          tmem_st16(tdP + cb + ch * 16, pk);
         }
-        tmem_st16(tdP + cb + ch * 16, pk);
       }
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(&bars->ds_full);
+      TRACE(0, 3, i);   // dS^T handed over
     }
     // ---- epilogue: dV_j, dK_j -> bf16 -> swizzled staging (the K / V tiles are no longer read) -> TMA store
     if (ok && !mbar_wait(&bars->acc_full, 0)) {
@@ -452,7 +519,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_const
                     const __grid_constant__ CUtensorMap mapdQ, const __grid_constant__ BwdParams p) {
   using C = BwdCfg<HD>;
   int b, h, it;
-  if (!bwd_cta_coords(p, false, b, h, it)) return;
+  if (!bwd_cta_coords(p, (int)blockIdx.x, false, b, h, it)) return;
   const int hq = p.hidx ? p.hidx[h] : h;
   const int n = it + 1;                    // key tiles 0 .. it
   const int i0 = it * 128;
@@ -461,12 +528,16 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_const
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* sQ = smem;
   uint8_t* sdO = smem + C::TILE_BYTES;
-  uint8_t* ring = smem + 2 * C::TILE_BYTES;           // stage s: [K_j | V_j]
-  BwdBars* bars = reinterpret_cast<BwdBars*>(ring + C::NSTAGE * 2 * C::TILE_BYTES);
+  uint8_t* ringK = smem + 2 * C::TILE_BYTES;          // K_j ring, KS tiles
+  uint8_t* ringV = ringK + C::KS * C::TILE_BYTES;     // V_j ring, VS tiles
+  BwdBars* bars = reinterpret_cast<BwdBars*>(ringV + C::VS * C::TILE_BYTES);
   const int tid = threadIdx.x, warp = tid >> 5;
   bwd_setup<HD>(bars, tid, warp);
   const uint32_t tmem = bars->tmem_base;
   constexpr uint32_t COL_S = 0 /* two buffers */, COL_DP = 256, COL_DQ = 384;
+#ifdef SAF_BWD_TRACE
+  const bool trace_on = (b == 0 && h == 0 && it == p.n_tiles - 1) && (tid == 0 || tid == 9 * 32);
+#endif
 
   if (warp >= 8) {
     breg_dec<56>();
@@ -482,64 +553,76 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_const
         bload_tile<HD>(sQ, &mapQ, &bars->res_full, i0, hq, b);
         bload_tile<HD>(sdO, &mapdO, &bars->res_full, i0, h, b);
         for (int j = 0; j < n; ++j) {
-          const int s = j % C::NSTAGE;
-          if (!mbar_wait(&bars->ring_empty[s], ((j / C::NSTAGE) & 1) ^ 1)) {
+          const int sk = j % C::KS, sv = j % C::VS;
+          if (!mbar_wait(&bars->ring_empty[sk], ((j / C::KS) & 1) ^ 1)) {
             dev_set_error(p.status, SAF_DEV_TIMEOUT_TMA, 50);
             break;
           }
-          uint8_t* dst = ring + s * 2 * C::TILE_BYTES;
-          mbar_expect_tx(&bars->ring_full[s], 2 * C::TILE_BYTES);
-          bload_tile<HD>(dst, &mapK, &bars->ring_full[s], j * 128, hq, b);
-          bload_tile<HD>(dst + C::TILE_BYTES, &mapV, &bars->ring_full[s], j * 128, h, b);
+          mbar_expect_tx(&bars->ring_full[sk], C::TILE_BYTES);
+          bload_tile<HD>(ringK + sk * C::TILE_BYTES, &mapK, &bars->ring_full[sk], j * 128, hq, b);
+          if (!mbar_wait(&bars->v_empty[sv], ((j / C::VS) & 1) ^ 1)) {
+            dev_set_error(p.status, SAF_DEV_TIMEOUT_TMA, 57);
+            break;
+          }
+          mbar_expect_tx(&bars->v_full[sv], C::TILE_BYTES);
+          bload_tile<HD>(ringV + sv * C::TILE_BYTES, &mapV, &bars->v_full[sv], j * 128, h, b);
         }
       }
     } else if (warp == 9) {
       // ------------------------------------------------------------ MMA issuer
       const uint32_t idesc_s = umma_idesc_bf16(128, 128, 0, 0);
       const uint32_t idesc_o = umma_idesc_bf16(128, HD, 0, 1);
-      const uint32_t aQ = smem_u32(sQ), adO = smem_u32(sdO), aR = smem_u32(ring);
+      const uint32_t aQ = smem_u32(sQ), adO = smem_u32(sdO), aK = smem_u32(ringK), aV = smem_u32(ringV);
       bool ok = mbar_wait(&bars->res_full, 0);
       if (!ok) dev_set_error(p.status, SAF_DEV_TIMEOUT_MMA, 51);
       // scores run up to two key tiles ahead (two score buffers), dP one ahead
       auto issue_scores = [&](int j) -> bool {
-        const int s = j % C::NSTAGE;
-        if (!mbar_wait(&bars->ring_full[s], (j / C::NSTAGE) & 1)) {
+        const int s = j % C::KS;
+        if (!mbar_wait(&bars->ring_full[s], (j / C::KS) & 1)) {
           dev_set_error(p.status, SAF_DEV_TIMEOUT_MMA, 52);
           return false;
         }
         tc_fence_after();
         if (leader) {
-          issue_ss<HD>(tmem + COL_S + (j & 1) * 128, aQ, aR + s * 2 * C::TILE_BYTES, idesc_s);
+          issue_ss<HD>(tmem + COL_S + (j & 1) * 128, aQ, aK + s * C::TILE_BYTES, idesc_s);
           umma_commit(&bars->s_full[j & 1]);
         }
         __syncwarp();
         return true;
       };
-      auto issue_dp = [&](int j) {   // its ring stage was waited for by issue_scores(j)
-        const int s = j % C::NSTAGE;
+      auto issue_dp = [&](int j) -> bool {
+        const int s = j % C::VS;
+        if (!mbar_wait(&bars->v_full[s], (j / C::VS) & 1)) {
+          dev_set_error(p.status, SAF_DEV_TIMEOUT_MMA, 58);
+          return false;
+        }
+        tc_fence_after();
         if (leader) {
-          issue_ss<HD>(tmem + COL_DP, adO, aR + s * 2 * C::TILE_BYTES + C::TILE_BYTES, idesc_s);
+          issue_ss<HD>(tmem + COL_DP, adO, aV + s * C::TILE_BYTES, idesc_s);
           umma_commit(&bars->dp_full);
+          umma_commit(&bars->v_empty[s]);     // V_j is not read again
         }
         __syncwarp();
+        return true;
       };
       if (ok) ok = issue_scores(0);
-      if (ok) issue_dp(0);
+      if (ok) ok = issue_dp(0);
       if (ok && n > 1) ok = issue_scores(1);
       for (int j = 0; j < n && ok; ++j) {
-        const int s = j % C::NSTAGE;
+        const int s = j % C::KS;
         if (!mbar_wait(&bars->ds_full, j & 1)) {
           dev_set_error(p.status, SAF_DEV_TIMEOUT_MMA, 53);
           break;
         }
         tc_fence_after();
+        TRACE(1, 5, j);
         if (leader) {
-          issue_ts(tmem + COL_DQ, tmem + COL_DP, aR + s * 2 * C::TILE_BYTES, idesc_o, j > 0);
-          umma_commit(&bars->ring_empty[s]);
+          issue_ts(tmem + COL_DQ, tmem + COL_DP, aK + s * C::TILE_BYTES, idesc_o, j > 0);
+          umma_commit(&bars->ring_empty[s]);          // K_j is not read again
         }
         __syncwarp();
-        if (j + 1 < n) issue_dp(j + 1);               // ordered behind the dQ product that read dS
-        if (j + 2 < n) ok = issue_scores(j + 2);      // score buffer j & 1 was read before ds_full(j)
+        if (j + 1 < n) ok = issue_dp(j + 1);          // ordered behind the dQ product that read dS
+        if (ok && j + 2 < n) ok = issue_scores(j + 2);   // score buffer j & 1 was read before ds_full(j)
       }
       if (leader) umma_commit(&bars->acc_full);
       __syncwarp();
@@ -568,6 +651,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_const
         break;
       }
       tc_fence_after();
+      TRACE(1, 0, j);
       float pf[64];
 #pragma unroll
       for (int ch = 0; ch < 2; ++ch) {
@@ -596,6 +680,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_const
         break;
       }
       tc_fence_after();
+      TRACE(1, 2, j);
 #pragma unroll
       for (int ch = 0; ch < 2; ++ch) {
         uint32_t d[32];
@@ -611,6 +696,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_const
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(&bars->ds_full);
+      TRACE(1, 3, j);
     }
     if (ok && !mbar_wait(&bars->acc_full, 0)) {
       dev_set_error(p.status, SAF_DEV_TIMEOUT_SOFTMAX, 56);
@@ -736,26 +822,46 @@ int bwd_launch_typed(const SafMixedAttnBwdArgs& g, cudaStream_t st) {
     p.delta_s[i] = g.delta.stride[i];
   }
   p.status = a.status;
+  if (a.sd_alpha && a.sd_rho) {
+    ScanArgs& sc = p.scan;
+    sc.in = g.dout.ptr;
+    sc.out = g.dv.ptr;
+    for (int i = 0; i < 4; ++i) {
+      sc.si[i] = g.dout.stride[i];
+      sc.so[i] = g.dv.stride[i];
+    }
+    sc.frozen = a.frozen; sc.kvidx = nullptr; sc.sd_alpha = a.sd_alpha; sc.sd_rho = a.sd_rho;
+    sc.B = a.B; sc.H = a.H; sc.T = a.T; sc.HD = a.HD; sc.force_state = a.force_state; sc.HKV = 0;
+    sc.vec_ok = 1;   // bwd_tma_ok() already demands 16-byte aligned bases and strides
+    p.scan_slots = a.B * a.H * (HD / SCAN_COLS);
+  }
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(flash_bwd_dkdv_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdCfg<HD>::SMEM_BYTES);
     if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(flash_bwd_dq_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdCfg<HD>::SMEM_BYTES);
+      e = cudaFuncSetAttribute(flash_bwd_dq_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdCfg<HD>::SMEM_BYTES_DQ);
     if (e != cudaSuccess) return fail(SAF_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     attr_set = true;
   }
   const int bh = a.B * a.H;
   const int groups = (bh + BWD_HEAD_GROUP - 1) / BWD_HEAD_GROUP;
   const unsigned grid = (unsigned)(groups * BWD_HEAD_GROUP * p.n_tiles);
-  flash_bwd_dkdv_kernel<HD><<<grid, BWD_THREADS, BwdCfg<HD>::SMEM_BYTES, st>>>(mq, mk, mv, mdo, mdk, mdv, p);
+  flash_bwd_dkdv_kernel<HD><<<grid + p.scan_slots, BWD_THREADS, BwdCfg<HD>::SMEM_BYTES, st>>>(mq, mk, mv, mdo, mdk, mdv, p);
   count_launch();
   if ((rc = check_launch("flash_bwd_dkdv_kernel"))) return rc;
-  flash_bwd_dq_kernel<HD><<<grid, BWD_THREADS, BwdCfg<HD>::SMEM_BYTES, st>>>(mq, mk, mv, mdo, mdq, p);
+  p.scan_slots = 0;
+  flash_bwd_dq_kernel<HD><<<grid, BWD_THREADS, BwdCfg<HD>::SMEM_BYTES_DQ, st>>>(mq, mk, mv, mdo, mdq, p);
   count_launch();
   return check_launch("flash_bwd_dq_kernel");
 }
 
 }  // namespace
+
+#ifdef SAF_BWD_TRACE
+extern "C" int saf_debug_trace(long long* host) {
+  return (int)cudaMemcpyFromSymbol(host, g_trace, sizeof(g_trace));
+}
+#endif
 
 // Live heads of a bf16 backward at head_dim 64 / 128 without in-kernel RoPE or GQA; everything else
 // stays with the generic kernels.
@@ -776,7 +882,7 @@ int launch_flash_bwd_sm100(const SafMixedAttnBwdArgs& g, uint32_t* handled, cuda
     if (!any) return SAF_ERR_UNSUPPORTED;
   }
   const int rc = (a.HD == 64) ? bwd_launch_typed<64>(g, st) : bwd_launch_typed<128>(g, st);
-  if (rc == SAF_OK) *handled = 1u << SAF_LIVE;
+  if (rc == SAF_OK) *handled = (1u << SAF_LIVE) | ((a.sd_alpha && a.sd_rho) ? (1u << SAF_SINK_DECAY) : 0u);
   return rc;
 }
 
