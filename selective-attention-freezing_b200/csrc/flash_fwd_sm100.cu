@@ -47,6 +47,14 @@ constexpr float RESCALE_THRESHOLD = 8.0f;
 #define SAF_POLY_EXP_PER_16 8       // of every 16 exponentials, this many run on the FMA pipe
 #endif
 
+#ifdef SAF_FWD_TRACE
+// timing probe (only in specially built libraries): clock64 stamps of one CTA's pipeline events
+__device__ long long g_ftrace[8][64];   // [event][key step]
+#define FTRACE(evt, step) do { if (trace_on && (step) < 64) g_ftrace[evt][step] = clock64(); } while (0)
+#else
+#define FTRACE(evt, step) do { } while (0)
+#endif
+
 template <int HD>
 struct Cfg {
   static constexpr int TILE_BYTES = 128 * HD * 2;
@@ -202,6 +210,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = bars->tmem_base;
+#ifdef SAF_FWD_TRACE
+  const bool trace_on = (b == 0 && h == 0 && mp == p.n_pairs - 1) && ((tid & 31) == 0);
+#endif
 
   if (warp >= 8) {
     reg_dec<56>();
@@ -264,6 +275,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
               break;
             }
             k_waited = j;
+            FTRACE(5, j);
           }
           // the PV product that read P from this buffer (its previous use) must have finished
           if (k >= C::NBUF && !mbar_wait(&bars->buf_free[buf], bph ^ 1)) {
@@ -271,6 +283,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
             break;
           }
           tc_fence_after();
+          if (t == 0) FTRACE(2, j);
           const uint32_t qa = qaddr0 + t * C::TILE_BYTES, ka = kbase + ks_ * C::TILE_BYTES;
           const uint32_t d = tmem + buf * FN;
           if (leader) {
@@ -305,12 +318,14 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
               break;
             }
             v_waited = j;
+            FTRACE(4, j);
           }
           if (!mbar_wait(&bars->p_full[buf], bph)) {
             dev_set_error(p.status, SAF_DEV_TIMEOUT_MMA, 26);
             break;
           }
           tc_fence_after();
+          if (t == 0) FTRACE(3, j);
           const uint32_t va = vbase + vs_ * C::TILE_BYTES;
           const uint32_t dO = tmem + C::O_COL + t * HD, aP = tmem + buf * FN;
           if (leader) {
@@ -446,6 +461,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
         break;
       }
       tc_fence_after();
+      if (warp == 0) FTRACE(0, j);
       uint32_t s[4][32];
 #pragma unroll
       for (int q = 0; q < 4; ++q) tmem_ld32(tS + q * 32, s[q]);
@@ -521,6 +537,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(&bars->p_full[buf]);
+      if (warp == 0) FTRACE(1, j);
       pbuf = buf;
       pph = bph;
       buf += kstep;
@@ -647,6 +664,12 @@ int launch_typed(const SafMixedAttnArgs& a, cudaStream_t st) {
 }
 
 }  // namespace
+
+#ifdef SAF_FWD_TRACE
+extern "C" int saf_debug_ftrace(long long* host) {
+  return (int)cudaMemcpyFromSymbol(host, g_ftrace, sizeof(g_ftrace));
+}
+#endif
 
 int launch_flash_fwd_sm100(const SafMixedAttnArgs& a, uint32_t* handled, cudaStream_t st) {
   *handled = 0;
