@@ -607,7 +607,7 @@ int make_map4(CUtensorMap* m, const SafTensor& t, int B, int Hn, int T, int HD) 
 }
 
 template <int HD>
-int launch_typed(const SafMixedAttnArgs& a, cudaStream_t st) {
+int launch_typed(const SafMixedAttnArgs& a, uint32_t want, cudaStream_t st) {
   CUtensorMap mq, mk, mv, mo;
   int rc;
   const int Hkv = a.HKV > 0 ? a.HKV : 0;
@@ -636,7 +636,9 @@ int launch_typed(const SafMixedAttnArgs& a, cudaStream_t st) {
     p.z_s[i] = a.z.stride[i];
   }
   p.dec_dtype = a.dec_dtype;
-  if (a.sd_alpha && a.sd_rho) {
+  if (!(want & (1u << SAF_DENSE))) p.patt = nullptr;       // another launch serves these heads: their CTAs exit
+  if (!(want & (1u << SAF_DECOMP))) p.alpha = nullptr;
+  if (a.sd_alpha && a.sd_rho && (want & (1u << SAF_SINK_DECAY))) {
     p.has_scan = 1;
     ScanArgs& s = p.scan;
     s.in = a.v.ptr;
@@ -671,7 +673,7 @@ extern "C" int saf_debug_ftrace(long long* host) {
 }
 #endif
 
-int launch_flash_fwd_sm100(const SafMixedAttnArgs& a, uint32_t* handled, cudaStream_t st) {
+int launch_flash_fwd_sm100(const SafMixedAttnArgs& a, uint32_t want, uint32_t* handled, cudaStream_t st) {
   *handled = 0;
   if (a.dtype != SAF_BF16 || (a.HD != 64 && a.HD != 128) || a.rope) return SAF_ERR_UNSUPPORTED;
   if (a.sm_scale <= 0.f) return SAF_ERR_UNSUPPORTED;
@@ -685,6 +687,7 @@ int launch_flash_fwd_sm100(const SafMixedAttnArgs& a, uint32_t* handled, cudaStr
   if (a.patt.ptr) can |= 1u << SAF_DENSE;
   if (a.alpha.ptr && a.rho.ptr && a.z.ptr) can |= 1u << SAF_DECOMP;
   if (a.sd_alpha && a.sd_rho) can |= 1u << SAF_SINK_DECAY;
+  can &= want;
   uint32_t present = can;
   if (a.force_state >= 0) present = 1u << a.force_state;
   else if (a.frozen_host) {
@@ -692,7 +695,7 @@ int launch_flash_fwd_sm100(const SafMixedAttnArgs& a, uint32_t* handled, cudaStr
     for (int h = 0; h < a.H; ++h) present |= 1u << a.frozen_host[h];
   }
   if (!(present & can)) return SAF_ERR_UNSUPPORTED;
-  const int rc = (a.HD == 64) ? launch_typed<64>(a, st) : launch_typed<128>(a, st);
+  const int rc = (a.HD == 64) ? launch_typed<64>(a, can, st) : launch_typed<128>(a, can, st);
   if (rc == SAF_OK) *handled = can;
   return rc;
 }

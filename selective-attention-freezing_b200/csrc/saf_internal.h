@@ -42,7 +42,10 @@ int launch_generic_bwd(const SafMixedAttnBwdArgs& a, uint32_t states_mask, cudaS
 int launch_scan_fwd(const SafMixedAttnArgs& a, cudaStream_t st);                       // state 3 heads
 int launch_scan_bwd(const SafMixedAttnBwdArgs& a, cudaStream_t st);                    // state 3 heads: dv
 // tcgen05 fast path; returns SAF_ERR_UNSUPPORTED when the call does not qualify
-int launch_flash_fwd_sm100(const SafMixedAttnArgs& a, uint32_t* handled_states, cudaStream_t st);
+// `want`: states still to be served; the launch covers the subset it can and reports it
+int launch_flash_fwd_sm100(const SafMixedAttnArgs& a, uint32_t want, uint32_t* handled_states, cudaStream_t st);
+// dense-stored frozen heads as a TMA-staged lower-triangular GEMM (bf16 patterns)
+int launch_dense_pv_sm100(const SafMixedAttnArgs& a, uint32_t* handled_states, cudaStream_t st);
 int launch_flash_bwd_sm100(const SafMixedAttnBwdArgs& a, uint32_t* handled_states, cudaStream_t st);
 int launch_gemm_sm100(const SafIndexedLinearArgs& a, cudaStream_t st);
 int launch_gemm_generic(const SafIndexedLinearArgs& a, cudaStream_t st);

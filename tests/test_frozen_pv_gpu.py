@@ -85,3 +85,26 @@ def test_frozen_pv_sink_decay_scan(shape, dtype):
         # gradients sum many rows and grow past 16, where one bf16 ulp is already 0.125:
         # bound the absolute error by the output magnitude (2^-7 relative) and keep rel-L2
         assert ba <= 2 ** -7 * max(1.0, v_ref.grad.abs().max().item()) and br <= 1e-2, f"bwd {ba} {br}"
+
+
+@pytest.mark.parametrize("cfg", [(5, 3, 700, 64), (2, 2, 1024, 128), (3, 2, 1300, 64), (1, 1, 130, 128)],
+                         ids=lambda c: f"B{c[0]}nf{c[1]}T{c[2]}hd{c[3]}")
+def test_dense_bf16_pattern_on_tensor_core_ignores_upper_triangle(cfg):
+    """TMA-staged lower-triangular GEMM: entries above the diagonal of the stored pattern never count
+    (Y_i = sum_{j<=i} P_ij V_j, kernel/frozen_attn.py:51-89), batch rows share one pattern tile, ragged T."""
+    from kernel import frozen_pv
+    from saf_b200 import launch_count
+    B, NF, T, hd = cfg
+    S = ((T + 63) // 64) * 64 + 64
+    g = torch.Generator().manual_seed(T + hd)
+    patt = torch.rand(NF + 1, S, S, generator=g)
+    patt = patt / patt.tril().sum(-1, keepdim=True).clamp_min(1e-6)     # rows of the lower triangle sum to one
+    patt = patt.bfloat16()                                               # upper triangle left non-zero on purpose
+    v = torch.randn(B, NF, T, hd, generator=g).bfloat16()
+    idx = torch.arange(1, NF + 1, dtype=torch.int32)                     # pattern planes 1..NF
+    ref = torch.matmul(patt[1:, :T, :T].float().tril(), v.float())
+    n0 = launch_count()
+    y = frozen_pv(patt.cuda(), v.cuda(), idx.cuda(), T)
+    assert launch_count() - n0 == 1
+    a, r = errs(y, ref)
+    assert a <= 2e-2 and r <= 1e-2, f"max-abs {a} rel-l2 {r}"
