@@ -175,13 +175,11 @@ int saf_mixed_attn_fwd(const SafMixedAttnArgs* args, void* stream) {
   uint32_t todo = possible_states(a);
   // tensor-core path first; it reports which states it covered
   uint32_t handled = 0;
-  if (todo & (1u << SAF_DENSE)) {
+  rc = launch_flash_fwd_sm100(a, todo, &handled, st);
+  if (rc == SAF_OK) todo &= ~handled;
+  else if (rc != SAF_ERR_UNSUPPORTED) return rc;
+  if (todo & (1u << SAF_DENSE)) {   // the mixed launch did not take the call: dense heads on their own
     rc = launch_dense_pv_sm100(a, &handled, st);
-    if (rc == SAF_OK) todo &= ~handled;
-    else if (rc != SAF_ERR_UNSUPPORTED) return rc;
-  }
-  if (todo) {
-    rc = launch_flash_fwd_sm100(a, todo, &handled, st);
     if (rc == SAF_OK) todo &= ~handled;
     else if (rc != SAF_ERR_UNSUPPORTED) return rc;
   }

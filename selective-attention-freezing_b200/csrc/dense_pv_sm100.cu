@@ -1,318 +1,41 @@
-// Dense-stored frozen heads (state 1) as a TMA-staged lower-triangular GEMM on tcgen05:
-//
-//   Y[b, h, i, :] = sum_{j <= i} P[pidx[h], i, j] * V[b, h, j, :]
-//
-// Replaces _acc_dense / _pv_fwd_kernel (kernel/fused_attn.py:125-143, kernel/frozen_attn.py:51-89), which
-// stream 64x64 pattern tiles through registers once per batch row.  Here a pattern tile never visits the
-// register file: TMA lands it in shared memory in the layout the tensor core reads (A operand, K-major),
-// and ONE copy of it multiplies the value tiles of up to 256/head_dim batch rows, so the T^2/2 pattern
-// elements -- the only large operand -- cross HBM once per group of batch rows instead of once per row.
-//
-// CTA = two consecutive 128-row tiles of one head for a group of NB = 256/head_dim batch rows:
-// 2 * NB accumulators of head_dim columns fill the 512 TMEM columns.  Keys advance 64 at a time:
-//   stage = [P tile 0: 128 x 64 | P tile 1: 128 x 64 | V of NB batch rows: 64 x head_dim each] = 64 KB, 3 stages
-//   warp 0      TMA producer
-//   warp 1      MMA issuer: O[t][b] += P_t (SS, K-major) * V_b (MN-major), 4 k-steps of 16 keys
-//   warps 2-5   zero the above-diagonal entries of the (at most four) diagonal stages in shared memory,
-//               then the epilogue: TMEM -> bf16 -> swizzled staging -> TMA store
-// Work per stage: 2 * NB * 128 * 64 * head_dim MACs against 32 KB of pattern read from HBM: at head_dim 64
-// that is ~1500 tensor cycles per 32 KB per SM, i.e. the kernel sits at the HBM roofline of the pattern.
-// All waits are bounded.
-#include "saf_internal.h"
-#include "sm100_prims.cuh"
+// Stand-alone launch of the dense-pattern GEMM (csrc/dense_pv_body.cuh) for calls the mixed launch does not
+// take (frozen heads only with in-kernel RoPE requested for the live ones, unsupported live-head layouts, ...).
+#include "dense_pv_body.cuh"
 
 namespace saf {
 namespace {
-
-constexpr int DP_THREADS = 192;
-constexpr int DP_NST = 3;
-constexpr int DP_PATOM = 128 * 64 * 2;     // 16 KB: 128 pattern rows x 64 keys
-
-template <int HD>
-struct DpCfg {
-  static constexpr int NB = 256 / HD;                 // batch rows per CTA
-  static constexpr int V_BYTES = 64 * HD * 2;         // 64 keys x head_dim
-  static constexpr int STAGE = 2 * DP_PATOM + NB * V_BYTES;   // 64 KB
-  static constexpr int SMEM_BYTES = 1024 + DP_NST * STAGE + 256;
-};
-
-struct DpParams {
-  int B, H, T, n_pairs, groups, force_state, HKV;
-  const int32_t* frozen;
-  const int32_t* pidx;
-  const int32_t* kvidx;
-  int* status;
-};
-
-struct DpBars {
-  uint64_t full[DP_NST], empty[DP_NST], need_mask, masked, acc_full;
-  uint32_t tmem_base;
-};
 
 template <int HD>
 __global__ void __launch_bounds__(DP_THREADS, 1)
 dense_pv_kernel(const __grid_constant__ CUtensorMap mapP, const __grid_constant__ CUtensorMap mapV,
                 const __grid_constant__ CUtensorMap mapO, const __grid_constant__ DpParams p) {
-  using C = DpCfg<HD>;
-  // CTA -> (head, batch group, row pair); heaviest row pairs first
-  const int per_mp = p.H * p.groups;
-  const int mp = p.n_pairs - 1 - (int)blockIdx.x / per_mp;
-  const int rem = (int)blockIdx.x % per_mp;
-  const int h = rem / p.groups, grp = rem % p.groups;
-  const int state = p.force_state >= 0 ? p.force_state : p.frozen[h];
-  if (state != SAF_DENSE) return;
-  const int hp = p.pidx ? p.pidx[h] : h;
-  const int hv = (p.HKV > 0) ? p.kvidx[h] : h;
-  const int b0 = grp * C::NB;
-  const int nb = min(C::NB, p.B - b0);
-  const int row0 = mp * 256;
-  const bool act1 = row0 + 128 < p.T;
-  const int n_half = (p.T + 63) / 64;
-  const int nk0 = min(4 * mp + 2, n_half);                 // 64-key steps of tile 0
-  const int nkh = act1 ? min(4 * mp + 4, n_half) : nk0;    // and of the CTA
-  // steps whose pattern tile holds above-diagonal entries: the two steps that cover a tile's own 128 keys
-  auto diag_of = [&](int kh, int t) { return kh >= 4 * mp + 2 * t && kh < 4 * mp + 2 * t + 2; };
-
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  DpBars* bars = reinterpret_cast<DpBars*>(smem + DP_NST * C::STAGE);
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-
-  if (tid == 0) {
-    for (int s = 0; s < DP_NST; ++s) {
-      mbar_init(&bars->full[s], 1);
-      mbar_init(&bars->empty[s], 1);
-    }
-    mbar_init(&bars->need_mask, 1);
-    mbar_init(&bars->masked, 128);
-    mbar_init(&bars->acc_full, 1);
-    fence_mbar_init();
-  }
-  if (warp == 1) {
-    tmem_alloc(&bars->tmem_base, 512);
-    tmem_relinquish();
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = bars->tmem_base;
-
-  if (warp == 0) {
-    // ---------------------------------------------------------------- TMA producer
-    if (lane == 0) {
-      tma_prefetch_desc(&mapP);
-      tma_prefetch_desc(&mapV);
-      for (int kh = 0; kh < nkh; ++kh) {
-        const int s = kh % DP_NST;
-        if (!mbar_wait(&bars->empty[s], ((kh / DP_NST) & 1) ^ 1)) {
-          dev_set_error(p.status, SAF_DEV_TIMEOUT_TMA, 70);
-          break;
-        }
-        uint8_t* st = smem + s * C::STAGE;
-        const bool t0 = kh < nk0;
-        mbar_expect_tx(&bars->full[s], (t0 ? DP_PATOM : 0) + (act1 ? DP_PATOM : 0) + nb * C::V_BYTES);
-        if (t0) tma_load_3d(st, &mapP, &bars->full[s], kh * 64, row0, hp);
-        if (act1) tma_load_3d(st + DP_PATOM, &mapP, &bars->full[s], kh * 64, row0 + 128, hp);
-        for (int bi = 0; bi < nb; ++bi)
-#pragma unroll
-          for (int hh = 0; hh < HD / 64; ++hh)
-            tma_load_4d(st + 2 * DP_PATOM + bi * C::V_BYTES + hh * 8192, &mapV, &bars->full[s], hh * 64, kh * 64, hv,
-                        b0 + bi);
-      }
-    }
-  } else if (warp == 1) {
-    // ---------------------------------------------------------------- MMA issuer
-    const bool leader = elect_one();
-    const uint32_t idesc = umma_idesc_bf16(128, HD, 0, 1);
-    const uint32_t sbase = smem_u32(smem);
-    int n_masked = 0;
-    for (int kh = 0; kh < nkh; ++kh) {
-      const int s = kh % DP_NST;
-      if (!mbar_wait(&bars->full[s], (kh / DP_NST) & 1)) {
-        dev_set_error(p.status, SAF_DEV_TIMEOUT_MMA, 71);
-        break;
-      }
-      if (diag_of(kh, 0) || diag_of(kh, 1)) {
-        // the tile has landed: hand it to the mask helpers (they follow this barrier, never the ring's,
-        // so they cannot run ahead of or behind the stage they are meant to edit)
-        if (leader) mbar_arrive(&bars->need_mask);
-        __syncwarp();
-        if (!mbar_wait(&bars->masked, n_masked & 1)) {
-          dev_set_error(p.status, SAF_DEV_TIMEOUT_MMA, 72);
-          break;
-        }
-        ++n_masked;
-      }
-      tc_fence_after();
-      const uint32_t st = sbase + s * C::STAGE;
-      if (leader) {
-        for (int t = 0; t < 2; ++t) {
-          if (t == 0 ? kh >= nk0 : !act1) continue;
-          const uint32_t pa = st + t * DP_PATOM;
-          for (int bi = 0; bi < nb; ++bi) {
-            const uint32_t va = st + 2 * DP_PATOM + bi * C::V_BYTES;
-            const uint32_t d = tmem + (t * C::NB + bi) * HD;
-#pragma unroll
-            for (int ks = 0; ks < 4; ++ks)
-              umma_ss(d, umma_smem_desc_sw128(pa + ks * 32, 16, 1024), umma_smem_desc_sw128(va + ks * 2048, 8192, 1024),
-                      idesc, (kh | ks) != 0);
-          }
-        }
-        umma_commit(&bars->empty[s]);
-      }
-      __syncwarp();
-    }
-    if (leader) umma_commit(&bars->acc_full);
-    __syncwarp();
-  } else {
-    // ---------------------------------------------------------------- mask helpers, then epilogue
-    const int quad = warp & 3;
-    const int r = quad * 32 + lane;            // row of the tile == TMEM lane
-    const int etid = tid - 64;
-    bool ok = true;
-    int n_masked = 0;
-    for (int kh = max(0, nkh - 4); kh < nkh && ok; ++kh) {
-      const bool d0 = diag_of(kh, 0), d1 = diag_of(kh, 1);
-      if (!d0 && !d1) continue;
-      const int s = kh % DP_NST;
-      if (!mbar_wait(&bars->need_mask, n_masked & 1)) {
-        dev_set_error(p.status, SAF_DEV_TIMEOUT_EPI, 73);
-        ok = false;
-        break;
-      }
-      ++n_masked;
-      const int t = d0 ? 0 : 1;
-      // key c of this step is column 64*(kh - first diagonal step) + c of the tile's own 128 keys
-      const int koff = (kh - (4 * mp + 2 * t)) * 64;
-      uint8_t* rowp = smem + s * C::STAGE + t * DP_PATOM + r * 128;
-#pragma unroll
-      for (int cc = 0; cc < 8; ++cc) {
-        const int c_lo = koff + cc * 8;                        // first key of this 16-byte chunk
-        if (c_lo + 7 <= r) continue;                            // all eight at or below the diagonal
-        uint4* q = reinterpret_cast<uint4*>(rowp + ((cc ^ (r & 7)) << 4));
-        uint4 v = *q;
-        uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          if (c_lo + 2 * e > r) w[e] &= 0xffff0000u;            // low half = key c_lo + 2e
-          if (c_lo + 2 * e + 1 > r) w[e] &= 0x0000ffffu;        // high half = key c_lo + 2e + 1
-        }
-        *q = make_uint4(w[0], w[1], w[2], w[3]);
-      }
-      fence_proxy_async_smem();
-      mbar_arrive(&bars->masked);
-    }
-    if (ok && !mbar_wait(&bars->acc_full, 0)) {
-      dev_set_error(p.status, SAF_DEV_TIMEOUT_EPI, 74);
-      ok = false;
-    }
-    tc_fence_after();
-    // accumulators -> bf16 -> staging (the ring is idle now) -> TMA store; two staging tiles in rotation
-    int n_st = 0;
-    for (int t = 0; t < 2; ++t) {
-      if (t == 1 && !act1) break;
-      for (int bi = 0; bi < nb; ++bi, ++n_st) {
-        uint8_t* stage = smem + (n_st & 1) * (128 * HD * 2);
-        if (etid == 0) tma_store_wait_read1();
-        named_bar_sync(1, 128);
-        const uint32_t tsrc = tmem + ((uint32_t)(quad * 32) << 16) + (t * C::NB + bi) * HD;
-#pragma unroll
-        for (int c0 = 0; c0 < HD; c0 += 32) {
-          uint32_t o[32];
-          tmem_ld32(tsrc + c0, o);
-          tmem_ld_wait();
-          uint8_t* dst = stage + (c0 >> 6) * 16384 + r * 128;
-          const int cbase = (c0 & 63) >> 3;
-#pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            uint4 q;
-            q.x = pack_bf16(__uint_as_float(o[c * 8 + 0]), __uint_as_float(o[c * 8 + 1]));
-            q.y = pack_bf16(__uint_as_float(o[c * 8 + 2]), __uint_as_float(o[c * 8 + 3]));
-            q.z = pack_bf16(__uint_as_float(o[c * 8 + 4]), __uint_as_float(o[c * 8 + 5]));
-            q.w = pack_bf16(__uint_as_float(o[c * 8 + 6]), __uint_as_float(o[c * 8 + 7]));
-            *reinterpret_cast<uint4*>(dst + (((cbase + c) ^ (r & 7)) << 4)) = q;
-          }
-        }
-        fence_proxy_async_smem();
-        named_bar_sync(1, 128);
-        if (etid == 0 && ok) {
-#pragma unroll
-          for (int hh = 0; hh < HD / 64; ++hh) tma_store_4d(&mapO, stage + hh * 16384, hh * 64, row0 + t * 128, h, b0 + bi);
-          tma_store_commit();
-        }
-      }
-    }
-    if (etid == 0) tma_store_wait_all();
-  }
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem, 512);
-}
-
-bool dp_aligned16(const void* q) { return ((uintptr_t)q & 15) == 0; }
-
-bool dp_tma_ok(const SafTensor& t) {
-  if (!t.ptr || !dp_aligned16(t.ptr) || t.stride[3] != 1) return false;
-  for (int i = 0; i < 3; ++i)
-    if (t.stride[i] % 8 || t.stride[i] <= 0) return false;
-  return true;
+  dense_pv_cta<HD>(mapP, mapV, mapO, p, (int)blockIdx.x, smem);
 }
 
 template <int HD>
 int dp_launch(const SafMixedAttnArgs& a, cudaStream_t st) {
   CUtensorMap mp_, mv, mo;
-  int rc;
-  {
-    // pattern (P, S, S): box 64 keys x 128 rows of one plane; planes counted from the strides
-    const uint64_t planes = 1u << 20;   // the plane index comes from pidx; its range is the caller's contract
-    uint64_t dims[3] = {(uint64_t)a.S, (uint64_t)a.S, planes};
-    uint64_t strides[3] = {0, (uint64_t)a.patt.stride[1] * 2, (uint64_t)a.patt.stride[0] * 2};
-    uint32_t box[3] = {64, 128, 1};
-    if ((rc = make_tensor_map_bf16(&mp_, a.patt.ptr, 3, dims, strides, box, true))) return rc;
-  }
-  const int Hkv = a.HKV > 0 ? a.HKV : a.H;
-  {
-    uint64_t dims[4] = {(uint64_t)HD, (uint64_t)a.T, (uint64_t)Hkv, (uint64_t)a.B};
-    uint64_t strides[4] = {0, (uint64_t)a.v.stride[2] * 2, (uint64_t)a.v.stride[1] * 2, (uint64_t)a.v.stride[0] * 2};
-    uint32_t box[4] = {64, 64, 1, 1};
-    if ((rc = make_tensor_map_bf16(&mv, a.v.ptr, 4, dims, strides, box, true))) return rc;
-  }
-  {
-    uint64_t dims[4] = {(uint64_t)HD, (uint64_t)a.T, (uint64_t)a.H, (uint64_t)a.B};
-    uint64_t strides[4] = {0, (uint64_t)a.out.stride[2] * 2, (uint64_t)a.out.stride[1] * 2, (uint64_t)a.out.stride[0] * 2};
-    uint32_t box[4] = {64, 128, 1, 1};
-    if ((rc = make_tensor_map_bf16(&mo, a.out.ptr, 4, dims, strides, box, false))) return rc;
-  }
   DpParams p;
-  memset(&p, 0, sizeof(p));
-  p.B = a.B; p.H = a.H; p.T = a.T; p.force_state = a.force_state; p.HKV = a.HKV;
-  p.n_pairs = (a.T + 255) / 256;
-  p.groups = (a.B + DpCfg<HD>::NB - 1) / DpCfg<HD>::NB;
-  p.frozen = a.frozen; p.pidx = a.pidx; p.kvidx = a.kvidx;
-  p.status = a.status;
+  int rc = dense_pv_prepare(a, &mp_, &mv, &mo, &p);
+  if (rc) return rc;
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(dense_pv_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, DpCfg<HD>::SMEM_BYTES);
     if (e != cudaSuccess) return fail(SAF_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     attr_set = true;
   }
-  const unsigned grid = (unsigned)(p.n_pairs * a.H * p.groups);
-  dense_pv_kernel<HD><<<grid, DP_THREADS, DpCfg<HD>::SMEM_BYTES, st>>>(mp_, mv, mo, p);
+  dense_pv_kernel<HD><<<dense_pv_slots(p), DP_THREADS, DpCfg<HD>::SMEM_BYTES, st>>>(mp_, mv, mo, p);
   count_launch();
   return check_launch("dense_pv_kernel");
 }
 
 }  // namespace
 
-// bf16 dense-stored frozen heads at head_dim 64 / 128 whose pattern rows TMA can address
 int launch_dense_pv_sm100(const SafMixedAttnArgs& a, uint32_t* handled, cudaStream_t st) {
   *handled = 0;
-  if (a.dtype != SAF_BF16 || (a.HD != 64 && a.HD != 128)) return SAF_ERR_UNSUPPORTED;
-  if (!a.patt.ptr || a.patt_dtype != SAF_BF16 || a.patt.stride[2] != 1 || !dp_aligned16(a.patt.ptr)) return SAF_ERR_UNSUPPORTED;
-  if (a.patt.stride[0] % 8 || a.patt.stride[1] % 8 || a.patt.stride[0] <= 0 || a.patt.stride[1] <= 0) return SAF_ERR_UNSUPPORTED;
-  if (a.S < a.T) return SAF_ERR_UNSUPPORTED;
-  if (!dp_tma_ok(a.v) || !dp_tma_ok(a.out)) return SAF_ERR_UNSUPPORTED;
-  if (!saf_device_supported()) return SAF_ERR_UNSUPPORTED;
+  if (!dense_pv_eligible(a) || !saf_device_supported()) return SAF_ERR_UNSUPPORTED;
   if (a.force_state >= 0 && a.force_state != SAF_DENSE) return SAF_ERR_UNSUPPORTED;
   if (a.frozen_host) {
     bool any = false;

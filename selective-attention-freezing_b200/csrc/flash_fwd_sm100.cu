@@ -31,8 +31,10 @@
 // live tiles, in groups of 8 (batch, head) pairs so the CTAs in flight share K/V in L2, heaviest
 // row tiles first inside a group.  CTAs of dense / decomposed heads exit (pattern kernels take them).
 #include "saf_internal.h"
+#include "dense_pv_body.cuh"
 #include "scan_body.cuh"
 #include "sm100_prims.cuh"
+#include <string.h>
 
 namespace saf {
 namespace {
@@ -61,7 +63,9 @@ struct Cfg {
   static constexpr int KSTAGE = (HD == 64) ? 4 : 2;    // K ring and V ring, powers of two
   static constexpr int Q_BYTES = 2 * TILE_BYTES;
   static constexpr int RING_BYTES = 2 * KSTAGE * TILE_BYTES;
-  static constexpr int SMEM_BYTES = 1024 + Q_BYTES + RING_BYTES + 4096;
+  static constexpr int SMEM_FLASH = 1024 + Q_BYTES + RING_BYTES + 4096;
+  // the dense-pattern role of the same launch needs its own ring
+  static constexpr int SMEM_BYTES = SMEM_FLASH > DpCfg<HD>::SMEM_BYTES ? SMEM_FLASH : DpCfg<HD>::SMEM_BYTES;
   static constexpr int TMEM_COLS = 512;
   static constexpr int NBUF = (HD == 64) ? 3 : 2;      // score buffers
   static constexpr int O_COL = NBUF * 128;
@@ -78,6 +82,8 @@ struct FlashParams {
   int* status;
   int has_scan;
   ScanArgs scan;
+  int dense_slots;           // CTAs of the TMA-staged dense-pattern role, right after the scan slots
+  DpParams dense;
   // frozen heads whose pattern is produced by the softmax warps (P -> TMEM -> P V on the tensor core)
   const void* patt;          // dense (P, S, S), state 1
   int64_t patt_s[3];
@@ -143,6 +149,7 @@ template <int HD>
 __global__ void __launch_bounds__(FLASH_THREADS, 1)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
                  const __grid_constant__ CUtensorMap mapV, const __grid_constant__ CUtensorMap mapO,
+                 const __grid_constant__ CUtensorMap mapP, const __grid_constant__ CUtensorMap mapV64,
                  const __grid_constant__ FlashParams p) {
   using C = Cfg<HD>;
   const int bh_count = p.B * p.H;
@@ -154,8 +161,15 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
       for (int col0 = 0; col0 < HD; col0 += SCAN_COLS) sink_decay_scan_cta<__nv_bfloat16, false>(p.scan, b, h, col0);
     return;
   }
+  // ---- dense-stored frozen heads: TMA-staged lower-triangular GEMM, pattern tiles shared by batch rows ---
+  if ((int)blockIdx.x < bh_count + p.dense_slots) {
+    extern __shared__ uint8_t dense_smem_raw[];
+    uint8_t* dsm = (uint8_t*)(((uintptr_t)dense_smem_raw + 1023) & ~(uintptr_t)1023);
+    dense_pv_cta<HD>(mapP, mapV64, mapO, p.dense, (int)blockIdx.x - bh_count, dsm);
+    return;
+  }
   // ---- live tiles: head groups, heaviest row-tile pairs first inside a group ------------------
-  const int li = blockIdx.x - bh_count;
+  const int li = blockIdx.x - bh_count - p.dense_slots;
   const int per_group = HEAD_GROUP * p.n_pairs;
   const int grp = li / per_group;
   const int gsize = min(HEAD_GROUP, bh_count - grp * HEAD_GROUP);
@@ -637,6 +651,16 @@ int launch_typed(const SafMixedAttnArgs& a, uint32_t want, cudaStream_t st) {
   }
   p.dec_dtype = a.dec_dtype;
   if (!(want & (1u << SAF_DENSE))) p.patt = nullptr;       // another launch serves these heads: their CTAs exit
+  CUtensorMap mpat, mv64;
+  memset(&mpat, 0, sizeof(mpat));
+  memset(&mv64, 0, sizeof(mv64));
+  if (p.patt && dense_pv_eligible(a)) {
+    // bf16 patterns TMA can address: the dense role takes these heads, the flash CTAs of dense heads exit
+    CUtensorMap mo2;
+    if ((rc = dense_pv_prepare(a, &mpat, &mv64, &mo2, &p.dense))) return rc;
+    p.dense_slots = (int)dense_pv_slots(p.dense);
+    p.patt = nullptr;
+  }
   if (!(want & (1u << SAF_DECOMP))) p.alpha = nullptr;
   if (a.sd_alpha && a.sd_rho && (want & (1u << SAF_SINK_DECAY))) {
     p.has_scan = 1;
@@ -659,8 +683,8 @@ int launch_typed(const SafMixedAttnArgs& a, uint32_t want, cudaStream_t st) {
   }
   const int bh = a.B * a.H;
   const int groups = (bh + HEAD_GROUP - 1) / HEAD_GROUP;
-  const unsigned grid = (unsigned)(bh + groups * HEAD_GROUP * p.n_pairs);
-  flash_fwd_kernel<HD><<<grid, FLASH_THREADS, Cfg<HD>::SMEM_BYTES, st>>>(mq, mk, mv, mo, p);
+  const unsigned grid = (unsigned)(bh + p.dense_slots + groups * HEAD_GROUP * p.n_pairs);
+  flash_fwd_kernel<HD><<<grid, FLASH_THREADS, Cfg<HD>::SMEM_BYTES, st>>>(mq, mk, mv, mo, mpat, mv64, p);
   count_launch();
   return check_launch("flash_fwd_kernel");
 }
