@@ -64,11 +64,15 @@ def main():
     for s, h in enumerate(live):
         hidx[h] = s
     hidx = hidx.to(dev)
-    q = torch.randn(B, U, T, hd, generator=g).bfloat16().to(dev).requires_grad_(True)
-    k = torch.randn(B, U, T, hd, generator=g).bfloat16().to(dev).requires_grad_(True)
-    v = torch.randn(B, H, T, hd, generator=g).bfloat16().to(dev).requires_grad_(True)
+    n_kv = w.get("n_kv")
+    gqa = n_kv is not None          # q head h reads K/V head kvidx[h]; forward only, as in the reference
+    q = torch.randn(B, U, T, hd, generator=g).bfloat16().to(dev).requires_grad_(not gqa)
+    k = torch.randn(B, n_kv if gqa else U, T, hd, generator=g).bfloat16().to(dev).requires_grad_(not gqa)
+    v = torch.randn(B, n_kv if gqa else H, T, hd, generator=g).bfloat16().to(dev).requires_grad_(not gqa)
     dy = torch.randn(B, H, T, hd, generator=g).bfloat16().to(dev)
     kw, patt = {}, None
+    if gqa:
+        kw["kvidx"] = torch.tensor([h * n_kv // H for h in range(H)], dtype=torch.int32, device=dev)
     if nf and args.frozen == "sink_decay":
         a, r = synthetic.sink_decay_params(H, 2337)
         kw["sink_decay"] = (a.float().to(dev), r.float().to(dev))
@@ -94,7 +98,7 @@ def main():
 
     fl_attn = 2.0 * B * U * T * T * hd
     fl_qk = 2.0 * B * T * C * 2 * U * hd
-    shape = f"B{B} T{T} H{H} hd{hd} live{U} frozen{nf}({args.frozen})"
+    shape = f"B{B} T{T} H{H}{'/kv%d' % n_kv if gqa else ''} hd{hd} live{U} frozen{nf}({args.frozen})"
     for op in args.ops.split(","):
         if op == "attn_fwd":
             with torch.no_grad():
