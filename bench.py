@@ -182,10 +182,33 @@ def main():
     def step_resident():
         return synthetic.stack_forward(layers, rope, x_dev)
 
+    # end to end: every step copies its input from pinned host memory and reads its result back.  The copy
+    # of step i+1 runs on a second stream into the other of two device buffers while step i computes.
+    copy_stream = torch.cuda.Stream(device=dev)
+    x_bufs = [torch.empty_like(x_dev), torch.empty_like(x_dev)]
+    copied = [torch.cuda.Event(), torch.cuda.Event()]
+    consumed = [torch.cuda.Event(), torch.cuda.Event()]
+    e2e_state = {"i": 0}
+
+    def issue_copy(slot):
+        with torch.cuda.stream(copy_stream):
+            copy_stream.wait_event(consumed[slot])        # the step that read this buffer has finished with it
+            x_bufs[slot].copy_(x_host, non_blocking=True)
+            copied[slot].record(copy_stream)
+
     def step_e2e():
-        xd = x_host.to(dev, non_blocking=True)
-        h = synthetic.stack_forward(layers, rope, xd)
+        i = e2e_state["i"]
+        slot = i & 1
+        if i == 0:
+            consumed[0].record()
+            consumed[1].record()
+            issue_copy(0)
+        issue_copy(slot ^ 1)                              # next step's input, overlapped with this step
+        torch.cuda.current_stream().wait_event(copied[slot])
+        h = synthetic.stack_forward(layers, rope, x_bufs[slot])
+        consumed[slot].record()
         last_host.copy_(h[:, -1, :], non_blocking=True)
+        e2e_state["i"] = i + 1
         return h
 
     with torch.inference_mode():
