@@ -174,6 +174,7 @@ int saf_mixed_attn_fwd(const SafMixedAttnArgs* args, void* stream) {
   cudaStream_t st = (cudaStream_t)stream;
   uint32_t todo = possible_states(a);
   // tensor-core path first; it reports which states it covered
+  if (todo == (1u << SAF_SINK_DECAY)) return launch_scan_fwd(a, st);   // scan only: the chunk-parallel scan
   uint32_t handled = 0;
   rc = launch_flash_fwd_sm100(a, todo, &handled, st);
   if (rc == SAF_OK) todo &= ~handled;

@@ -39,8 +39,35 @@ bool vec_ok(const void* p, const int64_t* s, int esize) {
   return true;
 }
 
+// chunked forward scan (three launches); returns false when the shape does not qualify
+template <typename T>
+bool scan_chunked(const ScanArgs& s, cudaStream_t st, int* rc) {
+  constexpr int STASH_ROWS = 256 / (SCAN_COLS * (int)sizeof(T));   // rows of an output slice that hold 64 fp32 words
+  if (!s.vec_ok || s.HD % SCAN_COLS || s.T < 4096) return false;
+  // as many chunks as the carry pass takes (64), in whole 256-row block steps
+  int chunk = ((s.T + 63) / 64 + SCAN_ROWS - 1) / SCAN_ROWS * SCAN_ROWS;
+  const int n_chunks = (s.T + chunk - 1) / chunk;
+  if (s.T - (n_chunks - 1) * chunk < STASH_ROWS) return false;     // the last chunk must hold its stash
+  dim3 grid(s.B * s.H, n_chunks, s.HD / SCAN_COLS);
+  sink_decay_chunk_kernel<T, 1><<<grid, SCAN_NT, 0, st>>>(s, chunk);
+  count_launch();
+  if ((*rc = check_launch("sink_decay_chunk_kernel<totals>"))) return true;
+  sink_decay_carry_kernel<T><<<dim3(s.B * s.H, s.HD / SCAN_COLS), SCAN_COLS, 0, st>>>(s, chunk, n_chunks);
+  count_launch();
+  if ((*rc = check_launch("sink_decay_carry_kernel"))) return true;
+  sink_decay_chunk_kernel<T, 2><<<grid, SCAN_NT, 0, st>>>(s, chunk);
+  count_launch();
+  *rc = check_launch("sink_decay_chunk_kernel<apply>");
+  return true;
+}
+
 int scan_dispatch(const ScanArgs& s, int dtype, bool bwd, cudaStream_t st) {
   if (s.T == 0 || s.B == 0 || s.H == 0) return SAF_OK;
+  if (!bwd) {
+    int rc = SAF_OK;
+    if (dtype == SAF_BF16 && scan_chunked<__nv_bfloat16>(s, st, &rc)) return rc;
+    if (dtype == SAF_F32 && scan_chunked<float>(s, st, &rc)) return rc;
+  }
   switch (dtype) {
     case SAF_F32: return scan_typed<float>(s, bwd, st);
     case SAF_BF16: return scan_typed<__nv_bfloat16>(s, bwd, st);

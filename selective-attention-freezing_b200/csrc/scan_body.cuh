@@ -80,10 +80,23 @@ struct ScanArgs {
 // 256-thread barrier that leaves barrier 0 (and any other warps of the CTA) alone
 __device__ __forceinline__ void scan_bar() { asm volatile("bar.sync 15, 256;" ::: "memory"); }
 
-// One CTA-wide pass over the whole sequence of head (b, h), columns [col0, col0+64).
+// Where the 64 fp32 words of a chunk's state are parked between the passes of the chunked scan: in the first
+// rows of the chunk's own OUTPUT slice (64 columns x sizeof(T) bytes per row), which the last pass overwrites
+// only after it has read them.  Word k of the chunk that starts at row p_lo:
+template <typename T>
+__device__ __forceinline__ float* scan_stash(T* ob_col0, int64_t row_stride, int p_lo, int k) {
+  constexpr int PER_ROW = SCAN_COLS * (int)sizeof(T) / 4;       // fp32 words per 64-column row slice
+  return reinterpret_cast<float*>(ob_col0 + (int64_t)(p_lo + k / PER_ROW) * row_stride) + (k % PER_ROW);
+}
+
+// One CTA-wide pass over positions [p_lo, p_hi) of head (b, h), columns [col0, col0+64).
 // Must be called by exactly the first 256 threads of the CTA, all of them.
-template <typename T, bool BWD>
-__device__ __forceinline__ void sink_decay_scan_cta(const ScanArgs& a, int b, int h, int col0) {
+// MODE 0: the whole job (carry starts at zero, outputs written).
+// MODE 1: state at the end of the range from a zero carry, parked in the stash; nothing else is written.
+// MODE 2: carry read from the stash (before any output is written), outputs written.
+template <typename T, bool BWD, int MODE = 0>
+__device__ __forceinline__ void sink_decay_scan_cta(const ScanArgs& a, int b, int h, int col0, int p_lo = 0,
+                                                    int p_hi = -1) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int cg = lane & 7, rl = lane >> 3;
   const int c0 = col0 + cg * 8;
@@ -112,6 +125,13 @@ __device__ __forceinline__ void sink_decay_scan_cta(const ScanArgs& a, int b, in
   for (int i = 0; i < rl; ++i) rg *= r8;
 
   const int Tn = a.T;
+  if (p_hi < 0) p_hi = Tn;
+  if (MODE == 2) {
+    T* ob0 = reinterpret_cast<T*>(a.out) + (int64_t)b * a.so[0] + (int64_t)h * a.so[1] + (int64_t)col0 * a.so[3];
+#pragma unroll
+    for (int c = 0; c < 8; ++c) carry[c] = *scan_stash<T>(ob0, a.so[2], p_lo, cg * 8 + c);
+    scan_bar();   // every thread holds its carry before the first output row lands on the stash
+  }
   // 16-bit vector path: the next block's rows are fetched (raw 16-byte words) while this block is scanned
   const bool pf = vec && sizeof(T) == 2;
   uint4 nraw[8];
@@ -120,12 +140,12 @@ __device__ __forceinline__ void sink_decay_scan_cta(const ScanArgs& a, int b, in
     for (int j = 0; j < 8; ++j) {
       const int p = blk + warp * 32 + rl * 8 + j;
       const int i = BWD ? (Tn - 1 - p) : p;
-      nraw[j] = (p < Tn) ? *reinterpret_cast<const uint4*>(ib + (int64_t)i * a.si[2]) : make_uint4(0, 0, 0, 0);
+      nraw[j] = (p < p_hi) ? *reinterpret_cast<const uint4*>(ib + (int64_t)i * a.si[2]) : make_uint4(0, 0, 0, 0);
     }
   };
-  if (pf) prefetch(0);
+  if (pf) prefetch(p_lo);
   int buf = 0;
-  for (int blk = 0; blk < Tn; blk += SCAN_ROWS, buf ^= 1) {
+  for (int blk = p_lo; blk < p_hi; blk += SCAN_ROWS, buf ^= 1) {
     const int p0 = blk + warp * 32 + rl * 8;   // scan position of this thread's first row
     float x[8][8];
     if (pf) {
@@ -139,13 +159,13 @@ __device__ __forceinline__ void sink_decay_scan_cta(const ScanArgs& a, int b, in
           x[j][2 * q + 1] = to_f<T>(*reinterpret_cast<const T*>(&h16));
         }
       }
-      if (blk + SCAN_ROWS < Tn) prefetch(blk + SCAN_ROWS);
+      if (blk + SCAN_ROWS < p_hi) prefetch(blk + SCAN_ROWS);
     }
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       const int p = p0 + j;
       const int i = BWD ? (Tn - 1 - p) : p;     // memory row
-      if (p < Tn && ncol > 0) {
+      if (p < p_hi && ncol > 0) {
         if (!pf) load8<T>(ib + (int64_t)i * a.si[2], a.si[3], vec, ncol, x[j]);
         if (BWD) {
           const float w = (1.f - alpha) * inv_z(r, log_r, i + 1);
@@ -201,6 +221,7 @@ __device__ __forceinline__ void sink_decay_scan_cta(const ScanArgs& a, int b, in
 #pragma unroll
       for (int c = 0; c < 8; ++c) carry[c] = nc[c];
     }
+    if (MODE == 1) continue;   // only the running state is wanted
     // state just before this thread's first row
     float cin[8];
 #pragma unroll
@@ -219,7 +240,7 @@ __device__ __forceinline__ void sink_decay_scan_cta(const ScanArgs& a, int b, in
 #pragma unroll
         for (int c = 0; c < 8; ++c) o[c] = fmaf(rp, cin[c], x[j][c]);
       }
-      if (p < Tn && ncol > 0) {
+      if (p < p_hi && ncol > 0) {
         if (BWD && i == 0) {
 #pragma unroll
           for (int c = 0; c < 8; ++c) row0[cg * 8 + c] = o[c];
@@ -229,6 +250,14 @@ __device__ __forceinline__ void sink_decay_scan_cta(const ScanArgs& a, int b, in
       }
       rp *= r;
     }
+  }
+  if (MODE == 1) {
+    if (warp == 0 && rl == 0) {
+      T* ob0 = reinterpret_cast<T*>(a.out) + (int64_t)b * a.so[0] + (int64_t)h * a.so[1] + (int64_t)col0 * a.so[3];
+#pragma unroll
+      for (int c = 0; c < 8; ++c) *scan_stash<T>(ob0, a.so[2], p_lo, cg * 8 + c) = carry[c];
+    }
+    return;
   }
   if (BWD) {
     // dV_0 = scan value + alpha * sum_i dY_i
@@ -253,6 +282,39 @@ __global__ void __launch_bounds__(SCAN_NT) sink_decay_scan_kernel(const __grid_c
   const int state = a.force_state >= 0 ? a.force_state : a.frozen[h];
   if (state != SAF_SINK_DECAY) return;
   sink_decay_scan_cta<T, BWD>(a, b, h, blockIdx.y * SCAN_COLS);
+}
+
+// ---- chunked forward scan: the sequence is cut into chunks of `chunk` rows that run in parallel ----------
+//   pass 1  every chunk: its state at the end from a zero carry              (reads V once)
+//   pass 2  per head: carries chained over the chunks, each chunk's incoming carry written back in place
+//   pass 3  every chunk: scan with its carry, outputs written                 (reads V again, writes Y)
+// 3/2 of the sequential scan's bytes, but nf*B*T/chunk CTAs instead of nf*B: bounded by HBM, not by latency.
+template <typename T, int MODE>
+__global__ void __launch_bounds__(SCAN_NT) sink_decay_chunk_kernel(const __grid_constant__ ScanArgs a, int chunk) {
+  const int bh = blockIdx.x, b = bh / a.H, h = bh % a.H;
+  const int state = a.force_state >= 0 ? a.force_state : a.frozen[h];
+  if (state != SAF_SINK_DECAY) return;
+  const int p_lo = blockIdx.y * chunk;
+  sink_decay_scan_cta<T, false, MODE>(a, b, h, blockIdx.z * SCAN_COLS, p_lo, min(a.T, p_lo + chunk));
+}
+
+template <typename T>
+__global__ void __launch_bounds__(SCAN_COLS) sink_decay_carry_kernel(const __grid_constant__ ScanArgs a, int chunk,
+                                                                     int n_chunks) {
+  const int bh = blockIdx.x, b = bh / a.H, h = bh % a.H;
+  const int state = a.force_state >= 0 ? a.force_state : a.frozen[h];
+  if (state != SAF_SINK_DECAY) return;
+  const int k = threadIdx.x;                 // column of the slice
+  const float r = a.sd_rho[h];
+  const float rL = (r <= 0.f) ? 0.f : (r >= 1.f ? 1.f : expf((float)chunk * log1pf(r - 1.f)));   // r^chunk
+  T* ob0 = reinterpret_cast<T*>(a.out) + (int64_t)b * a.so[0] + (int64_t)h * a.so[1] + (int64_t)(blockIdx.y * SCAN_COLS) * a.so[3];
+  __shared__ float tot[64][SCAN_COLS];       // host side keeps n_chunks <= 64
+  for (int c = 0; c < n_chunks; ++c) tot[c][k] = *scan_stash<T>(ob0, a.so[2], c * chunk, k);   // independent loads
+  float carry = 0.f;
+  for (int c = 0; c < n_chunks; ++c) {
+    *scan_stash<T>(ob0, a.so[2], c * chunk, k) = carry;
+    carry = fmaf(rL, carry, tot[c][k]);
+  }
 }
 
 }  // namespace saf

@@ -46,7 +46,8 @@ def test_frozen_pv(case, dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["fp32", "bf16"])
-@pytest.mark.parametrize("shape", [(2, 3, 1024, 64), (1, 4, 2500, 128), (2, 2, 333, 96), (1, 3, 16384, 64)],
+@pytest.mark.parametrize("shape", [(2, 3, 1024, 64), (1, 4, 2500, 128), (2, 2, 333, 96), (1, 3, 16384, 64),
+                                   (1, 2, 5000, 128), (1, 1, 4097, 64), (1, 1, 66000, 64)],   # chunk-parallel scan: ragged, 1-row tail, wider chunks
                          ids=lambda s: f"B{s[0]}nf{s[1]}T{s[2]}d{s[3]}")
 def test_frozen_pv_sink_decay_scan(shape, dtype):
     """Structured pattern through the scan == dense product with the materialised pattern
