@@ -30,6 +30,11 @@ struct DpParams {
   const int32_t* pidx;
   const int32_t* kvidx;
   int* status;
+  int dense_ok;              // dense-stored heads: pattern tiles come by TMA
+  // decomposed heads: pattern tiles exp(alpha_j + rho_{i-j} - z_i) are generated in shared memory
+  int dec_ok, dec_dtype;
+  const void *alpha, *rho, *z;
+  int64_t alpha_s[2], rho_s[2], z_s[2];
 };
 
 // can the bf16 TMA-staged kernel serve the dense heads of this call?
@@ -49,9 +54,11 @@ inline bool dense_pv_eligible(const SafMixedAttnArgs& a) {
 }
 
 // tensor maps (pattern planes, 64-key value tiles, output tiles) and parameters of the dense role
-inline int dense_pv_prepare(const SafMixedAttnArgs& a, CUtensorMap* mp_, CUtensorMap* mv, CUtensorMap* mo, DpParams* p) {
+inline int dense_pv_prepare(const SafMixedAttnArgs& a, bool dense, bool decomp, CUtensorMap* mp_, CUtensorMap* mv,
+                            CUtensorMap* mo, DpParams* p) {
   int rc;
-  {
+  memset(mp_, 0, sizeof(*mp_));
+  if (dense) {
     // pattern (P, S, S): box 64 keys x 128 rows of one plane; the plane index comes from pidx, its range is
     // the caller's contract
     uint64_t dims[3] = {(uint64_t)a.S, (uint64_t)a.S, (uint64_t)1 << 20};
@@ -78,7 +85,31 @@ inline int dense_pv_prepare(const SafMixedAttnArgs& a, CUtensorMap* mp_, CUtenso
   p->groups = (a.B + 256 / a.HD - 1) / (256 / a.HD);
   p->frozen = a.frozen; p->pidx = a.pidx; p->kvidx = a.kvidx;
   p->status = a.status;
+  p->dense_ok = dense ? 1 : 0;
+  p->dec_ok = decomp ? 1 : 0;
+  if (decomp) {
+    p->alpha = a.alpha.ptr; p->rho = a.rho.ptr; p->z = a.z.ptr;
+    for (int i = 0; i < 2; ++i) {
+      p->alpha_s[i] = a.alpha.stride[i];
+      p->rho_s[i] = a.rho.stride[i];
+      p->z_s[i] = a.z.stride[i];
+    }
+    p->dec_dtype = a.dec_dtype;
+  }
   return SAF_OK;
+}
+// decomposed heads need only the value / output layout the TMA path needs
+inline bool dense_pv_decomp_eligible(const SafMixedAttnArgs& a) {
+  auto al16 = [](const void* q) { return ((uintptr_t)q & 15) == 0; };
+  auto tma_ok = [&](const SafTensor& t) {
+    if (!t.ptr || !al16(t.ptr) || t.stride[3] != 1) return false;
+    for (int i = 0; i < 3; ++i)
+      if (t.stride[i] % 8 || t.stride[i] <= 0) return false;
+    return true;
+  };
+  if (a.dtype != SAF_BF16 || (a.HD != 64 && a.HD != 128)) return false;
+  if (!a.alpha.ptr || !a.rho.ptr || !a.z.ptr || a.SD < a.T) return false;
+  return tma_ok(a.v) && tma_ok(a.out);
 }
 inline unsigned dense_pv_slots(const DpParams& p) { return (unsigned)(p.n_pairs * p.H * p.groups); }
 
@@ -93,13 +124,17 @@ struct DpCfg {
   static constexpr int NB = 256 / HD;                 // batch rows per CTA
   static constexpr int V_BYTES = 64 * HD * 2;         // 64 keys x head_dim
   static constexpr int STAGE = 2 * DP_PATOM + NB * V_BYTES;   // 64 KB
-  static constexpr int SMEM_BYTES = 1024 + DP_NST * STAGE + 256;
+  static constexpr int SMEM_BYTES = 1024 + DP_NST * STAGE + 2048;
 };
 
 struct DpBars {
   uint64_t full[DP_NST], empty[DP_NST], need_mask, masked, acc_full;
+  uint64_t pgen[DP_NST];     // generated pattern tiles of a stage are in place (128 arrivals)
   uint32_t tmem_base;
+  alignas(16) float ga[64];  // decomposed heads: alpha of the step's 64 keys (x log2 e)
+  float gr[320];             // and rho over the distances the two tiles can see (x log2 e)
 };
+static_assert(sizeof(DpBars) <= 2048, "barrier block");
 
 // Body of one CTA; `slot` counts the CTAs of this role (heaviest row pairs first).  Every thread of the CTA
 // must call it (it contains CTA-wide barriers); warps 0-5 work, further warps only take part in the barriers.
@@ -113,7 +148,8 @@ __device__ __forceinline__ void dense_pv_cta(const CUtensorMap& mapP, const CUte
   const int rem = slot % per_mp;
   const int h = rem / p.groups, grp = rem % p.groups;
   const int state = p.force_state >= 0 ? p.force_state : p.frozen[h];
-  if (state != SAF_DENSE) return;
+  const bool gen = state == SAF_DECOMP && p.dec_ok;       // pattern tiles generated, not loaded
+  if (!gen && !(state == SAF_DENSE && p.dense_ok)) return;
   const int hp = p.pidx ? p.pidx[h] : h;
   const int hv = (p.HKV > 0) ? p.kvidx[h] : h;
   const int b0 = grp * C::NB;
@@ -134,6 +170,7 @@ __device__ __forceinline__ void dense_pv_cta(const CUtensorMap& mapP, const CUte
       mbar_init(&bars->full[s], 1);
       mbar_init(&bars->empty[s], 1);
     }
+    for (int s = 0; s < DP_NST; ++s) mbar_init(&bars->pgen[s], 128);
     mbar_init(&bars->need_mask, 1);
     mbar_init(&bars->masked, 128);
     mbar_init(&bars->acc_full, 1);
@@ -151,7 +188,7 @@ __device__ __forceinline__ void dense_pv_cta(const CUtensorMap& mapP, const CUte
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
     if (lane == 0) {
-      tma_prefetch_desc(&mapP);
+      if (!gen) tma_prefetch_desc(&mapP);
       tma_prefetch_desc(&mapV);
       for (int kh = 0; kh < nkh; ++kh) {
         const int s = kh % DP_NST;
@@ -161,9 +198,9 @@ __device__ __forceinline__ void dense_pv_cta(const CUtensorMap& mapP, const CUte
         }
         uint8_t* st = smem + s * C::STAGE;
         const bool t0 = kh < nk0;
-        mbar_expect_tx(&bars->full[s], (t0 ? DP_PATOM : 0) + (act1 ? DP_PATOM : 0) + nb * C::V_BYTES);
-        if (t0) tma_load_3d(st, &mapP, &bars->full[s], kh * 64, row0, hp);
-        if (act1) tma_load_3d(st + DP_PATOM, &mapP, &bars->full[s], kh * 64, row0 + 128, hp);
+        mbar_expect_tx(&bars->full[s], (gen ? 0 : (t0 ? DP_PATOM : 0) + (act1 ? DP_PATOM : 0)) + nb * C::V_BYTES);
+        if (!gen && t0) tma_load_3d(st, &mapP, &bars->full[s], kh * 64, row0, hp);
+        if (!gen && act1) tma_load_3d(st + DP_PATOM, &mapP, &bars->full[s], kh * 64, row0 + 128, hp);
         for (int bi = 0; bi < nb; ++bi)
 #pragma unroll
           for (int hh = 0; hh < HD / 64; ++hh)
@@ -183,7 +220,12 @@ __device__ __forceinline__ void dense_pv_cta(const CUtensorMap& mapP, const CUte
         dev_set_error(p.status, SAF_DEV_TIMEOUT_MMA, 71);
         break;
       }
-      if (diag_of(kh, 0) || diag_of(kh, 1)) {
+      if (gen) {
+        if (!mbar_wait(&bars->pgen[s], (kh / DP_NST) & 1)) {
+          dev_set_error(p.status, SAF_DEV_TIMEOUT_MMA, 75);
+          break;
+        }
+      } else if (diag_of(kh, 0) || diag_of(kh, 1)) {
         // the tile has landed: hand it to the mask helpers (they follow this barrier, never the ring's,
         // so they cannot run ahead of or behind the stage they are meant to edit)
         if (leader) mbar_arrive(&bars->need_mask);
@@ -221,8 +263,64 @@ __device__ __forceinline__ void dense_pv_cta(const CUtensorMap& mapP, const CUte
     const int r = quad * 32 + lane;            // row of the tile == TMEM lane
     const int etid = tid - 64;
     bool ok = true;
+    if (gen) {
+      // ---- decomposed head: this thread builds row r of both tiles, 64 keys per step
+      constexpr float L2E = 1.4426950408889634f;
+      const int i_row[2] = {row0 + r, row0 + 128 + r};
+      float zr[2];
+#pragma unroll
+      for (int t = 0; t < 2; ++t)   // +inf: rows past T give exact zeros
+        zr[t] = (i_row[t] < p.T) ? L2E * load_rt(p.z, (int64_t)h * p.z_s[0] + (int64_t)i_row[t] * p.z_s[1], p.dec_dtype) : INFINITY;
+      for (int kh = 0; kh < nkh && ok; ++kh) {
+        const int s = kh % DP_NST;
+        const int j0 = kh * 64;
+        // the vectors of this step: alpha of the 64 keys, rho over distances d0 .. d0 + 318
+        named_bar_sync(2, 128);                            // the previous step's readers are done
+        const int d0 = row0 - j0 - 63;
+        if (etid < 64) {
+          const int key = j0 + etid;
+          bars->ga[etid] = (key < p.T) ? L2E * load_rt(p.alpha, (int64_t)h * p.alpha_s[0] + (int64_t)key * p.alpha_s[1], p.dec_dtype) : 0.f;
+        }
+        for (int x = etid; x < 319; x += 128) {
+          const int d = d0 + x;
+          bars->gr[x] = (d >= 0 && d < p.T) ? L2E * load_rt(p.rho, (int64_t)h * p.rho_s[0] + (int64_t)d * p.rho_s[1], p.dec_dtype) : 0.f;
+        }
+        named_bar_sync(2, 128);
+        if (!mbar_wait(&bars->empty[s], ((kh / DP_NST) & 1) ^ 1)) {      // the stage's previous products are done
+          dev_set_error(p.status, SAF_DEV_TIMEOUT_EPI, 76);
+          ok = false;
+          break;
+        }
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+          if (t == 0 ? kh >= nk0 : !act1) continue;
+          uint8_t* rowp = smem + s * C::STAGE + t * DP_PATOM + r * 128;
+          // distance of key c from this row: (row0 + 128 t + r) - (j0 + c) = d0 + (63 + 128 t + r - c)
+          const float* grp_ = bars->gr + 63 + 128 * t + r;
+          const int lim = i_row[t] - j0;                    // keys c <= lim count
+#pragma unroll
+          for (int cc = 0; cc < 8; ++cc) {
+            uint32_t w[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int c = cc * 8 + 2 * e;
+              float x0 = bars->ga[c] + grp_[-c] - zr[t], x1 = bars->ga[c + 1] + grp_[-c - 1] - zr[t];
+              float p0, p1;
+              asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p0) : "f"(x0));
+              asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p1) : "f"(x1));
+              if (c > lim) p0 = 0.f;
+              if (c + 1 > lim) p1 = 0.f;
+              w[e] = pack_bf16(p0, p1);
+            }
+            *reinterpret_cast<uint4*>(rowp + ((cc ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+        }
+        fence_proxy_async_smem();
+        mbar_arrive(&bars->pgen[s]);
+      }
+    }
     int n_masked = 0;
-    for (int kh = max(0, nkh - 4); kh < nkh && ok; ++kh) {
+    for (int kh = gen ? nkh : max(0, nkh - 4); kh < nkh && ok; ++kh) {
       const bool d0 = diag_of(kh, 0), d1 = diag_of(kh, 1);
       if (!d0 && !d1) continue;
       const int s = kh % DP_NST;

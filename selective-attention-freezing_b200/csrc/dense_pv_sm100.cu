@@ -18,7 +18,7 @@ template <int HD>
 int dp_launch(const SafMixedAttnArgs& a, cudaStream_t st) {
   CUtensorMap mp_, mv, mo;
   DpParams p;
-  int rc = dense_pv_prepare(a, &mp_, &mv, &mo, &p);
+  int rc = dense_pv_prepare(a, true, false, &mp_, &mv, &mo, &p);
   if (rc) return rc;
   static bool attr_set = false;
   if (!attr_set) {

@@ -651,17 +651,23 @@ int launch_typed(const SafMixedAttnArgs& a, uint32_t want, cudaStream_t st) {
   }
   p.dec_dtype = a.dec_dtype;
   if (!(want & (1u << SAF_DENSE))) p.patt = nullptr;       // another launch serves these heads: their CTAs exit
+  if (!(want & (1u << SAF_DECOMP))) p.alpha = nullptr;
   CUtensorMap mpat, mv64;
   memset(&mpat, 0, sizeof(mpat));
   memset(&mv64, 0, sizeof(mv64));
-  if (p.patt && dense_pv_eligible(a)) {
-    // bf16 patterns TMA can address: the dense role takes these heads, the flash CTAs of dense heads exit
-    CUtensorMap mo2;
-    if ((rc = dense_pv_prepare(a, &mpat, &mv64, &mo2, &p.dense))) return rc;
-    p.dense_slots = (int)dense_pv_slots(p.dense);
-    p.patt = nullptr;
+  {
+    // the batch-shared pattern role: dense-stored bf16 patterns by TMA, decomposed patterns generated in
+    // shared memory; the flash CTAs of those heads then exit
+    const bool dense = p.patt && dense_pv_eligible(a);
+    const bool decomp = p.alpha && dense_pv_decomp_eligible(a);
+    if (dense || decomp) {
+      CUtensorMap mo2;
+      if ((rc = dense_pv_prepare(a, dense, decomp, &mpat, &mv64, &mo2, &p.dense))) return rc;
+      p.dense_slots = (int)dense_pv_slots(p.dense);
+      if (dense) p.patt = nullptr;
+      if (decomp) p.alpha = nullptr;
+    }
   }
-  if (!(want & (1u << SAF_DECOMP))) p.alpha = nullptr;
   if (a.sd_alpha && a.sd_rho && (want & (1u << SAF_SINK_DECAY))) {
     p.has_scan = 1;
     ScanArgs& s = p.scan;

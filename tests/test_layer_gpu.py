@@ -153,3 +153,34 @@ def test_capture_path_and_state_dict_round_trip():
     assert torch.equal(y, y2)
     for name in ("dyn_frozen", "dyn_pattern"):
         assert name in m.state_dict()
+
+
+def test_inference_layer_is_cuda_graph_capturable():
+    """The reference captures its prefill in a CUDA graph (nanogpt/bench_checkpoint_prefill.py:89-109): after one
+    warm-up call (host copies of the index tensors are cached then) nothing in the path synchronises or allocates
+    outside torch's graph pool, and a replay on new input matches the eager call bit for bit."""
+    B, T, C, H, fz, seed, kind = cases.LAYER_CASES["config0"]
+    x, ws = cases.layer_inputs(B, T, C, H, seed)
+    patt, _ = cases.layer_patterns(kind, len(fz), T, seed)
+    m, rope = build(C, H, T, ws, dtype=torch.bfloat16)
+    m.freeze_heads(fz, patt.cuda(), detect_structured=True)
+    static_x = x.bfloat16().cuda()
+    with torch.inference_mode():
+        y_eager = m(static_x, rope=rope).clone()      # warm-up
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            m(static_x, rope=rope)
+        torch.cuda.current_stream().wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            static_y = m(static_x, rope=rope)
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(static_y, y_eager)
+        x2 = torch.randn(B, T, C, generator=torch.Generator().manual_seed(5)).bfloat16().cuda()
+        y2_eager = m(x2, rope=rope).clone()
+        static_x.copy_(x2)
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(static_y, y2_eager)
