@@ -100,6 +100,9 @@ inline int dense_pv_prepare(const SafMixedAttnArgs& a, bool dense, bool decomp, 
 }
 // decomposed heads need only the value / output layout the TMA path needs
 inline bool dense_pv_decomp_eligible(const SafMixedAttnArgs& a) {
+#ifdef SAF_NO_DECOMP_ROLE
+  return false;   // comparison builds: decomposed heads stay on the per-batch-row register path
+#endif
   auto al16 = [](const void* q) { return ((uintptr_t)q & 15) == 0; };
   auto tma_ok = [&](const SafTensor& t) {
     if (!t.ptr || !al16(t.ptr) || t.stride[3] != 1) return false;
@@ -124,17 +127,18 @@ struct DpCfg {
   static constexpr int NB = 256 / HD;                 // batch rows per CTA
   static constexpr int V_BYTES = 64 * HD * 2;         // 64 keys x head_dim
   static constexpr int STAGE = 2 * DP_PATOM + NB * V_BYTES;   // 64 KB
-  static constexpr int SMEM_BYTES = 1024 + DP_NST * STAGE + 2048;
+  static constexpr int SMEM_BYTES = 1024 + DP_NST * STAGE + 6144;
 };
 
 struct DpBars {
   uint64_t full[DP_NST], empty[DP_NST], need_mask, masked, acc_full;
-  uint64_t pgen[DP_NST];     // generated pattern tiles of a stage are in place (128 arrivals)
+  uint64_t pgen[DP_NST];     // generated pattern tiles of a stage are in place (256 arrivals: both tile groups)
   uint32_t tmem_base;
-  alignas(16) float ga[64];  // decomposed heads: alpha of the step's 64 keys (x log2 e)
-  float gr[320];             // and rho over the distances the two tiles can see (x log2 e)
+  // decomposed heads, per tile group and double-buffered over the steps (all x log2 e):
+  float ga[2][2][64];        // alpha of the step's 64 keys
+  float gr[2][2][192];       // rho over the 191 distances a 128-row tile sees against 64 keys
 };
-static_assert(sizeof(DpBars) <= 2048, "barrier block");
+static_assert(sizeof(DpBars) <= 6144, "barrier block");
 
 // Body of one CTA; `slot` counts the CTAs of this role (heaviest row pairs first).  Every thread of the CTA
 // must call it (it contains CTA-wide barriers); warps 0-5 work, further warps only take part in the barriers.
@@ -170,7 +174,7 @@ __device__ __forceinline__ void dense_pv_cta(const CUtensorMap& mapP, const CUte
       mbar_init(&bars->full[s], 1);
       mbar_init(&bars->empty[s], 1);
     }
-    for (int s = 0; s < DP_NST; ++s) mbar_init(&bars->pgen[s], 128);
+    for (int s = 0; s < DP_NST; ++s) mbar_init(&bars->pgen[s], 256);
     mbar_init(&bars->need_mask, 1);
     mbar_init(&bars->masked, 128);
     mbar_init(&bars->acc_full, 1);
@@ -257,68 +261,85 @@ __device__ __forceinline__ void dense_pv_cta(const CUtensorMap& mapP, const CUte
     }
     if (leader) umma_commit(&bars->acc_full);
     __syncwarp();
-  } else if (warp < 6) {
+  }
+  if (gen && warp >= 2 && warp < 10) {
+    // ---------------------------------------------------------------- decomposed head: pattern generation
+    // warps 2-5 build tile 0, warps 6-9 tile 1 (needs a CTA of at least 320 threads): thread = row, 64 keys per
+    // step.  The step's alpha / rho values are fetched one step ahead into registers and handed over through
+    // double-buffered shared memory, so no global latency sits on the step.
+    constexpr float L2E = 1.4426950408889634f;
+    const int t = (warp - 2) >> 2;                       // tile of this group
+    const int gt = (tid - 64) & 127;                     // thread inside the group
+    const int r = gt;                                    // row of the tile
+    const int i_row = row0 + 128 * t + r;
+    const bool t_on = t == 0 || act1;
+    const int nk_t = t == 0 ? nk0 : nkh;                 // steps in which this tile takes part
+    // +inf: rows past T give exact zeros
+    const float zr = (i_row < p.T) ? L2E * load_rt(p.z, (int64_t)h * p.z_s[0] + (int64_t)i_row * p.z_s[1], p.dec_dtype) : INFINITY;
+    auto fetch_a = [&](int kh) -> float {                // alpha of key 64 kh + gt   (gt < 64)
+      const int key = kh * 64 + gt;
+      return (gt < 64 && key < p.T) ? L2E * load_rt(p.alpha, (int64_t)h * p.alpha_s[0] + (int64_t)key * p.alpha_s[1], p.dec_dtype) : 0.f;
+    };
+    auto fetch_r = [&](int kh, int x) -> float {         // rho at distance (row0 + 128 t - 64 kh - 63) + x
+      const int d = row0 + 128 * t - kh * 64 - 63 + x;
+      return (x < 191 && d >= 0 && d < p.T) ? L2E * load_rt(p.rho, (int64_t)h * p.rho_s[0] + (int64_t)d * p.rho_s[1], p.dec_dtype) : 0.f;
+    };
+    float na = 0.f, nr0 = 0.f, nr1 = 0.f;
+    if (t_on && nk_t > 0) {
+      na = fetch_a(0); nr0 = fetch_r(0, gt); nr1 = fetch_r(0, gt + 128);
+    }
+    bool ok = true;
+    for (int kh = 0; kh < nkh && ok; ++kh) {
+      const int s = kh % DP_NST, vb = kh & 1;
+      const bool on = t_on && kh < nk_t;
+      if (on) {
+        // hand this step's vectors over; the buffer was last read two steps ago (one barrier per step in between)
+        if (gt < 64) bars->ga[t][vb][gt] = na;
+        bars->gr[t][vb][gt] = nr0;
+        if (gt + 128 < 192) bars->gr[t][vb][gt + 128] = nr1;
+        named_bar_sync(2 + t, 128);
+        if (kh + 1 < nk_t) {
+          na = fetch_a(kh + 1); nr0 = fetch_r(kh + 1, gt); nr1 = fetch_r(kh + 1, gt + 128);
+        }
+      }
+      if (!mbar_wait(&bars->empty[s], ((kh / DP_NST) & 1) ^ 1)) {      // the stage's previous products are done
+        dev_set_error(p.status, SAF_DEV_TIMEOUT_EPI, 76);
+        ok = false;
+        break;
+      }
+      if (on) {
+        uint8_t* rowp = smem + s * C::STAGE + t * DP_PATOM + r * 128;
+        // distance of key c from this row = d0 + (63 + r - c)
+        const float* ga_ = bars->ga[t][vb];
+        const float* gr_ = bars->gr[t][vb] + 63 + r;
+        const int lim = i_row - kh * 64;                   // keys c <= lim count
+#pragma unroll
+        for (int cc = 0; cc < 8; ++cc) {
+          uint32_t w[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int c = cc * 8 + 2 * e;
+            const float x0 = ga_[c] + gr_[-c] - zr, x1 = ga_[c + 1] + gr_[-c - 1] - zr;
+            float p0, p1;
+            asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p0) : "f"(x0));
+            asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p1) : "f"(x1));
+            if (c > lim) p0 = 0.f;
+            if (c + 1 > lim) p1 = 0.f;
+            w[e] = pack_bf16(p0, p1);
+          }
+          *reinterpret_cast<uint4*>(rowp + ((cc ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+        fence_proxy_async_smem();
+      }
+      mbar_arrive(&bars->pgen[s]);
+    }
+  }
+  if (warp >= 2 && warp < 6) {
     // ---------------------------------------------------------------- mask helpers, then epilogue
     const int quad = warp & 3;
     const int r = quad * 32 + lane;            // row of the tile == TMEM lane
     const int etid = tid - 64;
     bool ok = true;
-    if (gen) {
-      // ---- decomposed head: this thread builds row r of both tiles, 64 keys per step
-      constexpr float L2E = 1.4426950408889634f;
-      const int i_row[2] = {row0 + r, row0 + 128 + r};
-      float zr[2];
-#pragma unroll
-      for (int t = 0; t < 2; ++t)   // +inf: rows past T give exact zeros
-        zr[t] = (i_row[t] < p.T) ? L2E * load_rt(p.z, (int64_t)h * p.z_s[0] + (int64_t)i_row[t] * p.z_s[1], p.dec_dtype) : INFINITY;
-      for (int kh = 0; kh < nkh && ok; ++kh) {
-        const int s = kh % DP_NST;
-        const int j0 = kh * 64;
-        // the vectors of this step: alpha of the 64 keys, rho over distances d0 .. d0 + 318
-        named_bar_sync(2, 128);                            // the previous step's readers are done
-        const int d0 = row0 - j0 - 63;
-        if (etid < 64) {
-          const int key = j0 + etid;
-          bars->ga[etid] = (key < p.T) ? L2E * load_rt(p.alpha, (int64_t)h * p.alpha_s[0] + (int64_t)key * p.alpha_s[1], p.dec_dtype) : 0.f;
-        }
-        for (int x = etid; x < 319; x += 128) {
-          const int d = d0 + x;
-          bars->gr[x] = (d >= 0 && d < p.T) ? L2E * load_rt(p.rho, (int64_t)h * p.rho_s[0] + (int64_t)d * p.rho_s[1], p.dec_dtype) : 0.f;
-        }
-        named_bar_sync(2, 128);
-        if (!mbar_wait(&bars->empty[s], ((kh / DP_NST) & 1) ^ 1)) {      // the stage's previous products are done
-          dev_set_error(p.status, SAF_DEV_TIMEOUT_EPI, 76);
-          ok = false;
-          break;
-        }
-#pragma unroll
-        for (int t = 0; t < 2; ++t) {
-          if (t == 0 ? kh >= nk0 : !act1) continue;
-          uint8_t* rowp = smem + s * C::STAGE + t * DP_PATOM + r * 128;
-          // distance of key c from this row: (row0 + 128 t + r) - (j0 + c) = d0 + (63 + 128 t + r - c)
-          const float* grp_ = bars->gr + 63 + 128 * t + r;
-          const int lim = i_row[t] - j0;                    // keys c <= lim count
-#pragma unroll
-          for (int cc = 0; cc < 8; ++cc) {
-            uint32_t w[4];
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const int c = cc * 8 + 2 * e;
-              float x0 = bars->ga[c] + grp_[-c] - zr[t], x1 = bars->ga[c + 1] + grp_[-c - 1] - zr[t];
-              float p0, p1;
-              asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p0) : "f"(x0));
-              asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p1) : "f"(x1));
-              if (c > lim) p0 = 0.f;
-              if (c + 1 > lim) p1 = 0.f;
-              w[e] = pack_bf16(p0, p1);
-            }
-            *reinterpret_cast<uint4*>(rowp + ((cc ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
-          }
-        }
-        fence_proxy_async_smem();
-        mbar_arrive(&bars->pgen[s]);
-      }
-    }
     int n_masked = 0;
     for (int kh = gen ? nkh : max(0, nkh - 4); kh < nkh && ok; ++kh) {
       const bool d0 = diag_of(kh, 0), d1 = diag_of(kh, 1);

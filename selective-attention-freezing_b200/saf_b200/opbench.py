@@ -43,7 +43,7 @@ def main():
     ap.add_argument("--B", type=int, default=None)
     ap.add_argument("--T", type=int, default=None)
     ap.add_argument("--reps", type=int, default=5)
-    ap.add_argument("--frozen", default="sink_decay", choices=["sink_decay", "dense", "none"])
+    ap.add_argument("--frozen", default="sink_decay", choices=["sink_decay", "dense", "decomposed", "none"])
     args = ap.parse_args()
     w = dict(synthetic.WORKLOADS[args.workload])
     if args.B:
@@ -58,7 +58,7 @@ def main():
     fz = synthetic.frozen_heads_for_layer(H, nf, 1337, 0) if nf else []
     live = [h for h in range(H) if h not in fz]
     g = torch.Generator().manual_seed(7)
-    state = 3 if args.frozen == "sink_decay" else 1
+    state = {"sink_decay": 3, "dense": 1, "decomposed": 2, "none": 0}[args.frozen]
     frozen = torch.tensor([state if h in fz else 0 for h in range(H)], dtype=torch.int32, device=dev)
     hidx = torch.zeros(H, dtype=torch.int32)
     for s, h in enumerate(live):
@@ -76,6 +76,10 @@ def main():
     if nf and args.frozen == "sink_decay":
         a, r = synthetic.sink_decay_params(H, 2337)
         kw["sink_decay"] = (a.float().to(dev), r.float().to(dev))
+    elif nf and args.frozen == "decomposed":
+        alpha = (torch.randn(H, T, generator=g) * 0.5).to(dev)
+        rho = (-0.002 * torch.arange(T).float()[None] + torch.randn(H, T, generator=g) * 0.3).to(dev)
+        kw.update(alpha=alpha, rho=rho, z=ops.decomposed_logz(alpha, rho))
     elif nf:
         p = torch.rand(nf, T, T, generator=g).tril_()
         patt = (p / p.sum(-1, keepdim=True)).bfloat16().to(dev)
