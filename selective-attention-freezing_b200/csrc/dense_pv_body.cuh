@@ -116,6 +116,54 @@ inline bool dense_pv_decomp_eligible(const SafMixedAttnArgs& a) {
 }
 inline unsigned dense_pv_slots(const DpParams& p) { return (unsigned)(p.n_pairs * p.H * p.groups); }
 
+// backward of dense-stored heads, dV = tril(P)^T dO: same role with the pattern read as a transposed (MN-major)
+// A operand in 64-query steps.  Maps: pattern in 64 x 64 boxes, dO in 64-row boxes, dV in 128-row boxes.
+inline bool dense_dv_eligible(const SafMixedAttnBwdArgs& g) {
+  const SafMixedAttnArgs& a = g.fwd;
+  auto al16 = [](const void* q) { return ((uintptr_t)q & 15) == 0; };
+  auto tma_ok = [&](const SafTensor& t) {
+    if (!t.ptr || !al16(t.ptr) || t.stride[3] != 1) return false;
+    for (int i = 0; i < 3; ++i)
+      if (t.stride[i] % 8 || t.stride[i] <= 0) return false;
+    return true;
+  };
+  if (a.dtype != SAF_BF16 || (a.HD != 64 && a.HD != 128) || a.HKV > 0) return false;
+  if (!a.patt.ptr || a.patt_dtype != SAF_BF16 || a.patt.stride[2] != 1 || !al16(a.patt.ptr)) return false;
+  if (a.patt.stride[0] % 8 || a.patt.stride[1] % 8 || a.patt.stride[0] <= 0 || a.patt.stride[1] <= 0) return false;
+  if (a.S < a.T) return false;
+  return tma_ok(g.dout) && tma_ok(g.dv);
+}
+inline int dense_dv_prepare(const SafMixedAttnBwdArgs& g, CUtensorMap* mp_, CUtensorMap* mdo, CUtensorMap* mdv, DpParams* p) {
+  const SafMixedAttnArgs& a = g.fwd;
+  int rc;
+  {
+    uint64_t dims[3] = {(uint64_t)a.S, (uint64_t)a.S, (uint64_t)1 << 20};
+    uint64_t strides[3] = {0, (uint64_t)a.patt.stride[1] * 2, (uint64_t)a.patt.stride[0] * 2};
+    uint32_t box[3] = {64, 64, 1};
+    if ((rc = make_tensor_map_bf16(mp_, a.patt.ptr, 3, dims, strides, box, true))) return rc;
+  }
+  {
+    uint64_t dims[4] = {(uint64_t)a.HD, (uint64_t)a.T, (uint64_t)a.H, (uint64_t)a.B};
+    uint64_t strides[4] = {0, (uint64_t)g.dout.stride[2] * 2, (uint64_t)g.dout.stride[1] * 2, (uint64_t)g.dout.stride[0] * 2};
+    uint32_t box[4] = {64, 64, 1, 1};
+    if ((rc = make_tensor_map_bf16(mdo, g.dout.ptr, 4, dims, strides, box, true))) return rc;
+  }
+  {
+    uint64_t dims[4] = {(uint64_t)a.HD, (uint64_t)a.T, (uint64_t)a.H, (uint64_t)a.B};
+    uint64_t strides[4] = {0, (uint64_t)g.dv.stride[2] * 2, (uint64_t)g.dv.stride[1] * 2, (uint64_t)g.dv.stride[0] * 2};
+    uint32_t box[4] = {64, 128, 1, 1};
+    if ((rc = make_tensor_map_bf16(mdv, g.dv.ptr, 4, dims, strides, box, false))) return rc;
+  }
+  memset(p, 0, sizeof(*p));
+  p->B = a.B; p->H = a.H; p->T = a.T; p->force_state = a.force_state; p->HKV = 0;
+  p->n_pairs = (a.T + 255) / 256;
+  p->groups = (a.B + 256 / a.HD - 1) / (256 / a.HD);
+  p->frozen = a.frozen; p->pidx = a.pidx; p->kvidx = nullptr;
+  p->status = a.status;
+  p->dense_ok = 1;
+  return SAF_OK;
+}
+
 namespace {
 
 constexpr int DP_THREADS = 192;
@@ -408,6 +456,207 @@ __device__ __forceinline__ void dense_pv_cta(const CUtensorMap& mapP, const CUte
         if (etid == 0 && ok) {
 #pragma unroll
           for (int hh = 0; hh < HD / 64; ++hh) tma_store_4d(&mapO, stage + hh * 16384, hh * 64, row0 + t * 128, h, b0 + bi);
+          tma_store_commit();
+        }
+      }
+    }
+    if (etid == 0) tma_store_wait_all();
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem, 512);
+}
+
+
+// ---------------------------------------------------------------------------------------------------------
+// Backward of dense-stored heads: dV[b, h, j, :] = sum_{i >= j} P[pidx[h], i, j] dO[b, h, i, :]
+// (_pv_bwd_kernel, kernel/frozen_attn.py:91-128).  CTA = two consecutive 128-key tiles of one head for NB batch
+// rows; queries advance 64 at a time from the tiles' own rows to the end of the sequence.  The pattern block
+// [64 queries x 128 keys] lands by TMA as two 64 x 64 boxes and is read by the tensor core as a transposed
+// (MN-major) A operand, dO tiles as MN-major B operands: nothing is transposed in shared memory.
+// Same calling rules as dense_pv_cta.
+template <int HD>
+__device__ __forceinline__ void dense_dv_cta(const CUtensorMap& mapP, const CUtensorMap& mapdO, const CUtensorMap& mapdV,
+                                             const DpParams& p, int slot, uint8_t* smem) {
+  using C = DpCfg<HD>;
+  // CTA -> (head, batch group, key pair); heaviest (first) key pairs first
+  const int per_kp = p.H * p.groups;
+  const int kp = slot / per_kp;
+  const int rem = slot % per_kp;
+  const int h = rem / p.groups, grp = rem % p.groups;
+  const int state = p.force_state >= 0 ? p.force_state : p.frozen[h];
+  if (!(state == SAF_DENSE && p.dense_ok)) return;
+  const int hp = p.pidx ? p.pidx[h] : h;
+  const int b0 = grp * C::NB;
+  const int nb = min(C::NB, p.B - b0);
+  const int key0 = kp * 256;
+  const bool act1 = key0 + 128 < p.T;
+  const int n_half = (p.T + 63) / 64;
+  const int qh0 = 4 * kp;                                  // first 64-query step (tile 0's own rows)
+  const int n_steps = n_half - qh0;
+  // tile 1 starts two steps later; a tile's first two steps hold its above-diagonal entries
+  auto tile_on = [&](int st, int t) { return t == 0 ? true : (act1 && st >= 2); };
+  auto diag_of = [&](int st, int t) { return st >= 2 * t && st < 2 * t + 2 && (t == 0 || act1); };
+
+  DpBars* bars = reinterpret_cast<DpBars*>(smem + DP_NST * C::STAGE);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid == 0) {
+    for (int s = 0; s < DP_NST; ++s) {
+      mbar_init(&bars->full[s], 1);
+      mbar_init(&bars->empty[s], 1);
+    }
+    mbar_init(&bars->need_mask, 1);
+    mbar_init(&bars->masked, 128);
+    mbar_init(&bars->acc_full, 1);
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&bars->tmem_base, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = bars->tmem_base;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      tma_prefetch_desc(&mapP);
+      tma_prefetch_desc(&mapdO);
+      for (int st = 0; st < n_steps; ++st) {
+        const int s = st % DP_NST, qh = qh0 + st;
+        if (!mbar_wait(&bars->empty[s], ((st / DP_NST) & 1) ^ 1)) {
+          dev_set_error(p.status, SAF_DEV_TIMEOUT_TMA, 80);
+          break;
+        }
+        uint8_t* sp = smem + s * C::STAGE;
+        const bool t1 = tile_on(st, 1);
+        mbar_expect_tx(&bars->full[s], (t1 ? 2 : 1) * DP_PATOM + nb * C::V_BYTES);
+        for (int t = 0; t < (t1 ? 2 : 1); ++t)
+#pragma unroll
+          for (int a = 0; a < 2; ++a)     // two 64-key atoms of [64 queries x 128 bytes]
+            tma_load_3d(sp + t * DP_PATOM + a * 8192, &mapP, &bars->full[s], key0 + 128 * t + 64 * a, qh * 64, hp);
+        for (int bi = 0; bi < nb; ++bi)
+#pragma unroll
+          for (int hh = 0; hh < HD / 64; ++hh)
+            tma_load_4d(sp + 2 * DP_PATOM + bi * C::V_BYTES + hh * 8192, &mapdO, &bars->full[s], hh * 64, qh * 64, h, b0 + bi);
+      }
+    }
+  } else if (warp == 1) {
+    const bool leader = elect_one();
+    const uint32_t idesc = umma_idesc_bf16(128, HD, 1, 1);     // A = P^T and B = dO both MN-major
+    const uint32_t sbase = smem_u32(smem);
+    int n_masked = 0;
+    for (int st = 0; st < n_steps; ++st) {
+      const int s = st % DP_NST;
+      if (!mbar_wait(&bars->full[s], (st / DP_NST) & 1)) {
+        dev_set_error(p.status, SAF_DEV_TIMEOUT_MMA, 81);
+        break;
+      }
+      if (diag_of(st, 0) || diag_of(st, 1)) {
+        if (leader) mbar_arrive(&bars->need_mask);
+        __syncwarp();
+        if (!mbar_wait(&bars->masked, n_masked & 1)) {
+          dev_set_error(p.status, SAF_DEV_TIMEOUT_MMA, 82);
+          break;
+        }
+        ++n_masked;
+      }
+      tc_fence_after();
+      const uint32_t sp = sbase + s * C::STAGE;
+      if (leader) {
+        for (int t = 0; t < 2; ++t) {
+          if (!tile_on(st, t)) continue;
+          const uint32_t pa = sp + t * DP_PATOM;
+          const bool first = (st == 2 * t);                   // this tile's first product
+          for (int bi = 0; bi < nb; ++bi) {
+            const uint32_t da = sp + 2 * DP_PATOM + bi * C::V_BYTES;
+            const uint32_t d = tmem + (t * C::NB + bi) * HD;
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks)
+              umma_ss(d, umma_smem_desc_sw128(pa + ks * 2048, 8192, 1024), umma_smem_desc_sw128(da + ks * 2048, 8192, 1024),
+                      idesc, !(first && ks == 0));
+          }
+        }
+        umma_commit(&bars->empty[s]);
+      }
+      __syncwarp();
+    }
+    if (leader) umma_commit(&bars->acc_full);
+    __syncwarp();
+  } else if (warp < 6) {
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;            // key row of the tile == TMEM lane
+    const int etid = tid - 64;
+    bool ok = true;
+    int n_masked = 0;
+    for (int st = 0; st < min(n_steps, 4) && ok; ++st) {
+      const bool d0 = diag_of(st, 0), d1 = diag_of(st, 1);
+      if (!d0 && !d1) continue;
+      const int s = st % DP_NST;
+      if (!mbar_wait(&bars->need_mask, n_masked & 1)) {
+        dev_set_error(p.status, SAF_DEV_TIMEOUT_EPI, 83);
+        ok = false;
+        break;
+      }
+      ++n_masked;
+      const int t = d0 ? 0 : 1;
+      // thread -> (64-key atom a, query row q of the step); query and key both counted from the tile's first row
+      const int a = etid >> 6, q = etid & 63;
+      const int q_rel = (st - 2 * t) * 64 + q;
+      uint8_t* rowp = smem + s * C::STAGE + t * DP_PATOM + a * 8192 + q * 128;
+#pragma unroll
+      for (int cc = 0; cc < 8; ++cc) {
+        const int k_lo = a * 64 + cc * 8;                      // first key of this 16-byte chunk
+        if (k_lo + 7 <= q_rel) continue;                       // all eight keys at or before the query
+        uint4* w4 = reinterpret_cast<uint4*>(rowp + ((cc ^ (q & 7)) << 4));
+        uint4 v = *w4;
+        uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          if (k_lo + 2 * e > q_rel) w[e] &= 0xffff0000u;
+          if (k_lo + 2 * e + 1 > q_rel) w[e] &= 0x0000ffffu;
+        }
+        *w4 = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+      fence_proxy_async_smem();
+      mbar_arrive(&bars->masked);
+    }
+    if (ok && !mbar_wait(&bars->acc_full, 0)) {
+      dev_set_error(p.status, SAF_DEV_TIMEOUT_EPI, 84);
+      ok = false;
+    }
+    tc_fence_after();
+    int n_st = 0;
+    for (int t = 0; t < 2; ++t) {
+      if (t == 1 && (!act1 || n_steps <= 2)) break;           // tile 1 never accumulated anything
+      for (int bi = 0; bi < nb; ++bi, ++n_st) {
+        uint8_t* stage = smem + (n_st & 1) * (128 * HD * 2);
+        if (etid == 0) tma_store_wait_read1();
+        named_bar_sync(1, 128);
+        const uint32_t tsrc = tmem + ((uint32_t)(quad * 32) << 16) + (t * C::NB + bi) * HD;
+#pragma unroll
+        for (int c0 = 0; c0 < HD; c0 += 32) {
+          uint32_t o[32];
+          tmem_ld32(tsrc + c0, o);
+          tmem_ld_wait();
+          uint8_t* dst = stage + (c0 >> 6) * 16384 + r * 128;
+          const int cbase = (c0 & 63) >> 3;
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            uint4 qv;
+            qv.x = pack_bf16(__uint_as_float(o[c * 8 + 0]), __uint_as_float(o[c * 8 + 1]));
+            qv.y = pack_bf16(__uint_as_float(o[c * 8 + 2]), __uint_as_float(o[c * 8 + 3]));
+            qv.z = pack_bf16(__uint_as_float(o[c * 8 + 4]), __uint_as_float(o[c * 8 + 5]));
+            qv.w = pack_bf16(__uint_as_float(o[c * 8 + 6]), __uint_as_float(o[c * 8 + 7]));
+            *reinterpret_cast<uint4*>(dst + (((cbase + c) ^ (r & 7)) << 4)) = qv;
+          }
+        }
+        fence_proxy_async_smem();
+        named_bar_sync(1, 128);
+        if (etid == 0 && ok) {
+#pragma unroll
+          for (int hh = 0; hh < HD / 64; ++hh) tma_store_4d(&mapdV, stage + hh * 16384, hh * 64, key0 + t * 128, h, b0 + bi);
           tma_store_commit();
         }
       }

@@ -25,8 +25,10 @@
 // The sm_scale factor of dS is applied once to the finished dK / dQ accumulators.
 // Every wait is bounded; on expiry the kernel records a code in *status and falls through.
 #include "saf_internal.h"
+#include "dense_pv_body.cuh"
 #include "scan_body.cuh"
 #include "sm100_prims.cuh"
+#include <string.h>
 
 namespace saf {
 namespace {
@@ -49,7 +51,9 @@ struct BwdCfg {
   static constexpr int NSTAGE = (HD == 64) ? 3 : 2;   // dK/dV kernel: ring of streamed (Q_i, dO_i) pairs
   static constexpr int KS = 3;                        // dQ kernel: K ring (a K tile lives until its dQ product)
   static constexpr int VS = (HD == 64) ? 3 : 2;       // dQ kernel: V ring (a V tile is done after its dP product)
-  static constexpr int SMEM_BYTES = 1024 + 2 * TILE_BYTES + NSTAGE * 2 * TILE_BYTES + 4096;
+  static constexpr int SMEM_DKDV = 1024 + 2 * TILE_BYTES + NSTAGE * 2 * TILE_BYTES + 4096;
+  // the dK/dV launch also hosts the dense-pattern dV role, which brings its own ring
+  static constexpr int SMEM_BYTES = SMEM_DKDV > DpCfg<HD>::SMEM_BYTES ? SMEM_DKDV : DpCfg<HD>::SMEM_BYTES;
   static constexpr int SMEM_BYTES_DQ = 1024 + 2 * TILE_BYTES + (KS + VS) * TILE_BYTES + 512;
   static constexpr int TMEM_COLS = 512;
 };
@@ -67,6 +71,9 @@ struct BwdParams {
   // structured frozen heads: their reverse scan (dV = P^T dO) runs in the leading CTAs of the dK/dV launch
   int scan_slots;
   ScanArgs scan;
+  // dense-stored frozen heads: dV = tril(P)^T dO as a TMA-staged GEMM in the next CTAs of the dK/dV launch
+  int dense_slots;
+  DpParams dense;
 };
 
 struct BwdBars {
@@ -233,6 +240,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
 flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
                       const __grid_constant__ CUtensorMap mapV, const __grid_constant__ CUtensorMap mapdO,
                       const __grid_constant__ CUtensorMap mapdK, const __grid_constant__ CUtensorMap mapdV,
+                      const __grid_constant__ CUtensorMap mapP64, const __grid_constant__ CUtensorMap mapdO64,
                       const __grid_constant__ BwdParams p) {
   using C = BwdCfg<HD>;
   if ((int)blockIdx.x < p.scan_slots) {
@@ -244,8 +252,14 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
     if (state == SAF_SINK_DECAY && threadIdx.x < SCAN_NT) sink_decay_scan_cta<__nv_bfloat16, true>(p.scan, sb, sh, col0);
     return;
   }
+  if ((int)blockIdx.x < p.scan_slots + p.dense_slots) {
+    extern __shared__ uint8_t dense_smem_raw[];
+    uint8_t* dsm = (uint8_t*)(((uintptr_t)dense_smem_raw + 1023) & ~(uintptr_t)1023);
+    dense_dv_cta<HD>(mapP64, mapdO64, mapdV, p.dense, (int)blockIdx.x - p.scan_slots, dsm);
+    return;
+  }
   int b, h, jt;
-  if (!bwd_cta_coords(p, (int)blockIdx.x - p.scan_slots, true, b, h, jt)) return;
+  if (!bwd_cta_coords(p, (int)blockIdx.x - p.scan_slots - p.dense_slots, true, b, h, jt)) return;
   const int hq = p.hidx ? p.hidx[h] : h;
   const int n = p.n_tiles - jt;            // query tiles jt .. n_tiles-1
   const int j0 = jt * 128;
@@ -780,7 +794,7 @@ int bwd_map4(CUtensorMap* m, const SafTensor& t, int B, int Hn, int T, int HD) {
 }
 
 template <int HD>
-int bwd_launch_typed(const SafMixedAttnBwdArgs& g, cudaStream_t st) {
+int bwd_launch_typed(const SafMixedAttnBwdArgs& g, bool* dense_done, cudaStream_t st) {
   const SafMixedAttnArgs& a = g.fwd;
   CUtensorMap mq, mk, mv, mdo, mdq, mdk, mdv;
   int rc;
@@ -835,6 +849,18 @@ int bwd_launch_typed(const SafMixedAttnBwdArgs& g, cudaStream_t st) {
     sc.vec_ok = 1;   // bwd_tma_ok() already demands 16-byte aligned bases and strides
     p.scan_slots = a.B * a.H * (HD / SCAN_COLS);
   }
+  CUtensorMap mp64, mdo64;
+  memset(&mp64, 0, sizeof(mp64));
+  memset(&mdo64, 0, sizeof(mdo64));
+  if (a.patt.ptr && dense_dv_eligible(g)) {
+    bool any = a.frozen_host == nullptr;
+    for (int hh = 0; a.frozen_host && hh < a.H; ++hh) any |= a.frozen_host[hh] == SAF_DENSE;
+    if (any) {
+      CUtensorMap mdv2;
+      if ((rc = dense_dv_prepare(g, &mp64, &mdo64, &mdv2, &p.dense))) return rc;
+      p.dense_slots = (int)dense_pv_slots(p.dense);
+    }
+  }
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(flash_bwd_dkdv_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdCfg<HD>::SMEM_BYTES);
@@ -846,10 +872,13 @@ int bwd_launch_typed(const SafMixedAttnBwdArgs& g, cudaStream_t st) {
   const int bh = a.B * a.H;
   const int groups = (bh + BWD_HEAD_GROUP - 1) / BWD_HEAD_GROUP;
   const unsigned grid = (unsigned)(groups * BWD_HEAD_GROUP * p.n_tiles);
-  flash_bwd_dkdv_kernel<HD><<<grid + p.scan_slots, BWD_THREADS, BwdCfg<HD>::SMEM_BYTES, st>>>(mq, mk, mv, mdo, mdk, mdv, p);
+  flash_bwd_dkdv_kernel<HD><<<grid + p.scan_slots + p.dense_slots, BWD_THREADS, BwdCfg<HD>::SMEM_BYTES, st>>>(
+      mq, mk, mv, mdo, mdk, mdv, mp64, mdo64, p);
   count_launch();
   if ((rc = check_launch("flash_bwd_dkdv_kernel"))) return rc;
+  *dense_done = p.dense_slots > 0;
   p.scan_slots = 0;
+  p.dense_slots = 0;
   flash_bwd_dq_kernel<HD><<<grid, BWD_THREADS, BwdCfg<HD>::SMEM_BYTES_DQ, st>>>(mq, mk, mv, mdo, mdq, p);
   count_launch();
   return check_launch("flash_bwd_dq_kernel");
@@ -881,8 +910,10 @@ int launch_flash_bwd_sm100(const SafMixedAttnBwdArgs& g, uint32_t* handled, cuda
     for (int h = 0; h < a.H; ++h) any |= a.frozen_host[h] == SAF_LIVE;
     if (!any) return SAF_ERR_UNSUPPORTED;
   }
-  const int rc = (a.HD == 64) ? bwd_launch_typed<64>(g, st) : bwd_launch_typed<128>(g, st);
-  if (rc == SAF_OK) *handled = (1u << SAF_LIVE) | ((a.sd_alpha && a.sd_rho) ? (1u << SAF_SINK_DECAY) : 0u);
+  bool dense_done = false;
+  const int rc = (a.HD == 64) ? bwd_launch_typed<64>(g, &dense_done, st) : bwd_launch_typed<128>(g, &dense_done, st);
+  if (rc == SAF_OK)
+    *handled = (1u << SAF_LIVE) | ((a.sd_alpha && a.sd_rho) ? (1u << SAF_SINK_DECAY) : 0u) | (dense_done ? (1u << SAF_DENSE) : 0u);
   return rc;
 }
 
