@@ -133,10 +133,26 @@ inline bool dense_dv_eligible(const SafMixedAttnBwdArgs& g) {
   if (a.S < a.T) return false;
   return tma_ok(g.dout) && tma_ok(g.dv);
 }
-inline int dense_dv_prepare(const SafMixedAttnBwdArgs& g, CUtensorMap* mp_, CUtensorMap* mdo, CUtensorMap* mdv, DpParams* p) {
+// decomposed heads in the backward need only the dO / dV layouts
+inline bool dense_dv_decomp_eligible(const SafMixedAttnBwdArgs& g) {
+  const SafMixedAttnArgs& a = g.fwd;
+  auto al16 = [](const void* q) { return ((uintptr_t)q & 15) == 0; };
+  auto tma_ok = [&](const SafTensor& t) {
+    if (!t.ptr || !al16(t.ptr) || t.stride[3] != 1) return false;
+    for (int i = 0; i < 3; ++i)
+      if (t.stride[i] % 8 || t.stride[i] <= 0) return false;
+    return true;
+  };
+  if (a.dtype != SAF_BF16 || (a.HD != 64 && a.HD != 128) || a.HKV > 0) return false;
+  if (!a.alpha.ptr || !a.rho.ptr || !a.z.ptr || a.SD < a.T) return false;
+  return tma_ok(g.dout) && tma_ok(g.dv);
+}
+inline int dense_dv_prepare(const SafMixedAttnBwdArgs& g, bool dense, bool decomp, CUtensorMap* mp_, CUtensorMap* mdo,
+                            CUtensorMap* mdv, DpParams* p) {
   const SafMixedAttnArgs& a = g.fwd;
   int rc;
-  {
+  memset(mp_, 0, sizeof(*mp_));
+  if (dense) {
     uint64_t dims[3] = {(uint64_t)a.S, (uint64_t)a.S, (uint64_t)1 << 20};
     uint64_t strides[3] = {0, (uint64_t)a.patt.stride[1] * 2, (uint64_t)a.patt.stride[0] * 2};
     uint32_t box[3] = {64, 64, 1};
@@ -160,7 +176,17 @@ inline int dense_dv_prepare(const SafMixedAttnBwdArgs& g, CUtensorMap* mp_, CUte
   p->groups = (a.B + 256 / a.HD - 1) / (256 / a.HD);
   p->frozen = a.frozen; p->pidx = a.pidx; p->kvidx = nullptr;
   p->status = a.status;
-  p->dense_ok = 1;
+  p->dense_ok = dense ? 1 : 0;
+  p->dec_ok = decomp ? 1 : 0;
+  if (decomp) {
+    p->alpha = a.alpha.ptr; p->rho = a.rho.ptr; p->z = a.z.ptr;
+    for (int i = 0; i < 2; ++i) {
+      p->alpha_s[i] = a.alpha.stride[i];
+      p->rho_s[i] = a.rho.stride[i];
+      p->z_s[i] = a.z.stride[i];
+    }
+    p->dec_dtype = a.dec_dtype;
+  }
   return SAF_OK;
 }
 
@@ -485,7 +511,8 @@ __device__ __forceinline__ void dense_dv_cta(const CUtensorMap& mapP, const CUte
   const int rem = slot % per_kp;
   const int h = rem / p.groups, grp = rem % p.groups;
   const int state = p.force_state >= 0 ? p.force_state : p.frozen[h];
-  if (!(state == SAF_DENSE && p.dense_ok)) return;
+  const bool gen = state == SAF_DECOMP && p.dec_ok;       // pattern blocks generated, not loaded
+  if (!gen && !(state == SAF_DENSE && p.dense_ok)) return;
   const int hp = p.pidx ? p.pidx[h] : h;
   const int b0 = grp * C::NB;
   const int nb = min(C::NB, p.B - b0);
@@ -505,6 +532,7 @@ __device__ __forceinline__ void dense_dv_cta(const CUtensorMap& mapP, const CUte
       mbar_init(&bars->full[s], 1);
       mbar_init(&bars->empty[s], 1);
     }
+    for (int s = 0; s < DP_NST; ++s) mbar_init(&bars->pgen[s], 256);
     mbar_init(&bars->need_mask, 1);
     mbar_init(&bars->masked, 128);
     mbar_init(&bars->acc_full, 1);
@@ -521,7 +549,7 @@ __device__ __forceinline__ void dense_dv_cta(const CUtensorMap& mapP, const CUte
 
   if (warp == 0) {
     if (lane == 0) {
-      tma_prefetch_desc(&mapP);
+      if (!gen) tma_prefetch_desc(&mapP);
       tma_prefetch_desc(&mapdO);
       for (int st = 0; st < n_steps; ++st) {
         const int s = st % DP_NST, qh = qh0 + st;
@@ -531,8 +559,8 @@ __device__ __forceinline__ void dense_dv_cta(const CUtensorMap& mapP, const CUte
         }
         uint8_t* sp = smem + s * C::STAGE;
         const bool t1 = tile_on(st, 1);
-        mbar_expect_tx(&bars->full[s], (t1 ? 2 : 1) * DP_PATOM + nb * C::V_BYTES);
-        for (int t = 0; t < (t1 ? 2 : 1); ++t)
+        mbar_expect_tx(&bars->full[s], (gen ? 0 : (t1 ? 2 : 1) * DP_PATOM) + nb * C::V_BYTES);
+        for (int t = 0; t < (gen ? 0 : (t1 ? 2 : 1)); ++t)
 #pragma unroll
           for (int a = 0; a < 2; ++a)     // two 64-key atoms of [64 queries x 128 bytes]
             tma_load_3d(sp + t * DP_PATOM + a * 8192, &mapP, &bars->full[s], key0 + 128 * t + 64 * a, qh * 64, hp);
@@ -553,7 +581,12 @@ __device__ __forceinline__ void dense_dv_cta(const CUtensorMap& mapP, const CUte
         dev_set_error(p.status, SAF_DEV_TIMEOUT_MMA, 81);
         break;
       }
-      if (diag_of(st, 0) || diag_of(st, 1)) {
+      if (gen) {
+        if (!mbar_wait(&bars->pgen[s], (st / DP_NST) & 1)) {
+          dev_set_error(p.status, SAF_DEV_TIMEOUT_MMA, 85);
+          break;
+        }
+      } else if (diag_of(st, 0) || diag_of(st, 1)) {
         if (leader) mbar_arrive(&bars->need_mask);
         __syncwarp();
         if (!mbar_wait(&bars->masked, n_masked & 1)) {
@@ -584,13 +617,89 @@ __device__ __forceinline__ void dense_dv_cta(const CUtensorMap& mapP, const CUte
     }
     if (leader) umma_commit(&bars->acc_full);
     __syncwarp();
-  } else if (warp < 6) {
+  }
+  if (gen && warp >= 2 && warp < 10) {
+    // ---------------------------------------------------------------- decomposed head: generate P^T blocks
+    // warps 2-5 build tile 0, warps 6-9 tile 1; thread -> (64-key atom a, query row q of the step).
+    // alpha of the tile's 128 keys is loaded once; rho over the step's 191 distances and z of the thread's
+    // query are fetched one step ahead.
+    constexpr float L2E = 1.4426950408889634f;
+    const int t = (warp - 2) >> 2;
+    const int gt = (tid - 64) & 127;
+    const int a = gt >> 6, q = gt & 63;
+    const int kt0 = key0 + 128 * t;                       // first key of this tile
+    const bool t_on = t == 0 || act1;
+    {
+      const int key = kt0 + gt;                           // ga[t] viewed as 128 consecutive keys
+      (&bars->ga[t][0][0])[gt] = (t_on && key < p.T)
+          ? L2E * load_rt(p.alpha, (int64_t)h * p.alpha_s[0] + (int64_t)key * p.alpha_s[1], p.dec_dtype) : 0.f;
+    }
+    auto fetch_r = [&](int st, int x) -> float {          // rho at distance (64 qh - kt0 - 127) + x
+      const int d = (qh0 + st) * 64 - kt0 - 127 + x;
+      return (x < 191 && d >= 0 && d < p.T) ? L2E * load_rt(p.rho, (int64_t)h * p.rho_s[0] + (int64_t)d * p.rho_s[1], p.dec_dtype) : 0.f;
+    };
+    auto fetch_z = [&](int st) -> float {                 // +inf: query rows past T give exact zeros
+      const int qi = (qh0 + st) * 64 + q;
+      return (qi < p.T) ? L2E * load_rt(p.z, (int64_t)h * p.z_s[0] + (int64_t)qi * p.z_s[1], p.dec_dtype) : INFINITY;
+    };
+    const int st_lo = 2 * t;                              // first step of this tile
+    float nr0 = 0.f, nr1 = 0.f, nz = INFINITY;
+    if (t_on && st_lo < n_steps) {
+      nr0 = fetch_r(st_lo, gt); nr1 = fetch_r(st_lo, gt + 128); nz = fetch_z(st_lo);
+    }
+    bool ok = true;
+    for (int st = 0; st < n_steps && ok; ++st) {
+      const int s = st % DP_NST, vb = st & 1;
+      const bool on = t_on && st >= st_lo;
+      float zq = INFINITY;
+      if (on) {
+        bars->gr[t][vb][gt] = nr0;
+        if (gt + 128 < 192) bars->gr[t][vb][gt + 128] = nr1;
+        zq = nz;
+        named_bar_sync(2 + t, 128);                        // also orders the one-time alpha stores
+        if (st + 1 < n_steps) {
+          nr0 = fetch_r(st + 1, gt); nr1 = fetch_r(st + 1, gt + 128); nz = fetch_z(st + 1);
+        }
+      }
+      if (!mbar_wait(&bars->empty[s], ((st / DP_NST) & 1) ^ 1)) {
+        dev_set_error(p.status, SAF_DEV_TIMEOUT_EPI, 86);
+        ok = false;
+        break;
+      }
+      if (on) {
+        uint8_t* rowp = smem + s * C::STAGE + t * DP_PATOM + a * 8192 + q * 128;
+        const float* ga_ = &bars->ga[t][0][0] + a * 64;
+        // distance of key (64 a + c) from this query = dlo + (127 + q - 64 a - c)
+        const float* gr_ = bars->gr[t][vb] + 127 + q - 64 * a;
+        const int lim = (qh0 + st) * 64 + q - kt0 - 64 * a;   // keys c <= lim count
+#pragma unroll
+        for (int cc = 0; cc < 8; ++cc) {
+          uint32_t w[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int c = cc * 8 + 2 * e;
+            const float x0 = ga_[c] + gr_[-c] - zq, x1 = ga_[c + 1] + gr_[-c - 1] - zq;
+            float p0, p1;
+            asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p0) : "f"(x0));
+            asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p1) : "f"(x1));
+            if (c > lim) p0 = 0.f;
+            if (c + 1 > lim) p1 = 0.f;
+            w[e] = pack_bf16(p0, p1);
+          }
+          *reinterpret_cast<uint4*>(rowp + ((cc ^ (q & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+        fence_proxy_async_smem();
+      }
+      mbar_arrive(&bars->pgen[s]);
+    }
+  }
+  if (warp >= 2 && warp < 6) {
     const int quad = warp & 3;
     const int r = quad * 32 + lane;            // key row of the tile == TMEM lane
     const int etid = tid - 64;
     bool ok = true;
     int n_masked = 0;
-    for (int st = 0; st < min(n_steps, 4) && ok; ++st) {
+    for (int st = 0; st < (gen ? 0 : min(n_steps, 4)) && ok; ++st) {
       const bool d0 = diag_of(st, 0), d1 = diag_of(st, 1);
       if (!d0 && !d1) continue;
       const int s = st % DP_NST;

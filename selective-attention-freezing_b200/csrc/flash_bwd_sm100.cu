@@ -794,7 +794,7 @@ int bwd_map4(CUtensorMap* m, const SafTensor& t, int B, int Hn, int T, int HD) {
 }
 
 template <int HD>
-int bwd_launch_typed(const SafMixedAttnBwdArgs& g, bool* dense_done, cudaStream_t st) {
+int bwd_launch_typed(const SafMixedAttnBwdArgs& g, bool* dense_done, bool* decomp_done, cudaStream_t st) {
   const SafMixedAttnArgs& a = g.fwd;
   CUtensorMap mq, mk, mv, mdo, mdq, mdk, mdv;
   int rc;
@@ -852,14 +852,24 @@ int bwd_launch_typed(const SafMixedAttnBwdArgs& g, bool* dense_done, cudaStream_
   CUtensorMap mp64, mdo64;
   memset(&mp64, 0, sizeof(mp64));
   memset(&mdo64, 0, sizeof(mdo64));
-  if (a.patt.ptr && dense_dv_eligible(g)) {
-    bool any = a.frozen_host == nullptr;
-    for (int hh = 0; a.frozen_host && hh < a.H; ++hh) any |= a.frozen_host[hh] == SAF_DENSE;
-    if (any) {
+  {
+    bool dense = a.patt.ptr && dense_dv_eligible(g), decomp = a.alpha.ptr && dense_dv_decomp_eligible(g);
+    if (a.frozen_host) {
+      bool any1 = false, any2 = false;
+      for (int hh = 0; hh < a.H; ++hh) {
+        any1 |= a.frozen_host[hh] == SAF_DENSE;
+        any2 |= a.frozen_host[hh] == SAF_DECOMP;
+      }
+      dense = dense && any1;
+      decomp = decomp && any2;
+    }
+    if (dense || decomp) {
       CUtensorMap mdv2;
-      if ((rc = dense_dv_prepare(g, &mp64, &mdo64, &mdv2, &p.dense))) return rc;
+      if ((rc = dense_dv_prepare(g, dense, decomp, &mp64, &mdo64, &mdv2, &p.dense))) return rc;
       p.dense_slots = (int)dense_pv_slots(p.dense);
     }
+    *dense_done = dense;
+    *decomp_done = decomp;
   }
   static bool attr_set = false;
   if (!attr_set) {
@@ -876,7 +886,6 @@ int bwd_launch_typed(const SafMixedAttnBwdArgs& g, bool* dense_done, cudaStream_
       mq, mk, mv, mdo, mdk, mdv, mp64, mdo64, p);
   count_launch();
   if ((rc = check_launch("flash_bwd_dkdv_kernel"))) return rc;
-  *dense_done = p.dense_slots > 0;
   p.scan_slots = 0;
   p.dense_slots = 0;
   flash_bwd_dq_kernel<HD><<<grid, BWD_THREADS, BwdCfg<HD>::SMEM_BYTES_DQ, st>>>(mq, mk, mv, mdo, mdq, p);
@@ -910,10 +919,12 @@ int launch_flash_bwd_sm100(const SafMixedAttnBwdArgs& g, uint32_t* handled, cuda
     for (int h = 0; h < a.H; ++h) any |= a.frozen_host[h] == SAF_LIVE;
     if (!any) return SAF_ERR_UNSUPPORTED;
   }
-  bool dense_done = false;
-  const int rc = (a.HD == 64) ? bwd_launch_typed<64>(g, &dense_done, st) : bwd_launch_typed<128>(g, &dense_done, st);
+  bool dense_done = false, decomp_done = false;
+  const int rc = (a.HD == 64) ? bwd_launch_typed<64>(g, &dense_done, &decomp_done, st)
+                              : bwd_launch_typed<128>(g, &dense_done, &decomp_done, st);
   if (rc == SAF_OK)
-    *handled = (1u << SAF_LIVE) | ((a.sd_alpha && a.sd_rho) ? (1u << SAF_SINK_DECAY) : 0u) | (dense_done ? (1u << SAF_DENSE) : 0u);
+    *handled = (1u << SAF_LIVE) | ((a.sd_alpha && a.sd_rho) ? (1u << SAF_SINK_DECAY) : 0u) |
+               (dense_done ? (1u << SAF_DENSE) : 0u) | (decomp_done ? (1u << SAF_DECOMP) : 0u);
   return rc;
 }
 
