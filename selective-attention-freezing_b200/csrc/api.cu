@@ -213,8 +213,8 @@ int saf_mixed_attn_bwd(const SafMixedAttnBwdArgs* args, void* stream) {
       return fail(SAF_ERR_INVALID, "live heads need dq, dk, delta and lse");
   }
   cudaStream_t st = (cudaStream_t)stream;
-  if (todo & 1u) {
-    // tensor-core path for the live heads; it reports what it covered
+  {
+    // tensor-core path (live heads, and frozen heads as roles of the same launch); it reports what it covered
     uint32_t handled = 0;
     rc = launch_flash_bwd_sm100(*args, &handled, st);
     if (rc == SAF_OK) todo &= ~handled;

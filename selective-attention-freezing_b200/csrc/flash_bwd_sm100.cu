@@ -794,16 +794,23 @@ int bwd_map4(CUtensorMap* m, const SafTensor& t, int B, int Hn, int T, int HD) {
 }
 
 template <int HD>
-int bwd_launch_typed(const SafMixedAttnBwdArgs& g, bool* dense_done, bool* decomp_done, cudaStream_t st) {
+int bwd_launch_typed(const SafMixedAttnBwdArgs& g, bool live, bool* dense_done, bool* decomp_done, cudaStream_t st) {
   const SafMixedAttnArgs& a = g.fwd;
   CUtensorMap mq, mk, mv, mdo, mdq, mdk, mdv;
   int rc;
-  if ((rc = bwd_map4(&mq, a.q, a.B, a.U, a.T, HD))) return rc;
-  if ((rc = bwd_map4(&mk, a.k, a.B, a.U, a.T, HD))) return rc;
-  if ((rc = bwd_map4(&mv, a.v, a.B, a.H, a.T, HD))) return rc;
+  // without live heads (frozen_pv backward) only the roles of the dK/dV launch run: the q/k maps are never used
+  const SafTensor& tq = live ? a.q : g.dv;
+  const SafTensor& tk = live ? a.k : g.dv;
+  const SafTensor& tdq = live ? g.dq : g.dv;
+  const SafTensor& tdk = live ? g.dk : g.dv;
+  const SafTensor& tv = live ? a.v : g.dv;               // frozen_pv passes no forward tensors
+  const int Uq = live ? a.U : a.H;
+  if ((rc = bwd_map4(&mq, tq, a.B, Uq, a.T, HD))) return rc;
+  if ((rc = bwd_map4(&mk, tk, a.B, Uq, a.T, HD))) return rc;
+  if ((rc = bwd_map4(&mv, tv, a.B, a.H, a.T, HD))) return rc;
   if ((rc = bwd_map4(&mdo, g.dout, a.B, a.H, a.T, HD))) return rc;
-  if ((rc = bwd_map4(&mdq, g.dq, a.B, a.U, a.T, HD))) return rc;
-  if ((rc = bwd_map4(&mdk, g.dk, a.B, a.U, a.T, HD))) return rc;
+  if ((rc = bwd_map4(&mdq, tdq, a.B, Uq, a.T, HD))) return rc;
+  if ((rc = bwd_map4(&mdk, tdk, a.B, Uq, a.T, HD))) return rc;
   if ((rc = bwd_map4(&mdv, g.dv, a.B, a.H, a.T, HD))) return rc;
 
   DeltaParams d;
@@ -818,9 +825,11 @@ int bwd_launch_typed(const SafMixedAttnBwdArgs& g, bool* dense_done, bool* decom
   d.frozen = a.frozen;
   d.B = a.B; d.H = a.H; d.T = a.T; d.force_state = a.force_state;
   constexpr int ROWS = 256 / (HD / 8);
-  flash_bwd_delta_kernel<HD><<<dim3((a.T + ROWS - 1) / ROWS, a.B * a.H), 256, 0, st>>>(d);
-  count_launch();
-  if ((rc = check_launch("flash_bwd_delta_kernel"))) return rc;
+  if (live) {
+    flash_bwd_delta_kernel<HD><<<dim3((a.T + ROWS - 1) / ROWS, a.B * a.H), 256, 0, st>>>(d);
+    count_launch();
+    if ((rc = check_launch("flash_bwd_delta_kernel"))) return rc;
+  }
 
   BwdParams p;
   memset(&p, 0, sizeof(p));
@@ -881,13 +890,15 @@ int bwd_launch_typed(const SafMixedAttnBwdArgs& g, bool* dense_done, bool* decom
   }
   const int bh = a.B * a.H;
   const int groups = (bh + BWD_HEAD_GROUP - 1) / BWD_HEAD_GROUP;
-  const unsigned grid = (unsigned)(groups * BWD_HEAD_GROUP * p.n_tiles);
+  const unsigned grid = live ? (unsigned)(groups * BWD_HEAD_GROUP * p.n_tiles) : 0u;
+  if (grid + p.scan_slots + p.dense_slots == 0) return SAF_ERR_UNSUPPORTED;
   flash_bwd_dkdv_kernel<HD><<<grid + p.scan_slots + p.dense_slots, BWD_THREADS, BwdCfg<HD>::SMEM_BYTES, st>>>(
       mq, mk, mv, mdo, mdk, mdv, mp64, mdo64, p);
   count_launch();
   if ((rc = check_launch("flash_bwd_dkdv_kernel"))) return rc;
   p.scan_slots = 0;
   p.dense_slots = 0;
+  if (!live) return SAF_OK;
   flash_bwd_dq_kernel<HD><<<grid, BWD_THREADS, BwdCfg<HD>::SMEM_BYTES_DQ, st>>>(mq, mk, mv, mdo, mdq, p);
   count_launch();
   return check_launch("flash_bwd_dq_kernel");
@@ -907,23 +918,23 @@ int launch_flash_bwd_sm100(const SafMixedAttnBwdArgs& g, uint32_t* handled, cuda
   *handled = 0;
   const SafMixedAttnArgs& a = g.fwd;
   if (a.dtype != SAF_BF16 || (a.HD != 64 && a.HD != 128) || a.rope || a.HKV > 0) return SAF_ERR_UNSUPPORTED;
-  if (a.U <= 0 || a.sm_scale <= 0.f) return SAF_ERR_UNSUPPORTED;
-  if (!bwd_tma_ok(a.q) || !bwd_tma_ok(a.k) || !bwd_tma_ok(a.v) || !bwd_tma_ok(g.dout) || !bwd_tma_ok(g.dq) ||
-      !bwd_tma_ok(g.dk) || !bwd_tma_ok(g.dv) || !bwd_tma_ok(a.out))
-    return SAF_ERR_UNSUPPORTED;
-  if (!a.lse.ptr || !g.delta.ptr) return SAF_ERR_UNSUPPORTED;
+  if (!bwd_tma_ok(g.dout) || !bwd_tma_ok(g.dv)) return SAF_ERR_UNSUPPORTED;
   if (!saf_device_supported()) return SAF_ERR_UNSUPPORTED;
-  if (a.force_state >= 0 && a.force_state != SAF_LIVE) return SAF_ERR_UNSUPPORTED;
-  if (a.frozen_host) {
-    bool any = false;
-    for (int h = 0; h < a.H; ++h) any |= a.frozen_host[h] == SAF_LIVE;
-    if (!any) return SAF_ERR_UNSUPPORTED;
+  // live heads need the full set of tensors; without them only the frozen-head roles are launched
+  bool live = a.U > 0 && a.sm_scale > 0.f && bwd_tma_ok(a.q) && bwd_tma_ok(a.k) && bwd_tma_ok(a.v) && bwd_tma_ok(g.dq) &&
+              bwd_tma_ok(g.dk) && bwd_tma_ok(a.out) && a.lse.ptr && g.delta.ptr;
+  bool live_present = a.force_state < 0 ? a.U > 0 : a.force_state == SAF_LIVE;
+  if (a.frozen_host && a.force_state < 0) {
+    live_present = false;
+    for (int h = 0; h < a.H; ++h) live_present |= a.frozen_host[h] == SAF_LIVE;
   }
+  if (live_present && !live) return SAF_ERR_UNSUPPORTED;   // live heads this launch cannot serve: leave everything
+  live = live && live_present;
   bool dense_done = false, decomp_done = false;
-  const int rc = (a.HD == 64) ? bwd_launch_typed<64>(g, &dense_done, &decomp_done, st)
-                              : bwd_launch_typed<128>(g, &dense_done, &decomp_done, st);
+  const int rc = (a.HD == 64) ? bwd_launch_typed<64>(g, live, &dense_done, &decomp_done, st)
+                              : bwd_launch_typed<128>(g, live, &dense_done, &decomp_done, st);
   if (rc == SAF_OK)
-    *handled = (1u << SAF_LIVE) | ((a.sd_alpha && a.sd_rho) ? (1u << SAF_SINK_DECAY) : 0u) |
+    *handled = (live ? (1u << SAF_LIVE) : 0u) | ((a.sd_alpha && a.sd_rho) ? (1u << SAF_SINK_DECAY) : 0u) |
                (dense_done ? (1u << SAF_DENSE) : 0u) | (decomp_done ? (1u << SAF_DECOMP) : 0u);
   return rc;
 }
