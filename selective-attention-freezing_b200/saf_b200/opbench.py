@@ -3,7 +3,8 @@ alone on seeded synthetic tensors and timed with CUDA events (median).  The coun
 per-operator probes (qwen/nanogpt/bench_qwen_prefill_triton.py:186-225); also the command the ncu captures
 of single kernels are taken from.
 
-    python -m saf_b200.opbench --workload c3 --ops attn_fwd,attn_bwd,qk_fwd,qk_bwd [--B 2 --T 8192] [--reps 5]
+    python -m saf_b200.opbench --workload c3 --ops attn_fwd,attn_bwd,qk_fwd,qk_bwd,layer_infer,layer_train \
+                               [--B 2 --T 8192] [--reps 5] [--frozen sink_decay|dense|decomposed|none]
 
 Prints one JSON line per operator: ms, algorithmic TFLOP/s (backward counted as 2.5x / 2x the forward
 FLOPs, as the reference's roofline does) and the library launches of one call.
@@ -140,6 +141,40 @@ def main():
                 y.backward(dqk, retain_graph=True)
             ms = _timed(run, args.reps)
             fl = 2.0 * fl_qk
+        elif op in ("layer_train", "layer_infer"):
+            # the whole attention module (projections + mixed attention + c_proj) at this shape
+            from types import SimpleNamespace
+            from saf_b200.attention import SafCausalSelfAttention
+            cfg = SimpleNamespace(n_embd=C, n_head=H, block_size=T, bias=False, dropout=0.0, position_encoding="rope",
+                                  rand_attn_prior_repr="dense", freeze_pattern_dtype="bfloat16")
+            m = SafCausalSelfAttention(cfg).to(dev)
+            if nf:
+                a_, r_ = synthetic.sink_decay_params(nf, 2337)
+                m.freeze_heads_sink_decay(fz, a_.tolist(), r_.tolist())
+            rope = (cos.view(1, 1, T, hd), sin.view(1, 1, T, hd))
+            if op == "layer_infer":
+                m = m.bfloat16().eval()
+                xi = x.detach()
+
+                def run():
+                    with torch.inference_mode():
+                        m(xi, rope=rope)
+                fl = fl_attn + 2.0 * B * T * C * (2 * U + 2 * H) * hd
+            else:
+                xi = x.detach().float().requires_grad_(True)     # fp32 master weights, bf16 autocast
+
+                def run():
+                    xi.grad = None
+                    for prm in m.parameters():
+                        prm.grad = None
+                    with torch.autocast("cuda", dtype=torch.bfloat16):
+                        out = m(xi, rope=rope)
+                    out.backward(dy.transpose(1, 2).reshape(B, T, C).to(out.dtype))
+                fl = 3.5 * fl_attn + 3 * 2.0 * B * T * C * (2 * U + 2 * H) * hd
+            n0 = ops.launch_count()
+            run()
+            n = ops.launch_count() - n0
+            ms = _timed(run, args.reps)
         else:
             raise SystemExit("unknown op %r" % op)
         print(json.dumps({"op": op, "shape": shape, "ms": round(ms, 4), "tflops": round(fl / ms / 1e9, 1),
