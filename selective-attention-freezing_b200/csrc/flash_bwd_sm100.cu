@@ -48,10 +48,13 @@ __device__ long long g_trace[2][8][64];   // [kernel][event][tile]
 template <int HD>
 struct BwdCfg {
   static constexpr int TILE_BYTES = 128 * HD * 2;
-  static constexpr int NSTAGE = (HD == 64) ? 3 : 2;   // dK/dV kernel: ring of streamed (Q_i, dO_i) pairs
+  // dK/dV kernel: Q_i lives from S^T(i) to dK(i), dO_i from dP^T(i) to dV(i); the Q ring is the one whose
+  // refill sits on the critical path, so it gets the third stage even at head_dim 128
+  static constexpr int NQ = 3;
+  static constexpr int ND = (HD == 64) ? 3 : 2;
   static constexpr int KS = 3;                        // dQ kernel: K ring (a K tile lives until its dQ product)
   static constexpr int VS = (HD == 64) ? 3 : 2;       // dQ kernel: V ring (a V tile is done after its dP product)
-  static constexpr int SMEM_DKDV = 1024 + 2 * TILE_BYTES + NSTAGE * 2 * TILE_BYTES + 4096;
+  static constexpr int SMEM_DKDV = 1024 + 2 * TILE_BYTES + (NQ + ND) * TILE_BYTES + 256 + 1040;
   // the dK/dV launch also hosts the dense-pattern dV role, which brings its own ring
   static constexpr int SMEM_BYTES = SMEM_DKDV > DpCfg<HD>::SMEM_BYTES ? SMEM_DKDV : DpCfg<HD>::SMEM_BYTES;
   static constexpr int SMEM_BYTES_DQ = 1024 + 2 * TILE_BYTES + (KS + VS) * TILE_BYTES + 512;
@@ -86,8 +89,8 @@ struct BwdBars {
 static_assert(sizeof(BwdBars) <= 256, "barrier block");
 // dK/dV kernel only, placed 256 bytes after the barriers: lse and delta of the current query tile (read as float4)
 struct BwdVectors {
-  alignas(16) float lse[2][128];
-  alignas(16) float dl[2][128];
+  alignas(16) float lse[128];
+  alignas(16) float dl[128];
 };
 
 __device__ __forceinline__ float ex2b(float x) {
@@ -249,7 +252,11 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
     const int bh = blockIdx.x / PER, col0 = (blockIdx.x % PER) * SCAN_COLS;
     const int sb = bh / p.H, sh = bh % p.H;
     const int state = p.force_state >= 0 ? p.force_state : p.frozen[sh];
-    if (state == SAF_SINK_DECAY && threadIdx.x < SCAN_NT) sink_decay_scan_cta<__nv_bfloat16, true>(p.scan, sb, sh, col0);
+    if (state == SAF_SINK_DECAY && threadIdx.x < SCAN_NT) {
+      extern __shared__ uint8_t scan_smem_raw[];
+      float* scratch = reinterpret_cast<float*>(((uintptr_t)scan_smem_raw + 1023) & ~(uintptr_t)1023);
+      sink_decay_scan_cta<__nv_bfloat16, true, 0, true>(p.scan, sb, sh, col0, 0, -1, scratch);
+    }
     return;
   }
   if ((int)blockIdx.x < p.scan_slots + p.dense_slots) {
@@ -269,7 +276,8 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
   uint8_t* sK = smem;
   uint8_t* sV = smem + C::TILE_BYTES;
   uint8_t* ring = smem + 2 * C::TILE_BYTES;           // stage s: [Q_i | dO_i]
-  BwdBars* bars = reinterpret_cast<BwdBars*>(ring + C::NSTAGE * 2 * C::TILE_BYTES);
+  uint8_t* ringdO = ring + C::NQ * C::TILE_BYTES;       // `ring` is the Q ring
+  BwdBars* bars = reinterpret_cast<BwdBars*>(ringdO + C::ND * C::TILE_BYTES);
   BwdVectors* vec = reinterpret_cast<BwdVectors*>(reinterpret_cast<uint8_t*>(bars) + 256);
   const int tid = threadIdx.x, warp = tid >> 5;
   bwd_setup<HD>(bars, tid, warp);
@@ -292,22 +300,21 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         mbar_expect_tx(&bars->res_full, 2 * C::TILE_BYTES);
         bload_tile<HD>(sK, &mapK, &bars->res_full, j0, hq, b);
         bload_tile<HD>(sV, &mapV, &bars->res_full, j0, h, b);
-        // stage s holds [Q_i | dO_i]; the two halves are loaded and released separately: dO_i is done after
-        // the dV product, Q_i only after the dK product, and S(i+1) must not wait for dO_{i+1}
+        // Q_i and dO_i travel in separate rings: dO_i is done after the dV product, Q_i only after the dK
+        // product, and S(i+1) must not wait for dO_{i+1}
         for (int i = 0; i < n; ++i) {
-          const int s = i % C::NSTAGE;
-          const uint32_t ph = ((i / C::NSTAGE) & 1) ^ 1;
-          uint8_t* dst = ring + s * 2 * C::TILE_BYTES;
-          if (!mbar_wait(&bars->v_empty[s], ph)) {
+          const int sd = i % C::ND, s = i % C::NQ;
+          if (!mbar_wait(&bars->v_empty[sd], ((i / C::ND) & 1) ^ 1)) {
             dev_set_error(p.status, SAF_DEV_TIMEOUT_TMA, 40);
             break;
           }
-          mbar_expect_tx(&bars->v_full[s], C::TILE_BYTES);
-          bload_tile<HD>(dst + C::TILE_BYTES, &mapdO, &bars->v_full[s], (jt + i) * 128, h, b);
-          if (!mbar_wait(&bars->ring_empty[s], ph)) {
+          mbar_expect_tx(&bars->v_full[sd], C::TILE_BYTES);
+          bload_tile<HD>(ringdO + sd * C::TILE_BYTES, &mapdO, &bars->v_full[sd], (jt + i) * 128, h, b);
+          if (!mbar_wait(&bars->ring_empty[s], ((i / C::NQ) & 1) ^ 1)) {
             dev_set_error(p.status, SAF_DEV_TIMEOUT_TMA, 49);
             break;
           }
+          uint8_t* dst = ring + s * C::TILE_BYTES;
           mbar_expect_tx(&bars->ring_full[s], C::TILE_BYTES);
           bload_tile<HD>(dst, &mapQ, &bars->ring_full[s], (jt + i) * 128, hq, b);
         }
@@ -316,12 +323,12 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
       // ------------------------------------------------------------ MMA issuer
       const uint32_t idesc_s = umma_idesc_bf16(128, 128, 0, 0);
       const uint32_t idesc_o = umma_idesc_bf16(128, HD, 0, 1);
-      const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aR = smem_u32(ring);
+      const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aR = smem_u32(ring), aRd = smem_u32(ringdO);
       bool ok = mbar_wait(&bars->res_full, 0);
       if (!ok) dev_set_error(p.status, SAF_DEV_TIMEOUT_MMA, 41);
       for (int i = 0; i < n && ok; ++i) {
-        const int s = i % C::NSTAGE;
-        const uint32_t aQ = aR + s * 2 * C::TILE_BYTES, adO = aQ + C::TILE_BYTES;
+        const int s = i % C::NQ, sd = i % C::ND;
+        const uint32_t aQ = aR + s * C::TILE_BYTES, adO = aRd + sd * C::TILE_BYTES;
         if (i == 0) {
           if (!mbar_wait(&bars->ring_full[0], 0) || !mbar_wait(&bars->v_full[0], 0)) {
             dev_set_error(p.status, SAF_DEV_TIMEOUT_MMA, 42);
@@ -344,13 +351,13 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         TRACE(0, 4, i);   // issuer saw p_full
         if (leader) {
           issue_ts(tmem + COL_DV, tmem + COL_S, adO, idesc_o, i > 0);
-          umma_commit(&bars->v_empty[s]);                 // dO_i is not read again
+          umma_commit(&bars->v_empty[sd]);                // dO_i is not read again
         }
         __syncwarp();
-        const int s2 = (i + 1) % C::NSTAGE;
-        const uint32_t aQ2 = aR + s2 * 2 * C::TILE_BYTES, adO2 = aQ2 + C::TILE_BYTES;
+        const int s2 = (i + 1) % C::NQ, sd2 = (i + 1) % C::ND;
+        const uint32_t aQ2 = aR + s2 * C::TILE_BYTES, adO2 = aRd + sd2 * C::TILE_BYTES;
         if (i + 1 < n) {
-          if (!mbar_wait(&bars->ring_full[s2], ((i + 1) / C::NSTAGE) & 1)) {
+          if (!mbar_wait(&bars->ring_full[s2], ((i + 1) / C::NQ) & 1)) {
             dev_set_error(p.status, SAF_DEV_TIMEOUT_MMA, 44);
             break;
           }
@@ -373,7 +380,7 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         }
         __syncwarp();
         if (i + 1 < n) {
-          if (!mbar_wait(&bars->v_full[s2], ((i + 1) / C::NSTAGE) & 1)) {
+          if (!mbar_wait(&bars->v_full[sd2], ((i + 1) / C::ND) & 1)) {
             dev_set_error(p.status, SAF_DEV_TIMEOUT_MMA, 59);
             break;
           }
@@ -407,9 +414,9 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
     float nxt = fetch(jt);
     bool ok = true;
     for (int i = 0; i < n; ++i) {
-      const int st = i & 1;
-      if (tid < 128) vec->lse[st][r] = nxt;
-      else vec->dl[st][r] = nxt;
+      named_bar_sync(1, 256);                 // the previous tile's readers are done with the vectors
+      if (tid < 128) vec->lse[r] = nxt;
+      else vec->dl[r] = nxt;
       named_bar_sync(1, 256);
       if (i + 1 < n) nxt = fetch(jt + i + 1);
       // ---- P^T
@@ -429,7 +436,7 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         tmem_ld_wait();
 #pragma unroll
         for (int ch = 0; ch < 2; ++ch) {
-          const float4* L4 = reinterpret_cast<const float4*>(&vec->lse[st][cb + ch * 32]);
+          const float4* L4 = reinterpret_cast<const float4*>(&vec->lse[cb + ch * 32]);
 #pragma unroll
           for (int x = 0; x < 8; ++x) {
             const uint32_t s4[4] = {s[ch][x * 4 + 0], s[ch][x * 4 + 1], s[ch][x * 4 + 2], s[ch][x * 4 + 3]};
@@ -470,7 +477,7 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         tmem_ld_wait();
 #pragma unroll
         for (int ch = 0; ch < 2; ++ch) {
-          const float4* D4 = reinterpret_cast<const float4*>(&vec->dl[st][cb + ch * 32]);
+          const float4* D4 = reinterpret_cast<const float4*>(&vec->dl[cb + ch * 32]);
           uint32_t pk[16];
 #pragma unroll
           for (int x = 0; x < 8; ++x) {

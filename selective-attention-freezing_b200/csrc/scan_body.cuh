@@ -94,9 +94,11 @@ __device__ __forceinline__ float* scan_stash(T* ob_col0, int64_t row_stride, int
 // MODE 0: the whole job (carry starts at zero, outputs written).
 // MODE 1: state at the end of the range from a zero carry, parked in the stash; nothing else is written.
 // MODE 2: carry read from the stash (before any output is written), outputs written.
-template <typename T, bool BWD, int MODE = 0>
+// EXT: the 12.5 KB of carry / column-sum scratch live at `ext` (caller's dynamic shared memory) instead of in
+// static shared memory, for kernels whose other roles need every static byte.
+template <typename T, bool BWD, int MODE = 0, bool EXT = false>
 __device__ __forceinline__ void sink_decay_scan_cta(const ScanArgs& a, int b, int h, int col0, int p_lo = 0,
-                                                    int p_hi = -1) {
+                                                    int p_hi = -1, float* ext = nullptr) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int cg = lane & 7, rl = lane >> 3;
   const int c0 = col0 + cg * 8;
@@ -109,9 +111,21 @@ __device__ __forceinline__ void sink_decay_scan_cta(const ScanArgs& a, int b, in
   const T* ib = reinterpret_cast<const T*>(a.in) + (int64_t)b * a.si[0] + (int64_t)hin * a.si[1] + (int64_t)c0 * a.si[3];
   T* ob = reinterpret_cast<T*>(a.out) + (int64_t)b * a.so[0] + (int64_t)h * a.so[1] + (int64_t)c0 * a.so[3];
 
-  __shared__ float wtot[2][8][SCAN_COLS];   // double-buffered: one barrier per block step
-  __shared__ float colsum[32][SCAN_COLS];   // bwd: per (warp, rl) partial column sums of dY
-  __shared__ float row0[SCAN_COLS];         // bwd: scanned value of row 0
+  float (*wtot)[8][SCAN_COLS];              // [2]: double-buffered, one barrier per block step
+  float (*colsum)[SCAN_COLS];               // [32]: bwd, per (warp, rl) partial column sums of dY
+  float* row0;                              // [64]: bwd, scanned value of row 0
+  if constexpr (EXT) {
+    wtot = reinterpret_cast<float (*)[8][SCAN_COLS]>(ext);
+    colsum = reinterpret_cast<float (*)[SCAN_COLS]>(ext + 2 * 8 * SCAN_COLS);
+    row0 = ext + 2 * 8 * SCAN_COLS + 32 * SCAN_COLS;
+  } else {
+    __shared__ float wtot_s[2][8][SCAN_COLS];
+    __shared__ float colsum_s[32][SCAN_COLS];
+    __shared__ float row0_s[SCAN_COLS];
+    wtot = wtot_s;
+    colsum = colsum_s;
+    row0 = row0_s;
+  }
 
   float v0[8];
 #pragma unroll
