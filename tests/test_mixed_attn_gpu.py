@@ -187,6 +187,16 @@ def test_sink_decay_scan_heads(T, dtype):
     run_case(2, 12, T, 64, max(T, 64), [1], [], dtype=dtype, sink=[2, 5, 8], no_patt=False)
 
 
+@pytest.mark.parametrize("cfg", [(3, 12, 700, 64), (5, 8, 1100, 128), (2, 12, 2048, 64)], ids=lambda c: f"B{c[0]}H{c[1]}T{c[2]}d{c[3]}")
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["fp32", "bf16"])
+def test_all_four_head_states_in_one_call(cfg, dtype):
+    """live + dense-stored + decomposed + structured heads together, forward and backward; batch sizes that leave
+    partial batch groups in the shared-pattern roles."""
+    B, H, T, hd = cfg
+    S = ((T + 63) // 64) * 64
+    run_case(B, H, T, hd, S, [1, H - 1], [2, 3], dtype=dtype, sink=[5, 6], buf_bf16=(dtype == torch.bfloat16))
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["fp32", "bf16"])
 def test_rope_on_load(dtype):
     run_case(2, 12, 700, 64, 1024, [2, 5, 8], dtype=dtype, rope=True)
