@@ -185,7 +185,14 @@ typedef struct SafIndexedLinearArgs {
   void* out;                  /* (M, n_slabs*slab) row-major, row stride ldo       */
   int64_t ldo;
   int32_t* status;
+  /* epilogue of the rest of the transformer block around the attention path (forward only, bf16 tensor-core
+   * path): out = [residual +] act(x W^T + b).  Replaces the separate GELU and residual-add kernels of
+   * MLP.forward / Block.forward (nanogpt/model.py:1202-1207, 1237-1240). */
+  int32_t act;                /* SAF_ACT_NONE or SAF_ACT_GELU (exact erf form, nn.GELU()) */
+  const void* residual;       /* (M, n_slabs*slab) same dtype, row stride ldr, or null    */
+  int64_t ldr;
 } SafIndexedLinearArgs;
+enum { SAF_ACT_NONE = 0, SAF_ACT_GELU = 1 };
 
 int saf_indexed_linear_fwd(const SafIndexedLinearArgs* args, void* stream);
 
@@ -212,6 +219,14 @@ int saf_indexed_linear_bwd_dw(const SafIndexedLinearArgs* args, const void* dout
 int saf_rope_slabs(void* x, int64_t ld, int32_t M, int32_t n_slabs, int32_t slab, int32_t T,
                    const int32_t* slab_rope, const float* rope_cos, const float* rope_sin, int32_t dtype,
                    int32_t inverse, void* stream);
+
+/* ---------------------------------------------------------------------------
+ * LayerNorm over the last dimension with optional bias (LayerNorm.forward, nanogpt/model.py:45-54:
+ * F.layer_norm(x, (C,), weight, bias, 1e-5)).  x, out (M, C) row-major in `dtype` (SAF_BF16 / SAF_F32),
+ * weight / bias (C,) in the same dtype (bias may be null); statistics in fp32.
+ * ------------------------------------------------------------------------- */
+int saf_layernorm_fwd(const void* x, int64_t ldx, const void* weight, const void* bias, void* out, int64_t ldo,
+                      int32_t M, int32_t C, float eps, int32_t dtype, void* stream);
 
 /* ---------------------------------------------------------------------------
  * Freeze-time helper: z[h,i] = logsumexp_{j<=i}(alpha[h,j] + rho[h,i-j]).

@@ -266,3 +266,22 @@ def sink_decay_params(n, seed):
     a = 0.05 + 0.25 * torch.rand(n, generator=g, dtype=torch.float64)
     r = 0.8 + 0.19 * torch.rand(n, generator=g, dtype=torch.float64)
     return a, r
+
+
+# ---------------------------------------------------------------------------
+# rest of the transformer block                       nanogpt/model.py:45-54, 1193-1240
+# ---------------------------------------------------------------------------
+def layer_norm(x, weight, bias=None, eps=1e-5):
+    """LayerNorm.forward (nanogpt/model.py:53-54)."""
+    return torch.nn.functional.layer_norm(x, weight.shape, weight, bias, eps)
+
+
+def mlp(x, w_fc, w_proj, b_fc=None, b_proj=None):
+    """MLP.forward without dropout (nanogpt/model.py:1202-1207): c_proj(gelu(c_fc(x))), exact (erf) GELU."""
+    return torch.nn.functional.linear(torch.nn.functional.gelu(torch.nn.functional.linear(x, w_fc, b_fc)), w_proj, b_proj)
+
+
+def block(x, ln1_w, ln2_w, attn, w_fc, w_proj):
+    """Block.forward (nanogpt/model.py:1237-1240) with `attn` a callable for the attention module."""
+    x = x + attn(layer_norm(x, ln1_w))
+    return x + mlp(layer_norm(x, ln2_w), w_fc, w_proj)

@@ -281,6 +281,7 @@ static int validate_linear(const SafIndexedLinearArgs* a) {
                 (int)sizeof(SafIndexedLinearArgs));
   if (a->dtype != SAF_F32 && a->dtype != SAF_BF16) return fail(SAF_ERR_UNSUPPORTED, "indexed linear takes fp32 or bf16");
   if (a->M < 0 || a->C <= 0 || a->n_slabs < 0 || a->slab <= 0) return fail(SAF_ERR_INVALID, "bad dimensions");
+  if (a->act != SAF_ACT_NONE && a->act != SAF_ACT_GELU) return fail(SAF_ERR_INVALID, "unknown activation %d", a->act);
   if (a->n_weights < 1 || a->n_weights > SAF_MAX_WEIGHTS) return fail(SAF_ERR_INVALID, "n_weights %d", a->n_weights);
   if (a->M == 0 || a->n_slabs == 0) return SAF_OK;
   if (!a->x || !a->slab_weight || !a->slab_row0) return fail(SAF_ERR_INVALID, "null x / slab tables");
@@ -311,6 +312,8 @@ int saf_indexed_linear_fwd(const SafIndexedLinearArgs* args, void* stream) {
   cudaStream_t st = (cudaStream_t)stream;
   rc = launch_gemm_sm100(*args, st);
   if (rc != SAF_ERR_UNSUPPORTED) return rc;
+  if (args->act != SAF_ACT_NONE || args->residual)
+    return fail(SAF_ERR_UNSUPPORTED, "the activation / residual epilogue exists on the bf16 tensor-core path only");
   return launch_gemm_generic(*args, st);
 }
 
@@ -344,6 +347,15 @@ int saf_rope_slabs(void* x, int64_t ld, int32_t M, int32_t n_slabs, int32_t slab
   if (M == 0 || n_slabs == 0) return SAF_OK;
   if (!x || !rope_cos || !rope_sin) return fail(SAF_ERR_INVALID, "null pointer");
   return launch_rope_slabs(x, ld, M, n_slabs, slab, T, slab_rope, rope_cos, rope_sin, dtype, inverse, (cudaStream_t)stream);
+}
+
+int saf_layernorm_fwd(const void* x, int64_t ldx, const void* weight, const void* bias, void* out, int64_t ldo,
+                      int32_t M, int32_t C, float eps, int32_t dtype, void* stream) {
+  if (M < 0 || C <= 0) return fail(SAF_ERR_INVALID, "bad dimensions");
+  if (dtype != SAF_F32 && dtype != SAF_BF16) return fail(SAF_ERR_UNSUPPORTED, "layernorm takes fp32 or bf16");
+  if (M == 0) return SAF_OK;
+  if (!x || !weight || !out) return fail(SAF_ERR_INVALID, "null pointer");
+  return launch_layernorm(x, ldx, weight, bias, out, ldo, M, C, eps, dtype, (cudaStream_t)stream);
 }
 
 int saf_decomposed_logz(const float* alpha, const float* rho, float* z, int32_t H, int32_t S, void* stream) {

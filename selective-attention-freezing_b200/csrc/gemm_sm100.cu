@@ -46,7 +46,24 @@ struct GemmParams {
   const float* cosT;
   const float* sinT;
   int* status;
+  int act;                       // SAF_ACT_*
+  const __nv_bfloat16* residual; // added to the output, or null
+  int64_t ldr;
 };
+
+// exact-form GELU, 0.5 x (1 + erf(x / sqrt 2)), with erf from Abramowitz-Stegun 7.1.26 (|error| < 1.5e-7):
+// one reciprocal and one exponential on the special-function unit, the rest FMAs
+__device__ __forceinline__ float gelu_erf(float x) {
+  const float z = fabsf(x) * 0.70710678118654752f;
+  const float t = __frcp_rn(fmaf(0.3275911f, z, 1.f));
+  float poly = fmaf(1.061405429f, t, -1.453152027f);
+  poly = fmaf(poly, t, 1.421413741f);
+  poly = fmaf(poly, t, -0.284496736f);
+  poly = fmaf(poly, t, 0.254829592f);
+  const float e = exp2f(-z * z * 1.4426950408889634f);
+  const float erf_abs = 1.f - poly * t * e;
+  return 0.5f * x * (1.f + copysignf(erf_abs, x));
+}
 
 struct SmemLayout {
   uint64_t full[STAGES], empty[STAGES], acc_full[2], acc_empty[2];
@@ -206,6 +223,23 @@ indexed_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_const
 #pragma unroll
           for (int j = 0; j < 64; ++j) v[j] += __bfloat162float(bp[j]);
         }
+        if (p.act == SAF_ACT_GELU) {
+#pragma unroll
+          for (int j = 0; j < 64; ++j) v[j] = gelu_erf(v[j]);
+        }
+        if (p.residual && m < p.M) {   // this row's 64 residual values: one 128-byte line
+          const uint4* rr = reinterpret_cast<const uint4*>(p.residual + (int64_t)m * p.ldr + tn * GN + u * 64);
+#pragma unroll
+          for (int c8 = 0; c8 < 8; ++c8) {
+            const uint4 q = rr[c8];
+            const uint32_t w4[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              v[c8 * 8 + 2 * e] += __uint_as_float(w4[e] << 16);
+              v[c8 * 8 + 2 * e + 1] += __uint_as_float(w4[e] & 0xffff0000u);
+            }
+          }
+        }
         if (rp) {   // warp-uniform: rows past M are rotated too (t stays a valid table row) and clipped by the store
           const float* cr = p.cosT + (int64_t)t * p.slab;
           const float* sr = p.sinT + (int64_t)t * p.slab;
@@ -290,6 +324,7 @@ int launch_gemm_sm100(const SafIndexedLinearArgs& a, cudaStream_t st) {
   if (N / 64 > MAX_SUB) return SAF_ERR_UNSUPPORTED;
   if (a.C % 8 || a.ldx % 8 || a.ldo % 8 || !aligned16(a.x) || !aligned16(a.out)) return SAF_ERR_UNSUPPORTED;
   if ((a.rope_cos && !aligned16(a.rope_cos)) || (a.rope_sin && !aligned16(a.rope_sin))) return SAF_ERR_UNSUPPORTED;
+  if (a.residual && (!aligned16(a.residual) || a.ldr % 8)) return SAF_ERR_UNSUPPORTED;
   for (int w = 0; w < a.n_weights; ++w) {
     if (!a.weights[w]) continue;
     if (a.ldw[w] % 8 || (a.cdw[w] != 0 && a.cdw[w] != 1) || !aligned16(a.weights[w])) return SAF_ERR_UNSUPPORTED;
@@ -335,6 +370,9 @@ int launch_gemm_sm100(const SafIndexedLinearArgs& a, cudaStream_t st) {
   p.cosT = a.rope_cos;
   p.sinT = a.rope_sin;
   p.status = a.status;
+  p.act = a.act;
+  p.residual = reinterpret_cast<const __nv_bfloat16*>(a.residual);
+  p.ldr = a.ldr;
 
   static int sm_count = 0;
   if (!sm_count) {

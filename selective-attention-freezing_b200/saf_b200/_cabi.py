@@ -63,14 +63,17 @@ class SafIndexedLinearArgs(C.Structure):
         ("slab_rope", C.POINTER(C.c_int32)),
         ("rope_cos", C.c_void_p), ("rope_sin", C.c_void_p),
         ("out", C.c_void_p), ("ldo", C.c_int64), ("status", C.c_void_p),
+        ("act", C.c_int32), ("residual", C.c_void_p), ("ldr", C.c_int64),
     ]
 
+
+ACT_NONE, ACT_GELU = 0, 1
 
 EXPORTS = (
     "saf_abi_version", "saf_last_error", "saf_launch_count", "saf_device_supported",
     "saf_mixed_attn_fwd", "saf_mixed_attn_bwd", "saf_mixed_attn_bwd_static", "saf_frozen_pv_fwd", "saf_frozen_pv_bwd",
     "saf_indexed_linear_fwd", "saf_indexed_linear_bwd_dx", "saf_indexed_linear_bwd_dw",
-    "saf_decomposed_logz", "saf_rope_slabs",
+    "saf_decomposed_logz", "saf_rope_slabs", "saf_layernorm_fwd",
 )
 
 
@@ -108,6 +111,9 @@ def _load():
     lib.saf_rope_slabs.argtypes = [C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
                                    C.POINTER(C.c_int32), C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p]
     lib.saf_rope_slabs.restype = C.c_int
+    lib.saf_layernorm_fwd.argtypes = [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64,
+                                      C.c_int32, C.c_int32, C.c_float, C.c_int32, C.c_void_p]
+    lib.saf_layernorm_fwd.restype = C.c_int
     if lib.saf_abi_version() != 1:
         raise ImportError("libsaf_b200.so ABI version %d, expected 1: rebuild" % lib.saf_abi_version())
     return lib

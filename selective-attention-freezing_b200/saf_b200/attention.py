@@ -318,7 +318,7 @@ class SafCausalSelfAttention(nn.Module):
             self._last_attn = att.detach()
         return att @ v
 
-    def _attend_cheap(self, x, rope=None):
+    def _attend_cheap(self, x, rope=None, residual=None):
         B, T, C = x.shape
         nh, hd = self.n_head, self.head_dim
         rp = self._rope_f32(rope, T, x.device)
@@ -342,7 +342,10 @@ class SafCausalSelfAttention(nn.Module):
             y = y.transpose(1, 2).reshape(B, T, nh * hd)
             cw = self.c_proj.weight if self.c_proj.weight.dtype == act_dt else self.c_proj.weight.to(act_dt)
             cb = None if self.c_proj.bias is None else self.c_proj.bias.to(act_dt)
-            return ops.linear_rows(y, cw, cb, self._all_rows)
+            if residual is not None and (nh * hd) % 64 == 0:
+                return ops.linear_act(y, cw, cb, residual=residual.to(act_dt))   # residual add in the GEMM epilogue
+            out = ops.linear_rows(y, cw, cb, self._all_rows)
+            return out if residual is None else residual + out
         # training / fp32: live-only Q,K projection with exact-zero frozen rows in the weight gradient
         v = self.v_proj(x).view(B, T, nh, hd).transpose(1, 2)
         if nuf == 0:
@@ -356,9 +359,10 @@ class SafCausalSelfAttention(nn.Module):
         y = ops.fused_mixed_attn(qu, ku, v, patt, self._fz_mask_i32, self._hidx_i32,
                                  alpha=dec[0], rho=dec[1], z=dec[2], validate=False, sink_decay=self._sd)
         y = y.transpose(1, 2).reshape(B, T, nh * hd)
-        return self.c_proj(y)
+        out = self.c_proj(y)
+        return out if residual is None else residual + out
 
-    def forward(self, x, rope=None):
+    def forward(self, x, rope=None, residual=None):
         """(B, T, C) -> (B, T, C), output of c_proj included (nanogpt/model.py:1063-1077)."""
         if self._fz_dirty:
             self._refresh_freeze_cache()
@@ -374,7 +378,8 @@ class SafCausalSelfAttention(nn.Module):
                 rot = lambda t: torch.cat((-t[..., hd // 2:], t[..., :hd // 2]), dim=-1)   # noqa: E731
                 q, k = q * cos + rot(q) * sin, k * cos + rot(k) * sin
             y = self._attend_dynamic(q, k, v).transpose(1, 2).contiguous().view(B, T, nh * hd)
-            return self.c_proj(y)
+            out = self.c_proj(y)
+            return out if residual is None else residual + out
         if not x.is_cuda:
             raise RuntimeError("SafCausalSelfAttention runs on CUDA only (set_capture(True) gives the eager torch path)")
-        return self._attend_cheap(x, rope=rope)
+        return self._attend_cheap(x, rope=rope, residual=residual)

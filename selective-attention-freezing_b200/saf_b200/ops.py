@@ -657,3 +657,54 @@ def qkv_projection(x, wq, wk, wv, live_heads, head_dim, rope=None, T=None, biase
     a.out, a.ldo = out.data_ptr(), out.stride(0)
     check(lib.saf_indexed_linear_fwd(C.byref(a), _stream(x)))
     return out
+
+
+# ---------------------------------------------------------------------------
+# rest of the transformer block around the attention path (inference, bf16)
+# ---------------------------------------------------------------------------
+def layer_norm(x, weight, bias=None, eps=1e-5):
+    """F.layer_norm(x, (C,), weight, bias, eps) as the reference's LayerNorm does (nanogpt/model.py:45-54).
+    No autograd (prefill path)."""
+    _require_cuda(x, "x")
+    x2 = _as_2d(x)
+    w = weight if weight.dtype == x.dtype else weight.to(x.dtype)
+    b = None if bias is None else (bias if bias.dtype == x.dtype else bias.to(x.dtype))
+    out = torch.empty_like(x2)
+    check(lib.saf_layernorm_fwd(x2.data_ptr(), x2.stride(0), w.data_ptr(), _ptr(b), out.data_ptr(), out.stride(0),
+                                x2.shape[0], x2.shape[1], float(eps), _dt(x2), _stream(x)))
+    return out.view(x.shape)
+
+
+_ALL_ROWS64 = {}
+
+
+def linear_act(x, weight, bias=None, act=None, residual=None):
+    """[residual +] act(F.linear(x, weight, bias)) in one GEMM launch: the c_fc + GELU and c_proj + residual
+    steps of the reference's MLP / Block (nanogpt/model.py:1202-1207, 1237-1240).  act: None or "gelu"
+    (exact erf form, nn.GELU()).  bf16 tensors, output features a multiple of 64; no autograd."""
+    _check_lin(x, weight)
+    if x.dtype != torch.bfloat16:
+        raise TypeError("linear_act runs on the bf16 tensor-core path only")
+    N = weight.shape[0]
+    if N % 64:
+        raise ValueError("output features must be a multiple of 64")
+    x2 = _as_2d(x)
+    row0 = _ALL_ROWS64.get(N)
+    if row0 is None:
+        row0 = _ALL_ROWS64[N] = list(range(0, N, 64))
+    keep = []
+    a = _lin_args(x2, [weight], [bias] if bias is not None else None, 64, [0] * len(row0), row0, keep)
+    out = torch.empty((x2.shape[0], N), device=x.device, dtype=x.dtype)
+    a.out, a.ldo = out.data_ptr(), out.stride(0)
+    if act is not None:
+        if act != "gelu":
+            raise ValueError("unknown activation %r" % (act,))
+        a.act = _cabi.ACT_GELU
+    if residual is not None:
+        r2 = _as_2d(residual)
+        if r2.shape != out.shape or r2.dtype != out.dtype:
+            raise ValueError("residual must match the output")
+        a.residual, a.ldr = r2.data_ptr(), r2.stride(0)
+        keep.append(r2)
+    check(lib.saf_indexed_linear_fwd(C.byref(a), _stream(x)))
+    return out.view(*x.shape[:-1], N)
