@@ -54,15 +54,17 @@ struct GemmParams {
 // exact-form GELU, 0.5 x (1 + erf(x / sqrt 2)), with erf from Abramowitz-Stegun 7.1.26 (|error| < 1.5e-7):
 // one reciprocal and one exponential on the special-function unit, the rest FMAs
 __device__ __forceinline__ float gelu_erf(float x) {
-  const float z = fabsf(x) * 0.70710678118654752f;
-  const float t = __frcp_rn(fmaf(0.3275911f, z, 1.f));
-  float poly = fmaf(1.061405429f, t, -1.453152027f);
-  poly = fmaf(poly, t, 1.421413741f);
-  poly = fmaf(poly, t, -0.284496736f);
-  poly = fmaf(poly, t, 0.254829592f);
-  const float e = exp2f(-z * z * 1.4426950408889634f);
-  const float erf_abs = 1.f - poly * t * e;
-  return 0.5f * x * (1.f + copysignf(erf_abs, x));
+  // Phi(-|x|) = 0.5 erfc(|x| / sqrt 2) = 0.5 t (a1 + t (a2 + t (a3 + t (a4 + t a5)))) exp(-x^2 / 2)
+  const float ax = fabsf(x);
+  float t, e;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(t) : "f"(fmaf(0.3275911f * 0.70710678118654752f, ax, 1.f)));
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(ax * ax * (-0.5f * 1.4426950408889634f)));
+  float poly = fmaf(0.5f * 1.061405429f, t, 0.5f * -1.453152027f);
+  poly = fmaf(poly, t, 0.5f * 1.421413741f);
+  poly = fmaf(poly, t, 0.5f * -0.284496736f);
+  poly = fmaf(poly, t, 0.5f * 0.254829592f);
+  const float q = poly * t * e;                 // Phi(-|x|)
+  return x * (x >= 0.f ? 1.f - q : q);          // x Phi(x)
 }
 
 struct SmemLayout {

@@ -175,6 +175,34 @@ def main():
             run()
             n = ops.launch_count() - n0
             ms = _timed(run, args.reps)
+        elif op in ("block_infer", "mlp_infer"):
+            # whole transformer block (LayerNorms, attention path, MLP with fused epilogues) or its MLP half
+            from types import SimpleNamespace
+            from saf_b200.block import SafBlock
+            cfg = SimpleNamespace(n_embd=C, n_head=H, block_size=T, bias=False, dropout=0.0, position_encoding="rope",
+                                  rand_attn_prior_repr="dense", freeze_pattern_dtype="bfloat16")
+            blk = SafBlock(cfg).to(dev)
+            if nf:
+                a_, r_ = synthetic.sink_decay_params(nf, 2337)
+                blk.main_block.freeze_heads_sink_decay(fz, a_.tolist(), r_.tolist())
+            blk = blk.bfloat16().eval()
+            rope = (cos.view(1, 1, T, hd), sin.view(1, 1, T, hd))
+            xi = x.detach()
+            fl_mlp = 2.0 * B * T * C * 8 * C
+            if op == "block_infer":
+                def run():
+                    with torch.inference_mode():
+                        blk(xi, rope=rope)
+                fl = fl_attn + 2.0 * B * T * C * (2 * U + 2 * H) * hd + fl_mlp
+            else:
+                def run():
+                    with torch.inference_mode():
+                        blk.mlp(blk.ln_2(xi), residual=xi)
+                fl = fl_mlp
+            n0 = ops.launch_count()
+            run()
+            n = ops.launch_count() - n0
+            ms = _timed(run, args.reps)
         else:
             raise SystemExit("unknown op %r" % op)
         print(json.dumps({"op": op, "shape": shape, "ms": round(ms, 4), "tflops": round(fl / ms / 1e9, 1),
