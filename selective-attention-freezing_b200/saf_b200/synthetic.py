@@ -31,9 +31,10 @@ def sink_decay_params(n, seed):
     return a, r
 
 
-def build_attention_stack(name, device, dtype=torch.bfloat16, seed=1337):
+def build_attention_stack(name, device, dtype=torch.bfloat16, seed=1337, blocks=False):
     """The attention+projection stack of a GPT-2-style model: one SafCausalSelfAttention per layer with
-    random-init N(0, 0.02^2) weights, 25 % of the heads of every layer frozen on seeded sink+decay patterns."""
+    random-init N(0, 0.02^2) weights, 25 % of the heads of every layer frozen on seeded sink+decay patterns.
+    blocks=True wraps every layer in its transformer block (LayerNorms, residuals, MLP with 4x expansion)."""
     w = WORKLOADS[name]
     C = w["n_head"] * w["head_dim"]
     cfg = SimpleNamespace(n_embd=C, n_head=w["n_head"], block_size=w["T"], bias=False, dropout=0.0,
@@ -48,6 +49,14 @@ def build_attention_stack(name, device, dtype=torch.bfloat16, seed=1337):
         fz = frozen_heads_for_layer(w["n_head"], w["n_frozen"], seed, li)
         a, r = sink_decay_params(len(fz), seed + 1000 + li)
         m.freeze_heads_sink_decay(fz, a.tolist(), r.tolist())
+        if blocks:
+            from .block import SafBlock
+            blk = SafBlock(cfg, layer_idx=li)
+            blk.main_block = m
+            with torch.no_grad():
+                blk.mlp.c_fc.weight.copy_(torch.randn(4 * C, C, generator=g) * 0.02)
+                blk.mlp.c_proj.weight.copy_(torch.randn(C, 4 * C, generator=g) * 0.02)
+            m = blk
         layers.append(m.to(device=device, dtype=dtype).eval())
     cos, sin = rope_tables(w["head_dim"], w["T"], base=w["rope_base"], device=device)
     rope = (cos.view(1, 1, w["T"], -1), sin.view(1, 1, w["T"], -1))
@@ -69,7 +78,8 @@ def hot_stack_flops(w):
     live = 2 * U * T * T * hd                     # causal half of 4 T^2 hd
     qkv = 2 * T * C * (2 * U + H) * hd
     oproj = 2 * T * C * C
-    return dict(live=live * w["n_layer"], qkv=qkv * w["n_layer"], oproj=oproj * w["n_layer"])
+    mlp = 2 * T * C * 8 * C                       # c_fc and c_proj of the 4x MLP
+    return dict(live=live * w["n_layer"], qkv=qkv * w["n_layer"], oproj=oproj * w["n_layer"], mlp=mlp * w["n_layer"])
 
 
 def per_layer_split(m, rope, x, reps=5):
