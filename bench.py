@@ -154,9 +154,10 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--scope", default="stack", choices=["stack", "block"],
+    ap.add_argument("--scope", default="stack", choices=["stack", "block", "model"],
                     help="stack: attention+projection stack (the metric's target); block: whole transformer blocks "
-                         "(LayerNorms, residuals, MLP added)")
+                         "(LayerNorms, residuals, MLP added); model: token ids -> embedding -> blocks -> final "
+                         "LayerNorm -> last-position logits")
     args = ap.parse_args()
 
     from saf_b200 import synthetic
@@ -175,15 +176,27 @@ def main():
     warmup = max(args.warmup, 3)
     steps = max(args.steps, 1)
 
-    layers, rope, w = synthetic.build_attention_stack(args.workload, dev, blocks=(args.scope == "block"))
-    B, T, C = w["B"], w["T"], w["n_head"] * w["head_dim"]
     g = torch.Generator().manual_seed(1000 + rank)
-    x_host = torch.randn(B, T, C, generator=g).bfloat16().pin_memory()
+    if args.scope == "model":
+        # the whole model: int32 token ids in, last-position logits out
+        model, w = synthetic.build_model(args.workload, dev)
+        layers, rope = list(model.transformer.h), None
+        B, T, C = w["B"], w["T"], w["n_head"] * w["head_dim"]
+        x_host = torch.randint(0, model.config.vocab_size, (B, T), generator=g, dtype=torch.int32).pin_memory()
+        last_host = torch.empty(B, model.config.vocab_size, dtype=torch.bfloat16).pin_memory()
+        run = lambda xin: model(xin)[:, 0, :]             # (B, vocab)
+        result_of = lambda out: out
+    else:
+        layers, rope, w = synthetic.build_attention_stack(args.workload, dev, blocks=(args.scope == "block"))
+        B, T, C = w["B"], w["T"], w["n_head"] * w["head_dim"]
+        x_host = torch.randn(B, T, C, generator=g).bfloat16().pin_memory()
+        last_host = torch.empty(B, C, dtype=torch.bfloat16).pin_memory()
+        run = lambda xin: synthetic.stack_forward(layers, rope, xin)
+        result_of = lambda out: out[:, -1, :]
     x_dev = x_host.to(dev, non_blocking=True)
-    last_host = torch.empty(B, C, dtype=torch.bfloat16).pin_memory()
 
     def step_resident():
-        return synthetic.stack_forward(layers, rope, x_dev)
+        return run(x_dev)
 
     # end to end: every step copies its input from pinned host memory and reads its result back.  The copy
     # of step i+1 runs on a second stream into the other of two device buffers while step i computes.
@@ -208,9 +221,9 @@ def main():
             issue_copy(0)
         issue_copy(slot ^ 1)                              # next step's input, overlapped with this step
         torch.cuda.current_stream().wait_event(copied[slot])
-        h = synthetic.stack_forward(layers, rope, x_bufs[slot])
+        h = run(x_bufs[slot])
         consumed[slot].record()
-        last_host.copy_(h[:, -1, :], non_blocking=True)
+        last_host.copy_(result_of(h), non_blocking=True)
         e2e_state["i"] = i + 1
         return h
 
@@ -255,8 +268,13 @@ def main():
         e2e_ms = e0.elapsed_time(e1)
 
         # per-layer split (outside the timed regions): each piece launched alone on layer 0's tensors
-        attn0 = layers[0].main_block if args.scope == "block" else layers[0]
-        split = synthetic.per_layer_split(attn0, rope, x_dev) if rank == 0 else None
+        attn0 = layers[0] if args.scope == "stack" else layers[0].main_block
+        if rank != 0:
+            split = None
+        elif args.scope == "model":
+            split = synthetic.per_layer_split(attn0, model.rope(T, dev), model.transformer.wte(x_dev))
+        else:
+            split = synthetic.per_layer_split(attn0, rope, x_dev)
 
     total_ms = parallel.max_over_ranks(total_ms, dev)
     e2e_ms = parallel.max_over_ranks(e2e_ms, dev)
@@ -273,18 +291,18 @@ def main():
     live_flops_per_launch = fl["live"] / w["n_layer"] * B
     attn_mean_ms = statistics.mean(attn_ms)
     achieved = live_flops_per_launch / (attn_mean_ms * 1e-3) / 1e12
-    stack_flops = (fl["live"] + fl["qkv"] + fl["oproj"] + (fl["mlp"] if args.scope == "block" else 0)) * B
+    stack_flops = (fl["live"] + fl["qkv"] + fl["oproj"] + (fl["mlp"] if args.scope != "stack" else 0)) * B
     line = {
-        "metric": METRIC if args.scope == "stack" else METRIC.replace("attention+projection stack", "whole transformer blocks"),
+        "metric": METRIC.replace("attention+projection stack", {"stack": "attention+projection stack", "block": "whole transformer blocks", "model": "whole model: embedding, blocks, final LayerNorm, last-position logits"}[args.scope]),
         "value": value, "unit": "tokens/s", "n_gpus": world, "steps": steps, "warmup": warmup,
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic",
         "config": {"workload": workload_name(args.workload, w) + ("; whole blocks: + LayerNorms, residuals, 4x MLP with "
-                                                                   "GELU" if args.scope == "block" else ""),
+                                                                   "GELU" if args.scope != "stack" else "") + ("; token ids in, last-position logits out" if args.scope == "model" else ""),
                    "l2": "per-layer working set (x 100 MB, qkv 250 MB, attention out 100 MB) exceeds the 126 MB L2",
                    "timing": "CUDA events on the launching stream, max over ranks"},
         "clocks": clocks,
-        "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": x_host.numel() * 2,
+        "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": x_host.numel() * x_host.element_size(),
                 "d2h_bytes_per_step": last_host.numel() * 2},
         "gpu_launches": launches,
         "roofline": {"bound": "tensor", "kernel": "flash_fwd_kernel (live heads on tcgen05 + co-scheduled frozen-head scan, one launch per layer)",

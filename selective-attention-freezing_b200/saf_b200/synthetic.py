@@ -132,3 +132,20 @@ def per_layer_split(m, rope, x, reps=5):
         y2 = y.transpose(1, 2).reshape(B, T, nh * hd)
         out["c_proj_gemm"], _ = timed(lambda: ops.linear_rows(y2, m.c_proj.weight, None, m._all_rows))
     return out
+
+
+def build_model(name, device, dtype=torch.bfloat16, seed=1337, vocab_size=50257):
+    """The whole GPT-2-style model of a workload (random init N(0, 0.02^2), tied embedding), blocks as in
+    build_attention_stack(blocks=True)."""
+    from .model import SafGPT
+    blocks, rope, w = build_attention_stack(name, "cpu", dtype=torch.float32, seed=seed, blocks=True)
+    C = w["n_head"] * w["head_dim"]
+    cfg = SimpleNamespace(n_embd=C, n_head=w["n_head"], n_layer=w["n_layer"], block_size=w["T"], bias=False, dropout=0.0,
+                          position_encoding="rope", rand_attn_prior_repr="dense", freeze_pattern_dtype="bfloat16",
+                          vocab_size=vocab_size, rope_base=w["rope_base"])
+    m = SafGPT(cfg)
+    m.transformer.h = torch.nn.ModuleList(blocks)
+    g = torch.Generator().manual_seed(seed + 7)
+    with torch.no_grad():
+        m.lm_head.weight.copy_(torch.randn(vocab_size, C, generator=g) * 0.02)
+    return m.to(device=device, dtype=dtype).eval(), w

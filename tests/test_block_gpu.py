@@ -90,3 +90,43 @@ def test_whole_block_bf16_inference():
     ref = O.block(x.float(), sd["ln_1.weight"], sd["ln_2.weight"], attn, sd["mlp.c_fc.weight"], sd["mlp.c_proj.weight"])
     aerr, rerr = errs(y, ref)
     assert aerr <= 6e-2 and rerr <= 1e-2, f"block: max-abs {aerr} rel-l2 {rerr}"
+
+
+def test_whole_model_last_position_logits():
+    """Token ids -> embedding -> blocks -> final LayerNorm -> tied lm_head at the last position
+    (GPT.forward for inference, nanogpt/model.py:1373-1416)."""
+    from saf_b200.model import SafGPT
+    B, T, C, H, L, V = 2, 300, 256, 4, 2, 1000
+    hd = C // H
+    cfg = SimpleNamespace(n_embd=C, n_head=H, n_layer=L, block_size=T, bias=False, dropout=0.0, position_encoding="rope",
+                          rand_attn_prior_repr="dense", freeze_pattern_dtype="float32", vocab_size=V, rope_base=10000.0)
+    torch.manual_seed(11)
+    m = SafGPT(cfg)
+    with torch.no_grad():
+        for prm in m.parameters():
+            prm.copy_(torch.randn_like(prm) * 0.05 if prm.ndim == 2 else 1 + 0.1 * torch.randn_like(prm))
+    m = m.cuda().bfloat16().eval()
+    fz = [1]
+    a, r = O.sink_decay_params(1, seed=3)
+    a, r = a.float().double(), r.float().double()
+    for blk in m.transformer.h:
+        blk.main_block.freeze_heads_sink_decay(fz, a.tolist(), r.tolist())
+    idx = torch.randint(0, V, (B, T), generator=torch.Generator().manual_seed(2), dtype=torch.int32)
+    with torch.inference_mode():
+        logits = m(idx.cuda())
+    assert logits.shape == (B, 1, V)
+    sd = {k: v.float().cpu() for k, v in m.state_dict().items()}
+    patt = torch.zeros(H, T, T)
+    patt[fz] = O.sink_decay_pattern(a, r, T).float()
+    states = [1 if h in fz else 0 for h in range(H)]
+    x = sd["lm_head.weight"][idx.long()]
+    for li in range(L):
+        pre = f"transformer.h.{li}."
+        attn = lambda t, pre=pre: O.attention_layer(t, sd[pre + "main_block.q_proj.weight"], sd[pre + "main_block.k_proj.weight"],
+                                                    sd[pre + "main_block.v_proj.weight"], sd[pre + "main_block.c_proj.weight"],
+                                                    states, patt, H, rope=O.rope_cache(hd, T))
+        x = O.block(x, sd[pre + "ln_1.weight"], sd[pre + "ln_2.weight"], attn, sd[pre + "mlp.c_fc.weight"],
+                    sd[pre + "mlp.c_proj.weight"])
+    ref = torch.nn.functional.linear(O.layer_norm(x, sd["transformer.ln_f.weight"])[:, -1:, :], sd["lm_head.weight"])
+    aerr, rerr = errs(logits, ref)
+    assert rerr <= 2e-2, f"logits: max-abs {aerr} rel-l2 {rerr}"
