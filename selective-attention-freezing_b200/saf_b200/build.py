@@ -22,6 +22,9 @@ NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", 
               "-Xcompiler", "-fPIC", "--use_fast_math", "-Xptxas", "-v"]
 # --use_fast_math would change exp2f/expf/division accuracy in the fp32 contract path: keep IEEE there
 NVCC_FLAGS.remove("--use_fast_math")
+# extra defines for special builds, e.g. SAF_B200_EXTRA_NVCC_FLAGS="-DSAF_FWD_TRACE -DSAF_BWD_TRACE" (clock stamps of one
+# CTA's pipeline events, read back with `python -m saf_b200.opbench --trace`); rebuild with --force afterwards
+NVCC_FLAGS += os.environ.get("SAF_B200_EXTRA_NVCC_FLAGS", "").split()
 
 
 def _sources():

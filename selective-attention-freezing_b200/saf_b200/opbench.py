@@ -45,6 +45,9 @@ def main():
     ap.add_argument("--T", type=int, default=None)
     ap.add_argument("--reps", type=int, default=5)
     ap.add_argument("--frozen", default="sink_decay", choices=["sink_decay", "dense", "decomposed", "none"])
+    ap.add_argument("--trace", action="store_true",
+                    help="after the runs, print the per-step clock stamps a library built with -DSAF_FWD_TRACE / "
+                         "-DSAF_BWD_TRACE recorded for one CTA (heaviest tile of batch 0, head 0; head 0 must be live)")
     args = ap.parse_args()
     w = dict(synthetic.WORKLOADS[args.workload])
     if args.B:
@@ -209,5 +212,39 @@ def main():
                           "launches": n}), flush=True)
 
 
+def print_trace():
+    """Steady-state cycle counts of one CTA's pipeline from the trace arrays of a special build."""
+    import ctypes
+    lib = ops.lib
+    if hasattr(lib, "saf_debug_ftrace"):
+        buf = (ctypes.c_longlong * (8 * 64))()
+        lib.saf_debug_ftrace.argtypes = [ctypes.c_void_p]
+        lib.saf_debug_ftrace(buf)
+        t = [buf[e * 64:(e + 1) * 64] for e in range(8)]
+        n = range(8, 40)
+        mean = lambda f: sum(f(j) for j in n) / len(n)
+        print(json.dumps({"trace": "flash_fwd, query tile 0 of the last row pair, cycles",
+                          "period_per_key_step": (t[0][40] - t[0][8]) / 32.0,
+                          "softmax_busy": mean(lambda j: t[1][j] - t[0][j]),
+                          "softmax_waits_for_next_scores": mean(lambda j: t[0][j + 1] - t[1][j]),
+                          "p_ready_to_issuer_saw_it": mean(lambda j: t[3][j] - t[1][j]),
+                          "scores_issued_to_visible": mean(lambda j: t[0][j] - t[2][j])}))
+    if hasattr(lib, "saf_debug_trace"):
+        buf = (ctypes.c_longlong * (2 * 8 * 64))()
+        lib.saf_debug_trace.argtypes = [ctypes.c_void_p]
+        lib.saf_debug_trace(buf)
+        for kern, name in ((0, "flash_bwd_dkdv, key tile 0"), (1, "flash_bwd_dq, last query tile")):
+            t = [buf[(kern * 8 + e) * 64:(kern * 8 + e + 1) * 64] for e in range(8)]
+            n = range(8, 40)
+            mean = lambda f: sum(f(j) for j in n) / len(n)
+            first = 1 if kern == 0 else 2
+            print(json.dumps({"trace": name + ", cycles", "period_per_tile": (t[0][40] - t[0][8]) / 32.0,
+                              "scores_visible_to_first_handover": mean(lambda j: t[first][j] - t[0][j]),
+                              "dP_visible_to_dS_handed_over": mean(lambda j: t[3][j] - t[2][j]),
+                              "dS_handed_over_to_next_scores_visible": mean(lambda j: t[0][j + 1] - t[3][j])}))
+
+
 if __name__ == "__main__":
     main()
+    if "--trace" in sys.argv:
+        print_trace()
