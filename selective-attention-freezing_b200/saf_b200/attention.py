@@ -267,6 +267,7 @@ class SafCausalSelfAttention(nn.Module):
         self._sd_any = 3 in states
         sd = self.sd_params()
         self._sd = (sd[:, 0].contiguous(), sd[:, 1].contiguous()) if self._sd_any else None
+        self._patt_cast = None      # compact copy of the dense heads' patterns in the activation dtype, built on demand
         self._fz_dirty = False
 
     # ---- forward --------------------------------------------------------------------------
@@ -322,9 +323,20 @@ class SafCausalSelfAttention(nn.Module):
         B, T, C = x.shape
         nh, hd = self.n_head, self.head_dim
         rp = self._rope_f32(rope, T, x.device)
-        patt = self.dyn_pattern
+        patt, pidx = self.dyn_pattern, None
         dec = (self.dyn_alpha, self.dyn_rho, self.dyn_z) if self._dec_any else (None, None, None)
         act_dt = torch.get_autocast_dtype("cuda") if torch.is_autocast_enabled("cuda") else x.dtype
+        if act_dt == torch.bfloat16 and patt is not None and patt.dtype != act_dt and 1 in self._states:
+            # The kernels multiply the pattern in the activation dtype (the reference casts P to v's dtype in
+            # registers, kernel/frozen_attn.py:81).  A compact bf16 copy of the dense heads' planes, made once per
+            # freeze set, gives the same products and lets them run on the TMA-fed tensor-core path.
+            if self._patt_cast is None:
+                dense = [h for h in range(nh) if self._states[h] == 1]
+                slot = [0] * nh
+                for i, h in enumerate(dense):
+                    slot[h] = i
+                self._patt_cast = (patt[dense].to(act_dt), torch.tensor(slot, dtype=torch.int32, device=patt.device))
+            patt, pidx = self._patt_cast
         nuf = len(self._live)
         if not torch.is_grad_enabled() and act_dt == torch.bfloat16:
             # inference: one GEMM, canonical weights read in place, RoPE in the epilogue
@@ -337,7 +349,7 @@ class SafCausalSelfAttention(nn.Module):
             qu = qkv[:, :, :nuf].transpose(1, 2)
             ku = qkv[:, :, nuf:2 * nuf].transpose(1, 2)
             v = qkv[:, :, 2 * nuf:].transpose(1, 2)
-            y = ops.fused_mixed_attn(qu, ku, v, patt, self._fz_mask_i32, self._hidx_i32,
+            y = ops.fused_mixed_attn(qu, ku, v, patt, self._fz_mask_i32, self._hidx_i32, pidx,
                                      alpha=dec[0], rho=dec[1], z=dec[2], validate=False, sink_decay=self._sd)
             y = y.transpose(1, 2).reshape(B, T, nh * hd)
             cw = self.c_proj.weight if self.c_proj.weight.dtype == act_dt else self.c_proj.weight.to(act_dt)
@@ -356,7 +368,7 @@ class SafCausalSelfAttention(nn.Module):
             qk = ops.linear_rows2(x, self.q_proj.weight, self.k_proj.weight, self.q_proj.bias, self.k_proj.bias,
                                   self._uf_cols, rope=rp, head_dim=hd).view(B, T, 2, nuf, hd)
             qu, ku = qk[:, :, 0].transpose(1, 2), qk[:, :, 1].transpose(1, 2)
-        y = ops.fused_mixed_attn(qu, ku, v, patt, self._fz_mask_i32, self._hidx_i32,
+        y = ops.fused_mixed_attn(qu, ku, v, patt, self._fz_mask_i32, self._hidx_i32, pidx,
                                  alpha=dec[0], rho=dec[1], z=dec[2], validate=False, sink_decay=self._sd)
         y = y.transpose(1, 2).reshape(B, T, nh * hd)
         out = self.c_proj(y)

@@ -205,9 +205,9 @@ def test_training_step_under_bf16_autocast(structured):
         y = m(xd, rope=rope)
     w = torch.randn(y.shape, generator=torch.Generator().manual_seed(3))
     (y.float() * w.cuda()).sum().backward()
-    # linear_rows2+RoPE, mixed attention | delta, dK/dV (+ frozen-head roles), dQ, adjoint RoPE, dx, dW; the
-    # fp32-stored dense pattern of this module takes one more launch in the backward (CUDA-core dV kernel)
-    assert launch_count() - n0 == (8 if structured else 9)
+    # linear_rows2+RoPE, mixed attention | delta, dK/dV (+ frozen-head roles), dQ, adjoint RoPE, dx, dW.  The module's
+    # fp32-stored dense pattern is used through a compact bf16 copy, so dense heads ride the same launches.
+    assert launch_count() - n0 == 8
     full = torch.zeros(H, T, T)
     full[fz] = O.freeze_normalise(patt)
     states = [1 if h in fz else 0 for h in range(H)]
