@@ -10,7 +10,8 @@ reference's behaviour travels.  What is recorded:
   * op level: ref() and decomp_materialize() of kernel/test_fused_attn.py:40-63, ref_fwd() of
     kernel/test_frozen_attn.py:27-28, decomp_logits / decomposed_logz / make_rho_band of
     kernel/fused_attn.py:65-116, linear_rows / linear_rows2 / linear_permuted_cols of
-    kernel/indexed_linear.py with their gradients, apply_rotary_pos_emb of nanogpt/model.py:63-68.
+    kernel/indexed_linear.py with their gradients, apply_rotary_pos_emb of nanogpt/model.py:63-68;
+  * block level: the reference's LayerNorm and MLP modules (nanogpt/model.py:45-54, 1193-1207) on seeded inputs.
 """
 import importlib.util
 import os
@@ -147,6 +148,27 @@ def main(ref_root):
     out["lin_pcols_y"] = y3.detach().numpy()
     for nme, t in zip(("dy", "dw", "db"), leaves):
         out[f"lin_pcols_{nme}"] = t.grad.numpy()
+
+    # ---- rest of the block: the reference's LayerNorm and MLP modules (nanogpt/model.py:45-54, 1193-1207) ----
+    g = torch.Generator().manual_seed(26)
+    Cb = 96
+    xb = torch.randn(2, 19, Cb, generator=g) * 1.5 + 0.3
+    ln = M.LayerNorm(Cb, bias=True)
+    cfgb = M.GPTConfig(block_size=32, vocab_size=64, n_layer=1, n_head=4, n_embd=Cb, dropout=0.0, bias=True)
+    mlp = M.MLP(cfgb)
+    with torch.no_grad():
+        ln.weight.copy_(1 + 0.1 * torch.randn(Cb, generator=g))
+        ln.bias.copy_(0.1 * torch.randn(Cb, generator=g))
+        mlp.c_fc.weight.copy_(torch.randn(4 * Cb, Cb, generator=g) * 0.1)
+        mlp.c_fc.bias.copy_(torch.randn(4 * Cb, generator=g) * 0.1)
+        mlp.c_proj.weight.copy_(torch.randn(Cb, 4 * Cb, generator=g) * 0.1)
+        mlp.c_proj.bias.copy_(torch.randn(Cb, generator=g) * 0.1)
+        out["blk_x"] = xb.numpy()
+        out["blk_ln_w"], out["blk_ln_b"] = ln.weight.numpy().copy(), ln.bias.numpy().copy()
+        out["blk_ln_y"] = ln(xb).numpy()
+        out["blk_fc_w"], out["blk_fc_b"] = mlp.c_fc.weight.numpy().copy(), mlp.c_fc.bias.numpy().copy()
+        out["blk_pr_w"], out["blk_pr_b"] = mlp.c_proj.weight.numpy().copy(), mlp.c_proj.bias.numpy().copy()
+        out["blk_mlp_y"] = mlp.eval()(xb).numpy()
 
     path = os.path.join(HERE, "reference_vectors.npz")
     np.savez_compressed(path, **out)

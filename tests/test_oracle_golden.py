@@ -133,3 +133,12 @@ def test_scan_identity_equals_dense_product():
     for i in range(2):
         assert O.max_abs(O.sink_decay_scan(v, a[i].item(), r[i].item()), P[i] @ v) <= 1e-12
     assert (P.sum(-1) - 1).abs().max().item() <= 1e-12
+
+
+def test_block_functions_match_reference_modules():
+    """layer_norm / mlp of the oracle against the reference's LayerNorm and MLP modules run on the same inputs."""
+    t = lambda k: torch.from_numpy(G[k])
+    y = O.layer_norm(t("blk_x"), t("blk_ln_w"), t("blk_ln_b"))
+    assert O.max_abs(y, t("blk_ln_y")) <= 1e-6
+    y = O.mlp(t("blk_x"), t("blk_fc_w"), t("blk_pr_w"), t("blk_fc_b"), t("blk_pr_b"))
+    assert O.max_abs(y, t("blk_mlp_y")) <= 1e-6
