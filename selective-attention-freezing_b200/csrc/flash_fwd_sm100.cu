@@ -42,7 +42,10 @@ namespace {
 constexpr int FM = 128;             // rows per query tile
 constexpr int FN = 128;             // keys per step
 constexpr int FLASH_THREADS = 384;
-constexpr int HEAD_GROUP = 8;
+#ifndef SAF_HEAD_GROUP
+#define SAF_HEAD_GROUP 8
+#endif
+constexpr int HEAD_GROUP = SAF_HEAD_GROUP;   // (batch, head) pairs whose tiles are in flight together (K/V shared in L2)
 constexpr float LOG2E_F = 1.4426950408889634f;
 constexpr float RESCALE_THRESHOLD = 8.0f;
 #ifndef SAF_POLY_EXP_PER_16
