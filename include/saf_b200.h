@@ -235,6 +235,43 @@ int saf_layernorm_fwd(const void* x, int64_t ldx, const void* weight, const void
 int saf_decomposed_logz(const float* alpha, const float* rho, float* z, int32_t H, int32_t S, void* stream);
 
 /* ---------------------------------------------------------------------------
+ * Trainable decomposed patterns (supplement/trainable_pattern_kernels.py).
+ *
+ * saf_pattern_normalisers replaces normalisers() (:62-66, kernel :8-18): rows i < T get
+ * z[h,i] = logsumexp_{j<=i}(alpha[h,j] + rho[h,i-j]); rows T..S-1 are set to zero.
+ *
+ * saf_pattern_param_grad replaces PatternGradient.backward / _parameter_backward (:21-58,
+ * :79-85): for every head whose state is SAF_DECOMP, with P_ij = exp(alpha_j + rho_{i-j} - z_i),
+ * dP = dout v^T and delta_i = dout_i . out_i,
+ *     dalpha[h,j] += sum_{b,i} P_ij (dP_ij - delta_i)      drho[h,d] += sum_{b, i-j=d} P_ij (dP_ij - delta_i).
+ * The call ADDS into dalpha / drho (fp32 atomics, like the reference): the caller zero-fills them.
+ * bf16 tensors with head_dim 64/128 run on the tensor cores, everything else on the CUDA cores in fp32.
+ * ------------------------------------------------------------------------- */
+int saf_pattern_normalisers(const float* alpha, const float* rho, float* z, int32_t H, int32_t S, int32_t T,
+                            void* stream);
+
+typedef struct SafPatternGradArgs {
+  int32_t struct_size; /* sizeof(SafPatternGradArgs), checked                        */
+  int32_t dtype;       /* SafDType of v, out, dout                                   */
+  int32_t B, H, T, HD;
+  int32_t SD;          /* alpha, rho, z, dalpha, drho are (H, SD) fp32, SD >= T      */
+  int32_t force_state; /* -1: heads with frozen[h] == SAF_DECOMP; 2: every head      */
+  SafTensor v;         /* (B, H, T, HD) values the pattern was applied to            */
+  SafTensor out;       /* (B, H, T, HD) forward result                               */
+  SafTensor dout;      /* (B, H, T, HD) gradient of the result                       */
+  const float* alpha;
+  const float* rho;
+  const float* z;
+  const int32_t* frozen;      /* device (H,), SafHeadState per head; may be null with force_state */
+  const int32_t* frozen_host; /* HOST copy of frozen (optional: skips the launch when no head trains) */
+  float* dalpha;
+  float* drho;
+  int32_t* status;     /* optional device int32, as in SafMixedAttnArgs              */
+} SafPatternGradArgs;
+
+int saf_pattern_param_grad(const SafPatternGradArgs* args, void* stream);
+
+/* ---------------------------------------------------------------------------
  * Library plumbing
  * ------------------------------------------------------------------------- */
 int saf_abi_version(void);

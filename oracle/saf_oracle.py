@@ -285,3 +285,41 @@ def block(x, ln1_w, ln2_w, attn, w_fc, w_proj):
     """Block.forward (nanogpt/model.py:1237-1240) with `attn` a callable for the attention module."""
     x = x + attn(layer_norm(x, ln1_w))
     return x + mlp(layer_norm(x, ln2_w), w_fc, w_proj)
+
+
+# ---------------------------------------------------------------------------
+# learnable decomposed patterns        supplement/trainable_patterns.py:7-13,
+#                                      supplement/trainable_pattern_kernels.py:8-58
+# ---------------------------------------------------------------------------
+def pattern_dense_reference(value, alpha, rho):
+    """dense_reference (supplement/trainable_patterns.py:7-13): softmax over j <= i of alpha_j + rho_{i-j},
+    times value.  value (B,H,T,D); alpha, rho (H,S), S >= T."""
+    T = value.shape[-2]
+    lg = decomp_logits(alpha[:, :T], rho[:, :T])
+    return torch.matmul(lg.softmax(-1).to(value.dtype), value)
+
+
+def pattern_normalisers(alpha, rho, length):
+    """normalisers (supplement/trainable_pattern_kernels.py:8-18, 62-66): logsumexp rows below `length`, zero beyond."""
+    z = torch.zeros_like(alpha)
+    z[:, :length] = decomposed_logz(alpha[:, :length].contiguous(), rho[:, :length].contiguous())
+    return z
+
+
+def pattern_param_grads(value, out, grad, alpha, rho, z, states=None):
+    """_parameter_backward (supplement/trainable_pattern_kernels.py:21-58) in closed form:
+    dS = P (dO V^T - delta), dalpha_j = sum_{b,i} dS_ij, drho_d = sum_{b,i-j=d} dS_ij for heads in state 2."""
+    B, H, T, D = value.shape
+    P = decomp_pattern(alpha.double(), rho.double(), z.double(), T)                      # (H,T,T), zero above diagonal
+    dP = torch.matmul(grad.double(), value.double().transpose(-1, -2))                   # (B,H,T,T)
+    delta = (grad.double() * out.double()).sum(-1, keepdim=True)
+    dS = (P[None] * (dP - delta)).sum(0)                                                 # (H,T,T)
+    da = torch.zeros_like(alpha, dtype=torch.float64)
+    dr = torch.zeros_like(rho, dtype=torch.float64)
+    da[:, :T] = dS.sum(1)
+    for d in range(T):
+        dr[:, d] = torch.diagonal(dS, offset=-d, dim1=1, dim2=2).sum(-1)
+    if states is not None:
+        keep = (torch.as_tensor(states) == 2).to(da.dtype)[:, None]
+        da, dr = da * keep, dr * keep
+    return da, dr

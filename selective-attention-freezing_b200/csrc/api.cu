@@ -362,7 +362,34 @@ int saf_decomposed_logz(const float* alpha, const float* rho, float* z, int32_t 
   if (H < 0 || S < 0) return fail(SAF_ERR_INVALID, "negative dimension");
   if (H == 0 || S == 0) return SAF_OK;
   if (!alpha || !rho || !z) return fail(SAF_ERR_INVALID, "null pointer");
-  return launch_logz(alpha, rho, z, H, S, (cudaStream_t)stream);
+  return launch_logz(alpha, rho, z, H, S, S, (cudaStream_t)stream);
+}
+
+int saf_pattern_normalisers(const float* alpha, const float* rho, float* z, int32_t H, int32_t S, int32_t T,
+                            void* stream) {
+  if (H < 0 || S < 0 || T < 0) return fail(SAF_ERR_INVALID, "negative dimension");
+  if (T > S) return fail(SAF_ERR_INVALID, "pattern normalisers: T > S");
+  if (H == 0 || S == 0) return SAF_OK;
+  if (!alpha || !rho || !z) return fail(SAF_ERR_INVALID, "null pointer");
+  return launch_logz(alpha, rho, z, H, S, T, (cudaStream_t)stream);
+}
+
+int saf_pattern_param_grad(const SafPatternGradArgs* a, void* stream) {
+  if (!a) return fail(SAF_ERR_INVALID, "null args");
+  if (a->struct_size != (int32_t)sizeof(SafPatternGradArgs))
+    return fail(SAF_ERR_INVALID, "SafPatternGradArgs size mismatch (%d vs %d)", a->struct_size,
+                (int)sizeof(SafPatternGradArgs));
+  if (a->B < 0 || a->H < 0 || a->T < 0 || a->HD <= 0 || a->SD < 0) return fail(SAF_ERR_INVALID, "bad dimension");
+  if (a->dtype != SAF_F32 && a->dtype != SAF_BF16 && a->dtype != SAF_F16) return fail(SAF_ERR_INVALID, "bad dtype");
+  if (a->force_state >= 0 && a->force_state != SAF_DECOMP) return SAF_OK;   // no head of that state has parameters
+  if (a->B == 0 || a->H == 0 || a->T == 0) return SAF_OK;
+  if (a->SD < a->T) return fail(SAF_ERR_INVALID, "pattern gradient: SD < T");
+  if (!a->v.ptr || !a->out.ptr || !a->dout.ptr || !a->alpha || !a->rho || !a->z || !a->dalpha || !a->drho)
+    return fail(SAF_ERR_INVALID, "null pointer");
+  if (a->force_state < 0 && !a->frozen) return fail(SAF_ERR_INVALID, "frozen is null and force_state < 0");
+  if (a->v.stride[3] != 1 || a->out.stride[3] != 1 || a->dout.stride[3] != 1)
+    return fail(SAF_ERR_INVALID, "pattern gradient: last stride must be 1");
+  return launch_pattern_grad(*a, (cudaStream_t)stream);
 }
 
 }  // extern "C"

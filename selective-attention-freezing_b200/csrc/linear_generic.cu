@@ -278,10 +278,14 @@ int gemm_generic_typed(const SafIndexedLinearArgs& a, int mode, const void* dout
 
 // z[h,i] = logsumexp_{j<=i}(alpha[h,j] + rho[h,i-j]); one warp per row
 __global__ void logz_kernel(const float* __restrict__ alpha, const float* __restrict__ rho, float* __restrict__ z,
-                            int H, int S) {
+                            int H, int S, int rows) {
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   if (warp >= H * S) return;
   const int h = warp / S, i = warp - h * S;
+  if (i >= rows) {
+    if (lane == 0) z[(int64_t)h * S + i] = 0.f;
+    return;
+  }
   const float* al = alpha + (int64_t)h * S;
   const float* rh = rho + (int64_t)h * S;
   float m = -INFINITY, s = 0.f;
@@ -346,10 +350,10 @@ int launch_rope_slabs(void* x, int64_t ld, int M, int n_slabs, int slab, int T, 
   count_launch();
   return check_launch("rope_slabs_kernel");
 }
-int launch_logz(const float* alpha, const float* rho, float* z, int H, int S, cudaStream_t st) {
+int launch_logz(const float* alpha, const float* rho, float* z, int H, int S, int rows, cudaStream_t st) {
   const int64_t warps = (int64_t)H * S;
   const int64_t blocks = (warps * 32 + 255) / 256;
-  logz_kernel<<<(unsigned)blocks, 256, 0, st>>>(alpha, rho, z, H, S);
+  logz_kernel<<<(unsigned)blocks, 256, 0, st>>>(alpha, rho, z, H, S, rows);
   count_launch();
   return check_launch("logz_kernel");
 }

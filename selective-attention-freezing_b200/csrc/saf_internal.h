@@ -60,7 +60,8 @@ int launch_rope_slabs(void* x, int64_t ld, int M, int n_slabs, int slab, int T, 
                       const float* cosT, const float* sinT, int dtype, int inverse, cudaStream_t st);
 int launch_layernorm(const void* x, int64_t ldx, const void* w, const void* b, void* out, int64_t ldo, int M, int C,
                      float eps, int dtype, cudaStream_t st);
-int launch_logz(const float* alpha, const float* rho, float* z, int H, int S, cudaStream_t st);
+int launch_logz(const float* alpha, const float* rho, float* z, int H, int S, int rows, cudaStream_t st);   // rows >= `rows` get 0
+int launch_pattern_grad(const SafPatternGradArgs& a, cudaStream_t st);
 
 // TMA descriptor encode through the driver entry point (no link-time libcuda dependency)
 typedef CUresult (*TensorMapEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,

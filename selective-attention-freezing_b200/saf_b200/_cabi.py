@@ -67,6 +67,18 @@ class SafIndexedLinearArgs(C.Structure):
     ]
 
 
+class SafPatternGradArgs(C.Structure):
+    _fields_ = [
+        ("struct_size", C.c_int32), ("dtype", C.c_int32),
+        ("B", C.c_int32), ("H", C.c_int32), ("T", C.c_int32), ("HD", C.c_int32), ("SD", C.c_int32),
+        ("force_state", C.c_int32),
+        ("v", SafTensor), ("out", SafTensor), ("dout", SafTensor),
+        ("alpha", C.c_void_p), ("rho", C.c_void_p), ("z", C.c_void_p),
+        ("frozen", C.c_void_p), ("frozen_host", C.POINTER(C.c_int32)),
+        ("dalpha", C.c_void_p), ("drho", C.c_void_p), ("status", C.c_void_p),
+    ]
+
+
 ACT_NONE, ACT_GELU = 0, 1
 
 EXPORTS = (
@@ -74,6 +86,7 @@ EXPORTS = (
     "saf_mixed_attn_fwd", "saf_mixed_attn_bwd", "saf_mixed_attn_bwd_static", "saf_frozen_pv_fwd", "saf_frozen_pv_bwd",
     "saf_indexed_linear_fwd", "saf_indexed_linear_bwd_dx", "saf_indexed_linear_bwd_dw",
     "saf_decomposed_logz", "saf_rope_slabs", "saf_layernorm_fwd",
+    "saf_pattern_normalisers", "saf_pattern_param_grad",
 )
 
 
@@ -97,7 +110,8 @@ def _load():
     for name, at in (("saf_mixed_attn_fwd", SafMixedAttnArgs), ("saf_mixed_attn_bwd", SafMixedAttnBwdArgs),
                      ("saf_mixed_attn_bwd_static", SafMixedAttnBwdArgs),
                      ("saf_frozen_pv_fwd", SafFrozenPvArgs), ("saf_frozen_pv_bwd", SafFrozenPvArgs),
-                     ("saf_indexed_linear_fwd", SafIndexedLinearArgs)):
+                     ("saf_indexed_linear_fwd", SafIndexedLinearArgs),
+                     ("saf_pattern_param_grad", SafPatternGradArgs)):
         f = getattr(lib, name)
         f.argtypes = [C.POINTER(at), C.c_void_p]
         f.restype = C.c_int
@@ -108,6 +122,9 @@ def _load():
     lib.saf_indexed_linear_bwd_dw.restype = C.c_int
     lib.saf_decomposed_logz.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p]
     lib.saf_decomposed_logz.restype = C.c_int
+    lib.saf_pattern_normalisers.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32,
+                                            C.c_void_p]
+    lib.saf_pattern_normalisers.restype = C.c_int
     lib.saf_rope_slabs.argtypes = [C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
                                    C.POINTER(C.c_int32), C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p]
     lib.saf_rope_slabs.restype = C.c_int

@@ -144,6 +144,20 @@ def main():
                 y.backward(dqk, retain_graph=True)
             ms = _timed(run, args.reps)
             fl = 2.0 * fl_qk
+        elif op == "pattern_grad":
+            # parameter gradients of the decomposed heads (needs --frozen decomposed): dS = P (dO V^T - delta)
+            from saf_b200.trainable_patterns import pattern_param_grad
+            assert nf and args.frozen == "decomposed", "pattern_grad needs --frozen decomposed"
+            with torch.no_grad():
+                y = attn()
+
+                def run():
+                    return pattern_param_grad(dy, y, v, kw["alpha"], kw["rho"], kw["z"], frozen)
+                n0 = ops.launch_count()
+                run()
+                n = ops.launch_count() - n0
+                ms = _timed(run, args.reps)
+            fl = 1.0 * B * nf * T * T * hd          # causal half of 2 T^2 hd per head
         elif op in ("layer_train", "layer_infer"):
             # the whole attention module (projections + mixed attention + c_proj) at this shape
             from types import SimpleNamespace

@@ -279,10 +279,22 @@ def fused_mixed_attn(q, k, v, patt, frozen, hidx=None, pidx=None,
       rope=(cos, sin): fp32 (T,hd) tables; q and k are rotated while they are loaded.
       sink_decay=(a, r): fp32 (H,) tensors; heads with state 3 use the structured
         pattern a[j=0] + (1-a) r^(i-j)/Z_i through an O(T) scan.
+    alpha / rho that require grad receive their exact gradients (z is then recomputed from them).
     """
     _require_cuda(v, "v")
     if sm_scale is None:
         sm_scale = 1.0 / math.sqrt(v.size(-1))
+    train_patterns = (alpha is not None and torch.is_grad_enabled()
+                      and (alpha.requires_grad or (rho is not None and rho.requires_grad)))
+    if train_patterns:
+        # learnable alpha / rho (supplement/trainable_patterns.py:62-88): the normalisers follow the current
+        # parameter values, the fused call sees detached buffers, and PatternGradient adds their gradients
+        if kvidx is not None:
+            raise NotImplementedError("trainable patterns with kvidx (GQA) are not implemented")
+        from . import trainable_patterns as _tp
+        alpha_p, rho_p = alpha, rho
+        z = _tp.current_normalisers(alpha, rho, v.shape[-2])
+        alpha, rho = alpha.detach(), rho.detach()
     if alpha is not None and z is None:
         z = decomposed_logz(alpha, rho)
     if validate:
@@ -330,8 +342,11 @@ def fused_mixed_attn(q, k, v, patt, frozen, hidx=None, pidx=None,
             assert states is None or 2 not in states, "decomposed-frozen heads require alpha/rho/z"
         if sink_decay is None:
             assert states is None or 3 not in states, "sink-decay heads require sink_decay=(a, r)"
-    return _FusedMixedAttn.apply(q, k, v, patt, alpha, rho, z, frozen, hidx, pidx, kvidx, sm_scale, rope,
-                                 sink_decay)
+    out = _FusedMixedAttn.apply(q, k, v, patt, alpha, rho, z, frozen, hidx, pidx, kvidx, sm_scale, rope,
+                                sink_decay)
+    if train_patterns:
+        out = _tp.PatternGradient.apply(out, v, alpha_p, rho_p, z, frozen)
+    return out
 
 
 # ---------------------------------------------------------------------------

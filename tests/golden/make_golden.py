@@ -11,7 +11,8 @@ reference's behaviour travels.  What is recorded:
     kernel/test_frozen_attn.py:27-28, decomp_logits / decomposed_logz / make_rho_band of
     kernel/fused_attn.py:65-116, linear_rows / linear_rows2 / linear_permuted_cols of
     kernel/indexed_linear.py with their gradients, apply_rotary_pos_emb of nanogpt/model.py:63-68;
-  * block level: the reference's LayerNorm and MLP modules (nanogpt/model.py:45-54, 1193-1207) on seeded inputs.
+  * block level: the reference's LayerNorm and MLP modules (nanogpt/model.py:45-54, 1193-1207) on seeded inputs;
+  * learnable patterns: dense_reference of supplement/trainable_patterns.py:7-13 with its autograd gradients.
 """
 import importlib.util
 import os
@@ -169,6 +170,26 @@ def main(ref_root):
         out["blk_fc_w"], out["blk_fc_b"] = mlp.c_fc.weight.numpy().copy(), mlp.c_fc.bias.numpy().copy()
         out["blk_pr_w"], out["blk_pr_b"] = mlp.c_proj.weight.numpy().copy(), mlp.c_proj.bias.numpy().copy()
         out["blk_mlp_y"] = mlp.eval()(xb).numpy()
+
+    # ---- learnable decomposed patterns: dense_reference of supplement/trainable_patterns.py:7-13 and its autograd
+    # gradients (what supplement/trainable_pattern_kernels.py:21-58 computes without the T x T buffer) ----
+    spec = importlib.util.spec_from_file_location("ref_trainable_patterns",
+                                                  os.path.join(ref_root, "supplement", "trainable_patterns.py"))
+    TP = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(TP)
+    g = torch.Generator().manual_seed(27)
+    Bt, Ht, Tt, Dt, St = 2, 3, 40, 16, 64
+    val = torch.randn(Bt, Ht, Tt, Dt, generator=g).requires_grad_(True)
+    al = (torch.randn(Ht, St, generator=g) * 0.7).requires_grad_(True)
+    rh = (-0.05 * torch.arange(St).float()[None, :] * torch.rand(Ht, 1, generator=g)
+          + 0.3 * torch.randn(Ht, St, generator=g)).requires_grad_(True)
+    wt = torch.randn(Bt, Ht, Tt, Dt, generator=g)
+    yt = TP.dense_reference(val, al, rh)
+    (yt * wt).sum().backward()
+    out["tp_value"], out["tp_alpha"], out["tp_rho"], out["tp_w"] = (val.detach().numpy(), al.detach().numpy(),
+                                                                      rh.detach().numpy(), wt.numpy())
+    out["tp_out"] = yt.detach().numpy()
+    out["tp_dvalue"], out["tp_dalpha"], out["tp_drho"] = val.grad.numpy(), al.grad.numpy(), rh.grad.numpy()
 
     path = os.path.join(HERE, "reference_vectors.npz")
     np.savez_compressed(path, **out)

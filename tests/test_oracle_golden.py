@@ -142,3 +142,23 @@ def test_block_functions_match_reference_modules():
     assert O.max_abs(y, t("blk_ln_y")) <= 1e-6
     y = O.mlp(t("blk_x"), t("blk_fc_w"), t("blk_pr_w"), t("blk_fc_b"), t("blk_pr_b"))
     assert O.max_abs(y, t("blk_mlp_y")) <= 1e-6
+
+
+def test_trainable_pattern_gradients():
+    """The closed-form parameter gradients equal autograd through the reference's dense_reference
+    (supplement/trainable_patterns.py:7-13), and the restated forward equals its output."""
+    val, al, rh, w = g("tp_value"), g("tp_alpha"), g("tp_rho"), g("tp_w")
+    T = val.shape[-2]
+    y = O.pattern_dense_reference(val, al, rh)
+    assert O.max_abs(y, g("tp_out")) <= 2e-6
+    z = O.pattern_normalisers(al, rh, T)
+    assert torch.equal(z[:, T:], torch.zeros_like(z[:, T:]))
+    da, dr = O.pattern_param_grads(val, y, w, al, rh, z)
+    assert O.max_abs(da, g("tp_dalpha")) <= 2e-5
+    assert O.max_abs(dr, g("tp_drho")) <= 2e-5
+    # heads outside state 2 contribute nothing
+    da2, dr2 = O.pattern_param_grads(val, y, w, al, rh, z, states=[2, 0, 2])
+    assert torch.equal(da2[1], torch.zeros_like(da2[1])) and O.max_abs(da2[0], g("tp_dalpha")[0]) <= 2e-5
+    # dV of these heads is the ordinary frozen-head backward: P^T dO
+    P = O.decomp_pattern(al, rh, z, T)
+    assert O.max_abs(torch.matmul(P.transpose(-1, -2)[None], w), g("tp_dvalue")) <= 2e-5
