@@ -266,6 +266,9 @@ typedef struct SafPatternGradArgs {
   const int32_t* frozen_host; /* HOST copy of frozen (optional: skips the launch when no head trains) */
   float* dalpha;
   float* drho;
+  float* delta;        /* caller-provided scratch, B*H*T fp32 (rows of training heads
+                          are written, then read); without it the call runs on the
+                          CUDA cores                                                */
   int32_t* status;     /* optional device int32, as in SafMixedAttnArgs              */
 } SafPatternGradArgs;
 

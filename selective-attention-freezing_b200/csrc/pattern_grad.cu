@@ -7,9 +7,9 @@
 //
 //   tensor-core kernel (bf16, head_dim 64/128): one CTA per (batch, head, 128-key tile j), walks query tiles i >= j
 //     dP^T = V_j dO_i^T   SS MMA 128x128xHD -> TMEM, two buffers (keys on lanes, queries on columns)
-//     warps 0-7: two warpgroups split the 128 query columns; thread = key row, so dalpha_j is thread-local;
-//                delta_i from the dO_i / O_i tiles in shared memory (same swizzle, so bytes pair up as they lie)
-//     warp 8: TMA producer ([dO_i | O_i] ring), warp 9: MMA issuer
+//     warps 0-15: four warpgroups split the 128 query columns; thread = key row, so dalpha_j is thread-local;
+//                 delta_i comes from a small pre-pass (one warp per row)
+//     warp 16: TMA producer (dO_i ring), warp 17: MMA issuer
 //   generic kernel (any dtype / head_dim): 32x32 tile pairs on the CUDA cores, fp32 throughout.
 // Every wait is bounded; on expiry the kernel records a code in *status and falls through.
 #include "saf_internal.h"
@@ -19,7 +19,8 @@ namespace saf {
 namespace {
 
 constexpr float LOG2E_P = 1.4426950408889634f;
-constexpr int PG_THREADS = 320;
+constexpr int PG_COMPUTE = 512;                 // 16 warps: four warpgroups, 32 query columns each
+constexpr int PG_THREADS = PG_COMPUTE + 64;     // + TMA producer warp + MMA issuer warp
 
 struct PgParams {
   int B, H, T, SD, n_tiles, force_state;
@@ -27,25 +28,26 @@ struct PgParams {
   const float* alpha;
   const float* rho;
   const float* z;
+  const float* delta;       // (B, H, T) from the pre-pass
   float* dalpha;
   float* drho;
   int* status;
 };
 
 struct PgShared {
-  uint64_t v_full, full[3], empty[3], dp_full[2], dp_empty[2];
+  uint64_t v_full, full[4], empty[4], dp_full[2], dp_empty[2];
   uint32_t tmem_base;
-  alignas(16) float z[2][128];        // z_i * log2e of the query tile (+inf past T)
-  alignas(16) float dl[2][2][128];    // the two halves of delta_i
-  float rw[2][256];                   // rho_d * log2e for d = D0 - 127 + k (-inf outside [0, T))
-  float wb[8][2][64];                 // per warp and 32-column chunk: 63 diagonal sums of the current tile pair
+  alignas(16) float z[128];          // z_i * log2e of the query tile (+inf past T)
+  alignas(16) float dl[128];         // delta_i
+  float rw[256];                     // rho_d * log2e for d = D0 - 127 + k (-inf outside [0, T))
+  alignas(16) float wb[16][64];      // per warp: 63 diagonal sums of the current tile pair
 };
 
 template <int HD>
 struct PgCfg {
   static constexpr int TILE_BYTES = 128 * HD * 2;
-  static constexpr int NS = (HD == 64) ? 3 : 2;   // stages of [dO_i | O_i]
-  static constexpr int SMEM_BYTES = 1024 + TILE_BYTES + NS * 2 * TILE_BYTES + (int)sizeof(PgShared) + 64;
+  static constexpr int NS = 4;                     // dO_i ring
+  static constexpr int SMEM_BYTES = 1024 + TILE_BYTES + NS * TILE_BYTES + (int)sizeof(PgShared) + 64;
   static constexpr int TMEM_COLS = 256;
 };
 
@@ -61,23 +63,41 @@ __device__ __forceinline__ void pg_load_tile(uint8_t* dst, const CUtensorMap* m,
   for (int hh = 0; hh < HD / 64; ++hh) tma_load_4d(dst + hh * 16384, m, bar, hh * 64, row, head, b);
 }
 
-// sum over 4 x 16 bytes of products of bf16 pairs lying at the same offsets of two tiles
-__device__ __forceinline__ float pg_dot16(const uint8_t* a, const uint8_t* b) {
-  const uint4 x = *reinterpret_cast<const uint4*>(a), y = *reinterpret_cast<const uint4*>(b);
-  const uint32_t xs[4] = {x.x, x.y, x.z, x.w}, ys[4] = {y.x, y.y, y.z, y.w};
+// delta[b,h,i] = sum_d dO[b,h,i,d] O[b,h,i,d] for the heads that train; one warp per row
+struct PgDeltaParams {
+  int B, H, T, HD, force_state;
+  const int32_t* frozen;
+  const __nv_bfloat16* o;
+  const __nv_bfloat16* g;
+  int64_t o_s[3], g_s[3];
+  float* delta;
+};
+
+__global__ void __launch_bounds__(256) pattern_delta_kernel(const PgDeltaParams p) {
+  const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= (int64_t)p.B * p.H * p.T) return;
+  const int t = (int)(row % p.T);
+  const int h = (int)((row / p.T) % p.H), b = (int)(row / ((int64_t)p.T * p.H));
+  const int state = p.force_state >= 0 ? p.force_state : p.frozen[h];
+  if (state != SAF_DECOMP) return;
+  const __nv_bfloat16* o = p.o + b * p.o_s[0] + h * p.o_s[1] + t * p.o_s[2];
+  const __nv_bfloat16* g = p.g + b * p.g_s[0] + h * p.g_s[1] + t * p.g_s[2];
   float s = 0.f;
-#pragma unroll
-  for (int k = 0; k < 4; ++k) {
-    s = fmaf(__uint_as_float(xs[k] << 16), __uint_as_float(ys[k] << 16), s);
-    s = fmaf(__uint_as_float(xs[k] & 0xffff0000u), __uint_as_float(ys[k] & 0xffff0000u), s);
+  for (int c = lane * 2; c < p.HD; c += 64) {
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(o + c));
+    const float2 d = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(g + c));
+    s = fmaf(a.x, d.x, fmaf(a.y, d.y, s));
   }
-  return s;
+#pragma unroll
+  for (int off = 16; off; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+  if (lane == 0) p.delta[row] = s;
 }
 
 template <int HD>
 __global__ void __launch_bounds__(PG_THREADS, 1)
 pattern_grad_kernel(const __grid_constant__ CUtensorMap mapV, const __grid_constant__ CUtensorMap mapdO,
-                    const __grid_constant__ CUtensorMap mapO, const __grid_constant__ PgParams p) {
+                    const __grid_constant__ PgParams p) {
   using C = PgCfg<HD>;
   const int BH = p.B * p.H;
   const int bh = (int)blockIdx.x % BH, jt = (int)blockIdx.x / BH;    // heaviest key tiles (most query tiles) first
@@ -90,23 +110,24 @@ pattern_grad_kernel(const __grid_constant__ CUtensorMap mapV, const __grid_const
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* sV = smem;
-  uint8_t* ring = smem + C::TILE_BYTES;               // stage s: [dO_i | O_i]
-  PgShared* sh = reinterpret_cast<PgShared*>(ring + C::NS * 2 * C::TILE_BYTES);
+  uint8_t* ring = smem + C::TILE_BYTES;               // dO_i stages
+  PgShared* sh = reinterpret_cast<PgShared*>(ring + C::NS * C::TILE_BYTES);
   const int tid = threadIdx.x, warp = tid >> 5;
+  constexpr int W_TMA = PG_COMPUTE / 32, W_MMA = W_TMA + 1;
 
   if (tid == 0) {
     mbar_init(&sh->v_full, 1);
-    for (int s = 0; s < 3; ++s) {
+    for (int s = 0; s < C::NS; ++s) {
       mbar_init(&sh->full[s], 1);
-      mbar_init(&sh->empty[s], 257);      // the MMA's commit + every compute thread (delta reads the tiles)
+      mbar_init(&sh->empty[s], 1);        // the MMA's commit: nothing else reads a dO stage
     }
     for (int k = 0; k < 2; ++k) {
       mbar_init(&sh->dp_full[k], 1);
-      mbar_init(&sh->dp_empty[k], 256);
+      mbar_init(&sh->dp_empty[k], PG_COMPUTE / 32);   // one lane of every compute warp
     }
     fence_mbar_init();
   }
-  if (warp == 9) {
+  if (warp == W_MMA) {
     tmem_alloc(&sh->tmem_base, C::TMEM_COLS);
     tmem_relinquish();
   }
@@ -115,12 +136,11 @@ pattern_grad_kernel(const __grid_constant__ CUtensorMap mapV, const __grid_const
   tc_fence_after();
   const uint32_t tmem = sh->tmem_base;
 
-  if (warp == 8) {
+  if (warp == W_TMA) {
     // ------------------------------------------------------------------ TMA producer
     if (elect_one()) {
       tma_prefetch_desc(&mapV);
       tma_prefetch_desc(&mapdO);
-      tma_prefetch_desc(&mapO);
       mbar_expect_tx(&sh->v_full, C::TILE_BYTES);
       pg_load_tile<HD>(sV, &mapV, &sh->v_full, j0, h, b);
       for (int i = 0; i < n; ++i) {
@@ -129,13 +149,11 @@ pattern_grad_kernel(const __grid_constant__ CUtensorMap mapV, const __grid_const
           dev_set_error(p.status, SAF_DEV_TIMEOUT_TMA, 70);
           break;
         }
-        uint8_t* dst = ring + s * 2 * C::TILE_BYTES;
-        mbar_expect_tx(&sh->full[s], 2 * C::TILE_BYTES);
-        pg_load_tile<HD>(dst, &mapdO, &sh->full[s], (jt + i) * 128, h, b);
-        pg_load_tile<HD>(dst + C::TILE_BYTES, &mapO, &sh->full[s], (jt + i) * 128, h, b);
+        mbar_expect_tx(&sh->full[s], C::TILE_BYTES);
+        pg_load_tile<HD>(ring + s * C::TILE_BYTES, &mapdO, &sh->full[s], (jt + i) * 128, h, b);
       }
     }
-  } else if (warp == 9) {
+  } else if (warp == W_MMA) {
     // ------------------------------------------------------------------ MMA issuer
     const bool leader = elect_one();
     const uint32_t idesc = umma_idesc_bf16(128, 128, 0, 0);
@@ -150,7 +168,7 @@ pattern_grad_kernel(const __grid_constant__ CUtensorMap mapV, const __grid_const
       }
       tc_fence_after();
       if (leader) {
-        const uint32_t adO = aR + s * 2 * C::TILE_BYTES;
+        const uint32_t adO = aR + s * C::TILE_BYTES;
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks) {
           const uint32_t off = (ks >> 2) * 16384 + (ks & 3) * 32;
@@ -164,115 +182,93 @@ pattern_grad_kernel(const __grid_constant__ CUtensorMap mapV, const __grid_const
     }
   } else {
     // ------------------------------------------------------------------ compute warpgroups
-    const int half = warp >> 2;
+    const int quarter = warp >> 2;
     const int r = tid & 127;                       // key row of the tile
-    const int cb = half * 64;                      // first query column of this group
+    const int lane = tid & 31;
+    const int cb = quarter * 32;                   // first query column of this group
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     const int64_t vrow = (int64_t)h * p.SD;
+    const float* delta_g = p.delta + ((int64_t)b * p.H + h) * p.T;
     const float a_r = (j0 + r < p.T) ? p.alpha[vrow + j0 + r] * LOG2E_P : -INFINITY;
     float acc_a = 0.f;
-    auto fetch_z = [&](int qt) -> float {
-      const int row = qt * 128 + r;
-      return row < p.T ? p.z[vrow + row] * LOG2E_P : INFINITY;    // +inf: P = 0 past T
-    };
-    auto fetch_rho = [&](int qt) -> float {
-      const int d = (qt - jt) * 128 - 127 + tid;
+    // every thread stages one value of the next tile's vectors: z (threads 0-127), delta (128-255), rho window (256-511)
+    auto fetch = [&](int qt) -> float {
+      if (tid < 128) {
+        const int row = qt * 128 + tid;
+        return row < p.T ? p.z[vrow + row] * LOG2E_P : INFINITY;            // +inf: P = 0 past T
+      }
+      if (tid < 256) {
+        const int row = qt * 128 + tid - 128;
+        return row < p.T ? delta_g[row] : 0.f;
+      }
+      const int d = (qt - jt) * 128 - 127 + (tid - 256);
       return (d >= 0 && d < p.T) ? p.rho[vrow + d] * LOG2E_P : -INFINITY;   // -inf: above the diagonal
     };
-    float nz = tid < 128 ? fetch_z(jt) : 0.f;
-    float nr = fetch_rho(jt);
+    float nxt = fetch(jt);
+    float* slot = tid < 128 ? &sh->z[tid] : tid < 256 ? &sh->dl[tid - 128] : &sh->rw[tid - 256];
     for (int i = 0; i < n; ++i) {
-      const int s = i % C::NS, k = i & 1;
-      if (!mbar_wait(&sh->full[s], (i / C::NS) & 1)) {
-        dev_set_error(p.status, SAF_DEV_TIMEOUT_SOFTMAX, 73);
-        break;
-      }
-      {
-        // half of delta_i for row r: both tiles carry the same swizzle, so equal offsets hold equal (row, column)
-        const uint8_t* tdo = ring + s * 2 * C::TILE_BYTES;
-        const uint8_t* to = tdo + C::TILE_BYTES;
-        float dsum = 0.f;
-        if (HD == 64) {
-          const int o0 = r * 128 + half * 64;
-#pragma unroll
-          for (int c = 0; c < 4; ++c) dsum += pg_dot16(tdo + o0 + c * 16, to + o0 + c * 16);
-        } else {
-          const int o0 = half * 16384 + r * 128;
-#pragma unroll
-          for (int c = 0; c < 8; ++c) dsum += pg_dot16(tdo + o0 + c * 16, to + o0 + c * 16);
-        }
-        sh->dl[k][half][r] = dsum;
-      }
-      if (tid < 128) sh->z[k][r] = nz;
-      sh->rw[k][tid] = nr;
-      named_bar_sync(1, 256);
-      mbar_arrive(&sh->empty[s]);
-      if (i + 1 < n) {
-        if (tid < 128) nz = fetch_z(jt + i + 1);
-        nr = fetch_rho(jt + i + 1);
-      }
+      const int k = i & 1;
+      *slot = nxt;
+      named_bar_sync(1, PG_COMPUTE);
+      if (i + 1 < n) nxt = fetch(jt + i + 1);
       if (!mbar_wait(&sh->dp_full[k], (i >> 1) & 1)) {
         dev_set_error(p.status, SAF_DEV_TIMEOUT_SOFTMAX, 74);
         break;
       }
       tc_fence_after();
-      uint32_t d[2][32];
-      tmem_ld32(tmem + lane_base + k * 128 + cb, d[0]);
-      tmem_ld32(tmem + lane_base + k * 128 + cb + 32, d[1]);
+      uint32_t d[32];
+      tmem_ld32(tmem + lane_base + k * 128 + cb, d);
       tmem_ld_wait();
       tc_fence_before();
-      mbar_arrive(&sh->dp_empty[k]);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sh->dp_empty[k]);
       // Diagonal sums without atomics: a running sum travels one lane up per column (the cell one column to the
       // right and one row down lies on the same diagonal), so a diagonal's partial sum stays in registers until
       // it leaves lane 31 or the chunk ends; every slot of the warp's array is then written exactly once.
-      // The two 32-column chunks are independent chains, interleaved for latency.
-      const float* rw = &sh->rw[k][cb - r + 127];
-      float* wb0 = sh->wb[warp][0];
-      float* wb1 = sh->wb[warp][1];
-      const int lane = tid & 31;
-      float run0 = 0.f, run1 = 0.f;
-      const float4* Z4 = reinterpret_cast<const float4*>(&sh->z[k][cb]);
-      const float4* A4 = reinterpret_cast<const float4*>(&sh->dl[k][0][cb]);
-      const float4* B4 = reinterpret_cast<const float4*>(&sh->dl[k][1][cb]);
+      const float* rw = &sh->rw[cb - r + 127];
+      float* wb = sh->wb[warp];
+      float run = 0.f;
+      float keep[3];
+      const float4* Z4 = reinterpret_cast<const float4*>(&sh->z[cb]);
+      const float4* D4 = reinterpret_cast<const float4*>(&sh->dl[cb]);
 #pragma unroll
       for (int x4 = 0; x4 < 8; ++x4) {
-        const float4 Za = Z4[x4], Aa = A4[x4], Ba = B4[x4];
-        const float4 Zb = Z4[8 + x4], Ab = A4[8 + x4], Bb = B4[8 + x4];
-        const float z0[4] = {Za.x, Za.y, Za.z, Za.w}, z1[4] = {Zb.x, Zb.y, Zb.z, Zb.w};
-        const float d0[4] = {Aa.x + Ba.x, Aa.y + Ba.y, Aa.z + Ba.z, Aa.w + Ba.w};
-        const float d1[4] = {Ab.x + Bb.x, Ab.y + Bb.y, Ab.z + Bb.z, Ab.w + Bb.w};
+        const float4 Z = Z4[x4], D = D4[x4];
+        const float zz[4] = {Z.x, Z.y, Z.z, Z.w}, dd[4] = {D.x, D.y, D.z, D.w};
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const int x = x4 * 4 + e;
-          const float p0 = pg_ex2(a_r + rw[x] - z0[e]);
-          const float p1 = pg_ex2(a_r + rw[32 + x] - z1[e]);
-          const float ds0 = p0 * (__uint_as_float(d[0][x]) - d0[e]);
-          const float ds1 = p1 * (__uint_as_float(d[1][x]) - d1[e]);
-          acc_a += ds0 + ds1;
-          if (x > 0 && lane == 31) {
-            wb0[x - 1] = run0;
-            wb1[x - 1] = run1;
+          const float pe = pg_ex2(a_r + rw[x] - zz[e]);
+          const float ds = pe * (__uint_as_float(d[x]) - dd[e]);
+          acc_a += ds;
+          // lane 31 holds the finished sum of diagonal slot x-1: kept in registers, stored four at a time
+          if (x > 0) {
+            const int m = x - 1;
+            if ((m & 3) == 3) {
+              if (lane == 31) *reinterpret_cast<float4*>(&wb[m - 3]) = make_float4(keep[0], keep[1], keep[2], run);
+            } else {
+              keep[m & 3] = run;
+            }
           }
-          run0 = __shfl_up_sync(0xffffffffu, run0, 1);
-          run1 = __shfl_up_sync(0xffffffffu, run1, 1);
-          if (lane == 0) run0 = run1 = 0.f;
-          run0 += ds0;
-          run1 += ds1;
+          run = __shfl_up_sync(0xffffffffu, run, 1);
+          if (lane == 0) run = 0.f;
+          run += ds;
         }
       }
-      wb0[62 - lane] = run0;
-      wb1[62 - lane] = run1;
-      named_bar_sync(1, 256);
+      if (lane == 31) {          // slots 28..30 left in the registers
+#pragma unroll
+        for (int m = 0; m < 3; ++m) wb[28 + m] = keep[m];
+      }
+      wb[62 - lane] = run;
+      named_bar_sync(1, PG_COMPUTE);
       if (tid < 255) {
-        // tile diagonal t = (query column) - (key row) + 127; slot m of (warp, chunk) is column - lane + 31
+        // tile diagonal t = (query column) - (key row) + 127; slot m of a warp is column - lane + 31
         float val = 0.f;
 #pragma unroll
-        for (int wq = 0; wq < 8; ++wq)
-#pragma unroll
-          for (int ch = 0; ch < 2; ++ch) {
-            const int m = tid - 96 - 64 * (wq >> 2) - 32 * ch + 32 * (wq & 3);
-            if (m >= 0 && m < 63) val += sh->wb[wq][ch][m];
-          }
+        for (int wq = 0; wq < PG_COMPUTE / 32; ++wq) {
+          const int m = tid - 96 - 32 * (wq >> 2) + 32 * (wq & 3);
+          if (m >= 0 && m < 63) val += sh->wb[wq][m];
+        }
         const int dist = i * 128 - 127 + tid;
         if (val != 0.f && dist >= 0 && dist < p.T) atomicAdd(&p.drho[vrow + dist], val);
       }
@@ -281,7 +277,7 @@ pattern_grad_kernel(const __grid_constant__ CUtensorMap mapV, const __grid_const
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 9) tmem_dealloc(tmem, C::TMEM_COLS);
+  if (warp == W_MMA) tmem_dealloc(tmem, C::TMEM_COLS);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -390,17 +386,28 @@ int pg_map4(CUtensorMap* m, const SafTensor& t, int B, int Hn, int T, int HD) {
 
 template <int HD>
 int pg_launch_sm100(const SafPatternGradArgs& a, cudaStream_t st) {
-  CUtensorMap mv, mdo, mo;
+  CUtensorMap mv, mdo;
   int rc;
   if ((rc = pg_map4(&mv, a.v, a.B, a.H, a.T, HD))) return rc;
   if ((rc = pg_map4(&mdo, a.dout, a.B, a.H, a.T, HD))) return rc;
-  if ((rc = pg_map4(&mo, a.out, a.B, a.H, a.T, HD))) return rc;
+  PgDeltaParams d;
+  d.B = a.B; d.H = a.H; d.T = a.T; d.HD = HD;
+  d.force_state = a.force_state;
+  d.frozen = a.frozen;
+  d.o = reinterpret_cast<const __nv_bfloat16*>(a.out.ptr);
+  d.g = reinterpret_cast<const __nv_bfloat16*>(a.dout.ptr);
+  for (int i = 0; i < 3; ++i) {
+    d.o_s[i] = a.out.stride[i];
+    d.g_s[i] = a.dout.stride[i];
+  }
+  d.delta = a.delta;
   PgParams p;
   p.B = a.B; p.H = a.H; p.T = a.T; p.SD = a.SD;
   p.n_tiles = (a.T + 127) / 128;
   p.force_state = a.force_state;
   p.frozen = a.frozen;
   p.alpha = a.alpha; p.rho = a.rho; p.z = a.z;
+  p.delta = a.delta;
   p.dalpha = a.dalpha; p.drho = a.drho;
   p.status = a.status;
   static bool attr_set = false;
@@ -410,10 +417,12 @@ int pg_launch_sm100(const SafPatternGradArgs& a, cudaStream_t st) {
     if (e != cudaSuccess) return fail(SAF_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     attr_set = true;
   }
+  const int64_t rows = (int64_t)a.B * a.H * a.T;
   const int64_t grid = (int64_t)a.B * a.H * p.n_tiles;
-  if (grid > 0x7fffffff) return fail(SAF_ERR_LIMIT, "pattern gradient grid too large");
-  pattern_grad_kernel<HD><<<(unsigned)grid, PG_THREADS, PgCfg<HD>::SMEM_BYTES, st>>>(mv, mdo, mo, p);
-  count_launch();
+  if (grid > 0x7fffffff || (rows + 7) / 8 > 0x7fffffff) return fail(SAF_ERR_LIMIT, "pattern gradient grid too large");
+  pattern_delta_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(d);
+  pattern_grad_kernel<HD><<<(unsigned)grid, PG_THREADS, PgCfg<HD>::SMEM_BYTES, st>>>(mv, mdo, p);
+  count_launch(2);
   return check_launch("pattern_grad_kernel");
 }
 
@@ -455,7 +464,7 @@ int launch_pattern_grad(const SafPatternGradArgs& a, cudaStream_t st) {
     if (!any) return SAF_OK;
   }
   const bool tc = a.dtype == SAF_BF16 && (a.HD == 64 || a.HD == 128) && pg_tensor_ok(a.v) && pg_tensor_ok(a.dout) &&
-                  pg_tensor_ok(a.out) && a.v.stride[3] == 1 && saf_device_supported();
+                  a.out.stride[3] == 1 && a.delta && saf_device_supported();
   if (tc) return a.HD == 64 ? pg_launch_sm100<64>(a, st) : pg_launch_sm100<128>(a, st);
   return pg_launch_generic(a, st);
 }

@@ -75,7 +75,7 @@ class SafPatternGradArgs(C.Structure):
         ("v", SafTensor), ("out", SafTensor), ("dout", SafTensor),
         ("alpha", C.c_void_p), ("rho", C.c_void_p), ("z", C.c_void_p),
         ("frozen", C.c_void_p), ("frozen_host", C.POINTER(C.c_int32)),
-        ("dalpha", C.c_void_p), ("drho", C.c_void_p), ("status", C.c_void_p),
+        ("dalpha", C.c_void_p), ("drho", C.c_void_p), ("delta", C.c_void_p), ("status", C.c_void_p),
     ]
 
 

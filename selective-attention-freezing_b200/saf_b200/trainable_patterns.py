@@ -64,6 +64,8 @@ def pattern_param_grad(grad, out, value, alpha, rho, z, states):
         keep = (C.c_int32 * H)(*host)
         g.frozen_host = keep
     g.dalpha, g.drho = da.data_ptr(), dr.data_ptr()
+    delta = torch.empty((B, H, T), device=value.device, dtype=torch.float32)   # scratch of the tensor-core path
+    g.delta = delta.data_ptr()
     check(lib.saf_pattern_param_grad(C.byref(g), ops._stream(value)))
     return da.to(alpha.dtype), dr.to(rho.dtype)
 
