@@ -63,6 +63,18 @@ def test_invalid_arguments_are_refused_before_launch():
     assert _cabi.lib.saf_indexed_linear_fwd(C.byref(ln), None) == _cabi.SAF_ERR_UNSUPPORTED
     assert _cabi.lib.saf_decomposed_logz(None, None, None, 2, 8, None) == _cabi.SAF_ERR_INVALID
     assert _cabi.lib.saf_decomposed_logz(None, None, None, 0, 8, None) == _cabi.SAF_OK
+    assert _cabi.lib.saf_pattern_normalisers(None, None, None, 2, 8, 4, None) == _cabi.SAF_ERR_INVALID
+    assert _cabi.lib.saf_pattern_normalisers(None, None, None, 2, 8, 9, None) == _cabi.SAF_ERR_INVALID   # T > S
+    assert "T > S" in _cabi.last_error()
+    assert _cabi.lib.saf_pattern_param_grad(None, None) == _cabi.SAF_ERR_INVALID
+    pg = _cabi.SafPatternGradArgs()
+    assert _cabi.lib.saf_pattern_param_grad(C.byref(pg), None) == _cabi.SAF_ERR_INVALID
+    assert "size mismatch" in _cabi.last_error()
+    pg.struct_size = C.sizeof(_cabi.SafPatternGradArgs)
+    pg.dtype, pg.B, pg.H, pg.T, pg.HD, pg.SD, pg.force_state = _cabi.SAF_BF16, 1, 2, 16, 64, 8, -1
+    assert _cabi.lib.saf_pattern_param_grad(C.byref(pg), None) == _cabi.SAF_ERR_INVALID    # SD < T
+    pg.force_state = 1
+    assert _cabi.lib.saf_pattern_param_grad(C.byref(pg), None) == _cabi.SAF_OK             # no such head trains
 
 
 def test_operators_refuse_cpu_tensors():
