@@ -275,6 +275,38 @@ typedef struct SafPatternGradArgs {
 int saf_pattern_param_grad(const SafPatternGradArgs* args, void* stream);
 
 /* ---------------------------------------------------------------------------
+ * Attention statistics of live heads for the freeze controller, without the
+ * (B, H, T, T) capture.  Replaces, for softmax heads, what FreezeController._measure
+ * does with the retained eager attention (nanogpt/dynamic_freeze.py:629-745):
+ * _centered_batch_reduced_moments (:96-127) + _merge_reduced_moments (:130-143) +
+ * _negative_entropy_sum (:146-173) of att = softmax(causal(q k^T * sm_scale)).
+ *   mean        (U, T, T) fp32, the running mean attention; with count_prev == 0 it is
+ *               overwritten (zeros above the diagonal), otherwise Chan-merged in place:
+ *               mean += (batch_mean - mean) * B / (count_prev + B)
+ *   head_m2     (U,) fp64, += sum over cells of the batch's centred squares
+ *               + sum((batch_mean - mean)^2) * count_prev * B / (count_prev + B)
+ *   neg_entropy (U,) fp64, += sum over samples and cells of p ln p
+ * lse is the (B, U, T) fp32 row log-sum-exp of the same q, k in the log2 domain, as
+ * saf_mixed_attn_fwd writes it.  bf16 q, k with head_dim 64 / 128 (tensor-core kernel);
+ * anything else returns SAF_ERR_UNSUPPORTED.
+ * ------------------------------------------------------------------------- */
+typedef struct SafAttnStatsArgs {
+  int32_t struct_size; /* sizeof(SafAttnStatsArgs), checked */
+  int32_t dtype;       /* SafDType of q, k */
+  int32_t B, U, T, HD;
+  float sm_scale;
+  SafTensor q, k;      /* (B, U, T, HD), rotated as the attention saw them */
+  SafTensor lse;       /* (B, U, T) fp32 */
+  float* mean;
+  int64_t count_prev;
+  double* head_m2;
+  double* neg_entropy;
+  int32_t* status;     /* optional device int32, as in SafMixedAttnArgs */
+} SafAttnStatsArgs;
+
+int saf_attention_moments(const SafAttnStatsArgs* args, void* stream);
+
+/* ---------------------------------------------------------------------------
  * Library plumbing
  * ------------------------------------------------------------------------- */
 int saf_abi_version(void);

@@ -323,3 +323,43 @@ def pattern_param_grads(value, out, grad, alpha, rho, z, states=None):
         keep = (torch.as_tensor(states) == 2).to(da.dtype)[:, None]
         da, dr = da * keep, dr * keep
     return da, dr
+
+
+# ---------------------------------------------------------------------------
+# controller statistics of captured attention        nanogpt/dynamic_freeze.py:96-193, 629-745
+# ---------------------------------------------------------------------------
+def attention_probs(q, k, sm_scale=None):
+    """The tensor the eager capture retains for live heads (nanogpt/model.py:829-835): softmax of the causal scores.
+    q, k (B,U,T,hd) -> (B,U,T,T)."""
+    T, hd = q.shape[-2], q.shape[-1]
+    sc = torch.matmul(q, k.transpose(-1, -2)) * (sm_scale if sm_scale is not None else 1.0 / math.sqrt(hd))
+    causal = torch.ones(T, T, dtype=torch.bool).tril()
+    return sc.masked_fill(~causal, float("-inf")).softmax(-1)
+
+
+def centered_batch_reduced_moments(att):
+    """_centered_batch_reduced_moments (:96-127): count, mean over samples (H,T,T), centred squares summed per head."""
+    bm = att.mean(0)
+    return int(att.shape[0]), bm.double(), (att - bm).square().sum(dim=(0, 2, 3)).double()
+
+
+def merge_reduced_moments(count, mean, head_m2, bn, bm, bm2):
+    """_merge_reduced_moments (:130-143): Chan's merge with the M2 kept as one scalar per head."""
+    if count == 0:
+        return bn, bm.clone(), bm2.clone()
+    total = count + bn
+    delta = bm - mean
+    return total, mean + delta * (bn / total), head_m2 + bm2 + delta.square().sum(dim=(-1, -2)) * (count * bn / total)
+
+
+def negative_entropy_sum(att, eps=1e-12):
+    """_negative_entropy_sum (:146-173): sum of p log p over samples, rows and columns per head, rows renormalised."""
+    pr = att.float()
+    pr = pr / pr.sum(-1, keepdim=True).clamp_min(eps)
+    return torch.xlogy(pr, pr).sum(dim=(0, 2, 3)).double()
+
+
+def mean_forward_kl(neg_entropy, mean, n):
+    """_mean_forward_kl_from_entropy (:176-193)."""
+    T = mean.shape[-1]
+    return (neg_entropy / (n * T) - negative_entropy_sum(mean.unsqueeze(0)) / T).clamp_min(0).float()

@@ -392,4 +392,15 @@ int saf_pattern_param_grad(const SafPatternGradArgs* a, void* stream) {
   return launch_pattern_grad(*a, (cudaStream_t)stream);
 }
 
+int saf_attention_moments(const SafAttnStatsArgs* a, void* stream) {
+  if (!a) return fail(SAF_ERR_INVALID, "null args");
+  if (a->struct_size != (int32_t)sizeof(SafAttnStatsArgs))
+    return fail(SAF_ERR_INVALID, "SafAttnStatsArgs size mismatch (%d vs %d)", a->struct_size, (int)sizeof(SafAttnStatsArgs));
+  if (a->B < 0 || a->U < 0 || a->T < 0 || a->HD <= 0 || a->count_prev < 0) return fail(SAF_ERR_INVALID, "bad dimension");
+  if (a->B == 0 || a->U == 0 || a->T == 0) return SAF_OK;
+  if (!a->q.ptr || !a->k.ptr || !a->lse.ptr || !a->mean || !a->head_m2 || !a->neg_entropy)
+    return fail(SAF_ERR_INVALID, "null pointer");
+  return launch_attn_stats_sm100(*a, (cudaStream_t)stream);
+}
+
 }  // extern "C"

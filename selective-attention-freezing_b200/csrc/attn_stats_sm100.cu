@@ -1,0 +1,321 @@
+// Attention statistics for the freeze controller without the (B, H, T, T) capture.
+//
+// The reference measures heads by running the eager path with capture on and reducing the retained
+// softmax(QK^T) tensor: batch mean per cell, centred sum of squares reduced per head, and sum p log p per head
+// (nanogpt/dynamic_freeze.py:96-127 _centered_batch_reduced_moments, :130-143 _merge_reduced_moments,
+// :146-173 _negative_entropy_sum, used by _measure :629-745).  Here one CTA owns a 128 x 128 cell tile of one head
+// and walks the batch: S_b = Q_b K_b^T on tcgen05 into TMEM, P_b = exp2(S_b scale - lse_b) with the row
+// log-sum-exp of the flash forward, per-cell Welford mean / M2 in registers, then the tile of the running mean is
+// Chan-merged in place and the per-head scalars are reduced to one double atomic per CTA.
+//
+//   warps 0-15: four warpgroups x 32 key columns, thread = query row (TMEM lane)
+//   warp 16: TMA producer ([Q_b tile | K_b tile] ring), warp 17: MMA issuer
+// Every wait is bounded; on expiry the kernel records a code in *status and falls through.
+#include "saf_internal.h"
+#include "sm100_prims.cuh"
+
+namespace saf {
+namespace {
+
+constexpr int AS_COMPUTE = 512;
+constexpr int AS_THREADS = AS_COMPUTE + 64;
+constexpr float AS_LN2 = 0.6931471805599453f;
+
+struct AsParams {
+  int B, U, T, n_tiles;
+  float scale_log2;
+  const float* lse;
+  int64_t lse_s[3];
+  float* mean;                 // (U, T, T)
+  long long count_prev;
+  double* head_m2;
+  double* neg_entropy;
+  int* status;
+};
+
+struct AsShared {
+  uint64_t full[3], empty[3], s_full[2], s_empty[2];
+  uint32_t tmem_base;
+  double red[2][AS_COMPUTE / 32];
+};
+
+template <int HD>
+struct AsCfg {
+  static constexpr int TILE_BYTES = 128 * HD * 2;
+  static constexpr int NS = 3;
+  static constexpr int SMEM_BYTES = 1024 + NS * 2 * TILE_BYTES + (int)sizeof(AsShared) + 64;
+  static constexpr int TMEM_COLS = 256;
+};
+
+__device__ __forceinline__ float as_ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+template <int HD>
+__device__ __forceinline__ void as_load_tile(uint8_t* dst, const CUtensorMap* m, uint64_t* bar, int row, int head, int b) {
+#pragma unroll
+  for (int hh = 0; hh < HD / 64; ++hh) tma_load_4d(dst + hh * 16384, m, bar, hh * 64, row, head, b);
+}
+
+template <int HD>
+__global__ void __launch_bounds__(AS_THREADS, 1)
+attn_stats_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
+                  const __grid_constant__ AsParams p) {
+  using C = AsCfg<HD>;
+  const int nn = p.n_tiles * p.n_tiles;
+  const int u = (int)blockIdx.x / nn, rem = (int)blockIdx.x - u * nn;
+  const int it = rem / p.n_tiles, jt = rem - it * p.n_tiles;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  float* mean_u = p.mean + (int64_t)u * p.T * p.T;
+  if (jt > it) {
+    // above the diagonal every probability is zero: the first batch writes the zeros, later ones leave them
+    if (p.count_prev == 0) {
+      for (int e = tid; e < 128 * 128; e += AS_THREADS) {
+        const int gi = it * 128 + (e >> 7), gj = jt * 128 + (e & 127);
+        if (gi < p.T && gj < p.T) mean_u[(int64_t)gi * p.T + gj] = 0.f;
+      }
+    }
+    return;
+  }
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* ring = smem;                                // stage s: [Q_b tile | K_b tile]
+  AsShared* sh = reinterpret_cast<AsShared*>(ring + C::NS * 2 * C::TILE_BYTES);
+  constexpr int W_TMA = AS_COMPUTE / 32, W_MMA = W_TMA + 1;
+
+  if (tid == 0) {
+    for (int s = 0; s < C::NS; ++s) {
+      mbar_init(&sh->full[s], 1);
+      mbar_init(&sh->empty[s], 1);                      // the MMA's commit
+    }
+    for (int k = 0; k < 2; ++k) {
+      mbar_init(&sh->s_full[k], 1);
+      mbar_init(&sh->s_empty[k], AS_COMPUTE / 32);      // one lane of every compute warp
+    }
+    fence_mbar_init();
+  }
+  if (warp == W_MMA) {
+    tmem_alloc(&sh->tmem_base, C::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = sh->tmem_base;
+
+  if (warp == W_TMA) {
+    if (elect_one()) {
+      tma_prefetch_desc(&mapQ);
+      tma_prefetch_desc(&mapK);
+      for (int b = 0; b < p.B; ++b) {
+        const int s = b % C::NS;
+        if (!mbar_wait(&sh->empty[s], ((b / C::NS) & 1) ^ 1)) {
+          dev_set_error(p.status, SAF_DEV_TIMEOUT_TMA, 80);
+          break;
+        }
+        uint8_t* dst = ring + s * 2 * C::TILE_BYTES;
+        mbar_expect_tx(&sh->full[s], 2 * C::TILE_BYTES);
+        as_load_tile<HD>(dst, &mapQ, &sh->full[s], it * 128, u, b);
+        as_load_tile<HD>(dst + C::TILE_BYTES, &mapK, &sh->full[s], jt * 128, u, b);
+      }
+    }
+  } else if (warp == W_MMA) {
+    const bool leader = elect_one();
+    const uint32_t idesc = umma_idesc_bf16(128, 128, 0, 0);
+    const uint32_t aR = smem_u32(ring);
+    for (int b = 0; b < p.B; ++b) {
+      const int s = b % C::NS, k = b & 1;
+      if (!mbar_wait(&sh->full[s], (b / C::NS) & 1) || !mbar_wait(&sh->s_empty[k], ((b >> 1) & 1) ^ 1)) {
+        dev_set_error(p.status, SAF_DEV_TIMEOUT_MMA, 81);
+        break;
+      }
+      tc_fence_after();
+      if (leader) {
+        const uint32_t aQ = aR + s * 2 * C::TILE_BYTES, aK = aQ + C::TILE_BYTES;
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks) {
+          const uint32_t off = (ks >> 2) * 16384 + (ks & 3) * 32;
+          umma_ss(tmem + k * 128, umma_smem_desc_sw128(aQ + off, 16, 1024), umma_smem_desc_sw128(aK + off, 16, 1024),
+                  idesc, ks > 0);
+        }
+        umma_commit(&sh->s_full[k]);
+        umma_commit(&sh->empty[s]);
+      }
+      __syncwarp();
+    }
+  } else {
+    // ------------------------------------------------------------------ compute warpgroups
+    const int quarter = warp >> 2;
+    const int r = tid & 127;                        // query row of the tile
+    const int cb = quarter * 32;                    // first key column of this group
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+    const int gi = it * 128 + r;
+    const bool row_ok = gi < p.T;
+    const int gj0 = jt * 128 + cb;
+    const bool diag = (it == jt);
+    const float sc = p.scale_log2;
+    const float* lse_u = p.lse + (int64_t)u * p.lse_s[1] + (int64_t)gi * p.lse_s[2];
+    float mean[32], m2[32];
+#pragma unroll
+    for (int c = 0; c < 32; ++c) mean[c] = m2[c] = 0.f;
+    float ent = 0.f;                                // sum p log2 p of this thread's cells
+    float nl = row_ok ? lse_u[0] : INFINITY;        // +inf: rows past T hold zeros
+    bool ok = true;
+    for (int b = 0; b < p.B; ++b) {
+      const int k = b & 1;
+      const float L = nl;
+      if (b + 1 < p.B && row_ok) nl = lse_u[(int64_t)(b + 1) * p.lse_s[0]];
+      if (!mbar_wait(&sh->s_full[k], (b >> 1) & 1)) {
+        dev_set_error(p.status, SAF_DEV_TIMEOUT_SOFTMAX, 82);
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const float inv = 1.f / (float)(b + 1);
+#pragma unroll
+      for (int hf = 0; hf < 2; ++hf) {
+        uint32_t d[16];
+        tmem_ld16(tmem + lane_base + k * 128 + cb + hf * 16, d);
+        tmem_ld_wait();
+#pragma unroll
+        for (int x = 0; x < 16; ++x) {
+          const int c = hf * 16 + x;
+          float xl = fmaf(__uint_as_float(d[x]), sc, -L);            // log2 of the probability
+          if (diag && gj0 + c > gi) xl = -INFINITY;                   // causal mask inside the diagonal tile
+          const float pe = as_ex2(xl);
+          ent = fmaf(pe, fmaxf(xl, -200.f), ent);                     // p = 0 there, so the clamp only avoids 0 * inf
+          // Welford update of the cell's mean and centred sum of squares over the batch
+          const float dlt = pe - mean[c];
+          mean[c] = fmaf(dlt, inv, mean[c]);
+          m2[c] = fmaf(dlt, pe - mean[c], m2[c]);
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sh->s_empty[k]);
+    }
+    // ---- merge the tile into the running mean (Chan), reduce the per-head scalars
+    double m2sum = 0.0, corr = 0.0;
+    if (ok) {
+      const double total = (double)p.count_prev + (double)p.B;
+      const float w = (float)((double)p.B / total);
+      float* dst = mean_u + (int64_t)gi * p.T + gj0;
+      const bool vec = (p.T & 3) == 0;
+#pragma unroll
+      for (int c4 = 0; c4 < 8; ++c4) {
+        float o[4] = {mean[c4 * 4], mean[c4 * 4 + 1], mean[c4 * 4 + 2], mean[c4 * 4 + 3]};
+        m2sum += (double)(m2[c4 * 4] + m2[c4 * 4 + 1]) + (double)(m2[c4 * 4 + 2] + m2[c4 * 4 + 3]);
+        const int gj = gj0 + c4 * 4;
+        if (!row_ok || gj >= p.T) continue;
+        if (vec) {
+          if (p.count_prev > 0) {
+            const float4 pv = *reinterpret_cast<const float4*>(dst + c4 * 4);
+            const float pr[4] = {pv.x, pv.y, pv.z, pv.w};
+            float cs = 0.f;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float dlt = o[e] - pr[e];
+              cs = fmaf(dlt, dlt, cs);
+              o[e] = fmaf(dlt, w, pr[e]);
+            }
+            corr += (double)cs;
+          }
+          *reinterpret_cast<float4*>(dst + c4 * 4) = make_float4(o[0], o[1], o[2], o[3]);
+        } else {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            if (gj + e >= p.T) continue;
+            float v = o[e];
+            if (p.count_prev > 0) {
+              const float pr = dst[c4 * 4 + e];
+              const float dlt = v - pr;
+              corr += (double)(dlt * dlt);
+              v = fmaf(dlt, w, pr);
+            }
+            dst[c4 * 4 + e] = v;
+          }
+        }
+      }
+      m2sum += corr * ((double)p.count_prev * (double)p.B / total);
+    }
+    double esum = (double)ent * (double)AS_LN2;      // natural log, as the reference's xlogy
+#pragma unroll
+    for (int off = 16; off; off >>= 1) {
+      m2sum += __shfl_xor_sync(0xffffffffu, m2sum, off);
+      esum += __shfl_xor_sync(0xffffffffu, esum, off);
+    }
+    if (lane == 0) {
+      sh->red[0][warp] = m2sum;
+      sh->red[1][warp] = esum;
+    }
+    named_bar_sync(1, AS_COMPUTE);
+    if (tid < 2 && ok) {
+      double tot = 0.0;
+      for (int wq = 0; wq < AS_COMPUTE / 32; ++wq) tot += sh->red[tid][wq];
+      atomicAdd(tid == 0 ? &p.head_m2[u] : &p.neg_entropy[u], tot);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == W_MMA) tmem_dealloc(tmem, C::TMEM_COLS);
+}
+
+bool as_tensor_ok(const SafTensor& t) {
+  if (!t.ptr || ((uintptr_t)t.ptr & 15) || t.stride[3] != 1) return false;
+  for (int i = 0; i < 3; ++i)
+    if (t.stride[i] % 8 || t.stride[i] <= 0) return false;
+  return true;
+}
+
+int as_map4(CUtensorMap* m, const SafTensor& t, int B, int Hn, int T, int HD) {
+  uint64_t dims[4] = {(uint64_t)HD, (uint64_t)T, (uint64_t)Hn, (uint64_t)B};
+  uint64_t strides[4] = {0, (uint64_t)t.stride[2] * 2, (uint64_t)t.stride[1] * 2, (uint64_t)t.stride[0] * 2};
+  uint32_t box[4] = {64, 128, 1, 1};
+  return make_tensor_map_bf16(m, t.ptr, 4, dims, strides, box, true);
+}
+
+template <int HD>
+int as_launch(const SafAttnStatsArgs& a, cudaStream_t st) {
+  CUtensorMap mq, mk;
+  int rc;
+  if ((rc = as_map4(&mq, a.q, a.B, a.U, a.T, HD))) return rc;
+  if ((rc = as_map4(&mk, a.k, a.B, a.U, a.T, HD))) return rc;
+  AsParams p;
+  p.B = a.B; p.U = a.U; p.T = a.T;
+  p.n_tiles = (a.T + 127) / 128;
+  p.scale_log2 = a.sm_scale * 1.4426950408889634f;
+  p.lse = reinterpret_cast<const float*>(a.lse.ptr);
+  for (int i = 0; i < 3; ++i) p.lse_s[i] = a.lse.stride[i];
+  p.mean = a.mean;
+  p.count_prev = a.count_prev;
+  p.head_m2 = a.head_m2;
+  p.neg_entropy = a.neg_entropy;
+  p.status = a.status;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(attn_stats_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         AsCfg<HD>::SMEM_BYTES);
+    if (e != cudaSuccess) return fail(SAF_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    attr_set = true;
+  }
+  const int64_t grid = (int64_t)a.U * p.n_tiles * p.n_tiles;
+  if (grid > 0x7fffffff) return fail(SAF_ERR_LIMIT, "attention statistics grid too large");
+  attn_stats_kernel<HD><<<(unsigned)grid, AS_THREADS, AsCfg<HD>::SMEM_BYTES, st>>>(mq, mk, p);
+  count_launch();
+  return check_launch("attn_stats_kernel");
+}
+
+}  // namespace
+
+int launch_attn_stats_sm100(const SafAttnStatsArgs& a, cudaStream_t st) {
+  if (a.dtype != SAF_BF16 || (a.HD != 64 && a.HD != 128)) return fail(SAF_ERR_UNSUPPORTED, "attention statistics: bf16 with head_dim 64 or 128 only");
+  if (!as_tensor_ok(a.q) || !as_tensor_ok(a.k))
+    return fail(SAF_ERR_UNSUPPORTED, "attention statistics: q, k need 16-byte aligned rows and unit last stride");
+  if (!saf_device_supported()) return fail(SAF_ERR_UNSUPPORTED, "attention statistics need an sm_100 device");
+  return a.HD == 64 ? as_launch<64>(a, st) : as_launch<128>(a, st);
+}
+
+}  // namespace saf

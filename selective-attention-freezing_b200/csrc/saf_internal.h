@@ -62,6 +62,7 @@ int launch_layernorm(const void* x, int64_t ldx, const void* w, const void* b, v
                      float eps, int dtype, cudaStream_t st);
 int launch_logz(const float* alpha, const float* rho, float* z, int H, int S, int rows, cudaStream_t st);   // rows >= `rows` get 0
 int launch_pattern_grad(const SafPatternGradArgs& a, cudaStream_t st);
+int launch_attn_stats_sm100(const SafAttnStatsArgs& a, cudaStream_t st);
 
 // TMA descriptor encode through the driver entry point (no link-time libcuda dependency)
 typedef CUresult (*TensorMapEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,

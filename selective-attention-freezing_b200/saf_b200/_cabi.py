@@ -79,6 +79,16 @@ class SafPatternGradArgs(C.Structure):
     ]
 
 
+class SafAttnStatsArgs(C.Structure):
+    _fields_ = [
+        ("struct_size", C.c_int32), ("dtype", C.c_int32),
+        ("B", C.c_int32), ("U", C.c_int32), ("T", C.c_int32), ("HD", C.c_int32), ("sm_scale", C.c_float),
+        ("q", SafTensor), ("k", SafTensor), ("lse", SafTensor),
+        ("mean", C.c_void_p), ("count_prev", C.c_int64), ("head_m2", C.c_void_p), ("neg_entropy", C.c_void_p),
+        ("status", C.c_void_p),
+    ]
+
+
 ACT_NONE, ACT_GELU = 0, 1
 
 EXPORTS = (
@@ -86,7 +96,7 @@ EXPORTS = (
     "saf_mixed_attn_fwd", "saf_mixed_attn_bwd", "saf_mixed_attn_bwd_static", "saf_frozen_pv_fwd", "saf_frozen_pv_bwd",
     "saf_indexed_linear_fwd", "saf_indexed_linear_bwd_dx", "saf_indexed_linear_bwd_dw",
     "saf_decomposed_logz", "saf_rope_slabs", "saf_layernorm_fwd",
-    "saf_pattern_normalisers", "saf_pattern_param_grad",
+    "saf_pattern_normalisers", "saf_pattern_param_grad", "saf_attention_moments",
 )
 
 
@@ -111,7 +121,8 @@ def _load():
                      ("saf_mixed_attn_bwd_static", SafMixedAttnBwdArgs),
                      ("saf_frozen_pv_fwd", SafFrozenPvArgs), ("saf_frozen_pv_bwd", SafFrozenPvArgs),
                      ("saf_indexed_linear_fwd", SafIndexedLinearArgs),
-                     ("saf_pattern_param_grad", SafPatternGradArgs)):
+                     ("saf_pattern_param_grad", SafPatternGradArgs),
+                     ("saf_attention_moments", SafAttnStatsArgs)):
         f = getattr(lib, name)
         f.argtypes = [C.POINTER(at), C.c_void_p]
         f.restype = C.c_int

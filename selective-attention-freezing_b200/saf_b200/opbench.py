@@ -158,6 +158,20 @@ def main():
                 n = ops.launch_count() - n0
                 ms = _timed(run, args.reps)
             fl = 1.0 * B * nf * T * T * hd          # causal half of 2 T^2 hd per head
+        elif op == "attn_stats":
+            # controller statistics of the live heads (flash forward for the row lse + the statistics kernel);
+            # the running mean is (U, T, T) fp32 on the device
+            from saf_b200.capture import AttentionMoments
+            acc = AttentionMoments(U, T, dev)
+            qd, kd = q.detach(), k.detach()
+            with torch.no_grad():
+                acc.update(qd, kd)                  # first batch: plain write of the mean
+                n0 = ops.launch_count()
+                acc.update(qd, kd)                  # later batches: read-merge-write
+                n = ops.launch_count() - n0
+                ms = _timed(lambda: acc.update(qd, kd), args.reps)
+            fl = 1.5 * fl_attn                      # the lse pass (QK^T and PV) + QK^T again
+            del acc
         elif op in ("layer_train", "layer_infer"):
             # the whole attention module (projections + mixed attention + c_proj) at this shape
             from types import SimpleNamespace

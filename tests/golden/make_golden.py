@@ -12,7 +12,9 @@ reference's behaviour travels.  What is recorded:
     kernel/fused_attn.py:65-116, linear_rows / linear_rows2 / linear_permuted_cols of
     kernel/indexed_linear.py with their gradients, apply_rotary_pos_emb of nanogpt/model.py:63-68;
   * block level: the reference's LayerNorm and MLP modules (nanogpt/model.py:45-54, 1193-1207) on seeded inputs;
-  * learnable patterns: dense_reference of supplement/trainable_patterns.py:7-13 with its autograd gradients.
+  * learnable patterns: dense_reference of supplement/trainable_patterns.py:7-13 with its autograd gradients;
+  * controller statistics: _centered_batch_reduced_moments, _merge_reduced_moments, _negative_entropy_sum and
+    _mean_forward_kl_from_entropy of nanogpt/dynamic_freeze.py:96-193 on two seeded batches of softmax attention.
 """
 import importlib.util
 import os
@@ -190,6 +192,25 @@ def main(ref_root):
                                                                       rh.detach().numpy(), wt.numpy())
     out["tp_out"] = yt.detach().numpy()
     out["tp_dvalue"], out["tp_dalpha"], out["tp_drho"] = val.grad.numpy(), al.grad.numpy(), rh.grad.numpy()
+
+    # ---- controller statistics: the reference's own reductions of captured attention
+    # (nanogpt/dynamic_freeze.py:96-193) on two seeded batches, merged with its Chan formula ----
+    import dynamic_freeze as DF  # noqa: E402  (nanogpt/ is on sys.path)
+    g = torch.Generator().manual_seed(28)
+    Bs, Us, Ts, Ds = 3, 2, 40, 16
+    count, mean, m2 = 0, None, None
+    negent = torch.zeros(Us, dtype=torch.float64)
+    for bi in range(2):
+        qs = torch.randn(Bs, Us, Ts, Ds, generator=g)
+        ks = torch.randn(Bs, Us, Ts, Ds, generator=g)
+        sc = (qs @ ks.transpose(-1, -2)) / Ds ** 0.5
+        att = sc.masked_fill(~torch.ones(Ts, Ts, dtype=torch.bool).tril(), float("-inf")).softmax(-1)
+        bn, bm, b2 = DF._centered_batch_reduced_moments(att)
+        count, mean, m2 = DF._merge_reduced_moments(count, mean, m2, bn, bm, b2)
+        negent += DF._negative_entropy_sum(att)
+        out[f"st_q{bi}"], out[f"st_k{bi}"] = qs.numpy(), ks.numpy()
+        out[f"st_mean{bi}"], out[f"st_m2_{bi}"], out[f"st_negent{bi}"] = mean.numpy().copy(), m2.numpy().copy(), negent.numpy().copy()
+    out["st_kl"] = DF._mean_forward_kl_from_entropy(negent, mean.float(), count).numpy()
 
     path = os.path.join(HERE, "reference_vectors.npz")
     np.savez_compressed(path, **out)

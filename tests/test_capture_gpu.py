@@ -1,0 +1,83 @@
+"""GPU parity of the fused controller statistics (saf_attention_moments) against the CPU oracle, which restates
+the reference's reductions of the captured attention tensor (nanogpt/dynamic_freeze.py:96-193)."""
+import pytest
+import torch
+
+from oracle import saf_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+CASES = [
+    # B, U, T, hd, batches
+    (3, 2, 300, 64, 2),
+    (2, 3, 517, 64, 3),        # ragged T, not a multiple of 4: scalar stores
+    (1, 2, 1024, 128, 2),      # single-sample batches: zero within-batch M2, all variance from the merge
+    (4, 1, 640, 128, 1),
+    (5, 2, 256, 64, 2),        # more samples than ring stages
+]
+
+
+@pytest.mark.parametrize("case", CASES, ids=lambda c: f"B{c[0]}U{c[1]}T{c[2]}d{c[3]}x{c[4]}")
+def test_attention_moments_match_captured_reductions(case):
+    from saf_b200.capture import AttentionMoments
+    B, U, T, hd, nb = case
+    gen = torch.Generator().manual_seed(T + hd + B)
+    acc = AttentionMoments(U, T, "cuda")
+    count, mean, m2 = 0, None, None
+    negent = torch.zeros(U, dtype=torch.float64)
+    for _ in range(nb):
+        q = (torch.randn(B, U, T, hd, generator=gen) * 1.3).bfloat16()
+        k = torch.randn(B, U, T, hd, generator=gen).bfloat16()
+        att = O.attention_probs(q.double(), k.double())
+        bn, bm, b2 = O.centered_batch_reduced_moments(att)
+        count, mean, m2 = O.merge_reduced_moments(count, mean, m2, bn, bm, b2)
+        negent += O.negative_entropy_sum(att)
+        acc.update(q.cuda(), k.cuda())
+    assert acc.count == count
+    got_mean = acc.mean.cpu().double()
+    # probabilities come from bf16 tensor-core scores with fp32 statistics: absolute error per cell well under 1e-3,
+    # relative L2 of the whole mean matrix under 1e-3
+    assert O.max_abs(got_mean, mean) <= 2e-3, O.max_abs(got_mean, mean)
+    assert O.rel_l2(got_mean, mean) <= 2e-3
+    assert not got_mean.triu(1).any()                       # exact zeros above the diagonal
+    rel = ((acc.head_m2.cpu() - m2).abs() / m2.abs().clamp_min(1e-12)).max().item()
+    assert rel <= 1e-2 or (m2.abs().max() < 1e-9 and acc.head_m2.abs().max() < 1e-6), rel
+    rel_e = ((acc.neg_entropy.cpu() - negent).abs() / negent.abs()).max().item()
+    assert rel_e <= 2e-3, rel_e
+    var = acc.per_head_variance().cpu()
+    ref_var = (m2 / max(count - 1, 1) / (T * T)).float()
+    assert torch.allclose(var, ref_var, rtol=1e-2, atol=1e-12)
+    kl = acc.mean_forward_kl().cpu()
+    ref_kl = O.mean_forward_kl(negent, mean.float(), count)
+    assert torch.allclose(kl, ref_kl, rtol=2e-2, atol=2e-4), (kl, ref_kl)
+
+
+def test_attention_moments_golden_vectors():
+    """On the reference's own vectors (q, k rounded to bf16 for the tensor cores)."""
+    import os
+    import numpy as np
+    from saf_b200.capture import AttentionMoments
+    G = np.load(os.path.join(os.path.dirname(__file__), "golden", "reference_vectors.npz"))
+    acc = AttentionMoments(2, 40, "cuda")
+    # head_dim 16 has no tensor-core kernel: pad q, k with zero columns to 64 (scores unchanged) and keep the scale
+    for bi in range(2):
+        q = torch.from_numpy(G[f"st_q{bi}"])
+        k = torch.from_numpy(G[f"st_k{bi}"])
+        qp = torch.zeros(*q.shape[:-1], 64)
+        kp = torch.zeros(*k.shape[:-1], 64)
+        qp[..., :16], kp[..., :16] = q, k
+        acc.update(qp.bfloat16().cuda(), kp.bfloat16().cuda(), sm_scale=16 ** -0.5)
+        assert O.max_abs(acc.mean.cpu(), torch.from_numpy(G[f"st_mean{bi}"])) <= 2e-2
+    m2 = torch.from_numpy(G["st_m2_1"])
+    assert ((acc.head_m2.cpu() - m2).abs() / m2).max() <= 5e-2
+    ne = torch.from_numpy(G["st_negent1"])
+    assert ((acc.neg_entropy.cpu() - ne).abs() / ne.abs()).max() <= 2e-2
+
+
+def test_attention_moments_refuses_unsupported():
+    from saf_b200.capture import AttentionMoments
+    from saf_b200._cabi import SafError
+    acc = AttentionMoments(1, 64, "cuda")
+    q = torch.randn(1, 1, 64, 32, device="cuda").bfloat16()
+    with pytest.raises(SafError):
+        acc.update(q, q)

@@ -162,3 +162,18 @@ def test_trainable_pattern_gradients():
     # dV of these heads is the ordinary frozen-head backward: P^T dO
     P = O.decomp_pattern(al, rh, z, T)
     assert O.max_abs(torch.matmul(P.transpose(-1, -2)[None], w), g("tp_dvalue")) <= 2e-5
+
+
+def test_controller_statistics():
+    """Restated capture reductions equal the reference's own (nanogpt/dynamic_freeze.py:96-193) on two merged batches."""
+    count, mean, m2 = 0, None, None
+    negent = torch.zeros(2, dtype=torch.float64)
+    for bi in range(2):
+        att = O.attention_probs(g(f"st_q{bi}"), g(f"st_k{bi}"))
+        bn, bm, b2 = O.centered_batch_reduced_moments(att)
+        count, mean, m2 = O.merge_reduced_moments(count, mean, m2, bn, bm, b2)
+        negent += O.negative_entropy_sum(att)
+        assert O.max_abs(mean, g(f"st_mean{bi}")) <= 1e-6
+        assert O.max_abs(m2, g(f"st_m2_{bi}")) <= 1e-5
+        assert O.max_abs(negent, g(f"st_negent{bi}")) <= 1e-4
+    assert O.max_abs(O.mean_forward_kl(negent, mean.float(), count), g("st_kl")) <= 1e-5
