@@ -3,8 +3,8 @@
 // The reference measures heads by running the eager path with capture on and reducing the retained
 // softmax(QK^T) tensor: batch mean per cell, centred sum of squares reduced per head, and sum p log p per head
 // (nanogpt/dynamic_freeze.py:96-127 _centered_batch_reduced_moments, :130-143 _merge_reduced_moments,
-// :146-173 _negative_entropy_sum, used by _measure :629-745).  Here one CTA owns a 128 x 128 cell tile of one head
-// and walks the batch: S_b = Q_b K_b^T on tcgen05 into TMEM, P_b = exp2(S_b scale - lse_b) with the row
+// :146-173 _negative_entropy_sum, used by _measure :629-745).  Here a CTA takes one 128 x 128 cell tile of one head
+// at a time and walks the batch: S_b = Q_b K_b^T on tcgen05 into TMEM, P_b = exp2(S_b scale - lse_b) with the row
 // log-sum-exp of the flash forward, per-cell Welford mean / M2 in registers, then the tile of the running mean is
 // Chan-merged in place and the per-head scalars are reduced to one double atomic per CTA.
 //
@@ -42,8 +42,10 @@ struct AsShared {
 template <int HD>
 struct AsCfg {
   static constexpr int TILE_BYTES = 128 * HD * 2;
-  static constexpr int NS = 3;
-  static constexpr int SMEM_BYTES = 1024 + NS * 2 * TILE_BYTES + (int)sizeof(AsShared) + 64;
+  static constexpr int NS = (HD == 64) ? 3 : 2;
+  static constexpr int STAGE_LD = 132;                       // floats per staged row: 128 + 4 keeps 16-byte row writes conflict-free
+  static constexpr int STAGE_BYTES = 128 * STAGE_LD * 4;     // the tile's batch mean on its way to coalesced global rows
+  static constexpr int SMEM_BYTES = 1024 + NS * 2 * TILE_BYTES + STAGE_BYTES + (int)sizeof(AsShared) + 64;
   static constexpr int TMEM_COLS = 256;
 };
 
@@ -59,31 +61,35 @@ __device__ __forceinline__ void as_load_tile(uint8_t* dst, const CUtensorMap* m,
   for (int hh = 0; hh < HD / 64; ++hh) tma_load_4d(dst + hh * 16384, m, bar, hh * 64, row, head, b);
 }
 
+// Persistent: CTA c owns tiles c, c + gridDim.x, ... of the (head, query tile, key tile) list, so the producer's loads
+// for the next tile run under the epilogue of the current one and the set-up is paid once.  `g` counts batch steps
+// over all tiles of the CTA; ring stages and TMEM buffers follow it.
+struct AsTile {
+  int u, it, jt;
+};
+__device__ __forceinline__ AsTile as_decode(const AsParams& p, int t) {
+  const int nn = p.n_tiles * p.n_tiles;
+  AsTile x;
+  x.u = t / nn;
+  const int rem = t - x.u * nn;
+  x.it = rem / p.n_tiles;
+  x.jt = rem - x.it * p.n_tiles;
+  return x;
+}
+
 template <int HD>
 __global__ void __launch_bounds__(AS_THREADS, 1)
 attn_stats_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
                   const __grid_constant__ AsParams p) {
   using C = AsCfg<HD>;
-  const int nn = p.n_tiles * p.n_tiles;
-  const int u = (int)blockIdx.x / nn, rem = (int)blockIdx.x - u * nn;
-  const int it = rem / p.n_tiles, jt = rem - it * p.n_tiles;
+  const int total_tiles = p.U * p.n_tiles * p.n_tiles;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  float* mean_u = p.mean + (int64_t)u * p.T * p.T;
-  if (jt > it) {
-    // above the diagonal every probability is zero: the first batch writes the zeros, later ones leave them
-    if (p.count_prev == 0) {
-      for (int e = tid; e < 128 * 128; e += AS_THREADS) {
-        const int gi = it * 128 + (e >> 7), gj = jt * 128 + (e & 127);
-        if (gi < p.T && gj < p.T) mean_u[(int64_t)gi * p.T + gj] = 0.f;
-      }
-    }
-    return;
-  }
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* ring = smem;                                // stage s: [Q_b tile | K_b tile]
-  AsShared* sh = reinterpret_cast<AsShared*>(ring + C::NS * 2 * C::TILE_BYTES);
+  float* stage = reinterpret_cast<float*>(ring + C::NS * 2 * C::TILE_BYTES);
+  AsShared* sh = reinterpret_cast<AsShared*>(ring + C::NS * 2 * C::TILE_BYTES + C::STAGE_BYTES);
   constexpr int W_TMA = AS_COMPUTE / 32, W_MMA = W_TMA + 1;
 
   if (tid == 0) {
@@ -110,41 +116,55 @@ attn_stats_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
     if (elect_one()) {
       tma_prefetch_desc(&mapQ);
       tma_prefetch_desc(&mapK);
-      for (int b = 0; b < p.B; ++b) {
-        const int s = b % C::NS;
-        if (!mbar_wait(&sh->empty[s], ((b / C::NS) & 1) ^ 1)) {
-          dev_set_error(p.status, SAF_DEV_TIMEOUT_TMA, 80);
-          break;
+      int g = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        const AsTile x = as_decode(p, t);
+        if (x.jt > x.it) continue;
+        for (int b = 0; b < p.B; ++b, ++g) {
+          const int s = g % C::NS;
+          if (!mbar_wait(&sh->empty[s], ((g / C::NS) & 1) ^ 1)) {
+            dev_set_error(p.status, SAF_DEV_TIMEOUT_TMA, 80);
+            ok = false;
+            break;
+          }
+          uint8_t* dst = ring + s * 2 * C::TILE_BYTES;
+          mbar_expect_tx(&sh->full[s], 2 * C::TILE_BYTES);
+          as_load_tile<HD>(dst, &mapQ, &sh->full[s], x.it * 128, x.u, b);
+          as_load_tile<HD>(dst + C::TILE_BYTES, &mapK, &sh->full[s], x.jt * 128, x.u, b);
         }
-        uint8_t* dst = ring + s * 2 * C::TILE_BYTES;
-        mbar_expect_tx(&sh->full[s], 2 * C::TILE_BYTES);
-        as_load_tile<HD>(dst, &mapQ, &sh->full[s], it * 128, u, b);
-        as_load_tile<HD>(dst + C::TILE_BYTES, &mapK, &sh->full[s], jt * 128, u, b);
       }
     }
   } else if (warp == W_MMA) {
     const bool leader = elect_one();
     const uint32_t idesc = umma_idesc_bf16(128, 128, 0, 0);
     const uint32_t aR = smem_u32(ring);
-    for (int b = 0; b < p.B; ++b) {
-      const int s = b % C::NS, k = b & 1;
-      if (!mbar_wait(&sh->full[s], (b / C::NS) & 1) || !mbar_wait(&sh->s_empty[k], ((b >> 1) & 1) ^ 1)) {
-        dev_set_error(p.status, SAF_DEV_TIMEOUT_MMA, 81);
-        break;
-      }
-      tc_fence_after();
-      if (leader) {
-        const uint32_t aQ = aR + s * 2 * C::TILE_BYTES, aK = aQ + C::TILE_BYTES;
-#pragma unroll
-        for (int ks = 0; ks < HD / 16; ++ks) {
-          const uint32_t off = (ks >> 2) * 16384 + (ks & 3) * 32;
-          umma_ss(tmem + k * 128, umma_smem_desc_sw128(aQ + off, 16, 1024), umma_smem_desc_sw128(aK + off, 16, 1024),
-                  idesc, ks > 0);
+    int g = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      const AsTile x = as_decode(p, t);
+      if (x.jt > x.it) continue;
+      for (int b = 0; b < p.B; ++b, ++g) {
+        const int s = g % C::NS, k = g & 1;
+        if (!mbar_wait(&sh->full[s], (g / C::NS) & 1) || !mbar_wait(&sh->s_empty[k], ((g >> 1) & 1) ^ 1)) {
+          dev_set_error(p.status, SAF_DEV_TIMEOUT_MMA, 81);
+          ok = false;
+          break;
         }
-        umma_commit(&sh->s_full[k]);
-        umma_commit(&sh->empty[s]);
+        tc_fence_after();
+        if (leader) {
+          const uint32_t aQ = aR + s * 2 * C::TILE_BYTES, aK = aQ + C::TILE_BYTES;
+#pragma unroll
+          for (int ks = 0; ks < HD / 16; ++ks) {
+            const uint32_t off = (ks >> 2) * 16384 + (ks & 3) * 32;
+            umma_ss(tmem + k * 128, umma_smem_desc_sw128(aQ + off, 16, 1024), umma_smem_desc_sw128(aK + off, 16, 1024),
+                    idesc, ks > 0);
+          }
+          umma_commit(&sh->s_full[k]);
+          umma_commit(&sh->empty[s]);
+        }
+        __syncwarp();
       }
-      __syncwarp();
     }
   } else {
     // ------------------------------------------------------------------ compute warpgroups
@@ -152,111 +172,159 @@ attn_stats_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
     const int r = tid & 127;                        // query row of the tile
     const int cb = quarter * 32;                    // first key column of this group
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-    const int gi = it * 128 + r;
-    const bool row_ok = gi < p.T;
-    const int gj0 = jt * 128 + cb;
-    const bool diag = (it == jt);
     const float sc = p.scale_log2;
-    const float* lse_u = p.lse + (int64_t)u * p.lse_s[1] + (int64_t)gi * p.lse_s[2];
-    float mean[32], m2[32];
+    const double total = (double)p.count_prev + (double)p.B;
+    const float w = (float)((double)p.B / total);
+    const bool vec = (p.T & 3) == 0;
+    // per-head scalars of this thread, handed to the head's two doubles when the CTA moves to another head
+    double m2sum = 0.0, esum = 0.0;
+    int cur_u = -1;
+    auto flush_head = [&]() {
 #pragma unroll
-    for (int c = 0; c < 32; ++c) mean[c] = m2[c] = 0.f;
-    float ent = 0.f;                                // sum p log2 p of this thread's cells
-    float nl = row_ok ? lse_u[0] : INFINITY;        // +inf: rows past T hold zeros
-    bool ok = true;
-    for (int b = 0; b < p.B; ++b) {
-      const int k = b & 1;
-      const float L = nl;
-      if (b + 1 < p.B && row_ok) nl = lse_u[(int64_t)(b + 1) * p.lse_s[0]];
-      if (!mbar_wait(&sh->s_full[k], (b >> 1) & 1)) {
-        dev_set_error(p.status, SAF_DEV_TIMEOUT_SOFTMAX, 82);
-        ok = false;
-        break;
+      for (int off = 16; off; off >>= 1) {
+        m2sum += __shfl_xor_sync(0xffffffffu, m2sum, off);
+        esum += __shfl_xor_sync(0xffffffffu, esum, off);
       }
-      tc_fence_after();
-      const float inv = 1.f / (float)(b + 1);
+      named_bar_sync(1, AS_COMPUTE);                // the previous flush has been read
+      if (lane == 0) {
+        sh->red[0][warp] = m2sum;
+        sh->red[1][warp] = esum;
+      }
+      named_bar_sync(1, AS_COMPUTE);
+      if (tid < 2) {
+        double tot = 0.0;
+        for (int wq = 0; wq < AS_COMPUTE / 32; ++wq) tot += sh->red[tid][wq];
+        atomicAdd(tid == 0 ? &p.head_m2[cur_u] : &p.neg_entropy[cur_u], tot);
+      }
+      m2sum = esum = 0.0;
+    };
+    int g = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      const AsTile x = as_decode(p, t);
+      float* mean_u = p.mean + (int64_t)x.u * p.T * p.T;
+      if (x.jt > x.it) {
+        // above the diagonal every probability is zero: the first batch writes the zeros, later ones leave them
+        if (p.count_prev == 0) {
+          for (int e = tid; e < 128 * 128; e += AS_COMPUTE) {
+            const int gi = x.it * 128 + (e >> 7), gj = x.jt * 128 + (e & 127);
+            if (gi < p.T && gj < p.T) mean_u[(int64_t)gi * p.T + gj] = 0.f;
+          }
+        }
+        continue;
+      }
+      if (x.u != cur_u) {
+        if (cur_u >= 0) flush_head();
+        cur_u = x.u;
+      }
+      const int gi = x.it * 128 + r;
+      const bool row_ok = gi < p.T;
+      const int gj0 = x.jt * 128 + cb;
+      const bool diag = (x.it == x.jt);
+      const float* lse_u = p.lse + (int64_t)x.u * p.lse_s[1] + (int64_t)gi * p.lse_s[2];
+      float mean[32], m2[32];
 #pragma unroll
-      for (int hf = 0; hf < 2; ++hf) {
-        uint32_t d[16];
-        tmem_ld16(tmem + lane_base + k * 128 + cb + hf * 16, d);
-        tmem_ld_wait();
+      for (int c = 0; c < 32; ++c) mean[c] = m2[c] = 0.f;
+      float ent = 0.f;                                // sum p log2 p of this thread's cells
+      float nl = row_ok ? lse_u[0] : INFINITY;        // +inf: rows past T hold zeros
+      for (int b = 0; b < p.B; ++b, ++g) {
+        const int k = g & 1;
+        const float L = nl;
+        if (b + 1 < p.B && row_ok) nl = lse_u[(int64_t)(b + 1) * p.lse_s[0]];
+        if (!mbar_wait(&sh->s_full[k], (g >> 1) & 1)) {
+          dev_set_error(p.status, SAF_DEV_TIMEOUT_SOFTMAX, 82);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const float inv = 1.f / (float)(b + 1);
 #pragma unroll
-        for (int x = 0; x < 16; ++x) {
-          const int c = hf * 16 + x;
-          float xl = fmaf(__uint_as_float(d[x]), sc, -L);            // log2 of the probability
-          if (diag && gj0 + c > gi) xl = -INFINITY;                   // causal mask inside the diagonal tile
-          const float pe = as_ex2(xl);
-          ent = fmaf(pe, fmaxf(xl, -200.f), ent);                     // p = 0 there, so the clamp only avoids 0 * inf
-          // Welford update of the cell's mean and centred sum of squares over the batch
-          const float dlt = pe - mean[c];
-          mean[c] = fmaf(dlt, inv, mean[c]);
-          m2[c] = fmaf(dlt, pe - mean[c], m2[c]);
+        for (int hf = 0; hf < 2; ++hf) {
+          uint32_t d[16];
+          tmem_ld16(tmem + lane_base + k * 128 + cb + hf * 16, d);
+          tmem_ld_wait();
+#pragma unroll
+          for (int xx = 0; xx < 16; ++xx) {
+            const int c = hf * 16 + xx;
+            float xl = fmaf(__uint_as_float(d[xx]), sc, -L);           // log2 of the probability
+            if (diag && gj0 + c > gi) xl = -INFINITY;                   // causal mask inside the diagonal tile
+            const float pe = as_ex2(xl);
+            ent = fmaf(pe, fmaxf(xl, -200.f), ent);                     // p = 0 there, so the clamp only avoids 0 * inf
+            // Welford update of the cell's mean and centred sum of squares over the batch
+            const float dlt = pe - mean[c];
+            mean[c] = fmaf(dlt, inv, mean[c]);
+            m2[c] = fmaf(dlt, pe - mean[c], m2[c]);
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sh->s_empty[k]);
+      }
+      if (!ok) break;
+      // ---- merge the tile into the running mean (Chan).  A thread holds 32 cells of one row; written from here the
+      // rows of a warp would be 32 separate 16-byte pieces per instruction, so the tile goes through shared memory
+      // and every warp then moves whole 512-byte rows.
+      named_bar_sync(2, AS_COMPUTE);                  // the previous tile's rows have left the staging tile
+      {
+        float* srow = stage + r * C::STAGE_LD + cb;
+#pragma unroll
+        for (int c4 = 0; c4 < 8; ++c4) {
+          *reinterpret_cast<float4*>(srow + c4 * 4) =
+              make_float4(mean[c4 * 4], mean[c4 * 4 + 1], mean[c4 * 4 + 2], mean[c4 * 4 + 3]);
+          m2sum += (double)(m2[c4 * 4] + m2[c4 * 4 + 1]) + (double)(m2[c4 * 4 + 2] + m2[c4 * 4 + 3]);
         }
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&sh->s_empty[k]);
-    }
-    // ---- merge the tile into the running mean (Chan), reduce the per-head scalars
-    double m2sum = 0.0, corr = 0.0;
-    if (ok) {
-      const double total = (double)p.count_prev + (double)p.B;
-      const float w = (float)((double)p.B / total);
-      float* dst = mean_u + (int64_t)gi * p.T + gj0;
-      const bool vec = (p.T & 3) == 0;
+      named_bar_sync(2, AS_COMPUTE);
+      double corr = 0.0;
+      const int gjl = x.jt * 128 + lane * 4;
+      float4 o[8], pv[8];
 #pragma unroll
-      for (int c4 = 0; c4 < 8; ++c4) {
-        float o[4] = {mean[c4 * 4], mean[c4 * 4 + 1], mean[c4 * 4 + 2], mean[c4 * 4 + 3]};
-        m2sum += (double)(m2[c4 * 4] + m2[c4 * 4 + 1]) + (double)(m2[c4 * 4 + 2] + m2[c4 * 4 + 3]);
-        const int gj = gj0 + c4 * 4;
-        if (!row_ok || gj >= p.T) continue;
+      for (int rr = 0; rr < 8; ++rr) {
+        const int row = warp * 8 + rr;
+        o[rr] = *reinterpret_cast<const float4*>(stage + row * C::STAGE_LD + lane * 4);
+        pv[rr] = make_float4(0.f, 0.f, 0.f, 0.f);
+        const int grow = x.it * 128 + row;
+        if (vec && p.count_prev > 0 && grow < p.T && gjl < p.T)
+          pv[rr] = *reinterpret_cast<const float4*>(mean_u + (int64_t)grow * p.T + gjl);
+      }
+#pragma unroll
+      for (int rr = 0; rr < 8; ++rr) {
+        const int grow = x.it * 128 + warp * 8 + rr;
+        if (grow >= p.T || gjl >= p.T) continue;
+        float* dst = mean_u + (int64_t)grow * p.T + gjl;
+        float ov[4] = {o[rr].x, o[rr].y, o[rr].z, o[rr].w};
         if (vec) {
           if (p.count_prev > 0) {
-            const float4 pv = *reinterpret_cast<const float4*>(dst + c4 * 4);
-            const float pr[4] = {pv.x, pv.y, pv.z, pv.w};
+            const float pr[4] = {pv[rr].x, pv[rr].y, pv[rr].z, pv[rr].w};
             float cs = 0.f;
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-              const float dlt = o[e] - pr[e];
+              const float dlt = ov[e] - pr[e];
               cs = fmaf(dlt, dlt, cs);
-              o[e] = fmaf(dlt, w, pr[e]);
+              ov[e] = fmaf(dlt, w, pr[e]);
             }
             corr += (double)cs;
           }
-          *reinterpret_cast<float4*>(dst + c4 * 4) = make_float4(o[0], o[1], o[2], o[3]);
+          *reinterpret_cast<float4*>(dst) = make_float4(ov[0], ov[1], ov[2], ov[3]);
         } else {
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            if (gj + e >= p.T) continue;
-            float v = o[e];
+            if (gjl + e >= p.T) continue;
+            float v = ov[e];
             if (p.count_prev > 0) {
-              const float pr = dst[c4 * 4 + e];
+              const float pr = dst[e];
               const float dlt = v - pr;
               corr += (double)(dlt * dlt);
               v = fmaf(dlt, w, pr);
             }
-            dst[c4 * 4 + e] = v;
+            dst[e] = v;
           }
         }
       }
       m2sum += corr * ((double)p.count_prev * (double)p.B / total);
+      esum += (double)ent * (double)AS_LN2;          // natural log, as the reference's xlogy
     }
-    double esum = (double)ent * (double)AS_LN2;      // natural log, as the reference's xlogy
-#pragma unroll
-    for (int off = 16; off; off >>= 1) {
-      m2sum += __shfl_xor_sync(0xffffffffu, m2sum, off);
-      esum += __shfl_xor_sync(0xffffffffu, esum, off);
-    }
-    if (lane == 0) {
-      sh->red[0][warp] = m2sum;
-      sh->red[1][warp] = esum;
-    }
-    named_bar_sync(1, AS_COMPUTE);
-    if (tid < 2 && ok) {
-      double tot = 0.0;
-      for (int wq = 0; wq < AS_COMPUTE / 32; ++wq) tot += sh->red[tid][wq];
-      atomicAdd(tid == 0 ? &p.head_m2[u] : &p.neg_entropy[u], tot);
-    }
+    if (ok && cur_u >= 0) flush_head();
   }
   tc_fence_before();
   __syncthreads();
@@ -301,8 +369,16 @@ int as_launch(const SafAttnStatsArgs& a, cudaStream_t st) {
     if (e != cudaSuccess) return fail(SAF_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     attr_set = true;
   }
-  const int64_t grid = (int64_t)a.U * p.n_tiles * p.n_tiles;
-  if (grid > 0x7fffffff) return fail(SAF_ERR_LIMIT, "attention statistics grid too large");
+  const int64_t tiles = (int64_t)a.U * p.n_tiles * p.n_tiles;
+  if (tiles > 0x7fffffff) return fail(SAF_ERR_LIMIT, "attention statistics: too many tiles");
+  static int sm_count = 0;
+  if (!sm_count) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+    if (sm_count <= 0) sm_count = 148;
+  }
+  const int grid = (int)(tiles < sm_count ? tiles : sm_count);      // one persistent CTA per SM
   attn_stats_kernel<HD><<<(unsigned)grid, AS_THREADS, AsCfg<HD>::SMEM_BYTES, st>>>(mq, mk, p);
   count_launch();
   return check_launch("attn_stats_kernel");

@@ -73,6 +73,14 @@ def test_invalid_arguments_are_refused_before_launch():
     pg.struct_size = C.sizeof(_cabi.SafPatternGradArgs)
     pg.dtype, pg.B, pg.H, pg.T, pg.HD, pg.SD, pg.force_state = _cabi.SAF_BF16, 1, 2, 16, 64, 8, -1
     assert _cabi.lib.saf_pattern_param_grad(C.byref(pg), None) == _cabi.SAF_ERR_INVALID    # SD < T
+    assert _cabi.lib.saf_attention_moments(None, None) == _cabi.SAF_ERR_INVALID
+    st = _cabi.SafAttnStatsArgs()
+    assert _cabi.lib.saf_attention_moments(C.byref(st), None) == _cabi.SAF_ERR_INVALID
+    st.struct_size = C.sizeof(_cabi.SafAttnStatsArgs)
+    st.dtype, st.B, st.U, st.T, st.HD = _cabi.SAF_BF16, 1, 1, 16, 64
+    assert _cabi.lib.saf_attention_moments(C.byref(st), None) == _cabi.SAF_ERR_INVALID     # null q / k / mean
+    st.T = 0
+    assert _cabi.lib.saf_attention_moments(C.byref(st), None) == _cabi.SAF_OK
     pg.force_state = 1
     assert _cabi.lib.saf_pattern_param_grad(C.byref(pg), None) == _cabi.SAF_OK             # no such head trains
 
