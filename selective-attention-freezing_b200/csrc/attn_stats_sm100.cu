@@ -274,19 +274,22 @@ attn_stats_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
           m2sum += (double)(m2[c4 * 4] + m2[c4 * 4 + 1]) + (double)(m2[c4 * 4 + 2] + m2[c4 * 4 + 3]);
         }
       }
-      named_bar_sync(2, AS_COMPUTE);
+      // the old rows are requested before the barrier (the accumulators are dead by now), so their latency and the
+      // wait for the slowest warp overlap
       double corr = 0.0;
       const int gjl = x.jt * 128 + lane * 4;
       float4 o[8], pv[8];
 #pragma unroll
       for (int rr = 0; rr < 8; ++rr) {
-        const int row = warp * 8 + rr;
-        o[rr] = *reinterpret_cast<const float4*>(stage + row * C::STAGE_LD + lane * 4);
         pv[rr] = make_float4(0.f, 0.f, 0.f, 0.f);
-        const int grow = x.it * 128 + row;
+        const int grow = x.it * 128 + warp * 8 + rr;
         if (vec && p.count_prev > 0 && grow < p.T && gjl < p.T)
           pv[rr] = *reinterpret_cast<const float4*>(mean_u + (int64_t)grow * p.T + gjl);
       }
+      named_bar_sync(2, AS_COMPUTE);
+#pragma unroll
+      for (int rr = 0; rr < 8; ++rr)
+        o[rr] = *reinterpret_cast<const float4*>(stage + (warp * 8 + rr) * C::STAGE_LD + lane * 4);
 #pragma unroll
       for (int rr = 0; rr < 8; ++rr) {
         const int grow = x.it * 128 + warp * 8 + rr;
