@@ -119,6 +119,7 @@ class SafCausalSelfAttention(nn.Module):
         self._capture = False
         self._last_attn = None
         self._retain_attention = True
+        self._stats = None
         self._fz_dirty = True
 
     # ---- freeze state ---------------------------------------------------------------------
@@ -128,6 +129,14 @@ class SafCausalSelfAttention(nn.Module):
         self._retain_attention = bool(retain_attention)
         if not flag:
             self._last_attn = None
+
+    def set_statistics(self, accumulator):
+        """Measurement without the capture: while an accumulator is set (a `saf_b200.capture.AttentionMoments` over
+        this layer's live heads, in their compact order), every fused forward merges the attention statistics of
+        its live heads into it from the rotated q, k -- what the controller derives from `_last_attn` after
+        `set_capture(True)` (nanogpt/dynamic_freeze.py:664-745) -- and the fast path keeps running.  None switches
+        it off.  Frozen heads are not measured: their attention is the stored pattern."""
+        self._stats = accumulator
 
     def sd_params(self):
         """(H, 2) fp32 view of the structured heads' (sink weight, decay)."""
@@ -349,6 +358,8 @@ class SafCausalSelfAttention(nn.Module):
             qu = qkv[:, :, :nuf].transpose(1, 2)
             ku = qkv[:, :, nuf:2 * nuf].transpose(1, 2)
             v = qkv[:, :, 2 * nuf:].transpose(1, 2)
+            if self._stats is not None and nuf:
+                self._stats.update(qu, ku)
             y = ops.fused_mixed_attn(qu, ku, v, patt, self._fz_mask_i32, self._hidx_i32, pidx,
                                      alpha=dec[0], rho=dec[1], z=dec[2], validate=False, sink_decay=self._sd)
             y = y.transpose(1, 2).reshape(B, T, nh * hd)
@@ -368,6 +379,8 @@ class SafCausalSelfAttention(nn.Module):
             qk = ops.linear_rows2(x, self.q_proj.weight, self.k_proj.weight, self.q_proj.bias, self.k_proj.bias,
                                   self._uf_cols, rope=rp, head_dim=hd).view(B, T, 2, nuf, hd)
             qu, ku = qk[:, :, 0].transpose(1, 2), qk[:, :, 1].transpose(1, 2)
+            if self._stats is not None:
+                self._stats.update(qu.detach(), ku.detach())
         y = ops.fused_mixed_attn(qu, ku, v, patt, self._fz_mask_i32, self._hidx_i32, pidx,
                                  alpha=dec[0], rho=dec[1], z=dec[2], validate=False, sink_decay=self._sd)
         y = y.transpose(1, 2).reshape(B, T, nh * hd)

@@ -81,3 +81,44 @@ def test_attention_moments_refuses_unsupported():
     q = torch.randn(1, 1, 64, 32, device="cuda").bfloat16()
     with pytest.raises(SafError):
         acc.update(q, q)
+
+
+def test_module_statistics_equal_reductions_of_the_eager_capture():
+    """SafCausalSelfAttention.set_statistics on the fused bf16 path gives, for the live heads, what the reference's
+    controller computes from the eager capture (`_last_attn`, nanogpt/dynamic_freeze.py:664-745)."""
+    from types import SimpleNamespace
+    from saf_b200.attention import SafCausalSelfAttention, rope_tables
+    from saf_b200.capture import AttentionMoments
+    C_, H, T, B = 512, 8, 384, 3
+    cfg = SimpleNamespace(n_embd=C_, n_head=H, block_size=T, bias=False, dropout=0.0, position_encoding="rope",
+                          rand_attn_prior_repr="dense", freeze_pattern_dtype="bfloat16")
+    torch.manual_seed(3)
+    m = SafCausalSelfAttention(cfg).cuda().bfloat16().eval()
+    a, r = O.sink_decay_params(2, seed=5)
+    m.freeze_heads_sink_decay([1, 6], a.float().cuda(), r.float().cuda())
+    live = [h for h in range(H) if h not in (1, 6)]
+    cos, sin = rope_tables(C_ // H, T, device="cuda")
+    rope = (cos.view(1, 1, T, -1), sin.view(1, 1, T, -1))
+    acc = AttentionMoments(len(live), T, "cuda")
+    count, mean, m2 = 0, None, None
+    negent = torch.zeros(len(live), dtype=torch.float64)
+    for step in range(2):
+        x = (torch.randn(B, T, C_, generator=torch.Generator().manual_seed(step)) * 2).bfloat16().cuda()
+        with torch.no_grad():
+            m.set_statistics(acc)
+            y_fast = m(x, rope=rope)
+            m.set_statistics(None)
+            m.set_capture(True)
+            y_eager = m(x, rope=rope)
+            att = m._last_attn[:, live].float().cpu()
+            m.set_capture(False)
+        assert (y_fast.float() - y_eager.float()).abs().max() <= 5e-2
+        bn, bm, b2 = O.centered_batch_reduced_moments(att)
+        count, mean, m2 = O.merge_reduced_moments(count, mean, m2, bn, bm, b2)
+        negent += O.negative_entropy_sum(att)
+    assert acc.count == count == 2 * B
+    # the eager capture holds bf16 probabilities, the fused path fp32 ones from bf16 q, k
+    assert O.max_abs(acc.mean.cpu(), mean) <= 1e-2
+    assert O.rel_l2(acc.mean.cpu(), mean) <= 2e-2
+    assert ((acc.head_m2.cpu() - m2).abs() / m2).max() <= 5e-2
+    assert ((acc.neg_entropy.cpu() - negent).abs() / negent.abs()).max() <= 2e-2
