@@ -393,6 +393,7 @@ int launch_attn_stats_sm100(const SafAttnStatsArgs& a, cudaStream_t st) {
   if (a.dtype != SAF_BF16 || (a.HD != 64 && a.HD != 128)) return fail(SAF_ERR_UNSUPPORTED, "attention statistics: bf16 with head_dim 64 or 128 only");
   if (!as_tensor_ok(a.q) || !as_tensor_ok(a.k))
     return fail(SAF_ERR_UNSUPPORTED, "attention statistics: q, k need 16-byte aligned rows and unit last stride");
+  if ((uintptr_t)a.mean & 15) return fail(SAF_ERR_INVALID, "attention statistics: mean must be 16-byte aligned");
   if (!saf_device_supported()) return fail(SAF_ERR_UNSUPPORTED, "attention statistics need an sm_100 device");
   return a.HD == 64 ? as_launch<64>(a, st) : as_launch<128>(a, st);
 }

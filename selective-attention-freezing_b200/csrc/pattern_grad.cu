@@ -464,7 +464,7 @@ int launch_pattern_grad(const SafPatternGradArgs& a, cudaStream_t st) {
     if (!any) return SAF_OK;
   }
   const bool tc = a.dtype == SAF_BF16 && (a.HD == 64 || a.HD == 128) && pg_tensor_ok(a.v) && pg_tensor_ok(a.dout) &&
-                  a.out.stride[3] == 1 && a.delta && saf_device_supported();
+                  pg_tensor_ok(a.out) && a.delta && saf_device_supported();   // the pre-pass reads out / dout as bf16 pairs
   if (tc) return a.HD == 64 ? pg_launch_sm100<64>(a, st) : pg_launch_sm100<128>(a, st);
   return pg_launch_generic(a, st);
 }
