@@ -62,6 +62,20 @@ int make_tensor_map_bf16(CUtensorMap* out, const void* base, int rank, const uin
   return SAF_OK;
 }
 
+bool tma_rows_ok(const SafTensor& t) {
+  if (!t.ptr || ((uintptr_t)t.ptr & 15) || t.stride[3] != 1) return false;
+  for (int i = 0; i < 3; ++i)
+    if (t.stride[i] % 8 || t.stride[i] <= 0) return false;
+  return true;
+}
+
+int make_row_tile_map_bf16(CUtensorMap* m, const SafTensor& t, int B, int Hn, int T, int HD) {
+  uint64_t dims[4] = {(uint64_t)HD, (uint64_t)T, (uint64_t)Hn, (uint64_t)B};
+  uint64_t strides[4] = {0, (uint64_t)t.stride[2] * 2, (uint64_t)t.stride[1] * 2, (uint64_t)t.stride[0] * 2};
+  uint32_t box[4] = {64, 128, 1, 1};
+  return make_tensor_map_bf16(m, t.ptr, 4, dims, strides, box, true);
+}
+
 namespace {
 
 bool valid_dtype(int d) { return d == SAF_F32 || d == SAF_BF16 || d == SAF_F16; }

@@ -334,26 +334,12 @@ attn_stats_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
   if (warp == W_MMA) tmem_dealloc(tmem, C::TMEM_COLS);
 }
 
-bool as_tensor_ok(const SafTensor& t) {
-  if (!t.ptr || ((uintptr_t)t.ptr & 15) || t.stride[3] != 1) return false;
-  for (int i = 0; i < 3; ++i)
-    if (t.stride[i] % 8 || t.stride[i] <= 0) return false;
-  return true;
-}
-
-int as_map4(CUtensorMap* m, const SafTensor& t, int B, int Hn, int T, int HD) {
-  uint64_t dims[4] = {(uint64_t)HD, (uint64_t)T, (uint64_t)Hn, (uint64_t)B};
-  uint64_t strides[4] = {0, (uint64_t)t.stride[2] * 2, (uint64_t)t.stride[1] * 2, (uint64_t)t.stride[0] * 2};
-  uint32_t box[4] = {64, 128, 1, 1};
-  return make_tensor_map_bf16(m, t.ptr, 4, dims, strides, box, true);
-}
-
 template <int HD>
 int as_launch(const SafAttnStatsArgs& a, cudaStream_t st) {
   CUtensorMap mq, mk;
   int rc;
-  if ((rc = as_map4(&mq, a.q, a.B, a.U, a.T, HD))) return rc;
-  if ((rc = as_map4(&mk, a.k, a.B, a.U, a.T, HD))) return rc;
+  if ((rc = make_row_tile_map_bf16(&mq, a.q, a.B, a.U, a.T, HD))) return rc;
+  if ((rc = make_row_tile_map_bf16(&mk, a.k, a.B, a.U, a.T, HD))) return rc;
   AsParams p;
   p.B = a.B; p.U = a.U; p.T = a.T;
   p.n_tiles = (a.T + 127) / 128;
@@ -391,7 +377,7 @@ int as_launch(const SafAttnStatsArgs& a, cudaStream_t st) {
 
 int launch_attn_stats_sm100(const SafAttnStatsArgs& a, cudaStream_t st) {
   if (a.dtype != SAF_BF16 || (a.HD != 64 && a.HD != 128)) return fail(SAF_ERR_UNSUPPORTED, "attention statistics: bf16 with head_dim 64 or 128 only");
-  if (!as_tensor_ok(a.q) || !as_tensor_ok(a.k))
+  if (!tma_rows_ok(a.q) || !tma_rows_ok(a.k))
     return fail(SAF_ERR_UNSUPPORTED, "attention statistics: q, k need 16-byte aligned rows and unit last stride");
   if ((uintptr_t)a.mean & 15) return fail(SAF_ERR_INVALID, "attention statistics: mean must be 16-byte aligned");
   if (!saf_device_supported()) return fail(SAF_ERR_UNSUPPORTED, "attention statistics need an sm_100 device");

@@ -370,26 +370,12 @@ __global__ void __launch_bounds__(256) pattern_grad_generic_kernel(const PgGener
   }
 }
 
-bool pg_tensor_ok(const SafTensor& t) {
-  if (!t.ptr || ((uintptr_t)t.ptr & 15) || t.stride[3] != 1) return false;
-  for (int i = 0; i < 3; ++i)
-    if (t.stride[i] % 8 || t.stride[i] <= 0) return false;
-  return true;
-}
-
-int pg_map4(CUtensorMap* m, const SafTensor& t, int B, int Hn, int T, int HD) {
-  uint64_t dims[4] = {(uint64_t)HD, (uint64_t)T, (uint64_t)Hn, (uint64_t)B};
-  uint64_t strides[4] = {0, (uint64_t)t.stride[2] * 2, (uint64_t)t.stride[1] * 2, (uint64_t)t.stride[0] * 2};
-  uint32_t box[4] = {64, 128, 1, 1};
-  return make_tensor_map_bf16(m, t.ptr, 4, dims, strides, box, true);
-}
-
 template <int HD>
 int pg_launch_sm100(const SafPatternGradArgs& a, cudaStream_t st) {
   CUtensorMap mv, mdo;
   int rc;
-  if ((rc = pg_map4(&mv, a.v, a.B, a.H, a.T, HD))) return rc;
-  if ((rc = pg_map4(&mdo, a.dout, a.B, a.H, a.T, HD))) return rc;
+  if ((rc = make_row_tile_map_bf16(&mv, a.v, a.B, a.H, a.T, HD))) return rc;
+  if ((rc = make_row_tile_map_bf16(&mdo, a.dout, a.B, a.H, a.T, HD))) return rc;
   PgDeltaParams d;
   d.B = a.B; d.H = a.H; d.T = a.T; d.HD = HD;
   d.force_state = a.force_state;
@@ -463,8 +449,8 @@ int launch_pattern_grad(const SafPatternGradArgs& a, cudaStream_t st) {
     for (int h = 0; h < a.H; ++h) any |= a.frozen_host[h] == SAF_DECOMP;
     if (!any) return SAF_OK;
   }
-  const bool tc = a.dtype == SAF_BF16 && (a.HD == 64 || a.HD == 128) && pg_tensor_ok(a.v) && pg_tensor_ok(a.dout) &&
-                  pg_tensor_ok(a.out) && a.delta && saf_device_supported();   // the pre-pass reads out / dout as bf16 pairs
+  const bool tc = a.dtype == SAF_BF16 && (a.HD == 64 || a.HD == 128) && tma_rows_ok(a.v) && tma_rows_ok(a.dout) &&
+                  tma_rows_ok(a.out) && a.delta && saf_device_supported();   // the pre-pass reads out / dout as bf16 pairs
   if (tc) return a.HD == 64 ? pg_launch_sm100<64>(a, st) : pg_launch_sm100<128>(a, st);
   return pg_launch_generic(a, st);
 }

@@ -74,4 +74,9 @@ TensorMapEncodeFn tensor_map_encoder();
 int make_tensor_map_bf16(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
                          const uint64_t* strides_bytes, const uint32_t* box, bool l2_256);
 
+// a (B, Hn, T, HD) bf16 tensor that TMA can tile: 16-byte aligned base, unit last stride, other strides multiples of 8
+bool tma_rows_ok(const SafTensor& t);
+// its map with boxes of 128 rows x 64 columns (one 128-byte-swizzled atom), coordinates (column, row, head, batch)
+int make_row_tile_map_bf16(CUtensorMap* m, const SafTensor& t, int B, int Hn, int T, int HD);
+
 }  // namespace saf
