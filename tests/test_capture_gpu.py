@@ -122,3 +122,20 @@ def test_module_statistics_equal_reductions_of_the_eager_capture():
     assert O.rel_l2(acc.mean.cpu(), mean) <= 2e-2
     assert ((acc.head_m2.cpu() - m2).abs() / m2).max() <= 5e-2
     assert ((acc.neg_entropy.cpu() - negent).abs() / negent.abs()).max() <= 2e-2
+
+
+@pytest.mark.parametrize("T", [1, 37, 129])
+def test_attention_moments_small_and_ragged(T):
+    from saf_b200.capture import AttentionMoments
+    B, U, hd = 3, 2, 64
+    gen = torch.Generator().manual_seed(T)
+    q = torch.randn(B, U, T, hd, generator=gen).bfloat16()
+    k = torch.randn(B, U, T, hd, generator=gen).bfloat16()
+    att = O.attention_probs(q.double(), k.double())
+    bn, bm, b2 = O.centered_batch_reduced_moments(att)
+    acc = AttentionMoments(U, T, "cuda").update(q.cuda(), k.cuda())
+    assert acc.count == B
+    assert O.max_abs(acc.mean.cpu().double(), bm) <= 2e-3
+    assert (acc.head_m2.cpu() - b2).abs().max() <= 1e-2 * max(b2.abs().max().item(), 1e-6) + 1e-9
+    ne = O.negative_entropy_sum(att)
+    assert (acc.neg_entropy.cpu() - ne).abs().max() <= 2e-3 * max(ne.abs().max().item(), 1.0)

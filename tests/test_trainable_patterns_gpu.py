@@ -138,3 +138,37 @@ def test_enable_turns_buffers_into_parameters_and_trains():
     sd = attn.state_dict()
     zz = normalisers(attn.dyn_alpha, attn.dyn_rho, 256)
     assert torch.allclose(sd["dyn_z"][[1, 3]].float(), zz[[1, 3]].float(), atol=1e-5)
+
+
+@pytest.mark.parametrize("T", [1, 37, 129])
+def test_pattern_param_grad_small_and_ragged(T):
+    """Tiny and ragged sequences on the tensor-core path (bf16, head_dim 64) against the closed form."""
+    from saf_b200.trainable_patterns import normalisers, pattern_param_grad
+    B, H, hd, S = 2, 2, 64, 192
+    gen = torch.Generator().manual_seed(T)
+    v = torch.randn(B, H, T, hd, generator=gen).bfloat16()
+    w = torch.randn(B, H, T, hd, generator=gen).bfloat16()
+    al, rh = _vectors(H, S, T + 1)
+    z = O.pattern_normalisers(al.double(), rh.double(), T)
+    y = torch.matmul(O.decomp_pattern(al.double(), rh.double(), z, T)[None], v.double()).bfloat16()
+    da_ref, dr_ref = O.pattern_param_grads(v.double(), y.double(), w.double(), al.double(), rh.double(), z)
+    states = torch.full((H,), 2, dtype=torch.int32, device="cuda")
+    zd = normalisers(al.cuda(), rh.cuda(), T)
+    da, dr = pattern_param_grad(w.cuda(), y.cuda(), v.cuda(), al.cuda(), rh.cuda(), zd, states)
+    for got, ref in ((da, da_ref), (dr, dr_ref)):
+        a, _ = errs(got, ref)
+        assert a <= 2e-2 * max(1.0, ref.abs().max().item()), a
+    assert not da[:, T:].any() and not dr[:, T:].any()
+
+
+def test_pattern_param_grad_without_training_heads_is_zero_and_launches_nothing():
+    from saf_b200 import launch_count
+    from saf_b200.trainable_patterns import pattern_param_grad
+    B, H, T, hd, S = 1, 3, 64, 64, 64
+    v = torch.randn(B, H, T, hd, device="cuda").bfloat16()
+    al, rh = _vectors(H, S, 9)
+    states = torch.tensor([0, 1, 3], dtype=torch.int32, device="cuda")
+    n0 = launch_count()
+    da, dr = pattern_param_grad(v, v, v, al.cuda(), rh.cuda(), torch.zeros(H, S, device="cuda"), states)
+    assert launch_count() == n0
+    assert not da.any() and not dr.any()
