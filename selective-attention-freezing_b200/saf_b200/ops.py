@@ -264,6 +264,38 @@ class _FusedMixedAttn(torch.autograd.Function):
         return (dq, dk, dv) + (None,) * 11
 
 
+class _RotatedCopy(torch.autograd.Function):
+    """Rotated private copy of q or k, (B, N, T, hd) -> same shape (token-major strides), with the adjoint rotation
+    of the gradient in backward.  Used when `fused_mixed_attn(rope=)` is asked for on tensors the tensor-core
+    kernels take: they read q, k by TMA straight into the MMA operands, so the rotation happens once here instead
+    of once per (query tile, key tile) pair."""
+
+    @staticmethod
+    def _rotate(y, B, N, T, hd, cos, sin, inverse):
+        check(lib.saf_rope_slabs(y.data_ptr(), N * hd, B * T, N, hd, T, None, cos.data_ptr(), sin.data_ptr(), _dt(y),
+                                 inverse, _stream(y)))
+
+    @staticmethod
+    def forward(ctx, x, cos, sin):
+        B, N, T, hd = x.shape
+        y = x.detach().transpose(1, 2).contiguous()
+        if y.data_ptr() == x.data_ptr():
+            y = y.clone()
+        _RotatedCopy._rotate(y, B, N, T, hd, cos, sin, 0)
+        ctx.save_for_backward(cos, sin)
+        return y.transpose(1, 2)
+
+    @staticmethod
+    def backward(ctx, g):
+        cos, sin = ctx.saved_tensors
+        B, N, T, hd = g.shape
+        g2 = g.transpose(1, 2).contiguous()
+        if g2.data_ptr() == g.data_ptr():
+            g2 = g2.clone()
+        _RotatedCopy._rotate(g2, B, N, T, hd, cos, sin, 1)
+        return g2.transpose(1, 2), None, None
+
+
 def fused_mixed_attn(q, k, v, patt, frozen, hidx=None, pidx=None,
                      sm_scale=None, alpha=None, rho=None, z=None,
                      rho_band=None, validate=True, kvidx=None, *, rope=None, sink_decay=None):
@@ -276,7 +308,8 @@ def fused_mixed_attn(q, k, v, patt, frozen, hidx=None, pidx=None,
       hidx/pidx/kvidx (H,) int32 maps, alpha/rho/z (H,S); rho_band is accepted and ignored
       (these kernels index rho directly).
     Additions (keyword-only, default off):
-      rope=(cos, sin): fp32 (T,hd) tables; q and k are rotated while they are loaded.
+      rope=(cos, sin): fp32 (T,hd) tables; q and k are rotated while they are loaded (CUDA-core kernels) or once
+        into private copies ahead of the tensor-core kernels (bf16, head_dim 64 / 128).
       sink_decay=(a, r): fp32 (H,) tensors; heads with state 3 use the structured
         pattern a[j=0] + (1-a) r^(i-j)/Z_i through an O(T) scan.
     alpha / rho that require grad receive their exact gradients (z is then recomputed from them).
@@ -342,6 +375,12 @@ def fused_mixed_attn(q, k, v, patt, frozen, hidx=None, pidx=None,
             assert states is None or 2 not in states, "decomposed-frozen heads require alpha/rho/z"
         if sink_decay is None:
             assert states is None or 3 not in states, "sink-decay heads require sink_decay=(a, r)"
+    if (rope is not None and q.dtype == torch.bfloat16 and v.size(-1) in (64, 128) and q.size(1) > 0
+            and rope[0].dtype == torch.float32 and rope[0].is_contiguous() and rope[1].is_contiguous()):
+        # tensor-core kernels: rotate q, k once into private copies (see _RotatedCopy) and run without in-kernel RoPE
+        q = _RotatedCopy.apply(q, rope[0], rope[1])
+        k = _RotatedCopy.apply(k, rope[0], rope[1])
+        rope = None
     out = _FusedMixedAttn.apply(q, k, v, patt, alpha, rho, z, frozen, hidx, pidx, kvidx, sm_scale, rope,
                                 sink_decay)
     if train_patterns:

@@ -202,6 +202,27 @@ def test_rope_on_load(dtype):
     run_case(2, 12, 700, 64, 1024, [2, 5, 8], dtype=dtype, rope=True)
 
 
+def test_rope_request_reaches_the_tensor_core_kernels():
+    """bf16 q, k with rope=: two rotated private copies + one mixed launch (not the CUDA-core kernel), same numbers."""
+    from kernel import fused_mixed_attn
+    from saf_b200 import launch_count
+    run_case(1, 8, 512, 128, 512, [1, 6], dtype=torch.bfloat16, rope=True)
+    B, U, T, hd = 2, 3, 384, 64
+    g = torch.Generator().manual_seed(11)
+    q = torch.randn(B, U, T, hd, generator=g).bfloat16().cuda()
+    k = torch.randn(B, U, T, hd, generator=g).bfloat16().cuda()
+    v = torch.randn(B, U, T, hd, generator=g).bfloat16().cuda()
+    cos, sin = O.rope_cache(hd, T)
+    frozen = torch.zeros(U, dtype=torch.int32, device="cuda")
+    n0 = launch_count()
+    y = fused_mixed_attn(q, k, v, None, frozen, rope=(cos.cuda(), sin.cuda()), validate=False)
+    assert launch_count() - n0 == 3
+    ref = O.mixed_attn(O.apply_rope(q.float().cpu(), cos, sin), O.apply_rope(k.float().cpu(), cos, sin),
+                       v.float().cpu(), None, [0] * U)
+    a, r = errs(y, ref)
+    assert a <= BF16_FWD_ABS and r <= BF16_FWD_REL
+
+
 def test_head_dim_128():
     run_case(2, 8, 512, 128, 512, [1, 6], dtype=torch.bfloat16)
     run_case(1, 8, 300, 128, 512, [1, 6], dtype=torch.float32)
