@@ -61,13 +61,13 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Wall-clock budget of one wait.  A healthy kernel never comes near it; a
+// Wall-clock limit of one wait.  A healthy kernel never comes near it; a
 // protocol bug ends the kernel with an error word instead of hanging the GPU.
 #ifndef SAF_WAIT_LIMIT_NS
 #define SAF_WAIT_LIMIT_NS 2000000000ull
 #endif
 
-// Bounded wait.  Returns false when the budget ran out (caller must bail out:
+// Bounded wait.  Returns false when the limit was reached (caller must bail out:
 // record the error, stop issuing work and fall through to the teardown).
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
   // the clock is read only after many failed polls: a healthy wait never pays for it
