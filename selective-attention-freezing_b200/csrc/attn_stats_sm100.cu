@@ -222,11 +222,16 @@ attn_stats_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
       const int gj0 = x.jt * 128 + cb;
       const bool diag = (x.it == x.jt);
       const float* lse_u = p.lse + (int64_t)x.u * p.lse_s[1] + (int64_t)gi * p.lse_s[2];
-      float mean[32], m2[32];
+      // The running batch mean of the tile lives in the padded staging tile (each thread owns 32 cells of its row
+      // until the tile is finished), the centred squares in registers: that leaves room to fetch a sample's 32
+      // scores in one TMEM load and to hand the buffer back before the arithmetic.
+      float m2[32];
 #pragma unroll
-      for (int c = 0; c < 32; ++c) mean[c] = m2[c] = 0.f;
+      for (int c = 0; c < 32; ++c) m2[c] = 0.f;
+      float* srow = stage + r * C::STAGE_LD + cb;
       float ent = 0.f;                                // sum p log2 p of this thread's cells
       float nl = row_ok ? lse_u[0] : INFINITY;        // +inf: rows past T hold zeros
+      named_bar_sync(2, AS_COMPUTE);                  // the previous tile's rows have left the staging tile
       for (int b = 0; b < p.B; ++b, ++g) {
         const int k = g & 1;
         const float L = nl;
@@ -237,43 +242,40 @@ attn_stats_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
           break;
         }
         tc_fence_after();
+        uint32_t d[32];
+        tmem_ld32(tmem + lane_base + k * 128 + cb, d);
+        tmem_ld_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sh->s_empty[k]);
         const float inv = 1.f / (float)(b + 1);
 #pragma unroll
-        for (int hf = 0; hf < 2; ++hf) {
-          uint32_t d[16];
-          tmem_ld16(tmem + lane_base + k * 128 + cb + hf * 16, d);
-          tmem_ld_wait();
+        for (int c4 = 0; c4 < 8; ++c4) {
+          float4 mv = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (b > 0) mv = *reinterpret_cast<const float4*>(srow + c4 * 4);
+          float mm[4] = {mv.x, mv.y, mv.z, mv.w};
 #pragma unroll
-          for (int xx = 0; xx < 16; ++xx) {
-            const int c = hf * 16 + xx;
-            float xl = fmaf(__uint_as_float(d[xx]), sc, -L);           // log2 of the probability
+          for (int e = 0; e < 4; ++e) {
+            const int c = c4 * 4 + e;
+            float xl = fmaf(__uint_as_float(d[c]), sc, -L);             // log2 of the probability
             if (diag && gj0 + c > gi) xl = -INFINITY;                   // causal mask inside the diagonal tile
             const float pe = as_ex2(xl);
             ent = fmaf(pe, fmaxf(xl, -200.f), ent);                     // p = 0 there, so the clamp only avoids 0 * inf
             // Welford update of the cell's mean and centred sum of squares over the batch
-            const float dlt = pe - mean[c];
-            mean[c] = fmaf(dlt, inv, mean[c]);
-            m2[c] = fmaf(dlt, pe - mean[c], m2[c]);
+            const float dlt = pe - mm[e];
+            mm[e] = fmaf(dlt, inv, mm[e]);
+            m2[c] = fmaf(dlt, pe - mm[e], m2[c]);
           }
+          *reinterpret_cast<float4*>(srow + c4 * 4) = make_float4(mm[0], mm[1], mm[2], mm[3]);
         }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&sh->s_empty[k]);
       }
       if (!ok) break;
-      // ---- merge the tile into the running mean (Chan).  A thread holds 32 cells of one row; written from here the
-      // rows of a warp would be 32 separate 16-byte pieces per instruction, so the tile goes through shared memory
-      // and every warp then moves whole 512-byte rows.
-      named_bar_sync(2, AS_COMPUTE);                  // the previous tile's rows have left the staging tile
-      {
-        float* srow = stage + r * C::STAGE_LD + cb;
+      // ---- merge the tile into the running mean (Chan).  A thread holds 32 cells of one row; written from there the
+      // rows of a warp would be 32 separate 16-byte pieces per instruction, so every warp now takes whole 512-byte
+      // rows out of the staging tile.
 #pragma unroll
-        for (int c4 = 0; c4 < 8; ++c4) {
-          *reinterpret_cast<float4*>(srow + c4 * 4) =
-              make_float4(mean[c4 * 4], mean[c4 * 4 + 1], mean[c4 * 4 + 2], mean[c4 * 4 + 3]);
-          m2sum += (double)(m2[c4 * 4] + m2[c4 * 4 + 1]) + (double)(m2[c4 * 4 + 2] + m2[c4 * 4 + 3]);
-        }
-      }
+      for (int c4 = 0; c4 < 8; ++c4)
+        m2sum += (double)(m2[c4 * 4] + m2[c4 * 4 + 1]) + (double)(m2[c4 * 4 + 2] + m2[c4 * 4 + 3]);
       // the old rows are requested before the barrier (the accumulators are dead by now), so their latency and the
       // wait for the slowest warp overlap
       double corr = 0.0;
