@@ -5,7 +5,7 @@
 // (nanogpt/dynamic_freeze.py:96-127 _centered_batch_reduced_moments, :130-143 _merge_reduced_moments,
 // :146-173 _negative_entropy_sum, used by _measure :629-745).  Here a CTA takes one 128 x 128 cell tile of one head
 // at a time and walks the batch: S_b = Q_b K_b^T on tcgen05 into TMEM, P_b = exp2(S_b scale - lse_b) with the row
-// log-sum-exp of the flash forward, per-cell Welford mean / M2 in registers, then the tile of the running mean is
+// log-sum-exp of the flash forward, per-cell Welford mean (staging tile) / M2 (registers), then the tile of the running mean is
 // Chan-merged in place and the per-head scalars are reduced to one double atomic per CTA.
 //
 //   warps 0-15: four warpgroups x 32 key columns, thread = query row (TMEM lane)
