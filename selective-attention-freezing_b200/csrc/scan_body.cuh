@@ -304,7 +304,7 @@ __global__ void __launch_bounds__(SCAN_NT) sink_decay_scan_kernel(const __grid_c
 //   pass 3  every chunk: scan with its carry, outputs written                 (reads V again, writes Y)
 // 3/2 of the sequential scan's bytes, but nf*B*T/chunk CTAs instead of nf*B: bounded by HBM, not by latency.
 template <typename T, int MODE>
-__global__ void __launch_bounds__(SCAN_NT) sink_decay_chunk_kernel(const __grid_constant__ ScanArgs a, int chunk) {
+__global__ void __launch_bounds__(SCAN_NT, 2) sink_decay_chunk_kernel(const __grid_constant__ ScanArgs a, int chunk) {
   const int bh = blockIdx.x, b = bh / a.H, h = bh % a.H;
   const int state = a.force_state >= 0 ? a.force_state : a.frozen[h];
   if (state != SAF_SINK_DECAY) return;

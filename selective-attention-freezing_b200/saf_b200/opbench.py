@@ -108,6 +108,7 @@ def main():
     fl_qk = 2.0 * B * T * C * 2 * U * hd
     shape = f"B{B} T{T} H{H}{'/kv%d' % n_kv if gqa else ''} hd{hd} live{U} frozen{nf}({args.frozen})"
     for op in args.ops.split(","):
+        extra = {}
         if op == "attn_fwd":
             with torch.no_grad():
                 n0 = ops.launch_count()
@@ -144,6 +145,40 @@ def main():
                 y.backward(dqk, retain_graph=True)
             ms = _timed(run, args.reps)
             fl = 2.0 * fl_qk
+        elif op in ("frozen_pv", "frozen_pv_bwd"):
+            # the frozen heads alone through frozen_pv: scan for sink+decay patterns (HBM-bound: V read + Y written),
+            # lower-triangular GEMM for dense stored ones
+            assert nf and args.frozen in ("sink_decay", "dense"), "frozen_pv needs --frozen sink_decay or dense"
+            vf = v.detach()[:, fz].contiguous().requires_grad_(op == "frozen_pv_bwd")
+            if args.frozen == "sink_decay":
+                sd = (kw["sink_decay"][0][fz].contiguous(), kw["sink_decay"][1][fz].contiguous())
+
+                def fpv():
+                    return ops.frozen_pv(None, vf, None, T, sink_decay=sd)
+            else:
+                fidx = torch.arange(nf, dtype=torch.int32, device=dev)
+
+                def fpv():
+                    return ops.frozen_pv(patt, vf, fidx, T)
+            if op == "frozen_pv":
+                with torch.no_grad():
+                    n0 = ops.launch_count()
+                    fpv()
+                    n = ops.launch_count() - n0
+                    ms = _timed(fpv, args.reps)
+            else:
+                yf = fpv()
+                dyf = dy[:, fz].contiguous()
+                n0 = ops.launch_count()
+                yf.backward(dyf, retain_graph=True)
+                n = ops.launch_count() - n0
+
+                def run():
+                    vf.grad = None
+                    yf.backward(dyf, retain_graph=True)
+                ms = _timed(run, args.reps)
+            fl = 1.0 * B * nf * T * T * hd if args.frozen == "dense" else 0.0
+            extra["gbs"] = round(B * nf * T * hd * 2 * 2 / ms / 1e6, 1)      # values read + result written
         elif op == "pattern_grad":
             # parameter gradients of the decomposed heads (needs --frozen decomposed): dS = P (dO V^T - delta)
             from saf_b200.trainable_patterns import pattern_param_grad
@@ -237,7 +272,7 @@ def main():
         else:
             raise SystemExit("unknown op %r" % op)
         print(json.dumps({"op": op, "shape": shape, "ms": round(ms, 4), "tflops": round(fl / ms / 1e9, 1),
-                          "launches": n}), flush=True)
+                          "launches": n, **extra}), flush=True)
 
 
 def print_trace():
