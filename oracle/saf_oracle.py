@@ -12,7 +12,11 @@ itself (its eager ``CausalSelfAttention`` capture path, its cheap split path,
 all of which run on CPU) and stores their outputs on seeded inputs under
 ``tests/golden/``; ``tests/test_oracle_golden.py`` checks every function below
 against those vectors.  The GQA ``kvidx`` variant has no test in the reference;
-it is pinned against the reference's eager formula with repeated KV heads.
+``tests/golden/make_golden_gqa.py`` runs the reference's own Qwen3 hybrid
+attention module (its split torch path, qwen/nanogpt/hybrid_prior_attention.py:
+586-640) on a random-init HF ``Qwen3Attention`` and stores inputs, intermediate
+q/k/v and outputs in ``tests/golden/gqa_vectors.npz``, which pin ``mixed_attn(kvidx=)``
+and ``gqa_attention_layer``.
 
 Each function cites the reference file:line it follows (paths are relative to
 the reference project root).
@@ -138,48 +142,75 @@ def decomp_pattern(alpha, rho, z, T):
 # mixed attention                     nanogpt/model.py:824-844 (eager oracle),
 #                                     kernel/test_fused_attn.py:53-63 (ref())
 # ---------------------------------------------------------------------------
+def sink_decay_rows(a, r, rows, n_cols, dtype=torch.float64, device=None):
+    """Rows `rows` (1-D long tensor) of sink_decay_pattern(a, r) for ONE head, columns [0, n_cols): the
+    same formula evaluated without the T x T matrix (what freeze_heads stores for that head, row by row,
+    nanogpt/model.py:705-733)."""
+    i = rows.to(device=device, dtype=dtype)[:, None]
+    j = torch.arange(n_cols, dtype=dtype, device=device)[None, :]
+    dist = i - j
+    rr = torch.tensor(float(r), dtype=dtype, device=device)
+    dec = torch.where(dist >= 0, rr ** dist.clamp(min=0), torch.zeros((), dtype=dtype, device=device))
+    dec = dec / dec.sum(-1, keepdim=True) * (1.0 - float(a))
+    dec[:, 0] += float(a)
+    return dec
+
+
 def mixed_attn(q, k, v, patt, frozen, hidx=None, pidx=None, sm_scale=None,
                alpha=None, rho=None, z=None, kvidx=None, dtype=torch.float32,
-               row_chunk=1024):
+               row_chunk=1024, rows=None, sink_decay=None):
     """Eager mixed attention, one (batch, head) and one row chunk at a time.
 
     q, k: (B, U, T, hd) compact live heads (or (B, HKV, T, hd) k with kvidx);
     v: (B, H, T, hd) (or (B, HKV, T, hd) with kvidx); frozen: (H,) ints with
     0 = live softmax(q k^T * sm_scale) v, 1 = patt[pidx[h] or h, :T, :T] @ v,
-    2 = exp(alpha[j] + rho[i-j] - z[i]) @ v.  Returns (B, H, T, hd) in `dtype`.
-    Differentiable w.r.t. q, k, v (autograd gives the backward oracle).
+    2 = exp(alpha[j] + rho[i-j] - z[i]) @ v, 3 = the dense pattern
+    sink_decay_pattern(a[h], r[h]) @ v with sink_decay = (a, r) per head (a state-1
+    head whose stored rows are produced on the fly).  Returns (B, H, T, hd) in `dtype`;
+    with rows = 1-D long tensor of query positions, only those rows: (B, H, len(rows), hd).
+    Runs on the device of v.  Differentiable w.r.t. q, k, v (autograd gives the backward oracle).
     """
     frozen = [int(x) for x in torch.as_tensor(frozen).tolist()]
     H = len(frozen)
     B, T, hd = v.shape[0], v.shape[2], v.shape[3]
+    dev = v.device
     if sm_scale is None:
         sm_scale = 1.0 / math.sqrt(hd)
     hidx = list(range(H)) if hidx is None else [int(x) for x in torch.as_tensor(hidx).tolist()]
     pidx = list(range(H)) if pidx is None else [int(x) for x in torch.as_tensor(pidx).tolist()]
     kv = None if kvidx is None else [int(x) for x in torch.as_tensor(kvidx).tolist()]
-    ar = torch.arange(T)
+    if rows is None:
+        chunks = [torch.arange(i0, min(i0 + row_chunk, T), device=dev) for i0 in range(0, T, row_chunk)]
+    else:
+        rows = torch.as_tensor(rows, dtype=torch.long, device=dev)
+        chunks = [rows[i0:i0 + row_chunk] for i0 in range(0, rows.numel(), row_chunk)]
     outs = []
     for b in range(B):
         per_head = []
         for h in range(H):
             vh = v[b, kv[h] if kv is not None else h].to(dtype)
-            rows = []
-            for i0 in range(0, T, row_chunk):
-                i1 = min(i0 + row_chunk, T)
+            acc = []
+            for ri in chunks:
+                i1 = int(ri.max().item()) + 1          # keys past the chunk's last row are masked for every row
+                cols = torch.arange(i1, device=dev)
                 if frozen[h] == 0:
-                    qh = q[b, hidx[h], i0:i1].to(dtype)
+                    qh = q[b, hidx[h]].index_select(0, ri).to(dtype)
                     kh = k[b, kv[h] if kv is not None else hidx[h], :i1].to(dtype)
                     s = (qh @ kh.t()) * sm_scale
-                    mask = ar[i0:i1, None] >= ar[None, :i1]
-                    p = s.masked_fill(~mask, float("-inf")).softmax(-1)
+                    p = s.masked_fill(ri[:, None] < cols[None, :], float("-inf")).softmax(-1)
                 elif frozen[h] == 1:
-                    p = patt[pidx[h], i0:i1, :i1].to(dtype)
+                    p = patt[pidx[h]].index_select(0, ri.to(patt.device))[:, :i1].to(device=dev, dtype=dtype)
+                elif frozen[h] == 3:
+                    p = sink_decay_rows(float(sink_decay[0][h]), float(sink_decay[1][h]), ri, i1,
+                                        dtype=torch.float64, device=dev).to(dtype)
                 else:
-                    lg = decomp_logits(alpha[h:h + 1, :T].to(dtype), rho[h:h + 1, :T].to(dtype),
-                                       rows=(i0, i1))[0, :, :i1]
-                    p = torch.exp(lg - z[h, i0:i1, None].to(dtype))
-                rows.append(p @ vh[:i1])
-            per_head.append(torch.cat(rows, 0))
+                    dist = ri[:, None] - cols[None, :]
+                    lg = alpha[h, :i1].to(device=dev, dtype=dtype)[None, :] + \
+                        rho[h].to(device=dev, dtype=dtype)[dist.clamp(min=0)]
+                    lg = lg.masked_fill(dist < 0, float("-inf"))
+                    p = torch.exp(lg - z[h].to(device=dev, dtype=dtype).index_select(0, ri)[:, None])
+                acc.append(p @ vh[:i1])
+            per_head.append(torch.cat(acc, 0))
         outs.append(torch.stack(per_head))
     return torch.stack(outs)
 
@@ -232,11 +263,12 @@ def linear_permuted_cols(y, weight, bias, cols):
 # one attention layer (the module hook)     nanogpt/model.py:1063-1077, 824-844
 # ---------------------------------------------------------------------------
 def attention_layer(x, wq, wk, wv, wo, frozen, patt, n_head, rope=None, alpha=None, rho=None,
-                    z=None, dtype=torch.float32, row_chunk=1024, pidx=None):
+                    z=None, dtype=torch.float32, row_chunk=1024, pidx=None, rows=None, sink_decay=None):
     """Eager capture path of the reference's CausalSelfAttention in dynamic mode:
     full q/k/v projections, RoPE on q,k, softmax for live heads and stored pattern
     for frozen ones, then c_proj.  x: (B,T,C); w*: (C,C) in F.linear layout.
-    `frozen`: (H,) ints 0/1/2; patt: (H,S,S) or None.  rope = (cos, sin) (T,hd)."""
+    `frozen`: (H,) ints 0/1/2/3 (see mixed_attn); patt: (H,S,S) or None.  rope = (cos, sin) (T,hd).
+    rows = query positions to evaluate (all when None): the result is then (B, len(rows), C)."""
     B, T, C = x.shape
     hd = C // n_head
     x = x.to(dtype)
@@ -246,8 +278,54 @@ def attention_layer(x, wq, wk, wv, wo, frozen, patt, n_head, rope=None, alpha=No
     if rope is not None:
         cos, sin = rope[0].to(dtype), rope[1].to(dtype)
         q, k = apply_rope(q, cos, sin), apply_rope(k, cos, sin)
-    y = mixed_attn(q, k, v, patt, frozen, pidx=pidx, alpha=alpha, rho=rho, z=z, dtype=dtype, row_chunk=row_chunk)
-    y = y.transpose(1, 2).reshape(B, T, C)
+    y = mixed_attn(q, k, v, patt, frozen, pidx=pidx, alpha=alpha, rho=rho, z=z, dtype=dtype, row_chunk=row_chunk,
+                   rows=rows, sink_decay=sink_decay)
+    y = y.transpose(1, 2).reshape(B, y.shape[2], C)
+    return y @ wo.to(dtype).t()
+
+
+# ---------------------------------------------------------------------------
+# GQA layer (Qwen3-style)      qwen/nanogpt/hybrid_prior_attention.py:530-640
+# ---------------------------------------------------------------------------
+def rms_norm_heads(x, weight, eps=1e-6):
+    """Per-head RMSNorm over the last dim, as the q_norm / k_norm the reference adopts from the HF module
+    (hybrid_prior_attention.py:522-523; transformers Qwen3RMSNorm: x * rsqrt(mean(x^2) + eps) * weight,
+    statistics in fp32)."""
+    xf = x.float()
+    xf = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
+    return weight * xf.to(x.dtype)
+
+
+def gqa_attention_layer(x, wq_std, wk, wv, wo, frozen, hidx, pidx, kvidx, patt, cos, sin, sm_scale,
+                        q_norm_w=None, k_norm_w=None, eps=1e-6, alpha=None, rho=None, z=None,
+                        dtype=torch.float32, row_chunk=1024, rows=None, sink_decay=None):
+    """The reference's Qwen3 hybrid attention (hybrid_prior_attention.py:530-584 fused call,
+    :586-640 split path; both give the same function): K, V for the HKV raw heads, Q for the live
+    ("standard") heads only through the shrunken projection, per-head RMSNorm on q and k when their
+    weights are given, RoPE on q and k, query head h reads KV head kvidx[h], frozen heads apply their
+    pattern to V[kvidx[h]], then o_proj.  x (B,T,C); wq_std (n_std*hd, C); wk, wv (HKV*hd, C);
+    wo (C, H*hd); cos, sin (T, hd)."""
+    B, T, C = x.shape
+    H = len([int(t) for t in torch.as_tensor(frozen).tolist()])
+    hd = wk.shape[0] // (int(torch.as_tensor(kvidx).max().item()) + 1)
+    hkv = wk.shape[0] // hd
+    n_std = wq_std.shape[0] // hd if wq_std is not None else 0
+    x = x.to(dtype)
+    k = (x @ wk.to(dtype).t()).view(B, T, hkv, hd)
+    v = (x @ wv.to(dtype).t()).view(B, T, hkv, hd).transpose(1, 2)
+    if k_norm_w is not None:
+        k = rms_norm_heads(k, k_norm_w.to(dtype), eps)
+    k = apply_rope(k.transpose(1, 2), cos.to(dtype), sin.to(dtype))
+    if n_std:
+        q = (x @ wq_std.to(dtype).t()).view(B, T, n_std, hd)
+        if q_norm_w is not None:
+            q = rms_norm_heads(q, q_norm_w.to(dtype), eps)
+        q = apply_rope(q.transpose(1, 2), cos.to(dtype), sin.to(dtype))
+    else:
+        q = v[:, :0]
+    y = mixed_attn(q, k, v, patt, frozen, hidx=hidx, pidx=pidx, kvidx=kvidx, sm_scale=sm_scale, alpha=alpha,
+                   rho=rho, z=z, dtype=dtype, row_chunk=row_chunk, rows=rows, sink_decay=sink_decay)
+    y = y.transpose(1, 2).reshape(B, y.shape[2], H * hd)
     return y @ wo.to(dtype).t()
 
 

@@ -177,3 +177,64 @@ def test_controller_statistics():
         assert O.max_abs(m2, g(f"st_m2_{bi}")) <= 1e-5
         assert O.max_abs(negent, g(f"st_negent{bi}")) <= 1e-4
     assert O.max_abs(O.mean_forward_kl(negent, mean.float(), count), g("st_kl")) <= 1e-5
+
+
+# ---- grouped-query variant: vectors from the reference's own Qwen3 hybrid attention module (split torch path) ----
+GQ = np.load(os.path.join(os.path.dirname(__file__), "golden", "gqa_vectors.npz"))
+
+
+def gq(case, name):
+    return torch.from_numpy(GQ[f"gqa_{case}_{name}"])
+
+
+def gqa_prior(case):
+    if case == "dense":
+        return dict(patt=gq(case, "patt"))
+    return dict(patt=None, alpha=gq(case, "alpha"), rho=gq(case, "rho"), z=gq(case, "z"))
+
+
+@pytest.mark.parametrize("case", ["dense", "decomp"])
+def test_gqa_operator_matches_reference_module(case):
+    """mixed_attn(kvidx=) on the exact q, k, v the reference module hands to its fused call, then its o_proj,
+    equals the module's own (split torch path) output."""
+    pr = gqa_prior(case)
+    y = O.mixed_attn(gq(case, "q"), gq(case, "k"), gq(case, "v"), pr.pop("patt"), gq(case, "frozen_mask_i32"),
+                     hidx=gq(case, "hidx_i32"), pidx=gq(case, "pidx_i32"), kvidx=gq(case, "kvidx_i32"),
+                     sm_scale=float(GQ[f"gqa_{case}_scaling"][0]), **pr)
+    B, H, T, hd = y.shape
+    out = y.transpose(1, 2).reshape(B, T, H * hd) @ gq(case, "wo").t()
+    assert O.max_abs(out, gq(case, "y")) <= 2e-6
+    # sampled rows give the same numbers as the full evaluation
+    rows = torch.tensor([0, 1, 37, 63, 64, 99])
+    pr = gqa_prior(case)
+    ys = O.mixed_attn(gq(case, "q"), gq(case, "k"), gq(case, "v"), pr.pop("patt"), gq(case, "frozen_mask_i32"),
+                      hidx=gq(case, "hidx_i32"), pidx=gq(case, "pidx_i32"), kvidx=gq(case, "kvidx_i32"),
+                      sm_scale=float(GQ[f"gqa_{case}_scaling"][0]), rows=rows, **pr)
+    assert O.max_abs(ys, y[:, :, rows]) <= 1e-6
+
+
+@pytest.mark.parametrize("case", ["dense", "decomp"])
+def test_gqa_layer_matches_reference_module(case):
+    """The whole layer restated (projections, per-head RMSNorm, RoPE base 1e6, kvidx attention, o_proj)."""
+    pr = gqa_prior(case)
+    y = O.gqa_attention_layer(gq(case, "x"), gq(case, "wq_std"), gq(case, "wk"), gq(case, "wv"), gq(case, "wo"),
+                              gq(case, "frozen_mask_i32"), gq(case, "hidx_i32"), gq(case, "pidx_i32"),
+                              gq(case, "kvidx_i32"), pr.pop("patt"), gq(case, "cos"), gq(case, "sin"),
+                              float(GQ[f"gqa_{case}_scaling"][0]), q_norm_w=gq(case, "q_norm"),
+                              k_norm_w=gq(case, "k_norm"), eps=float(GQ[f"gqa_{case}_eps"][0]), **pr)
+    assert O.max_abs(y, gq(case, "y")) <= 3e-6
+
+
+def test_sampled_rows_and_structured_state_match_full_evaluation():
+    """rows= and state 3 (pattern rows produced on the fly) agree with the dense state-1 evaluation that the
+    reference-generated layer vectors pin."""
+    B, H, T, hd = 1, 4, 150, 16
+    gq_ = torch.Generator().manual_seed(5)
+    q, k, v = [torch.randn(B, H, T, hd, generator=gq_) for _ in range(3)]
+    a, r = O.sink_decay_params(H, 9)
+    patt = O.sink_decay_pattern(a, r, T).float()
+    full = O.mixed_attn(q, k, v, patt, [0, 1, 0, 1])
+    struct = O.mixed_attn(q, k, v, None, [0, 3, 0, 3], sink_decay=(a, r))
+    assert O.max_abs(struct, full) <= 1e-6
+    rows = torch.tensor([0, 5, 64, 127, 128, 149])
+    assert O.max_abs(O.mixed_attn(q, k, v, None, [0, 3, 0, 3], sink_decay=(a, r), rows=rows), full[:, :, rows]) <= 1e-6
