@@ -15,9 +15,13 @@ data-path collective).  Prints ONE JSON line on rank 0.
              duration measured with event pairs inside the timed steps, against the measured dense bf16 peak
   cpu_baseline  the CPU restatement of the reference's eager path on the host cores, bounded sample
 
---impl reference times that CPU restatement as the whole run (the reference project itself is Python +
-Triton and cannot travel to a box without its source tree; oracle/saf_oracle.py is pinned to it by
-tests/golden).
+  parity     layer 0 of the stack on one sequence of the step's own input, sampled query rows against the CPU
+             oracle (computed after the timed regions)
+
+--impl reference times that CPU restatement as the whole run: every step is the full 12-layer stack on ONE
+sequence of the batch on the host cores (the reference project itself is Python + Triton and cannot travel to a
+box without its source tree; oracle/saf_oracle.py is pinned to it by tests/golden).  That arm never imports the
+CUDA library.
 """
 import argparse
 import json
@@ -33,9 +37,29 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.join(ROOT, "selective-attention-freezing_b200"))
 
 METRIC = "prefill tokens/s, SAF-25% 124M @16K ctx (attention+projection stack)"
-# DRAM bytes per launch of the mixed-attention kernel at the c2 shape (dram__bytes_read.sum + dram__bytes_write.sum
-# of the ncu capture summarised in profiles/flash_fwd_hd64_c2.md); other workloads report null
-ATTN_TRAFFIC_BYTES = {"c2": 279262208 + 86932736}
+
+
+def load_workloads():
+    """The workload table, read by path so that the CPU reference arm does not import the package (and with it
+    the CUDA library)."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location(
+        "saf_b200_workloads", os.path.join(ROOT, "selective-attention-freezing_b200", "saf_b200", "workloads.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod.WORKLOADS
+
+
+def attention_traffic_bytes(workload):
+    """DRAM bytes per launch of the mixed-attention kernel (dram__bytes_read.sum + dram__bytes_write.sum of one ncu
+    capture), from the record the profiling step leaves beside its summary; None when there is none."""
+    path = os.path.join(ROOT, "profiles", "mixed_attention_traffic.json")
+    try:
+        with open(path) as f:
+            rec = json.load(f).get(workload)
+        return None if rec is None else int(rec["dram_bytes_read"]) + int(rec["dram_bytes_write"])
+    except (OSError, ValueError, KeyError):
+        return None
 
 
 def measured_peaks():
@@ -43,8 +67,8 @@ def measured_peaks():
     if os.path.exists(path):
         with open(path) as f:
             d = json.load(f)
-        return d["bf16_tflops_sustained"], d["hbm_gbs"], "measured"
-    return 1400.0, 6650.0, "fallback"
+        return d["bf16_tflops_sustained"], d["bf16_tflops"], d["hbm_gbs"], "measured"
+    return 1400.0, 1590.0, 6650.0, "fallback"
 
 
 class ClockSampler:
@@ -90,50 +114,81 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
+class CpuStack:
+    """The CPU restatement of the reference's eager attention layers for one workload: per-layer weights drawn
+    exactly as the CUDA arm draws them, seeded frozen-head sets, dense stored patterns for the frozen heads
+    (what the reference holds for this pattern family).  One dense (n_frozen, T, T) fp32 pattern buffer is built
+    once and shared by all layers (each layer addresses it through pidx; every layer reads the same number of
+    pattern bytes as it would from its own), which bounds host memory at T=16384."""
+
+    def __init__(self, w, n_layer, seed=1337):
+        from oracle import saf_oracle as O
+        self.O, self.w = O, w
+        self.cores = os.cpu_count() or 1
+        torch.set_num_threads(self.cores)
+        T, H, hd, nf = w["T"], w["n_head"], w["head_dim"], w["n_frozen"]
+        C = H * hd
+        g = torch.Generator().manual_seed(seed)
+        self.layers = []
+        for li in range(n_layer):
+            ws = [torch.randn(C, C, generator=g) * 0.02 for _ in range(4)]
+            fz = O.frozen_heads_for_layer(H, nf, seed, li)
+            states = [1 if h in fz else 0 for h in range(H)]
+            pidx = [fz.index(h) if h in fz else 0 for h in range(H)]
+            self.layers.append((ws, states, pidx))
+        a, r = O.sink_decay_params(nf, seed + 1000)
+        rows = torch.arange(T)
+        self.patt = torch.stack([torch.cat([O.sink_decay_rows(a[i], r[i], rows[i0:i0 + 1024], T, dtype=torch.float32)
+                                            for i0 in range(0, T, 1024)]) for i in range(nf)])
+        self.rope = O.rope_cache(hd, T, base=w["rope_base"])
+        self.x = torch.randn(1, T, C, generator=torch.Generator().manual_seed(1000))
+
+    def step(self):
+        """x -> layer_L(... layer_1(x)) on one sequence; returns seconds."""
+        w = self.w
+        t0 = time.perf_counter()
+        h = self.x
+        with torch.no_grad():
+            for ws, states, pidx in self.layers:
+                h = self.O.attention_layer(h, *ws, states, self.patt, w["n_head"], rope=self.rope, row_chunk=2048,
+                                           pidx=pidx)
+        return time.perf_counter() - t0
+
+
 def cpu_reference_sample(w, steps, warmup):
-    """CPU restatement of the reference's eager attention layer on the host cores: one layer of the
-    workload at batch 1 and full sequence length per step; tokens/s is scaled to the full stack."""
-    from oracle import saf_oracle as O
-    cores = os.cpu_count() or 1
-    torch.set_num_threads(cores)
-    T, H, hd, nf = w["T"], w["n_head"], w["head_dim"], w["n_frozen"]
-    C = H * hd
-    g = torch.Generator().manual_seed(1337)
-    x = torch.randn(1, T, C, generator=g)
-    ws = [torch.randn(C, C, generator=g) * 0.02 for _ in range(4)]
-    fz = O.frozen_heads_for_layer(H, nf, 1337, 0)
-    a, r = O.sink_decay_params(nf, 2337)
-    states = [1 if h in fz else 0 for h in range(H)]
-    patt = O.sink_decay_pattern(a, r, T, dtype=torch.float32)      # compact (nf, T, T), addressed through pidx
-    pidx = [fz.index(h) if h in fz else 0 for h in range(H)]
-    rope = O.rope_cache(hd, T)
-    times = []
-    with torch.no_grad():
-        for i in range(warmup + steps):
-            t0 = time.perf_counter()
-            O.attention_layer(x, *ws, states, patt, H, rope=rope, row_chunk=2048, pidx=pidx)
-            dt = time.perf_counter() - t0
-            if i >= warmup:
-                times.append(dt)
+    """Bounded CPU sample beside the GPU number: one layer of the workload at batch 1 and full sequence length per
+    run; tokens/s is scaled to the full stack (stated in `sample`)."""
+    st = CpuStack(w, 1)
+    times = [st.step() for _ in range(warmup + steps)][warmup:]
     t_layer = statistics.median(times)
-    tok_s = T / (t_layer * w["n_layer"])
-    sample = (f"1 of {w['n_layer']} layers, batch 1 of {w['B']}, T={T}, fp32 torch-eager restatement "
+    tok_s = w["T"] / (t_layer * w["n_layer"])
+    sample = (f"1 of {w['n_layer']} layers, batch 1 of {w['B']}, T={w['T']}, fp32 torch-eager restatement "
               f"(dense stored pattern for frozen heads); median of {steps} runs, x{w['n_layer']} layers")
-    return tok_s, t_layer, cores, sample
+    return tok_s, t_layer, st.cores, sample
 
 
 def run_reference(args, w):
+    """CPU arm: each step is the whole stack (all layers) on one sequence of the batch.  The step count follows
+    --steps but is cut so that the run ends within a few minutes; the line reports the steps actually timed."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    steps, warmup = max(1, min(args.steps, 3)), min(args.warmup, 1)
-    tok_s, t_layer, cores, sample = cpu_reference_sample(w, steps, warmup)
+    budget_s = float(os.environ.get("SAF_BENCH_REFERENCE_BUDGET_S", "240"))
+    st = CpuStack(w, w["n_layer"])
+    t_first = st.step()                                       # warm-up (page faults, thread pool)
+    steps = max(1, min(args.steps, int(budget_s / max(t_first, 1e-3)) - 1))
+    times = [st.step() for _ in range(steps)]
+    t_step = statistics.mean(times)
+    tok_s = w["T"] / t_step
+    sample = (f"all {w['n_layer']} layers on 1 of {w['B']} sequences, T={w['T']}, fp32 torch-eager restatement of the "
+              f"reference's attention layer (dense stored patterns for frozen heads); {steps} timed steps after 1 "
+              f"warm-up step (asked for {args.steps}/{args.warmup}; cut to fit {budget_s:.0f} s)")
     line = {
         "impl": "reference", "metric": METRIC, "value": tok_s, "unit": "tokens/s", "n_gpus": args.gpus,
-        "steps": steps, "warmup": warmup, "ms_per_step": t_layer * w["n_layer"] * 1e3, "higher_is_better": True,
+        "steps": steps, "warmup": 1, "ms_per_step": t_step * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": workload_name(args.workload, w)},
-        "cpu_baseline": {"value": tok_s, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
+        "config": bench_config(args.workload, w, "stack"),
+        "cpu_baseline": {"value": tok_s, "unit": "tokens/s", "cores": st.cores, "kind": "port", "sample": sample},
         "e2e": {"value": tok_s, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -144,6 +199,37 @@ def workload_name(key, w):
     return (f"{key}: GPT-2 124M SAF-25% attention+projection stack, {w['n_layer']} layers x "
             f"(indexed QKV GEMM + RoPE, mixed attention, c_proj), {w['n_head']} heads x {w['head_dim']}, "
             f"{w['n_frozen']} sink+decay frozen heads per layer, T={w['T']}, B={w['B']} per GPU")
+
+
+def bench_config(key, w, scope):
+    extra = {"stack": "", "block": "; whole blocks: + LayerNorms, residuals, 4x MLP with GELU",
+             "model": "; whole blocks: + LayerNorms, residuals, 4x MLP with GELU; token ids in, last-position logits out"}
+    return {"workload": workload_name(key, w) + extra[scope],
+            "l2": "per-layer working set (x 100 MB, qkv 250 MB, attention out 100 MB) exceeds the 126 MB L2"}
+
+
+def parity_block(layer, rope, w, x_one):
+    """Layer 0 on one sequence of the benchmark's own input against the CPU oracle on 64 sampled query rows
+    (all heads, all columns of those rows).  Runs after the timed regions."""
+    from oracle import saf_oracle as O
+    T, H, hd = w["T"], w["n_head"], w["head_dim"]
+    with torch.inference_mode():
+        y = layer(x_one, rope=rope)
+    torch.cuda.synchronize()
+    rows = sorted(set([0, 1, 127, 128, 255, 256, T // 2, T // 2 + 129, T - 256, T - 129, T - 128, T - 2, T - 1]
+                      + torch.linspace(0, T - 1, 51).long().tolist()))
+    rows = torch.tensor([r for r in rows if 0 <= r < T])
+    ws = [lin.weight.detach().float().cpu() for lin in (layer.q_proj, layer.k_proj, layer.v_proj, layer.c_proj)]
+    sd = layer.sd_params().double().cpu()
+    torch.set_num_threads(os.cpu_count() or 1)
+    with torch.no_grad():
+        ref = O.attention_layer(x_one.float().cpu(), *ws, list(layer._states), None, H,
+                                rope=O.rope_cache(hd, T, base=w["rope_base"]), rows=rows,
+                                sink_decay=(sd[:, 0], sd[:, 1]))
+    got = y[:, rows.to(y.device)].float().cpu()
+    return {"max_abs": O.max_abs(got, ref), "rel_l2": O.rel_l2(got, ref), "rows": int(rows.numel()),
+            "against": "fp32 CPU oracle of the reference's eager layer, layer 0, 1 sequence, all heads",
+            "bar": "max_abs <= 2e-2 and rel_l2 <= 1e-2"}
 
 
 def main():
@@ -160,14 +246,13 @@ def main():
                          "LayerNorm -> last-position logits")
     args = ap.parse_args()
 
-    from saf_b200 import synthetic
-    w = synthetic.WORKLOADS[args.workload]
+    w = load_workloads()[args.workload]
     if args.impl == "reference":
-        run_reference(args, w)
+        run_reference(args, w)          # CPU only: the package and its CUDA library are never imported here
         return
 
-    import saf_b200
-    from saf_b200 import ops, parallel
+    import saf_b200  # noqa: F401
+    from saf_b200 import ops, parallel, synthetic
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
     rank, world, local = parallel.init()
@@ -231,6 +316,12 @@ def main():
         for _ in range(warmup):
             step_resident()
         torch.cuda.synchronize()
+        # settle: untimed steps for about a second more, so that the timed region starts at the clocks and power
+        # state of sustained load instead of the first burst after idle
+        t_settle = time.perf_counter()
+        while time.perf_counter() - t_settle < float(os.environ.get("SAF_BENCH_SETTLE_S", "1.0")):
+            step_resident()
+            torch.cuda.synchronize()
 
         # ---- timed region 1: inputs resident in HBM ------------------------------------------
         sampler = ClockSampler(local)
@@ -282,11 +373,12 @@ def main():
     parallel.finalize()
     if rank != 0:
         return
+    parity = parity_block(layers[0], rope, w, x_dev[:1]) if args.scope == "stack" else None
 
     ms_per_step = total_ms / steps
     value = tokens / (ms_per_step * 1e-3)
     e2e_value = tokens / (e2e_ms / steps * 1e-3)
-    peak_tf, peak_hbm, peak_kind = measured_peaks()
+    peak_tf, peak_burst_tf, peak_hbm, peak_kind = measured_peaks()
     fl = synthetic.hot_stack_flops(w)
     live_flops_per_launch = fl["live"] / w["n_layer"] * B
     attn_mean_ms = statistics.mean(attn_ms)
@@ -297,22 +389,22 @@ def main():
         "value": value, "unit": "tokens/s", "n_gpus": world, "steps": steps, "warmup": warmup,
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": workload_name(args.workload, w) + ("; whole blocks: + LayerNorms, residuals, 4x MLP with "
-                                                                   "GELU" if args.scope != "stack" else "") + ("; token ids in, last-position logits out" if args.scope == "model" else ""),
-                   "l2": "per-layer working set (x 100 MB, qkv 250 MB, attention out 100 MB) exceeds the 126 MB L2",
-                   "timing": "CUDA events on the launching stream, max over ranks"},
+        "config": bench_config(args.workload, w, args.scope),
+        "timing": "CUDA events on the launching stream, max over ranks; untimed settle period after the warm-up steps",
         "clocks": clocks,
         "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": x_host.numel() * x_host.element_size(),
                 "d2h_bytes_per_step": last_host.numel() * 2},
         "gpu_launches": launches,
         "roofline": {"bound": "tensor", "kernel": "flash_fwd_kernel (live heads on tcgen05 + co-scheduled frozen-head scan, one launch per layer)",
                      "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s", "frac": achieved / peak_tf,
-                     "peak_kind": f"{peak_kind} sustained dense bf16", "traffic": ATTN_TRAFFIC_BYTES.get(args.workload),
+                     "peak_kind": f"{peak_kind} sustained dense bf16 (kernel timed inside a long step)",
+                     "frac_of_burst_peak": achieved / peak_burst_tf, "traffic": attention_traffic_bytes(args.workload),
                      "flops_per_launch": live_flops_per_launch, "ms_per_launch": attn_mean_ms,
                      "launches_timed": len(attn_ms)},
         "stack": {"tflops": stack_flops / (ms_per_step * 1e-3) / 1e12, "frac_of_peak": stack_flops / (ms_per_step * 1e-3) / 1e12 / peak_tf,
                   "attention_share_of_step": sum(attn_ms) / total_ms},
         "per_layer_ms": split,
+        "parity": parity,
     }
     if world == 1 and not args.no_cpu_baseline:
         tok_s, t_layer, cores, sample = cpu_reference_sample(w, 2, 1)

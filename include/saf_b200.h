@@ -111,10 +111,13 @@ int saf_mixed_attn_bwd(const SafMixedAttnBwdArgs* args, void* stream);
  * because it may synchronise the GPU.  `args->delta` is ignored: delta lives in a
  * fixed array of SAF_STATIC_DELTA_FLOATS fp32 values (4 MiB) that every GPU loading
  * this library holds until the process exits.
- *   - B*H*T must not exceed SAF_STATIC_DELTA_FLOATS, else SAF_ERR_LIMIT (nothing runs).
+ *   - B*H*T must not exceed SAF_STATIC_DELTA_FLOATS, else SAF_ERR_LIMIT (nothing runs);
+ *     calls that cannot contain a live head (U == 0, force_state or frozen_host naming
+ *     frozen states only) never touch delta and have no such limit.
  *   - The call allocates nothing.  The first call on each device looks up the
  *     array's device address (once per device, with that device current); make
- *     that first call before starting any stream capture.
+ *     that first call before starting any stream capture.  The address is remembered
+ *     per device ordinal: do not call this after cudaDeviceReset() on that device.
  *   - All calls on a device share the array, which keeps the last call's values;
  *     nothing in it needs clearing (rows are written before they are read), but
  *     two calls that overlap on the GPU race on it -- keep them on one stream or
@@ -316,6 +319,19 @@ int saf_last_error(char* buf, size_t n);
 int64_t saf_launch_count(void);
 /* 1 when the device under the current context is an sm_100 part, else 0 */
 int saf_device_supported(void);
+
+/* ---------------------------------------------------------------------------
+ * Self-checks (no counterpart in the reference).  Every wait inside the kernels is bounded; a wait that runs
+ * out records (kind | site << 8) in the call's `status` word, the kernel stops issuing work, skips its stores
+ * and returns, so the context stays usable.
+ * ------------------------------------------------------------------------- */
+/* Launches one CTA that waits, with a limit of limit_ns nanoseconds (at most 1e8), on a barrier nothing ever
+ * arrives on, and then records (6 | 99 << 8) = 0x6306 in *status (device int32, zero before the call) through
+ * the same path the kernels use.  Nothing traps, nothing hangs. */
+int saf_selftest_wait_timeout(int32_t* status, int64_t limit_ns, void* stream);
+/* Host-only check of the per-device bookkeeping (dynamic shared memory limits and SM counts are remembered per
+ * device ordinal, never per process): 0 when it behaves, else the number of the failing step.  No CUDA call. */
+int saf_selftest_per_device_once(void);
 
 #ifdef __cplusplus
 }

@@ -27,18 +27,42 @@ int check_launch(const char* what) {
   return SAF_OK;
 }
 
-TensorMapEncodeFn tensor_map_encoder() {
-  static TensorMapEncodeFn fn = nullptr;
-  static bool tried = false;
-  if (!tried) {
-    tried = true;
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = (TensorMapEncodeFn)p;
+int current_device() {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess) {
     cudaGetLastError();
+    return -1;
   }
+  return dev;
+}
+
+int device_sm_count() {
+  static std::atomic<int> cache[SAF_MAX_DEVICES];
+  const int dev = current_device();
+  const bool slot = dev >= 0 && dev < SAF_MAX_DEVICES;
+  int n = slot ? cache[dev].load(std::memory_order_relaxed) : 0;
+  if (n > 0) return n;
+  if (dev < 0 || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) {
+    cudaGetLastError();
+    return 148;
+  }
+  if (slot) cache[dev].store(n, std::memory_order_relaxed);
+  return n;
+}
+
+TensorMapEncodeFn tensor_map_encoder() {
+  // the driver entry point is a property of the process, not of a device; a failed lookup is retried
+  static std::atomic<TensorMapEncodeFn> cached{nullptr};
+  TensorMapEncodeFn fn = cached.load(std::memory_order_acquire);
+  if (fn) return fn;
+  void* p = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+      q == cudaDriverEntryPointSuccess) {
+    fn = (TensorMapEncodeFn)p;
+    cached.store(fn, std::memory_order_release);
+  }
+  cudaGetLastError();
   return fn;
 }
 
@@ -146,6 +170,10 @@ uint32_t possible_states(const SafMixedAttnArgs& a) {
 }
 
 }  // namespace
+
+int validate_mixed_args(const SafMixedAttnArgs* a) { return validate_mixed(a); }
+uint32_t mixed_possible_states(const SafMixedAttnArgs& a) { return possible_states(a); }
+
 }  // namespace saf
 
 using namespace saf;
@@ -178,6 +206,22 @@ int saf_device_supported(void) {
     return 0;
   }
   return major == 10 ? 1 : 0;
+}
+
+/* Host-only self-check of the per-device bookkeeping (no CUDA call): every device ordinal gets its own
+ * "first time" exactly once, ordinals do not disturb one another, a forgotten ordinal is first again, and
+ * ordinals outside the table always count as first.  Returns 0 when all of that holds, else the failing step. */
+int saf_selftest_per_device_once(void) {
+  PerDeviceOnce once{};
+  for (int d = 0; d < SAF_MAX_DEVICES; ++d)
+    if (!once.first(d)) return 1;
+  for (int d = 0; d < SAF_MAX_DEVICES; ++d)
+    if (once.first(d)) return 2;
+  once.forget(3);
+  if (!once.first(3)) return 3;
+  if (once.first(3) || once.first(2) || once.first(4)) return 4;
+  if (!once.first(-1) || !once.first(-1) || !once.first(SAF_MAX_DEVICES) || !once.first(SAF_MAX_DEVICES)) return 5;
+  return 0;
 }
 
 int saf_mixed_attn_fwd(const SafMixedAttnArgs* args, void* stream) {

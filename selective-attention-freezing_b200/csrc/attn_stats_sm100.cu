@@ -353,22 +353,11 @@ int as_launch(const SafAttnStatsArgs& a, cudaStream_t st) {
   p.head_m2 = a.head_m2;
   p.neg_entropy = a.neg_entropy;
   p.status = a.status;
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(attn_stats_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         AsCfg<HD>::SMEM_BYTES);
-    if (e != cudaSuccess) return fail(SAF_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-    attr_set = true;
-  }
+  static PerDeviceOnce smem_once;
+  if (int rc2 = ensure_dyn_smem(attn_stats_kernel<HD>, AsCfg<HD>::SMEM_BYTES, smem_once)) return rc2;
   const int64_t tiles = (int64_t)a.U * p.n_tiles * p.n_tiles;
   if (tiles > 0x7fffffff) return fail(SAF_ERR_LIMIT, "attention statistics: too many tiles");
-  static int sm_count = 0;
-  if (!sm_count) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
-    if (sm_count <= 0) sm_count = 148;
-  }
+  const int sm_count = device_sm_count();
   const int grid = (int)(tiles < sm_count ? tiles : sm_count);      // one persistent CTA per SM
   attn_stats_kernel<HD><<<(unsigned)grid, AS_THREADS, AsCfg<HD>::SMEM_BYTES, st>>>(mq, mk, p);
   count_launch();

@@ -20,12 +20,8 @@ int dp_launch(const SafMixedAttnArgs& a, cudaStream_t st) {
   DpParams p;
   int rc = dense_pv_prepare(a, true, false, &mp_, &mv, &mo, &p);
   if (rc) return rc;
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(dense_pv_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, DpCfg<HD>::SMEM_BYTES);
-    if (e != cudaSuccess) return fail(SAF_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-    attr_set = true;
-  }
+  static PerDeviceOnce smem_once;
+  if ((rc = ensure_dyn_smem(dense_pv_kernel<HD>, DpCfg<HD>::SMEM_BYTES, smem_once))) return rc;
   dense_pv_kernel<HD><<<dense_pv_slots(p), DP_THREADS, DpCfg<HD>::SMEM_BYTES, st>>>(mp_, mv, mo, p);
   count_launch();
   return check_launch("dense_pv_kernel");

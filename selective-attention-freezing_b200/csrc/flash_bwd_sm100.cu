@@ -887,14 +887,9 @@ int bwd_launch_typed(const SafMixedAttnBwdArgs& g, bool live, bool* dense_done, 
     *dense_done = dense;
     *decomp_done = decomp;
   }
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(flash_bwd_dkdv_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdCfg<HD>::SMEM_BYTES);
-    if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(flash_bwd_dq_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdCfg<HD>::SMEM_BYTES_DQ);
-    if (e != cudaSuccess) return fail(SAF_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-    attr_set = true;
-  }
+  static PerDeviceOnce smem_once_dkdv, smem_once_dq;
+  if ((rc = ensure_dyn_smem(flash_bwd_dkdv_kernel<HD>, BwdCfg<HD>::SMEM_BYTES, smem_once_dkdv))) return rc;
+  if ((rc = ensure_dyn_smem(flash_bwd_dq_kernel<HD>, BwdCfg<HD>::SMEM_BYTES_DQ, smem_once_dq))) return rc;
   const int bh = a.B * a.H;
   const int groups = (bh + BWD_HEAD_GROUP - 1) / BWD_HEAD_GROUP;
   const unsigned grid = live ? (unsigned)(groups * BWD_HEAD_GROUP * p.n_tiles) : 0u;

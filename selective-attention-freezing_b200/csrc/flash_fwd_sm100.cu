@@ -388,7 +388,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
         const uint32_t tS = tmem + lane_base + buf * FN;
         const int j0 = j * FN;
         // the P V product that read this buffer (three score tiles ago) must have finished
-        if ((act1 ? 2 * j + t : j) >= C::NBUF && !mbar_wait(&bars->buf_free[buf], bph ^ 1)) {
+        bool gave_up = (act1 ? 2 * j + t : j) >= C::NBUF && !mbar_wait(&bars->buf_free[buf], bph ^ 1);
+        // decomposed heads meet at named barriers below: the decision to leave is taken by all 128 threads
+        // together (the same barrier tells that the previous step's readers are done with the vectors)
+        if (state == SAF_DECOMP) gave_up = named_bar_or(1 + t, 128, gave_up);
+        if (gave_up) {
           dev_set_error(p.status, SAF_DEV_TIMEOUT_SOFTMAX, 31);
           ok = false;
           break;
@@ -396,7 +400,6 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
         tc_fence_after();
         const bool diag = (j == nk - 1);
         if (state == SAF_DECOMP) {
-          named_bar_sync(1 + t, 128);                      // previous step's readers are done with the vectors
           const int key = j0 + r;
           al_s[r] = (key < p.T) ? load_rt(p.alpha, (int64_t)h * p.alpha_s[0] + (int64_t)key * p.alpha_s[1], p.dec_dtype) : 0.f;
           const int d0 = row0 + t * FM - j0 - 127;         // distance of rh_s[0]
@@ -684,12 +687,8 @@ int launch_typed(const SafMixedAttnArgs& a, uint32_t want, cudaStream_t st) {
     s.B = a.B; s.H = a.H; s.T = a.T; s.HD = a.HD; s.force_state = a.force_state; s.HKV = a.HKV;
     s.vec_ok = 1;   // tma_ok() already demands 16-byte aligned bases and strides
   }
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(flash_fwd_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<HD>::SMEM_BYTES);
-    if (e != cudaSuccess) return fail(SAF_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-    attr_set = true;
-  }
+  static PerDeviceOnce smem_once;
+  if ((rc = ensure_dyn_smem(flash_fwd_kernel<HD>, Cfg<HD>::SMEM_BYTES, smem_once))) return rc;
   const int bh = a.B * a.H;
   const int groups = (bh + HEAD_GROUP - 1) / HEAD_GROUP;
   const unsigned grid = (unsigned)(bh + p.dense_slots + groups * HEAD_GROUP * p.n_pairs);

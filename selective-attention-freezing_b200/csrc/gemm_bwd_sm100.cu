@@ -257,19 +257,10 @@ void fill_blocks(const SafIndexedLinearArgs& a, BlockTable* tb) {
 template <int MODE>
 int launch_mode(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap* mw, const CUtensorMap& mo,
                 const BwdGemmParams& p, const BlockTable& tb, cudaStream_t st) {
-  static int sm_count = 0;
-  if (!sm_count) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
-  }
+  const int sm_count = device_sm_count();
   const size_t smem = 1024 + NSTG * BSTAGE + BOUT_BYTES + sizeof(BSmem);
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(indexed_gemm_bwd_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return fail(SAF_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-    attr_set = true;
-  }
+  static PerDeviceOnce smem_once;
+  if (int rc = ensure_dyn_smem(indexed_gemm_bwd_kernel<MODE>, (int)smem, smem_once)) return rc;
   const int grid = std::min(sm_count, p.tiles_m * p.tiles_n);
   indexed_gemm_bwd_kernel<MODE><<<grid, BGEMM_THREADS, smem, st>>>(ma, mb, mw[0], mw[1], mw[2], mw[3], mo, p, tb);
   count_launch();

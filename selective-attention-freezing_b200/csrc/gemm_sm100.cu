@@ -376,19 +376,10 @@ int launch_gemm_sm100(const SafIndexedLinearArgs& a, cudaStream_t st) {
   p.residual = reinterpret_cast<const __nv_bfloat16*>(a.residual);
   p.ldr = a.ldr;
 
-  static int sm_count = 0;
-  if (!sm_count) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
-  }
+  const int sm_count = device_sm_count();
   const size_t smem = 1024 + STAGES * STAGE_BYTES + OUT_BYTES + sizeof(SmemLayout);
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(indexed_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return fail(SAF_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-    attr_set = true;
-  }
+  static PerDeviceOnce smem_once;
+  if ((rc = ensure_dyn_smem(indexed_gemm_kernel, (int)smem, smem_once))) return rc;
   const int grid = std::min(sm_count, p.tiles_m * p.tiles_n);
   indexed_gemm_kernel<<<grid, GEMM_THREADS, smem, st>>>(mx, mw[0], mw[1], mw[2], mw[3], mo, p, tb);
   count_launch();

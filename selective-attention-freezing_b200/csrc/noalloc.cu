@@ -13,6 +13,11 @@
 // that overlap on the GPU (different streams) race on it; serialise them.  Nothing
 // in it has to start at zero -- every row that is read is written first by the same
 // call -- so no clearing pass is needed and the previous call's contents are harmless.
+// The array's device address is remembered per device ordinal; a process that calls
+// cudaDeviceReset() must not use this entry point on that device afterwards (the
+// remembered address belongs to the destroyed context).
+#include <atomic>
+
 #include "saf_internal.h"
 
 namespace saf {
@@ -20,8 +25,8 @@ namespace {
 
 static __device__ __align__(256) float g_static_delta[SAF_STATIC_DELTA_FLOATS];
 
-constexpr int kMaxDevices = 64;
-float* g_delta_addr[kMaxDevices] = {nullptr};
+constexpr int kMaxDevices = SAF_MAX_DEVICES;
+std::atomic<float*> g_delta_addr[kMaxDevices];   // zero-initialised; racing first calls store the same value
 
 // Device address of the scratch array on the current device.  In host code the name
 // g_static_delta is only a handle for the runtime, not an address a kernel could use:
@@ -31,13 +36,15 @@ int static_delta_ptr(float** out) {
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return fail(SAF_ERR_CUDA, "cudaGetDevice: %s", cudaGetErrorString(e));
   if (dev < 0 || dev >= kMaxDevices) return fail(SAF_ERR_LIMIT, "device ordinal %d beyond %d", dev, kMaxDevices);
-  if (!g_delta_addr[dev]) {
+  float* addr = g_delta_addr[dev].load(std::memory_order_relaxed);
+  if (!addr) {
     void* p = nullptr;
     e = cudaGetSymbolAddress(&p, g_static_delta);
     if (e != cudaSuccess) return fail(SAF_ERR_CUDA, "cudaGetSymbolAddress(static delta scratch): %s", cudaGetErrorString(e));
-    g_delta_addr[dev] = reinterpret_cast<float*>(p);
+    addr = reinterpret_cast<float*>(p);
+    g_delta_addr[dev].store(addr, std::memory_order_relaxed);
   }
-  *out = g_delta_addr[dev];
+  *out = addr;
   return SAF_OK;
 }
 
@@ -52,14 +59,17 @@ extern "C" int saf_mixed_attn_bwd_static(const SafMixedAttnBwdArgs* args, void* 
     return fail(SAF_ERR_INVALID, "SafMixedAttnBwdArgs size mismatch: caller %d, library %d", args->struct_size,
                 (int)sizeof(SafMixedAttnBwdArgs));
   const SafMixedAttnArgs& a = args->fwd;
-  if (a.B < 0 || a.H < 0 || a.T < 0) return fail(SAF_ERR_INVALID, "negative dimension");
+  int rc = validate_mixed_args(&a);       // a malformed struct is reported as such, not as a size limit
+  if (rc) return rc;
+  // delta is read and written for live heads only: a call that cannot contain one has no size limit
+  const bool may_be_live = (mixed_possible_states(a) & (1u << SAF_LIVE)) != 0;
   const int64_t need = (int64_t)a.B * a.H * a.T;
-  if (need > (int64_t)SAF_STATIC_DELTA_FLOATS)
+  if (may_be_live && need > (int64_t)SAF_STATIC_DELTA_FLOATS)
     return fail(SAF_ERR_LIMIT,
                 "B*H*T = %lld rows exceed the static scratch of %d rows; use saf_mixed_attn_bwd with caller-provided delta",
                 (long long)need, (int)SAF_STATIC_DELTA_FLOATS);
   float* scratch = nullptr;
-  int rc = static_delta_ptr(&scratch);
+  rc = static_delta_ptr(&scratch);
   if (rc) return rc;
   SafMixedAttnBwdArgs g = *args;
   g.delta.ptr = scratch;

@@ -396,13 +396,8 @@ int pg_launch_sm100(const SafPatternGradArgs& a, cudaStream_t st) {
   p.delta = a.delta;
   p.dalpha = a.dalpha; p.drho = a.drho;
   p.status = a.status;
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(pattern_grad_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         PgCfg<HD>::SMEM_BYTES);
-    if (e != cudaSuccess) return fail(SAF_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-    attr_set = true;
-  }
+  static PerDeviceOnce smem_once;
+  if (int rc2 = ensure_dyn_smem(pattern_grad_kernel<HD>, PgCfg<HD>::SMEM_BYTES, smem_once)) return rc2;
   const int64_t rows = (int64_t)a.B * a.H * a.T;
   const int64_t grid = (int64_t)a.B * a.H * p.n_tiles;
   if (grid > 0x7fffffff || (rows + 7) / 8 > 0x7fffffff) return fail(SAF_ERR_LIMIT, "pattern gradient grid too large");
@@ -428,11 +423,11 @@ int pg_launch_generic(const SafPatternGradArgs& a, cudaStream_t st) {
   p.alpha = a.alpha; p.rho = a.rho; p.z = a.z;
   p.dalpha = a.dalpha; p.drho = a.drho;
   const int smem = (2 * 32 * (a.HD + 1) + 32 * 3 + 64) * (int)sizeof(float);
-  static int attr_bytes = 0;
-  if (smem > 48 * 1024 && smem > attr_bytes) {
-    cudaError_t e = cudaFuncSetAttribute(pattern_grad_generic_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e != cudaSuccess) return fail(SAF_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-    attr_bytes = smem;
+  if (smem > 48 * 1024) {
+    // head_dim <= 256 bounds this at 66.8 KB: raise the limit to that maximum once per device
+    static PerDeviceOnce smem_once;
+    constexpr int SMEM_MAX = (2 * 32 * (256 + 1) + 32 * 3 + 64) * (int)sizeof(float);
+    if (int rc2 = ensure_dyn_smem(pattern_grad_generic_kernel, SMEM_MAX, smem_once)) return rc2;
   }
   const int nt = (a.T + 31) / 32;
   if (a.H > 65535 || a.B > 65535) return fail(SAF_ERR_LIMIT, "pattern gradient: B or H > 65535");

@@ -7,6 +7,8 @@
 #include <stdint.h>
 #include <stdio.h>
 
+#include <atomic>
+
 #include "../../include/saf_b200.h"
 
 namespace saf {
@@ -15,6 +17,40 @@ namespace saf {
 int fail(int code, const char* fmt, ...);
 void count_launch(int n = 1);
 int check_launch(const char* what);   // cudaGetLastError -> SAF_ERR_CUDA
+
+// ---- per-device bookkeeping ---------------------------------------------------
+// One process may drive several GPUs: anything that CUDA keeps per device (a kernel's dynamic shared memory
+// limit, the SM count) is remembered per device ordinal, never per process.
+constexpr int SAF_MAX_DEVICES = 64;
+
+// "has this been done on device d yet?" -- first(d) returns true exactly once per device ordinal (ordinals
+// outside [0, SAF_MAX_DEVICES) always return true: the caller then simply repeats its idempotent set-up).
+struct PerDeviceOnce {
+  std::atomic<bool> done[SAF_MAX_DEVICES];
+  bool first(int dev) {
+    if (dev < 0 || dev >= SAF_MAX_DEVICES) return true;
+    return !done[dev].exchange(true, std::memory_order_acq_rel);
+  }
+  void forget(int dev) {
+    if (dev >= 0 && dev < SAF_MAX_DEVICES) done[dev].store(false, std::memory_order_release);
+  }
+};
+
+int current_device();        // cudaGetDevice; -1 when it fails
+int device_sm_count();       // SM count of the current device, cached per device (148 when the query fails)
+
+// Raises `kernel`'s dynamic shared memory limit to `bytes` on the current device, once per device.
+template <typename K>
+int ensure_dyn_smem(K kernel, int bytes, PerDeviceOnce& once) {
+  const int dev = current_device();
+  if (!once.first(dev)) return SAF_OK;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e != cudaSuccess) {
+    once.forget(dev);
+    return fail(SAF_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+  }
+  return SAF_OK;
+}
 
 // ---- element conversion -----------------------------------------------------
 template <typename T> __device__ __forceinline__ float to_f(T x);
@@ -34,6 +70,10 @@ __device__ __forceinline__ float load_rt(const void* base, int64_t idx, int dtyp
 }
 
 inline int dtype_size(int dt) { return dt == SAF_F32 ? 4 : 2; }
+
+// argument checks of the mixed-attention entry points, and the head states a call can contain (bit s = state s)
+int validate_mixed_args(const SafMixedAttnArgs* a);
+uint32_t mixed_possible_states(const SafMixedAttnArgs& a);
 
 // ---- kernels' host launchers (each returns SAF_OK or an error code) ----------
 // states_mask: bit s set -> heads in state s are processed by this launch

@@ -21,6 +21,7 @@ enum : int {
   SAF_DEV_TIMEOUT_EPI = 3,
   SAF_DEV_TIMEOUT_SOFTMAX = 4,
   SAF_DEV_TIMEOUT_SCAN = 5,
+  SAF_DEV_TIMEOUT_SELFTEST = 6,
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -69,7 +70,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 
 // Bounded wait.  Returns false when the limit was reached (caller must bail out:
 // record the error, stop issuing work and fall through to the teardown).
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_wait_limit(uint64_t* bar, uint32_t parity, uint64_t limit_ns) {
   // the clock is read only after many failed polls: a healthy wait never pays for it
   uint64_t t0 = 0;
   uint32_t it = 0;
@@ -77,10 +78,13 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     if ((++it & 0xfff) == 0) {
       const uint64_t now = globaltimer_ns();
       if (t0 == 0) t0 = now;
-      else if (now - t0 > SAF_WAIT_LIMIT_NS) return false;
+      else if (now - t0 > limit_ns) return false;
     }
   }
   return true;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+  return mbar_wait_limit(bar, parity, SAF_WAIT_LIMIT_NS);
 }
 
 __device__ __forceinline__ void dev_set_error(int* err, int code, int where) {
@@ -260,6 +264,20 @@ __device__ __forceinline__ bool elect_one() {
 // named barrier among a subset of warps
 __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+
+// named barrier that also ORs a predicate over its threads: every thread gets the same answer, so a
+// decision such as "somebody's wait ran out" is taken by the whole group and nobody is left behind at a
+// later barrier
+__device__ __forceinline__ bool named_bar_or(int id, int nthreads, bool pred) {
+  uint32_t r;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %3, 0;\n\t"
+      "bar.red.or.pred q, %1, %2, p;\n\tselp.u32 %0, 1, 0, q;\n\t}"
+      : "=r"(r)
+      : "r"(id), "r"(nthreads), "r"((uint32_t)pred)
+      : "memory");
+  return r != 0;
 }
 
 }  // namespace saf

@@ -97,6 +97,7 @@ EXPORTS = (
     "saf_indexed_linear_fwd", "saf_indexed_linear_bwd_dx", "saf_indexed_linear_bwd_dw",
     "saf_decomposed_logz", "saf_rope_slabs", "saf_layernorm_fwd",
     "saf_pattern_normalisers", "saf_pattern_param_grad", "saf_attention_moments",
+    "saf_selftest_wait_timeout", "saf_selftest_per_device_once",
 )
 
 
@@ -142,6 +143,9 @@ def _load():
     lib.saf_layernorm_fwd.argtypes = [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64,
                                       C.c_int32, C.c_int32, C.c_float, C.c_int32, C.c_void_p]
     lib.saf_layernorm_fwd.restype = C.c_int
+    lib.saf_selftest_wait_timeout.argtypes = [C.c_void_p, C.c_int64, C.c_void_p]
+    lib.saf_selftest_wait_timeout.restype = C.c_int
+    lib.saf_selftest_per_device_once.restype = C.c_int
     if lib.saf_abi_version() != 1:
         raise ImportError("libsaf_b200.so ABI version %d, expected 1: rebuild" % lib.saf_abi_version())
     return lib

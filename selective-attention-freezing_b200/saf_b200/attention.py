@@ -277,6 +277,7 @@ class SafCausalSelfAttention(nn.Module):
         sd = self.sd_params()
         self._sd = (sd[:, 0].contiguous(), sd[:, 1].contiguous()) if self._sd_any else None
         self._patt_cast = None      # compact copy of the dense heads' patterns in the activation dtype, built on demand
+        self._mask_frozen_only = None   # head states with live heads masked out (training with attention dropout)
         self._fz_dirty = False
 
     # ---- forward --------------------------------------------------------------------------
@@ -347,7 +348,7 @@ class SafCausalSelfAttention(nn.Module):
                 self._patt_cast = (patt[dense].to(act_dt), torch.tensor(slot, dtype=torch.int32, device=patt.device))
             patt, pidx = self._patt_cast
         nuf = len(self._live)
-        if not torch.is_grad_enabled() and act_dt == torch.bfloat16:
+        if not torch.is_grad_enabled() and act_dt == torch.bfloat16 and (self.dropout == 0.0 or not self.training):
             # inference: one GEMM, canonical weights read in place, RoPE in the epilogue
             w = [m.weight if m.weight.dtype == act_dt else m.weight.to(act_dt) for m in (self.q_proj, self.k_proj, self.v_proj)]
             bs = None
@@ -381,10 +382,30 @@ class SafCausalSelfAttention(nn.Module):
             qu, ku = qk[:, :, 0].transpose(1, 2), qk[:, :, 1].transpose(1, 2)
             if self._stats is not None:
                 self._stats.update(qu.detach(), ku.detach())
-        y = ops.fused_mixed_attn(qu, ku, v, patt, self._fz_mask_i32, self._hidx_i32, pidx,
-                                 alpha=dec[0], rho=dec[1], z=dec[2], validate=False, sink_decay=self._sd)
+        if self.dropout > 0.0 and self.training and nuf:
+            # The fused kernels implement no attention dropout.  As in the reference, which leaves its fused path
+            # in this case and lets the SDPA half of its split path apply the dropout (nanogpt/model.py:971-974,
+            # 1017-1061): live heads go through torch's SDPA with dropout_p, frozen heads through the library
+            # (their patterns carry no dropout).  The library call marks the live heads as structured heads with
+            # zero parameters -- an O(T) scan whose rows are then overwritten -- so they cost no attention FLOPs.
+            if self._mask_frozen_only is None:
+                st = self._fz_mask_i32.clone()
+                st[st == 0] = 3
+                sd = self.sd_params().clone()
+                sd[torch.as_tensor(self._live, device=sd.device)] = torch.tensor([0.0, 0.5], device=sd.device)
+                self._mask_frozen_only = (st, (sd[:, 0].contiguous(), sd[:, 1].contiguous()))
+            st, sd = self._mask_frozen_only
+            y = ops.fused_mixed_attn(v[:, :0], v[:, :0], v, patt, st, self._hidx_i32, pidx,
+                                     alpha=dec[0], rho=dec[1], z=dec[2], validate=False, sink_decay=sd)
+            live = torch.as_tensor(self._live, device=x.device)
+            y_live = F.scaled_dot_product_attention(qu, ku, v.index_select(1, live), dropout_p=self.dropout,
+                                                    is_causal=True)
+            y = y.index_copy(1, live, y_live.to(y.dtype))
+        else:
+            y = ops.fused_mixed_attn(qu, ku, v, patt, self._fz_mask_i32, self._hidx_i32, pidx,
+                                     alpha=dec[0], rho=dec[1], z=dec[2], validate=False, sink_decay=self._sd)
         y = y.transpose(1, 2).reshape(B, T, nh * hd)
-        out = self.c_proj(y)
+        out = F.dropout(self.c_proj(y), self.dropout, self.training)     # resid_dropout (nanogpt/model.py:1169)
         return out if residual is None else residual + out
 
     def forward(self, x, rope=None, residual=None):
@@ -403,7 +424,7 @@ class SafCausalSelfAttention(nn.Module):
                 rot = lambda t: torch.cat((-t[..., hd // 2:], t[..., :hd // 2]), dim=-1)   # noqa: E731
                 q, k = q * cos + rot(q) * sin, k * cos + rot(k) * sin
             y = self._attend_dynamic(q, k, v).transpose(1, 2).contiguous().view(B, T, nh * hd)
-            out = self.c_proj(y)
+            out = F.dropout(self.c_proj(y), self.dropout, self.training)
             return out if residual is None else residual + out
         if not x.is_cuda:
             raise RuntimeError("SafCausalSelfAttention runs on CUDA only (set_capture(True) gives the eager torch path)")

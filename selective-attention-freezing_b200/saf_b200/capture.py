@@ -14,7 +14,7 @@ import math
 import torch
 
 from . import ops
-from ._cabi import SafAttnStatsArgs, SafMixedAttnArgs, check, lib
+from ._cabi import SafAttnStatsArgs, SafMixedAttnArgs, lib
 
 
 def _row_lse(q, k, sm_scale):
@@ -26,7 +26,7 @@ def _row_lse(q, k, sm_scale):
     live = torch.zeros(U, dtype=torch.int32, device=q.device)
     a, keep = SafMixedAttnArgs(), []
     ops._fill_mixed(a, q, k, k, out, lse, None, None, None, None, live, None, None, None, sm_scale, None, None, keep)
-    check(lib.saf_mixed_attn_fwd(C.byref(a), ops._stream(q)))
+    ops._call(q, lib.saf_mixed_attn_fwd, C.byref(a))
     return lse
 
 
@@ -55,7 +55,8 @@ def attention_moments(q, k, mean, count_prev, head_m2, neg_entropy, sm_scale=Non
     a.mean = mean.data_ptr()
     a.count_prev = int(count_prev)
     a.head_m2, a.neg_entropy = head_m2.data_ptr(), neg_entropy.data_ptr()
-    check(lib.saf_attention_moments(C.byref(a), ops._stream(q)))
+    a.status = ops._status_ptr(q.device)
+    ops._call(q, lib.saf_attention_moments, C.byref(a))
     return int(count_prev) + B
 
 

@@ -9,6 +9,7 @@ bookkeeping and the current stream only; every FLOP runs in libsaf_b200.
 """
 import ctypes as C
 import math
+import os
 import weakref
 
 import torch
@@ -46,6 +47,63 @@ def _ptr(t):
 
 def _stream(t):
     return C.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
+
+
+def _call(t, fn, *args):
+    """Run one library entry on tensor t's device and current stream.  The library works on the CURRENT device
+    (per-device kernel attributes, SM count, tensor maps), so a tensor that lives on another GPU of this process
+    makes its device current for the call."""
+    if t.device.index is not None and t.device.index != torch.cuda.current_device():
+        with torch.cuda.device(t.device):
+            rc = fn(*args, _stream(t))
+    else:
+        rc = fn(*args, _stream(t))
+    check(rc)
+    if _CHECK_EVERY_CALL:
+        device_status(t.device)
+
+
+# ---------------------------------------------------------------------------
+# device-side error word
+# ---------------------------------------------------------------------------
+# Every wait inside the kernels is bounded.  A wait that runs out records (kind | where << 8) in an int32 word
+# the call was given, stops issuing work, skips its stores and returns.  One word per device, handed to every call.
+_STATUS = {}
+_CHECK_EVERY_CALL = os.environ.get("SAF_B200_CHECK_STATUS", "0") not in ("", "0")
+_DEV_KINDS = {1: "TMA producer wait", 2: "MMA issuer wait", 3: "epilogue wait", 4: "softmax / compute wait",
+              5: "scan wait", 6: "self-test wait"}
+
+
+def _status_ptr(device):
+    """Device address of this device's status word (allocated and zeroed at first use; make that first use
+    before a CUDA graph capture -- any warm-up call does)."""
+    key = torch.device(device).index
+    if key is None:
+        key = torch.cuda.current_device()
+    w = _STATUS.get(key)
+    if w is None:
+        w = _STATUS[key] = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", key))
+    return w.data_ptr()
+
+
+def device_status(device=None, clear=True):
+    """Reads the device's status word (synchronises with that device) and raises SafError if a kernel gave up
+    on a wait since the last check; returns 0 otherwise.  Outputs of a call that gave up are undefined.
+    Set SAF_B200_CHECK_STATUS=1 to run this check after every library call (debugging; it synchronises)."""
+    key = torch.cuda.current_device() if device is None else torch.device(device).index
+    if key is None:
+        key = torch.cuda.current_device()
+    w = _STATUS.get(key)
+    if w is None:
+        return 0
+    code = int(w.item())
+    if code == 0:
+        return 0
+    if clear:
+        w.zero_()
+    kind, where = code & 0xff, code >> 8
+    raise _cabi.SafError(_cabi.SAF_ERR_CUDA, "a kernel gave up on a bounded wait: %s (site %d, raw 0x%x); the outputs of "
+                         "that call are undefined" % (_DEV_KINDS.get(kind, "kind %d" % kind), where, code))
 
 
 def _require_cuda(t, name):
@@ -132,7 +190,7 @@ def decomposed_logz(alpha, rho, chunk=None):
         r = rho.detach().float().contiguous()
         z = torch.empty_like(a)
         H, S = a.shape
-        check(lib.saf_decomposed_logz(a.data_ptr(), r.data_ptr(), z.data_ptr(), H, S, _stream(a)))
+        _call(a, lib.saf_decomposed_logz, a.data_ptr(), r.data_ptr(), z.data_ptr(), H, S)
         return z.to(alpha.dtype)
     H, S = alpha.shape
     if chunk is None:
@@ -167,6 +225,7 @@ def _fill_mixed(a, q, k, v, out, lse, patt, alpha, rho, z, frozen, hidx, pidx, k
     a.U = q.shape[1] if q is not None else 0
     a.HKV = Hv if kvidx is not None else 0
     a.force_state = -1
+    a.status = _status_ptr(v.device)
     a.sm_scale = float(sm_scale)
     a.q, a.k, a.v, a.out = _st(q), _st(k), _st(v), _st(out)
     a.lse = _st(lse)
@@ -227,11 +286,11 @@ class _FusedMixedAttn(torch.autograd.Function):
         if _ATTN_EVENTS is not None:
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
-            check(lib.saf_mixed_attn_fwd(C.byref(a), _stream(v)))
+            _call(v, lib.saf_mixed_attn_fwd, C.byref(a))
             e1.record()
             _ATTN_EVENTS.append((e0, e1))
         else:
-            check(lib.saf_mixed_attn_fwd(C.byref(a), _stream(v)))
+            _call(v, lib.saf_mixed_attn_fwd, C.byref(a))
         ctx.save_for_backward(q, k, v, patt, alpha, rho, z, frozen, hidx, pidx, out, lse,
                               *(rope or ()), *(sink_decay or ()))
         ctx.sm_scale = sm_scale
@@ -260,7 +319,7 @@ class _FusedMixedAttn(torch.autograd.Function):
         _fill_mixed(g.fwd, q, k, v, out, lse, patt, alpha, rho, z, frozen, hidx, pidx, None, ctx.sm_scale, rope,
                     sink_decay, keep)
         g.dout, g.dq, g.dk, g.dv, g.delta = _st(do), _st(dq), _st(dk), _st(dv), _st(delta)
-        check(lib.saf_mixed_attn_bwd(C.byref(g), _stream(v)))
+        _call(v, lib.saf_mixed_attn_bwd, C.byref(g))
         return (dq, dk, dv) + (None,) * 11
 
 
@@ -272,8 +331,8 @@ class _RotatedCopy(torch.autograd.Function):
 
     @staticmethod
     def _rotate(y, B, N, T, hd, cos, sin, inverse):
-        check(lib.saf_rope_slabs(y.data_ptr(), N * hd, B * T, N, hd, T, None, cos.data_ptr(), sin.data_ptr(), _dt(y),
-                                 inverse, _stream(y)))
+        _call(y, lib.saf_rope_slabs, y.data_ptr(), N * hd, B * T, N, hd, T, None, cos.data_ptr(), sin.data_ptr(), _dt(y),
+                                 inverse)
 
     @staticmethod
     def forward(ctx, x, cos, sin):
@@ -401,6 +460,7 @@ def _fill_pv(p, patt, v, y, fz_idx, T, sink_decay):
         p.patt_dtype = _dt(patt)
         p.S = patt.shape[1]
     p.v, p.y = _st(v), _st(y)
+    p.status = _status_ptr(v.device)
     p.fz_idx = _ptr(fz_idx)
     if sink_decay is not None:
         p.sd_alpha, p.sd_rho = _ptr(sink_decay[0]), _ptr(sink_decay[1])
@@ -415,7 +475,7 @@ class _FrozenPV(torch.autograd.Function):
         y = torch.empty((B, nf, T, hd), device=v.device, dtype=v.dtype)
         p = SafFrozenPvArgs()
         _fill_pv(p, patt, v, y, fz_idx, T, sink_decay)
-        check(lib.saf_frozen_pv_fwd(C.byref(p), _stream(v)))
+        _call(v, lib.saf_frozen_pv_fwd, C.byref(p))
         ctx.save_for_backward(patt, fz_idx, *(sink_decay or ()))
         ctx.has_sd = sink_decay is not None
         ctx.v_shape, ctx.v_dtype, ctx.T = v.shape, v.dtype, T
@@ -432,7 +492,7 @@ class _FrozenPV(torch.autograd.Function):
             dv.zero_()
         p = SafFrozenPvArgs()
         _fill_pv(p, patt, dy, dv, fz_idx, ctx.T, sink_decay)
-        check(lib.saf_frozen_pv_bwd(C.byref(p), _stream(dy)))
+        _call(dy, lib.saf_frozen_pv_bwd, C.byref(p))
         return None, dv, None, None, None
 
 
@@ -514,6 +574,7 @@ def _lin_args(x2, weights, biases, slab, slab_weight, slab_row0, keep, transpose
     a.n_slabs, a.slab = len(slab_row0), slab
     a.T = T
     a.x, a.ldx = x2.data_ptr(), x2.stride(0)
+    a.status = _status_ptr(x2.device)
     for i, w in enumerate(weights):
         a.weights[i] = w.data_ptr()
         a.biases[i] = _ptr(biases[i]) if biases is not None else None
@@ -571,7 +632,7 @@ class _RowSlicedLinearN(torch.autograd.Function):
             a = _lin_args(x2, weights, biases, slab, sw, sr, keep)
         out = torch.empty((x2.shape[0], nw * n_per * slab), device=x.device, dtype=x.dtype)
         a.out, a.ldo = out.data_ptr(), out.stride(0)
-        check(lib.saf_indexed_linear_fwd(C.byref(a), _stream(x)))
+        _call(x, lib.saf_indexed_linear_fwd, C.byref(a))
         ctx.save_for_backward(x, rows, *weights, *(rope[:2] if rope is not None else ()))
         ctx.nw = nw
         ctx.rope = None if rope is None else (rope[2], rope[3])
@@ -593,8 +654,8 @@ class _RowSlicedLinearN(torch.autograd.Function):
             # gradient w.r.t. the un-rotated projection: adjoint rotation of a private copy
             cos, sin = ctx.saved_tensors[2 + nw:4 + nw]
             dout2 = dout2.clone() if dout2.data_ptr() == dout.data_ptr() else dout2
-            check(lib.saf_rope_slabs(dout2.data_ptr(), dout2.stride(0), dout2.shape[0], len(sr), slab, ctx.rope[0],
-                                     None, cos.data_ptr(), sin.data_ptr(), _dt(dout2), 1, _stream(x)))
+            _call(x, lib.saf_rope_slabs, dout2.data_ptr(), dout2.stride(0), dout2.shape[0], len(sr), slab, ctx.rope[0],
+                                     None, cos.data_ptr(), sin.data_ptr(), _dt(dout2), 1)
         dx = None
         grads_w = [None] * nw
         grads_b = [None] * nw
@@ -602,8 +663,8 @@ class _RowSlicedLinearN(torch.autograd.Function):
             keep = []
             a = _lin_args(x2, weights, None, slab, sw, sr, keep)
             dx2 = torch.empty_like(x2)
-            check(lib.saf_indexed_linear_bwd_dx(C.byref(a), dout2.data_ptr(), dout2.stride(0), dx2.data_ptr(),
-                                                dx2.stride(0), None, _stream(x)))
+            _call(x, lib.saf_indexed_linear_bwd_dx, C.byref(a), dout2.data_ptr(), dout2.stride(0), dx2.data_ptr(),
+                                                dx2.stride(0), None)
             dx = dx2.view(x.shape)
         need_w = any(ctx.needs_input_grad[3 + i] for i in range(nw))
         need_b = any(ctx.has_bias[i] and ctx.needs_input_grad[3 + nw + i] for i in range(nw))
@@ -614,7 +675,7 @@ class _RowSlicedLinearN(torch.autograd.Function):
                    for i, w in enumerate(weights)]
             keep = []
             a = _lin_args(x2, dws, dbs, slab, sw, sr, keep)
-            check(lib.saf_indexed_linear_bwd_dw(C.byref(a), dout2.data_ptr(), dout2.stride(0), _stream(x)))
+            _call(x, lib.saf_indexed_linear_bwd_dw, C.byref(a), dout2.data_ptr(), dout2.stride(0))
             grads_w, grads_b = dws, dbs
         return (dx, None, None, None, *grads_w, *grads_b)
 
@@ -631,8 +692,8 @@ class _ColPermutedLinear(torch.autograd.Function):
         # selection rows = columns of W: address W through its transpose
         a = _lin_args(y2, [weight], None, slab, [0] * len(col0), col0, keep, transposed=True)
         out = torch.empty((y2.shape[0], weight.shape[0]), device=y.device, dtype=y.dtype)
-        check(lib.saf_indexed_linear_bwd_dx(C.byref(a), y2.data_ptr(), y2.stride(0), out.data_ptr(), out.stride(0),
-                                            _ptr(bias), _stream(y)))
+        _call(y, lib.saf_indexed_linear_bwd_dx, C.byref(a), y2.data_ptr(), y2.stride(0), out.data_ptr(), out.stride(0),
+                                            _ptr(bias))
         ctx.save_for_backward(y, weight, cols)
         ctx.has_bias = bias is not None
         return out.view(*y.shape[:-1], weight.shape[0])
@@ -650,14 +711,14 @@ class _ColPermutedLinear(torch.autograd.Function):
             dy2 = torch.empty_like(y2)
             a.out, a.ldo = dy2.data_ptr(), dy2.stride(0)
             # dy[m, j] = sum_o dout[m, o] W[o, cols[j]]: a forward product over the transposed weight
-            check(lib.saf_indexed_linear_fwd(C.byref(a), _stream(y)))
+            _call(y, lib.saf_indexed_linear_fwd, C.byref(a))
             dy = dy2.view(y.shape)
         if ctx.needs_input_grad[1]:
             dw = torch.empty_like(weight)  # full permutation: every column written
             keep = []
             a = _lin_args(dout2, [dw], None, slab, [0] * len(col0), col0, keep, transposed=True)
             # dW[o, cols[j]] = sum_m dout[m, o] y[m, j]:  "dout" role = y, "x" role = dout
-            check(lib.saf_indexed_linear_bwd_dw(C.byref(a), y2.data_ptr(), y2.stride(0), _stream(y)))
+            _call(y, lib.saf_indexed_linear_bwd_dw, C.byref(a), y2.data_ptr(), y2.stride(0))
         if ctx.has_bias and ctx.needs_input_grad[2]:
             db = dout2.sum(0)
         return dy, dw, db, None
@@ -709,7 +770,7 @@ def qkv_projection(x, wq, wk, wv, live_heads, head_dim, rope=None, T=None, biase
                   T=(T if T is not None else x.shape[-2]), slab_rope=srope)
     out = torch.empty((x2.shape[0], (2 * U + H) * head_dim), device=x.device, dtype=x.dtype)
     a.out, a.ldo = out.data_ptr(), out.stride(0)
-    check(lib.saf_indexed_linear_fwd(C.byref(a), _stream(x)))
+    _call(x, lib.saf_indexed_linear_fwd, C.byref(a))
     return out
 
 
@@ -724,8 +785,8 @@ def layer_norm(x, weight, bias=None, eps=1e-5):
     w = weight if weight.dtype == x.dtype else weight.to(x.dtype)
     b = None if bias is None else (bias if bias.dtype == x.dtype else bias.to(x.dtype))
     out = torch.empty_like(x2)
-    check(lib.saf_layernorm_fwd(x2.data_ptr(), x2.stride(0), w.data_ptr(), _ptr(b), out.data_ptr(), out.stride(0),
-                                x2.shape[0], x2.shape[1], float(eps), _dt(x2), _stream(x)))
+    _call(x, lib.saf_layernorm_fwd, x2.data_ptr(), x2.stride(0), w.data_ptr(), _ptr(b), out.data_ptr(), out.stride(0),
+                                x2.shape[0], x2.shape[1], float(eps), _dt(x2))
     return out.view(x.shape)
 
 
@@ -760,5 +821,5 @@ def linear_act(x, weight, bias=None, act=None, residual=None):
             raise ValueError("residual must match the output")
         a.residual, a.ldr = r2.data_ptr(), r2.stride(0)
         keep.append(r2)
-    check(lib.saf_indexed_linear_fwd(C.byref(a), _stream(x)))
+    _call(x, lib.saf_indexed_linear_fwd, C.byref(a))
     return out.view(*x.shape[:-1], N)

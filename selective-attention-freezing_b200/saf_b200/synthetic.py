@@ -6,16 +6,7 @@ from types import SimpleNamespace
 import torch
 
 from .attention import SafCausalSelfAttention, rope_tables
-
-WORKLOADS = {
-    # name: layers, heads, head_dim, frozen heads per layer, sequence, batch per GPU
-    "c1": dict(n_layer=12, n_head=12, head_dim=64, n_frozen=3, T=4096, B=16, rope_base=10000.0),
-    "c2": dict(n_layer=12, n_head=12, head_dim=64, n_frozen=3, T=16384, B=4, rope_base=10000.0),
-    "c3": dict(n_layer=24, n_head=16, head_dim=128, n_frozen=4, T=8192, B=2, rope_base=10000.0),
-    # Qwen2.5-1.5B-shaped GQA prefill: 12 query heads on 2 KV heads (attention operator only; kv heads in n_kv)
-    "c4": dict(n_layer=28, n_head=12, n_kv=2, head_dim=128, n_frozen=3, T=8192, B=8, rope_base=1000000.0),
-    "tiny": dict(n_layer=2, n_head=4, head_dim=64, n_frozen=1, T=512, B=2, rope_base=10000.0),
-}
+from .workloads import WORKLOADS  # noqa: F401  (plain data, importable without the CUDA library)
 
 
 def frozen_heads_for_layer(n_head, n_frozen, seed, layer):
@@ -31,24 +22,40 @@ def sink_decay_params(n, seed):
     return a, r
 
 
-def build_attention_stack(name, device, dtype=torch.bfloat16, seed=1337, blocks=False):
+def workload_config(w):
+    C = w["n_head"] * w["head_dim"]
+    return SimpleNamespace(n_embd=C, n_head=w["n_head"], block_size=w["T"], bias=False, dropout=0.0,
+                           position_encoding="rope", rand_attn_prior_repr="dense", freeze_pattern_dtype="bfloat16")
+
+
+def build_attention_layer(w, li, g, seed=1337):
+    """Layer `li` of a workload's stack on the CPU in fp32: weights drawn from generator `g` (the stack's
+    running generator), frozen heads and their (sink weight, decay) from the layer's own seeds."""
+    C = w["n_head"] * w["head_dim"]
+    m = SafCausalSelfAttention(workload_config(w), layer_idx=li)
+    with torch.no_grad():
+        for lin in (m.q_proj, m.k_proj, m.v_proj, m.c_proj):
+            lin.weight.copy_(torch.randn(C, C, generator=g) * 0.02)
+    fz = frozen_heads_for_layer(w["n_head"], w["n_frozen"], seed, li)
+    a, r = sink_decay_params(len(fz), seed + 1000 + li)
+    m.freeze_heads_sink_decay(fz, a.tolist(), r.tolist())
+    return m
+
+
+def build_attention_stack(name, device, dtype=torch.bfloat16, seed=1337, blocks=False, n_layer=None):
     """The attention+projection stack of a GPT-2-style model: one SafCausalSelfAttention per layer with
     random-init N(0, 0.02^2) weights, 25 % of the heads of every layer frozen on seeded sink+decay patterns.
-    blocks=True wraps every layer in its transformer block (LayerNorms, residuals, MLP with 4x expansion)."""
+    blocks=True wraps every layer in its transformer block (LayerNorms, residuals, MLP with 4x expansion);
+    n_layer builds only the first layers (same weights as the full stack's)."""
     w = WORKLOADS[name]
+    if w.get("n_kv") is not None:
+        raise ValueError("workload %r is grouped-query: build it with saf_b200.gqa.build_gqa_stack" % name)
     C = w["n_head"] * w["head_dim"]
-    cfg = SimpleNamespace(n_embd=C, n_head=w["n_head"], block_size=w["T"], bias=False, dropout=0.0,
-                          position_encoding="rope", rand_attn_prior_repr="dense", freeze_pattern_dtype="bfloat16")
+    cfg = workload_config(w)
     g = torch.Generator().manual_seed(seed)
     layers = []
-    for li in range(w["n_layer"]):
-        m = SafCausalSelfAttention(cfg, layer_idx=li)
-        with torch.no_grad():
-            for lin in (m.q_proj, m.k_proj, m.v_proj, m.c_proj):
-                lin.weight.copy_(torch.randn(C, C, generator=g) * 0.02)
-        fz = frozen_heads_for_layer(w["n_head"], w["n_frozen"], seed, li)
-        a, r = sink_decay_params(len(fz), seed + 1000 + li)
-        m.freeze_heads_sink_decay(fz, a.tolist(), r.tolist())
+    for li in range(w["n_layer"] if n_layer is None else n_layer):
+        m = build_attention_layer(w, li, g, seed)
         if blocks:
             from .block import SafBlock
             blk = SafBlock(cfg, layer_idx=li)

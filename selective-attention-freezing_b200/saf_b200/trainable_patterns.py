@@ -28,7 +28,7 @@ def normalisers(alpha, rho, length):
     a = alpha.detach().float().contiguous()
     r = rho.detach().float().contiguous()
     z = torch.empty_like(a)
-    check(lib.saf_pattern_normalisers(a.data_ptr(), r.data_ptr(), z.data_ptr(), H, S, int(length), ops._stream(a)))
+    ops._call(a, lib.saf_pattern_normalisers, a.data_ptr(), r.data_ptr(), z.data_ptr(), H, S, int(length))
     return z.to(alpha.dtype)
 
 
@@ -66,7 +66,8 @@ def pattern_param_grad(grad, out, value, alpha, rho, z, states):
     g.dalpha, g.drho = da.data_ptr(), dr.data_ptr()
     delta = torch.empty((B, H, T), device=value.device, dtype=torch.float32)   # scratch of the tensor-core path
     g.delta = delta.data_ptr()
-    check(lib.saf_pattern_param_grad(C.byref(g), ops._stream(value)))
+    g.status = ops._status_ptr(value.device)
+    ops._call(value, lib.saf_pattern_param_grad, C.byref(g))
     return da.to(alpha.dtype), dr.to(rho.dtype)
 
 

@@ -125,3 +125,32 @@ def test_slab_decomposition_and_pattern_classifier():
         assert got is not None and abs(got[0] - a[i].item()) < 1e-5 and abs(got[1] - r[i].item()) < 1e-5
     rnd = torch.rand(64, 64).tril()
     assert classify_sink_decay(rnd / rnd.sum(-1, keepdim=True)) is None
+
+
+def test_per_device_bookkeeping_self_check():
+    """Kernel attributes and SM counts are remembered per device ordinal (one process may drive several GPUs):
+    the library's host-only self-check walks every ordinal, repeats, forgets one and probes out-of-range ones."""
+    from saf_b200 import _cabi
+    assert _cabi.lib.saf_selftest_per_device_once() == 0
+
+
+def test_static_backward_validates_before_it_applies_its_limit():
+    """A malformed struct is INVALID, not LIMIT; a call that cannot contain a live head has no size limit
+    (it is refused later for its null tensors, not for its size)."""
+    from saf_b200 import _cabi
+    g = _cabi.SafMixedAttnBwdArgs()
+    g.struct_size = C.sizeof(_cabi.SafMixedAttnBwdArgs)
+    g.fwd.struct_size = 8                                   # wrong inner size, huge dims
+    g.fwd.B, g.fwd.H, g.fwd.T, g.fwd.HD = 64, 64, 65536, 64
+    assert _cabi.lib.saf_mixed_attn_bwd_static(C.byref(g), None) == _cabi.SAF_ERR_INVALID
+    g.fwd.struct_size = C.sizeof(_cabi.SafMixedAttnArgs)
+    g.fwd.dtype, g.fwd.force_state, g.fwd.U = _cabi.SAF_BF16, _cabi.SINK_DECAY, 0
+    rc = _cabi.lib.saf_mixed_attn_bwd_static(C.byref(g), None)
+    assert rc == _cabi.SAF_ERR_INVALID and "non-null" in _cabi.last_error()    # no LIMIT for a frozen-only call
+    g.fwd.force_state, g.fwd.U = -1, 4
+    dummy = (C.c_int32 * 64)()
+    g.fwd.frozen = C.cast(dummy, C.c_void_p)
+    g.fwd.v.ptr = g.fwd.out.ptr = g.fwd.q.ptr = g.fwd.k.ptr = C.cast(dummy, C.c_void_p)
+    for t in (g.fwd.v, g.fwd.out, g.fwd.q, g.fwd.k):
+        t.stride[3] = 1
+    assert _cabi.lib.saf_mixed_attn_bwd_static(C.byref(g), None) == _cabi.SAF_ERR_LIMIT

@@ -225,3 +225,46 @@ def test_training_step_under_bf16_autocast(structured):
         rows = slice(h * hd, (h + 1) * hd)
         assert m.q_proj.weight.grad[rows].abs().max().item() == 0.0
         assert m.k_proj.weight.grad[rows].abs().max().item() == 0.0
+
+
+def test_dropout_is_applied_in_training_and_absent_in_eval():
+    """dropout > 0: the reference leaves its fused path while training (nanogpt/model.py:971-974) so that its SDPA
+    half applies attention dropout, and always applies the residual dropout (:1169).  Here: eval output equals
+    the dropout-free module; train-mode outputs differ from it and from one another; with the seed fixed they
+    repeat; frozen heads' Q/K rows still get exactly zero gradient."""
+    import copy
+    B, T, C, H, fz, seed, kind = cases.LAYER_CASES["small_sink"]
+    x, ws = cases.layer_inputs(B, T, C, H, seed)
+    patt, _ = cases.layer_patterns(kind, len(fz), T, seed)
+    m0, rope = build(C, H, T, ws)
+    m0.freeze_heads(fz, patt.cuda(), detect_structured=True)
+    m1 = copy.deepcopy(m0)
+    m1.dropout = 0.25
+    xd = x.cuda()
+    m0.eval()
+    m1.eval()
+    with torch.no_grad():
+        y0, y1 = m0(xd, rope=rope), m1(xd, rope=rope)
+    assert torch.equal(y0, y1)
+    m1.train()
+    torch.manual_seed(11)
+    ya = m1(xd, rope=rope)
+    yb = m1(xd, rope=rope)
+    torch.manual_seed(11)
+    yc = m1(xd, rope=rope)
+    assert not torch.allclose(ya, y0, atol=1e-4) and not torch.allclose(ya, yb, atol=1e-4)
+    assert torch.equal(ya, yc)
+    assert torch.isfinite(ya).all()
+    # same expectation: the mean over many masks approaches the dropout-free output
+    acc = torch.zeros_like(y0)
+    n = 64
+    with torch.no_grad():
+        for _ in range(n):
+            acc += m1(xd, rope=rope)
+    assert O.rel_l2(acc.cpu() / n, y0.cpu()) < 0.25
+    ya.square().sum().backward()
+    hd = m1.head_dim
+    for h in fz:
+        assert m1.q_proj.weight.grad[h * hd:(h + 1) * hd].abs().max().item() == 0.0
+        assert m1.k_proj.weight.grad[h * hd:(h + 1) * hd].abs().max().item() == 0.0
+    assert m1.v_proj.weight.grad.abs().max().item() > 0.0
