@@ -5,6 +5,13 @@ of single kernels are taken from.
 
     python -m saf_b200.opbench --workload c3 --ops attn_fwd,attn_bwd,qk_fwd,qk_bwd,layer_infer,layer_train \
                                [--B 2 --T 8192] [--reps 5] [--frozen sink_decay|dense|decomposed|none]
+                               [--impl ours|ref-triton|sdpa-flash|sdpa-cudnn]
+
+--impl times the same attention call (attn_fwd / attn_bwd) through another implementation on the same box with the
+same CUDA-event protocol: `ref-triton` = the reference's own Triton `fused_mixed_attn` (kernel/fused_attn.py:650-734;
+qwen/kernel/fused_attn.py for grouped-query shapes), loaded from the checkout named by SAF_REFERENCE_ROOT, with the
+frozen heads' patterns stored densely as the reference must hold them; `sdpa-flash` / `sdpa-cudnn` = torch's
+scaled_dot_product_attention on the live heads only, restricted to that backend.
 
 Prints one JSON line per operator: ms, algorithmic TFLOP/s (backward counted as 2.5x / 2x the forward
 FLOPs, as the reference's roofline does) and the library launches of one call.
@@ -37,6 +44,70 @@ def _timed(fn, reps):
     return sorted(ts)[len(ts) // 2]
 
 
+def _load_reference_kernel(gqa):
+    """The reference's kernel package under a private module name (this process already owns `kernel`)."""
+    import importlib.util
+    root = os.environ.get("SAF_REFERENCE_ROOT")
+    if not root:
+        raise SystemExit("--impl ref-triton needs SAF_REFERENCE_ROOT (a checkout of the reference project)")
+    pkg_dir = os.path.join(root, "qwen", "kernel") if gqa else os.path.join(root, "kernel")
+    name = "saf_reference_kernel_gqa" if gqa else "saf_reference_kernel"
+    spec = importlib.util.spec_from_file_location(name, os.path.join(pkg_dir, "__init__.py"),
+                                                  submodule_search_locations=[pkg_dir])
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules[name] = mod
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def _other_attention(impl, q, k, v, patt, frozen, hidx, kw, fz, live, T, gqa):
+    """The same attention call through the reference's Triton kernel or torch SDPA (live heads only)."""
+    dev = q.device
+    H = frozen.numel()
+    if impl == "ref-triton":
+        ref = _load_reference_kernel(gqa)
+        rkw = {n: t for n, t in kw.items() if n in ("alpha", "rho", "z", "pidx", "kvidx")}
+        rfrozen, rpatt = frozen, patt
+        if "sink_decay" in kw:
+            # the reference can hold this pattern family only as dense stored planes (state 1)
+            a, r = kw["sink_decay"]
+            planes = []
+            for h in fz:
+                pl = torch.empty(T, T, device=dev, dtype=torch.bfloat16)
+                for i0 in range(0, T, 2048):
+                    i = torch.arange(i0, min(i0 + 2048, T), device=dev, dtype=torch.float64)[:, None]
+                    j = torch.arange(T, device=dev, dtype=torch.float64)[None, :]
+                    dec = torch.where(i >= j, r[h].double() ** (i - j).clamp(min=0), torch.zeros((), device=dev, dtype=torch.float64))
+                    dec = dec / dec.sum(-1, keepdim=True) * (1.0 - a[h].double())
+                    dec[:, 0] += a[h].double()
+                    pl[i0:i0 + 2048] = dec.to(torch.bfloat16)
+                planes.append(pl)
+            rpatt = torch.stack(planes)
+            pidx = torch.zeros(H, dtype=torch.int32)
+            for s_, h in enumerate(fz):
+                pidx[h] = s_
+            rkw["pidx"] = pidx.to(dev)
+            rfrozen = (frozen != 0).to(torch.int32)
+        if "alpha" in rkw:
+            rkw["rho_band"] = ref.make_rho_band(rkw["rho"])
+        return lambda: ref.fused_mixed_attn(q, k, v, rpatt, rfrozen, hidx, validate=False, **rkw)
+    from torch.nn.attention import SDPBackend, sdpa_kernel
+    backend = SDPBackend.FLASH_ATTENTION if impl == "sdpa-flash" else SDPBackend.CUDNN_ATTENTION
+    li = torch.tensor(live, device=dev)
+    if gqa:
+        kvh = kw["kvidx"].long()[li]
+        kk, vv = k.detach()[:, kvh].contiguous(), v.detach()[:, kvh].contiguous()
+    else:
+        kk, vv = k, v.detach()[:, li].contiguous().requires_grad_(v.requires_grad)
+
+    def run():
+        with sdpa_kernel([backend]):
+            out = torch.nn.functional.scaled_dot_product_attention(q, kk, vv, is_causal=True)
+        return out
+    run.live_only = True
+    return run
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--workload", default="c3")
@@ -45,6 +116,7 @@ def main():
     ap.add_argument("--T", type=int, default=None)
     ap.add_argument("--reps", type=int, default=5)
     ap.add_argument("--frozen", default="sink_decay", choices=["sink_decay", "dense", "decomposed", "none"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "ref-triton", "sdpa-flash", "sdpa-cudnn"])
     ap.add_argument("--trace", action="store_true",
                     help="after the runs, print the per-step clock stamps a library built with -DSAF_FWD_TRACE / "
                          "-DSAF_BWD_TRACE recorded for one CTA (heaviest tile of batch 0, head 0; head 0 must be live)")
@@ -101,6 +173,9 @@ def main():
     def attn():
         return ops.fused_mixed_attn(q, k, v, patt, frozen, hidx, validate=False, **kw)
 
+    if args.impl != "ours":
+        attn = _other_attention(args.impl, q, k, v, patt, frozen, hidx, kw, fz, live, T, gqa)
+
     def qk():
         return ops.linear_rows2(x, w1, w2, None, None, rows, rope=(cos, sin), head_dim=hd)
 
@@ -118,13 +193,14 @@ def main():
             fl = fl_attn
         elif op == "attn_bwd":
             y = attn()
+            gy = dy[:, live].contiguous() if getattr(attn, "live_only", False) else dy
             n0 = ops.launch_count()
-            y.backward(dy, retain_graph=True)
+            y.backward(gy, retain_graph=True)
             n = ops.launch_count() - n0
 
             def run():
                 q.grad = k.grad = v.grad = None
-                y.backward(dy, retain_graph=True)
+                y.backward(gy, retain_graph=True)
             ms = _timed(run, args.reps)
             fl = 2.5 * fl_attn
         elif op == "qk_fwd":
@@ -271,8 +347,8 @@ def main():
             ms = _timed(run, args.reps)
         else:
             raise SystemExit("unknown op %r" % op)
-        print(json.dumps({"op": op, "shape": shape, "ms": round(ms, 4), "tflops": round(fl / ms / 1e9, 1),
-                          "launches": n, **extra}), flush=True)
+        print(json.dumps({"op": op, "impl": args.impl, "shape": shape, "ms": round(ms, 4),
+                          "tflops": round(fl / ms / 1e9, 1), "launches": n, **extra}), flush=True)
 
 
 def print_trace():

@@ -80,6 +80,14 @@ def test_static_scratch_rejects_sizes_past_the_limit():
     from saf_b200 import _cabi
     g = _cabi.SafMixedAttnBwdArgs()
     g.struct_size = C.sizeof(_cabi.SafMixedAttnBwdArgs)
+    # an otherwise well-formed call (the entry validates its arguments before it looks at the size) with live heads
+    g.fwd.struct_size = C.sizeof(_cabi.SafMixedAttnArgs)
+    g.fwd.dtype, g.fwd.force_state, g.fwd.HD, g.fwd.U = _cabi.SAF_BF16, -1, 64, 16
     g.fwd.B, g.fwd.H, g.fwd.T = 8, 16, 16384          # 2,097,152 rows > 1,048,576
+    word = (C.c_int32 * 16)()
+    for t in (g.fwd.q, g.fwd.k, g.fwd.v, g.fwd.out):
+        t.ptr = C.cast(word, C.c_void_p)              # never dereferenced: the call is refused on the host
+        t.stride[3] = 1
+    g.fwd.frozen = C.cast(word, C.c_void_p)
     assert _cabi.lib.saf_mixed_attn_bwd_static(C.byref(g), None) == _cabi.SAF_ERR_LIMIT
     assert "static scratch" in _cabi.last_error()
