@@ -232,6 +232,108 @@ def parity_block(layer, rope, w, x_one):
             "bar": "max_abs <= 2e-2 and rel_l2 <= 1e-2"}
 
 
+def run_train(args, w):
+    """One data-parallel training step per timed step: rank r trains on its own micro-batch of B sequences (weak
+    scaling), gradients averaged by DDP's bucketed NCCL all-reduce overlapped with the backward, fp32 AdamW.
+    `value`: token ids resident on the device; `e2e`: ids and targets copied from pinned host memory and the loss
+    read back every step.  At N > 1 the same steps are timed once more without the gradient synchronisation to
+    report the share of the step the all-reduce costs."""
+    import saf_b200  # noqa: F401
+    from saf_b200 import ops, parallel, train_step
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
+    rank, world, local = parallel.init()
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    warmup, steps = max(args.warmup, 3), max(args.steps, 1)
+    vocab = 50257
+    model, w = train_step.build_training_model(args.workload, dev, n_layer=args.layers, vocab_size=vocab)
+    n_layer = len(model.transformer.h)
+    ts = train_step.TrainStep(model)
+    B, T = w["B"], w["T"]
+    g = torch.Generator().manual_seed(1000 + rank)
+    ids_host = torch.randint(0, vocab, (2, B, T), generator=g, dtype=torch.int64).pin_memory()   # ids, targets
+    ids_dev = ids_host.to(dev, non_blocking=True)
+    loss_host = torch.zeros(1, dtype=torch.float32).pin_memory()
+
+    def timed(fn, n):
+        parallel.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        parallel.barrier()
+        return parallel.max_over_ranks(e0.elapsed_time(e1), dev)
+
+    def step_resident(sync=True):
+        return ts.step(ids_dev[0], ids_dev[1], sync=sync)
+
+    def step_e2e():
+        buf = ids_host.to(dev, non_blocking=True)
+        loss = ts.step(buf[0], buf[1])
+        loss_host.copy_(loss.float().reshape(1), non_blocking=True)
+
+    for _ in range(warmup):
+        step_resident()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    n0 = ops.launch_count()
+    ops.attention_timing(True)
+    total_ms = timed(step_resident, steps)
+    attn_events = ops.attention_timing(False)
+    launches = ops.launch_count() - n0
+    clocks = sampler.stop() if rank == 0 else None
+    attn_ms = [a.elapsed_time(b) for a, b in attn_events]
+    e2e_ms = timed(step_e2e, steps)
+    nosync_ms = timed(lambda: step_resident(sync=False), steps) if world > 1 else None
+    torch.cuda.synchronize()
+    final_loss = float(loss_host.item())
+    status = ops.device_status(dev)
+    tokens = parallel.sum_over_ranks(B * T, dev)
+    parallel.finalize()
+    if rank != 0:
+        return
+    ms_per_step = total_ms / steps
+    peak_tf, peak_burst_tf, _, peak_kind = measured_peaks()
+    wl = dict(w, n_layer=n_layer)
+    flops = train_step.train_flops_per_sequence(wl, vocab) * B
+    live_fwd = 2.0 * B * (w["n_head"] - w["n_frozen"]) * T * T * w["head_dim"]
+    attn_mean = statistics.mean(attn_ms) if attn_ms else float("nan")
+    achieved = live_fwd / (attn_mean * 1e-3) / 1e12
+    n_params = sum(p.numel() for p in model.parameters())
+    line = {
+        "metric": "training tokens/s, SAF-25% GPT (24 x [16 heads x 128], d=2048), T=8192, forward + backward + AdamW",
+        "value": tokens / (ms_per_step * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": steps, "warmup": warmup,
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"{args.workload}: training step, {n_layer} layers x {w['n_head']} heads x {w['head_dim']}, "
+                               f"{w['n_frozen']} sink+decay frozen heads per layer, MLP 4x, vocab {vocab}, T={T}, "
+                               f"micro-batch {B} per GPU, bf16 autocast, fp32 AdamW, DDP (find_unused_parameters) over NCCL",
+                   "l2": "activations of one layer (x 67 MB, qkv 168 MB, MLP hidden 268 MB) exceed the 126 MB L2"},
+        "timing": "CUDA events on the launching stream, max over ranks",
+        "clocks": clocks,
+        "e2e": {"value": tokens / (e2e_ms / steps * 1e-3), "unit": "tokens/s",
+                "h2d_bytes_per_step": ids_host.numel() * ids_host.element_size(), "d2h_bytes_per_step": 4},
+        "gpu_launches": launches,
+        "roofline": {"bound": "tensor", "kernel": "mixed-attention forward launch inside the training step",
+                     "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s", "frac": achieved / peak_tf,
+                     "peak_kind": f"{peak_kind} sustained dense bf16 (kernel timed inside a long step)",
+                     "frac_of_burst_peak": achieved / peak_burst_tf, "traffic": None,
+                     "flops_per_launch": live_fwd, "ms_per_launch": attn_mean, "launches_timed": len(attn_ms)},
+        "step": {"tflops": flops / (ms_per_step * 1e-3) / 1e12, "frac_of_peak": flops / (ms_per_step * 1e-3) / 1e12 / peak_tf,
+                 "parameters": n_params, "gradient_bytes_all_reduced": 4 * n_params if world > 1 else 0,
+                 "ms_per_step_without_gradient_sync": None if nosync_ms is None else nosync_ms / steps,
+                 "all_reduce_share_of_step": None if nosync_ms is None else max(0.0, 1.0 - nosync_ms / total_ms),
+                 "final_loss": final_loss, "device_status": status},
+    }
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -240,15 +342,22 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--scope", default="stack", choices=["stack", "block", "model"],
+    ap.add_argument("--scope", default="stack", choices=["stack", "block", "model", "train"],
                     help="stack: attention+projection stack (the metric's target); block: whole transformer blocks "
                          "(LayerNorms, residuals, MLP added); model: token ids -> embedding -> blocks -> final "
-                         "LayerNorm -> last-position logits")
+                         "LayerNorm -> last-position logits; train: one data-parallel training step of the whole "
+                         "model (forward + backward under bf16 autocast, fp32 AdamW, DDP gradient all-reduce over "
+                         "NCCL), normally with --workload c3")
+    ap.add_argument("--layers", type=int, default=None, help="train scope: build only this many layers (debugging)")
     args = ap.parse_args()
 
     w = load_workloads()[args.workload]
     if args.impl == "reference":
         run_reference(args, w)          # CPU only: the package and its CUDA library are never imported here
+        return
+
+    if args.scope == "train":
+        run_train(args, w)
         return
 
     import saf_b200  # noqa: F401
@@ -269,7 +378,7 @@ def main():
         B, T, C = w["B"], w["T"], w["n_head"] * w["head_dim"]
         x_host = torch.randint(0, model.config.vocab_size, (B, T), generator=g, dtype=torch.int32).pin_memory()
         last_host = torch.empty(B, model.config.vocab_size, dtype=torch.bfloat16).pin_memory()
-        run = lambda xin: model(xin)[:, 0, :]             # (B, vocab)
+        run = lambda xin: model(xin)[0][:, 0, :]          # (B, vocab)
         result_of = lambda out: out
     else:
         layers, rope, w = synthetic.build_attention_stack(args.workload, dev, blocks=(args.scope == "block"))

@@ -20,7 +20,7 @@
 extern "C" {
 #endif
 
-#define SAF_ABI_VERSION 1
+#define SAF_ABI_VERSION 2
 
 enum SafStatus {
   SAF_OK = 0,
@@ -85,6 +85,13 @@ typedef struct SafMixedAttnArgs {
   const float* rope_sin;
   int32_t* status;         /* optional device int32; a kernel that gave up on a
                               bounded wait writes a non-zero code here              */
+  int32_t* sched;          /* optional device int32[2], ZERO on entry, private to this
+                              call while it runs: the tile queue of the persistent
+                              forward kernel (one CTA per SM pulling row-tile pairs;
+                              the kernel leaves both words zero again, so a caller may
+                              reuse them for its next call on the same stream).  Null:
+                              one CTA per row-tile pair, no scratch at all.  The
+                              backward ignores it.                                   */
 } SafMixedAttnArgs;
 
 int saf_mixed_attn_fwd(const SafMixedAttnArgs* args, void* stream);

@@ -34,10 +34,19 @@
 #include "dense_pv_body.cuh"
 #include "scan_body.cuh"
 #include "sm100_prims.cuh"
+#include <stdlib.h>
 #include <string.h>
+
+#include <algorithm>
 
 namespace saf {
 namespace {
+
+// a build-free off switch for measurements: NAME=0 in the environment
+bool getenv_off(const char* name) {
+  const char* v = getenv(name);
+  return v && v[0] == '0' && v[1] == 0;
+}
 
 constexpr int FM = 128;             // rows per query tile
 constexpr int FN = 128;             // keys per step
@@ -69,6 +78,10 @@ struct Cfg {
   static constexpr int SMEM_FLASH = 1024 + Q_BYTES + RING_BYTES + 4096;
   // the dense-pattern role of the same launch needs its own ring
   static constexpr int SMEM_BYTES = SMEM_FLASH > DpCfg<HD>::SMEM_BYTES ? SMEM_FLASH : DpCfg<HD>::SMEM_BYTES;
+  // persistent kernel: Q, rings, two 16 KB output staging buffers, barriers
+  static constexpr int SMEM_PERSIST_OWN = 1024 + Q_BYTES + RING_BYTES + 2 * 128 * 128 + 1024;
+  static constexpr int SMEM_PERSIST = SMEM_PERSIST_OWN > DpCfg<HD>::SMEM_BYTES ? SMEM_PERSIST_OWN : DpCfg<HD>::SMEM_BYTES;
+  static_assert(SMEM_PERSIST_OWN <= 232448, "persistent kernel exceeds the 227 KB of shared memory per CTA");
   static constexpr int TMEM_COLS = 512;
   static constexpr int NBUF = (HD == 64) ? 3 : 2;      // score buffers
   static constexpr int O_COL = NBUF * 128;
@@ -95,6 +108,10 @@ struct FlashParams {
   const void *alpha, *rho, *z;   // decomposed (H, S), state 2
   int64_t alpha_s[2], rho_s[2], z_s[2];
   int dec_dtype;
+  // persistent live-tile role: dynamic tile queue over the live heads only
+  int* sched;                // [0] next item, [1] CTAs that have seen the end; zero on entry, left zero
+  int n_items, U, lead;      // live items B * U * n_pairs; live heads; CTAs in front of the persistent ones
+  uint8_t live_head[64];     // head of live slot u
 };
 
 struct FlashBars {
@@ -694,6 +711,500 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
   if (warp == 9) tmem_dealloc(tmem, C::TMEM_COLS);
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// Persistent live-tile kernel.  Same warp roles, tiles and softmax as flash_fwd_kernel above, but a CTA stays on
+// its SM and pulls (batch, live head, row-tile pair) items from a queue: TMEM and barriers are set up once, the
+// K/V rings and the score buffers keep rotating across items, and while the softmax warpgroups finish an item
+// (last P V, O / l, TMA store) the producer and the issuing warps are already loading and multiplying the next
+// one.  A one-shot CTA pays about 10 us of set-up, pipeline fill and drain per tile pair (measured: slope of
+// the launch time over the CTA count); this removes most of it.
+//
+// The queue is an atomic counter in two ints the caller provides (zero on entry): items are handed out in the
+// order the one-shot launch uses (head groups, heaviest row pairs first), so the balance is the same greedy
+// longest-first schedule.  The last CTA to see the end of the queue sets both ints back to zero.
+//
+//   warp 8      TMA and queue: claims the next item only when it has issued every load of the current one (an
+//               item claimed early would sit in this CTA while other SMs run dry), publishes it in a 2-slot
+//               ring in shared memory (w_full / w_empty), then Q_0, K_0, Q_1, (K_{j+1}, V_j); Q_t of the next
+//               item lands as soon as the last score product of tile t has retired (q_free, an MMA commit)
+//   warp 9      scores, warp 10 outputs: as above, with running tile counters instead of per-CTA ones
+//   warps 0-7   softmax; the epilogue releases O_t (o_free) as soon as it sits in registers and stages the
+//               tile through its own 16 KB buffer (64 columns at a time), so Q is never held back by a store
+// Score tiles of an item are produced in the order (0,0) (1,0) (0,1) (1,1) ... with the extra diagonal step
+// of tile 1 last, so every index of the running counter is a real tile and barrier phases follow from it.
+struct PersistBars {
+  uint64_t q_full[2], q_free[2];
+  uint64_t k_full[4], k_empty[4], v_full[4], v_empty[4];
+  uint64_t s_full[3], p_full[3], buf_free[3];
+  uint64_t o_free[2];
+  uint64_t w_full[2], w_empty[2];
+  volatile int32_t work[2];
+  uint32_t tmem_base;
+};
+constexpr int W_CONSUMERS = 10;   // warps 9, 10 and the eight softmax warps, one arrival each
+constexpr int O_STAGE_BYTES = 128 * 128;   // 128 rows x 64 bf16 columns, per query tile
+
+struct TileGeom {
+  int b, h, mp, row0, nkv0, nkv1, nkv, n_prod;
+  bool act1;
+};
+
+__device__ __forceinline__ TileGeom decode_item(const FlashParams& p, int li) {
+  TileGeom g;
+  const int per_group = HEAD_GROUP * p.n_pairs;
+  const int grp = li / per_group;
+  const int gsize = min(HEAD_GROUP, p.B * p.U - grp * HEAD_GROUP);
+  const int rem = li - grp * per_group;
+  g.mp = p.n_pairs - 1 - rem / gsize;
+  const int bu = grp * HEAD_GROUP + rem % gsize;
+  g.b = bu / p.U;
+  g.h = p.live_head[bu % p.U];
+  g.row0 = g.mp * 2 * FM;
+  g.act1 = g.row0 + FM < p.T;
+  g.nkv0 = 2 * g.mp + 1;
+  g.nkv1 = g.act1 ? 2 * g.mp + 2 : 0;
+  g.nkv = g.act1 ? g.nkv1 : g.nkv0;
+  g.n_prod = g.nkv0 + g.nkv1;
+  return g;
+}
+// (tile, key step) of the idx-th score tile of an item
+__device__ __forceinline__ void tile_of(const TileGeom& g, int idx, int& t, int& j) {
+  if (!g.act1) { t = 0; j = idx; }
+  else if (idx == 2 * g.nkv0) { t = 1; j = g.nkv0; }
+  else { t = idx & 1; j = idx >> 1; }
+}
+
+template <int HD>
+__global__ void __launch_bounds__(FLASH_THREADS, 1)
+flash_fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
+                            const __grid_constant__ CUtensorMap mapV, const __grid_constant__ CUtensorMap mapO,
+                            const __grid_constant__ CUtensorMap mapP, const __grid_constant__ CUtensorMap mapV64,
+                            const __grid_constant__ FlashParams p) {
+  using C = Cfg<HD>;
+  const int bh_count = p.B * p.H;
+  if ((int)blockIdx.x < bh_count) {          // scan slots, as in flash_fwd_kernel
+    const int b = blockIdx.x / p.H, h = blockIdx.x % p.H;
+    const int state = p.force_state >= 0 ? p.force_state : p.frozen[h];
+    if (state == SAF_SINK_DECAY && p.has_scan && threadIdx.x < SCAN_NT)
+      for (int col0 = 0; col0 < HD; col0 += SCAN_COLS) sink_decay_scan_cta<__nv_bfloat16, false>(p.scan, b, h, col0);
+    return;
+  }
+  if ((int)blockIdx.x < bh_count + p.dense_slots) {   // dense-pattern role
+    extern __shared__ uint8_t dense_smem_raw[];
+    uint8_t* dsm = (uint8_t*)(((uintptr_t)dense_smem_raw + 1023) & ~(uintptr_t)1023);
+    dense_pv_cta<HD>(mapP, mapV64, mapO, p.dense, (int)blockIdx.x - bh_count, dsm);
+    return;
+  }
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* sQ = smem;
+  uint8_t* sK = smem + C::Q_BYTES;
+  uint8_t* sV = sK + C::KSTAGE * C::TILE_BYTES;
+  uint8_t* sO = sK + C::RING_BYTES;                       // 2 x O_STAGE_BYTES
+  PersistBars* bars = reinterpret_cast<PersistBars*>(sO + 2 * O_STAGE_BYTES);
+  const int tid = threadIdx.x, warp = tid >> 5;
+
+  if (tid == 0) {
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(&bars->q_full[t], 1);
+      mbar_init(&bars->q_free[t], 1);
+      mbar_init(&bars->o_free[t], 128);
+      mbar_init(&bars->w_full[t], 1);
+      mbar_init(&bars->w_empty[t], W_CONSUMERS);
+    }
+    for (int s = 0; s < C::KSTAGE; ++s) {
+      mbar_init(&bars->k_full[s], 1);
+      mbar_init(&bars->k_empty[s], 1);
+      mbar_init(&bars->v_full[s], 1);
+      mbar_init(&bars->v_empty[s], 1);
+    }
+    for (int i = 0; i < 3; ++i) {
+      mbar_init(&bars->s_full[i], 1);
+      mbar_init(&bars->p_full[i], 128);
+      mbar_init(&bars->buf_free[i], 1);
+    }
+    fence_mbar_init();
+  }
+  if (warp == 9) {
+    tmem_alloc(&bars->tmem_base, C::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = bars->tmem_base;
+
+  // next item of this CTA's sequence (n-th fetch); -1 = queue empty, -2 = the wait ran out.  `arrive`: this
+  // thread reports the slot as read (one thread per consumer warp)
+  auto fetch = [&](int n, bool arrive) -> int {      // whole warp
+    const int slot = n & 1;
+    if (!mbar_wait(&bars->w_full[slot], (n >> 1) & 1)) return -2;
+    const int it = bars->work[slot];
+    __syncwarp();                                      // every lane has read the slot before it is handed back
+    if (arrive) mbar_arrive(&bars->w_empty[slot]);
+    return it;
+  };
+  if (warp >= 8) {
+    reg_dec<56>();
+    const bool leader = elect_one();
+    if (warp == 8) {
+      // ---------------------------------------------------------- TMA producer and tile queue
+      if (leader) {
+        tma_prefetch_desc(&mapQ);
+        tma_prefetch_desc(&mapK);
+        tma_prefetch_desc(&mapV);
+        uint32_t kc = 0, vc = 0, use_q[2] = {0, 0};
+        bool ok = true;
+        for (int n = 0; ok; ++n) {
+          // claim the next item and publish it to the other warps
+          const int slot = n & 1;
+          if (n >= 2 && !mbar_wait(&bars->w_empty[slot], ((n >> 1) & 1) ^ 1)) {
+            dev_set_error(p.status, SAF_DEV_TIMEOUT_TMA, 40);
+            bars->work[slot] = -1;
+            mbar_arrive(&bars->w_full[slot]);
+            break;
+          }
+          const int idx = atomicAdd(p.sched, 1);
+          const int it = idx < p.n_items ? idx : -1;
+          bars->work[slot] = it;
+          mbar_arrive(&bars->w_full[slot]);
+          if (it < 0) {
+            const int seen = atomicAdd(p.sched + 1, 1);
+            if (seen == (int)gridDim.x - p.lead - 1) {   // every persistent CTA has reached the end of the queue
+              p.sched[0] = 0;
+              p.sched[1] = 0;
+            }
+            break;
+          }
+          const TileGeom g = decode_item(p, it);
+          const int hq = p.hidx ? p.hidx[g.h] : g.h;
+          const int hk = (p.HKV > 0) ? p.kvidx[g.h] : hq;
+          const int hv = (p.HKV > 0) ? p.kvidx[g.h] : g.h;
+          auto load_q = [&](int t) {
+            if (use_q[t] > 0 && !mbar_wait(&bars->q_free[t], (use_q[t] - 1) & 1)) {
+              dev_set_error(p.status, SAF_DEV_TIMEOUT_TMA, 42);
+              ok = false;
+              return;
+            }
+            mbar_expect_tx(&bars->q_full[t], C::TILE_BYTES);
+            load_tile<HD>(sQ + t * C::TILE_BYTES, &mapQ, &bars->q_full[t], g.row0 + t * FM, hq, g.b);
+            ++use_q[t];
+          };
+          auto load_k = [&](int j) {
+            const int s = kc & (C::KSTAGE - 1);
+            if (!mbar_wait(&bars->k_empty[s], ((kc / C::KSTAGE) & 1) ^ 1)) {
+              dev_set_error(p.status, SAF_DEV_TIMEOUT_TMA, 43);
+              ok = false;
+              return;
+            }
+            mbar_expect_tx(&bars->k_full[s], C::TILE_BYTES);
+            load_tile<HD>(sK + s * C::TILE_BYTES, &mapK, &bars->k_full[s], j * FN, hk, g.b);
+            ++kc;
+          };
+          auto load_v = [&](int j) {
+            const int s = vc & (C::KSTAGE - 1);
+            if (!mbar_wait(&bars->v_empty[s], ((vc / C::KSTAGE) & 1) ^ 1)) {
+              dev_set_error(p.status, SAF_DEV_TIMEOUT_TMA, 44);
+              ok = false;
+              return;
+            }
+            mbar_expect_tx(&bars->v_full[s], C::TILE_BYTES);
+            load_tile<HD>(sV + s * C::TILE_BYTES, &mapV, &bars->v_full[s], j * FN, hv, g.b);
+            ++vc;
+          };
+          load_q(0);
+          if (ok) load_k(0);
+          if (ok && g.act1) load_q(1);
+          for (int j = 0; j < g.nkv && ok; ++j) {
+            if (j + 1 < g.nkv) load_k(j + 1);
+            if (ok) load_v(j);
+          }
+        }
+      }
+    } else if (warp == 9) {
+      // ---------------------------------------------------------- score MMA issuer
+      const uint32_t idesc_s = umma_idesc_bf16(FM, FN, 0, 0);
+      const uint32_t qaddr0 = smem_u32(sQ), kbase = smem_u32(sK);
+      uint32_t gs = 0, kc = 0, use_q[2] = {0, 0};
+      bool ok = true;
+      for (int n = 0; ok; ++n) {
+        const int it = fetch(n, leader);
+        if (it < 0) {
+          if (it == -2) dev_set_error(p.status, SAF_DEV_TIMEOUT_MMA, 45);
+          break;
+        }
+        const TileGeom g = decode_item(p, it);
+        int k_waited = -1;
+        bool q_waited[2] = {false, false};
+        for (int idx = 0; idx < g.n_prod; ++idx, ++gs) {
+          int t, j;
+          tile_of(g, idx, t, j);
+          if (!q_waited[t]) {
+            if (!mbar_wait(&bars->q_full[t], use_q[t] & 1)) {
+              dev_set_error(p.status, SAF_DEV_TIMEOUT_MMA, 46);
+              ok = false;
+              break;
+            }
+            q_waited[t] = true;
+          }
+          const uint32_t kt = kc + j;
+          const int ks_ = kt & (C::KSTAGE - 1);
+          if (j > k_waited) {
+            if (!mbar_wait(&bars->k_full[ks_], (kt / C::KSTAGE) & 1)) {
+              dev_set_error(p.status, SAF_DEV_TIMEOUT_MMA, 47);
+              ok = false;
+              break;
+            }
+            k_waited = j;
+          }
+          const uint32_t buf = gs % C::NBUF;
+          if (gs >= (uint32_t)C::NBUF && !mbar_wait(&bars->buf_free[buf], ((gs / C::NBUF) & 1) ^ 1)) {
+            dev_set_error(p.status, SAF_DEV_TIMEOUT_MMA, 48);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t qa = qaddr0 + t * C::TILE_BYTES, ka = kbase + ks_ * C::TILE_BYTES;
+          const uint32_t d = tmem + buf * FN;
+          if (leader) {
+#pragma unroll
+            for (int ks = 0; ks < HD / 16; ++ks) {
+              const uint32_t off = (ks >> 2) * 16384 + (ks & 3) * 32;
+              umma_ss(d, umma_smem_desc_sw128(qa + off, 16, 1024), umma_smem_desc_sw128(ka + off, 16, 1024), idesc_s,
+                      ks > 0);
+            }
+            umma_commit(&bars->s_full[buf]);
+            if (t == 1 || !g.act1) umma_commit(&bars->k_empty[ks_]);   // last reader of K_j
+            if (j == (t ? g.nkv1 : g.nkv0) - 1) umma_commit(&bars->q_free[t]);   // last reader of Q_t
+          }
+          __syncwarp();
+        }
+        kc += g.nkv;
+        ++use_q[0];
+        if (g.act1) ++use_q[1];
+      }
+    } else if (warp == 10) {
+      // ---------------------------------------------------------- output MMA issuer
+      const uint32_t idesc_o = umma_idesc_bf16(FM, HD, 0, 1);
+      const uint32_t vbase = smem_u32(sV);
+      uint32_t gs = 0, vc = 0, use_o[2] = {0, 0};
+      bool ok = true;
+      for (int n = 0; ok; ++n) {
+        const int it = fetch(n, leader);
+        if (it < 0) {
+          if (it == -2) dev_set_error(p.status, SAF_DEV_TIMEOUT_MMA, 49);
+          break;
+        }
+        const TileGeom g = decode_item(p, it);
+        int v_waited = -1;
+        for (int idx = 0; idx < g.n_prod; ++idx, ++gs) {
+          int t, j;
+          tile_of(g, idx, t, j);
+          const uint32_t vt = vc + j;
+          const int vs_ = vt & (C::KSTAGE - 1);
+          if (j > v_waited) {
+            if (!mbar_wait(&bars->v_full[vs_], (vt / C::KSTAGE) & 1)) {
+              dev_set_error(p.status, SAF_DEV_TIMEOUT_MMA, 50);
+              ok = false;
+              break;
+            }
+            v_waited = j;
+          }
+          // the epilogue of the previous item must have taken O_t out of TMEM before it is overwritten
+          if (j == 0 && use_o[t] > 0 && !mbar_wait(&bars->o_free[t], (use_o[t] - 1) & 1)) {
+            dev_set_error(p.status, SAF_DEV_TIMEOUT_MMA, 51);
+            ok = false;
+            break;
+          }
+          const uint32_t buf = gs % C::NBUF;
+          if (!mbar_wait(&bars->p_full[buf], (gs / C::NBUF) & 1)) {
+            dev_set_error(p.status, SAF_DEV_TIMEOUT_MMA, 52);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t va = vbase + vs_ * C::TILE_BYTES;
+          const uint32_t dO = tmem + C::O_COL + t * HD, aP = tmem + buf * FN;
+          if (leader) {
+#pragma unroll
+            for (int ks = 0; ks < FN / 16; ++ks)
+              umma_ts(dO, aP + ks * 8, umma_smem_desc_sw128(va + ks * 2048, 16384, 1024), idesc_o, (j > 0) || (ks > 0));
+            umma_commit(&bars->buf_free[buf]);
+            if (t == 1 || !g.act1) umma_commit(&bars->v_empty[vs_]);   // last reader of V_j
+          }
+          __syncwarp();
+        }
+        vc += g.nkv;
+        ++use_o[0];
+        if (g.act1) ++use_o[1];
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ softmax warpgroups
+    reg_inc<224>();
+    const int t = warp >> 2;
+    const int r = tid & 127;
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+    const uint32_t tO = tmem + lane_base + C::O_COL + t * HD;
+    const float sc = p.scale_log2;
+    const bool warp_lead = (tid & 31) == 0;
+    uint32_t g_base = 0;
+    bool ok = true;
+    for (int n = 0; ok; ++n) {
+      const int it = fetch(n, warp_lead);
+      if (it < 0) {
+        if (it == -2) dev_set_error(p.status, SAF_DEV_TIMEOUT_SOFTMAX, 53);
+        break;
+      }
+      const TileGeom g = decode_item(p, it);
+      const int nk = t ? g.nkv1 : g.nkv0;
+      if (nk > 0) {
+        float m_ref = -INFINITY, l = 0.f;
+        uint32_t pbuf = 0, pph = 0;
+        for (int j = 0; j < nk; ++j) {
+          const uint32_t gi = g_base + (g.act1 ? ((t == 1 && j == g.nkv0) ? 2 * g.nkv0 : 2 * j + t) : j);
+          const uint32_t buf = gi % C::NBUF, bph = (gi / C::NBUF) & 1;
+          const uint32_t tS = tmem + lane_base + buf * FN;
+          if (!mbar_wait(&bars->s_full[buf], bph)) {
+            dev_set_error(p.status, SAF_DEV_TIMEOUT_SOFTMAX, 54);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          uint32_t s[4][32];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) tmem_ld32(tS + q * 32, s[q]);
+          tmem_ld_wait();
+          if (j == nk - 1) {  // diagonal tile: keys after the row are masked
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                if (q * 32 + i > r) s[q][i] = 0xff800000u;
+          }
+          float mx0 = __uint_as_float(s[0][0]), mx1 = __uint_as_float(s[1][0]);
+          float mx2 = __uint_as_float(s[2][0]), mx3 = __uint_as_float(s[3][0]);
+#pragma unroll
+          for (int i = 1; i < 31; i += 2) {
+            mx0 = fmax3(mx0, __uint_as_float(s[0][i]), __uint_as_float(s[0][i + 1]));
+            mx1 = fmax3(mx1, __uint_as_float(s[1][i]), __uint_as_float(s[1][i + 1]));
+            mx2 = fmax3(mx2, __uint_as_float(s[2][i]), __uint_as_float(s[2][i + 1]));
+            mx3 = fmax3(mx3, __uint_as_float(s[3][i]), __uint_as_float(s[3][i + 1]));
+          }
+          mx0 = fmax3(mx0, __uint_as_float(s[0][31]), __uint_as_float(s[1][31]));
+          mx2 = fmax3(mx2, __uint_as_float(s[2][31]), __uint_as_float(s[3][31]));
+          const float mx = fmax3(mx0, mx1, fmaxf(mx2, mx3)) * sc;
+          if (j == 0) {
+            m_ref = mx;
+          } else {
+            const bool need = mx > m_ref + RESCALE_THRESHOLD;
+            if (__any_sync(0xffffffffu, need)) {
+              if (!mbar_wait(&bars->buf_free[pbuf], pph)) {
+                dev_set_error(p.status, SAF_DEV_TIMEOUT_SOFTMAX, 55);
+                ok = false;
+                break;
+              }
+              tc_fence_after();
+              const float f = need ? ex2(m_ref - mx) : 1.f;
+              if (need) m_ref = mx;
+              l *= f;
+#pragma unroll
+              for (int c0 = 0; c0 < HD; c0 += 32) {
+                uint32_t o[32];
+                tmem_ld32(tO + c0, o);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
+                tmem_st32(tO + c0, o);
+              }
+            }
+          }
+          const float2 sc2 = make_float2(sc, sc), nm2 = make_float2(-m_ref, -m_ref);
+          float2 acc0 = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            uint32_t pk[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const float2 x = __ffma2_rn(make_float2(__uint_as_float(s[q][2 * i]), __uint_as_float(s[q][2 * i + 1])), sc2, nm2);
+              float2 e;
+              if (i < SAF_POLY_EXP_PER_16 / 2) {
+                e = exp2_poly2(x);
+              } else {
+                e.x = ex2(x.x);
+                e.y = ex2(x.y);
+              }
+              if (i & 1) acc1 = __fadd2_rn(acc1, e);
+              else acc0 = __fadd2_rn(acc0, e);
+              pk[i] = pack_bf16(e.x, e.y);
+            }
+            tmem_st16(tS + q * 16, pk);
+          }
+          acc0 = __fadd2_rn(acc0, acc1);
+          l += acc0.x + acc0.y;
+          tmem_st_wait();
+          tc_fence_before();
+          mbar_arrive(&bars->p_full[buf]);
+          pbuf = buf;
+          pph = bph;
+        }
+        if (!ok) break;
+        // ---- epilogue of tile t: O / l -> bf16 -> the tile's own Q buffer -> TMA store
+        if (!mbar_wait(&bars->buf_free[pbuf], pph)) {
+          dev_set_error(p.status, SAF_DEV_TIMEOUT_SOFTMAX, 56);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const float inv = 1.f / l;
+        uint8_t* stage = sO + t * O_STAGE_BYTES;
+        const int trow = g.row0 + t * FM;
+#pragma unroll
+        for (int hh = 0; hh < HD / 64; ++hh) {
+          // the staging buffer is free once the store that last read it (previous half or previous item) is done
+          if (r == 0) tma_store_wait_read();
+          named_bar_sync(1 + t, 128);
+#pragma unroll
+          for (int c0 = hh * 64; c0 < hh * 64 + 64; c0 += 32) {
+            uint32_t o[32];
+            tmem_ld32(tO + c0, o);
+            tmem_ld_wait();
+            if (c0 + 32 >= HD) {   // O_t is in registers: the next item may overwrite it
+              tc_fence_before();
+              mbar_arrive(&bars->o_free[t]);
+            }
+            uint8_t* dst = stage + r * 128;
+            const int cbase = (c0 & 63) >> 3;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              uint4 q;
+              q.x = pack_bf16(__uint_as_float(o[c * 8 + 0]) * inv, __uint_as_float(o[c * 8 + 1]) * inv);
+              q.y = pack_bf16(__uint_as_float(o[c * 8 + 2]) * inv, __uint_as_float(o[c * 8 + 3]) * inv);
+              q.z = pack_bf16(__uint_as_float(o[c * 8 + 4]) * inv, __uint_as_float(o[c * 8 + 5]) * inv);
+              q.w = pack_bf16(__uint_as_float(o[c * 8 + 6]) * inv, __uint_as_float(o[c * 8 + 7]) * inv);
+              *reinterpret_cast<uint4*>(dst + (((cbase + c) ^ (r & 7)) << 4)) = q;
+            }
+          }
+          fence_proxy_async_smem();
+          named_bar_sync(1 + t, 128);
+          if (r == 0) {
+            tma_store_4d(&mapO, stage, hh * 64, trow, g.h, g.b);
+            tma_store_commit();
+          }
+        }
+        if (p.lse && trow + r < p.T)
+          p.lse[(int64_t)g.b * p.lse_s[0] + (int64_t)g.h * p.lse_s[1] + (int64_t)(trow + r) * p.lse_s[2]] = m_ref + log2f(l);
+      }
+      g_base += g.n_prod;
+    }
+    if (r == 0) tma_store_wait_all();
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 9) tmem_dealloc(tmem, C::TMEM_COLS);
+}
+
 bool aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
 
 bool tma_ok(const SafTensor& t) {
@@ -771,9 +1282,36 @@ int launch_typed(const SafMixedAttnArgs& a, uint32_t want, cudaStream_t st) {
     s.B = a.B; s.H = a.H; s.T = a.T; s.HD = a.HD; s.force_state = a.force_state; s.HKV = a.HKV;
     s.vec_ok = 1;   // tma_ok() already demands 16-byte aligned bases and strides
   }
+  const int bh = a.B * a.H;
+  // Persistent live-tile kernel: needs the caller's two-int queue scratch and the head states on the host (the
+  // queue walks live heads only); calls whose frozen heads are produced by the softmax warps (fp32-stored
+  // patterns and the like) keep the one-shot kernel, which has that role.
+  bool persistent = a.sched && any_live && a.frozen_host && a.force_state < 0 && !p.patt && !p.alpha && a.U <= 64 &&
+                    !getenv_off("SAF_B200_PERSISTENT");
+  if (persistent) {
+    int u = 0;
+    for (int h = 0; h < a.H && persistent; ++h)
+      if (a.frozen_host[h] == SAF_LIVE) {
+        if (u < 64 && h < 256) p.live_head[u++] = (uint8_t)h;
+        else persistent = false;
+      }
+    if (u != a.U || u == 0) persistent = false;
+  }
+  if (persistent) {
+    p.sched = a.sched;
+    p.U = a.U;
+    p.n_items = a.B * a.U * p.n_pairs;
+    p.lead = bh + p.dense_slots;
+    static PerDeviceOnce smem_once_p;
+    if ((rc = ensure_dyn_smem(flash_fwd_persistent_kernel<HD>, Cfg<HD>::SMEM_PERSIST, smem_once_p))) return rc;
+    const int workers = std::min(device_sm_count(), p.n_items);
+    const unsigned grid = (unsigned)(p.lead + workers);
+    flash_fwd_persistent_kernel<HD><<<grid, FLASH_THREADS, Cfg<HD>::SMEM_PERSIST, st>>>(mq, mk, mv, mo, mpat, mv64, p);
+    count_launch();
+    return check_launch("flash_fwd_persistent_kernel");
+  }
   static PerDeviceOnce smem_once;
   if ((rc = ensure_dyn_smem(flash_fwd_kernel<HD>, Cfg<HD>::SMEM_BYTES, smem_once))) return rc;
-  const int bh = a.B * a.H;
   const int groups = (bh + HEAD_GROUP - 1) / HEAD_GROUP;
   const unsigned grid = (unsigned)(bh + p.dense_slots + groups * HEAD_GROUP * p.n_pairs);
   flash_fwd_kernel<HD><<<grid, FLASH_THREADS, Cfg<HD>::SMEM_BYTES, st>>>(mq, mk, mv, mo, mpat, mv64, p);

@@ -32,7 +32,7 @@ class SafMixedAttnArgs(C.Structure):
         ("frozen", C.c_void_p), ("hidx", C.c_void_p), ("pidx", C.c_void_p), ("kvidx", C.c_void_p),
         ("frozen_host", C.POINTER(C.c_int32)),
         ("sd_alpha", C.c_void_p), ("sd_rho", C.c_void_p), ("rope_cos", C.c_void_p), ("rope_sin", C.c_void_p),
-        ("status", C.c_void_p),
+        ("status", C.c_void_p), ("sched", C.c_void_p),
     ]
 
 
@@ -146,8 +146,8 @@ def _load():
     lib.saf_selftest_wait_timeout.argtypes = [C.c_void_p, C.c_int64, C.c_void_p]
     lib.saf_selftest_wait_timeout.restype = C.c_int
     lib.saf_selftest_per_device_once.restype = C.c_int
-    if lib.saf_abi_version() != 1:
-        raise ImportError("libsaf_b200.so ABI version %d, expected 1: rebuild" % lib.saf_abi_version())
+    if lib.saf_abi_version() != 2:
+        raise ImportError("libsaf_b200.so ABI version %d, expected 2: rebuild" % lib.saf_abi_version())
     return lib
 
 

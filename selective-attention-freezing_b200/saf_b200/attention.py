@@ -14,8 +14,8 @@ and routes them to the O(T) scan instead of the dense product.
 Hot path (`_attend_cheap`):
   inference: ONE tensor-core GEMM for [Q(live) | K(live) | V(all)] reading the canonical weights in
              place with RoPE in its epilogue -> fused mixed attention -> c_proj GEMM.
-  training : linear_rows2 (live-only Q/K, exact-zero grads for frozen rows) + v_proj, RoPE applied
-             while q/k are loaded by the attention kernel (backward un-rotates), c_proj.
+  training : linear_rows2 (live-only Q/K, exact-zero grads for frozen rows, RoPE in its epilogue and the adjoint
+             rotation in its backward), v_proj and c_proj through the same indexed GEMMs with every row selected.
 The eager capture path (`set_capture(True)`) is the reference's semantic definition
 (nanogpt/model.py:824-844) written with torch ops; it exists for measurement by a freeze
 controller, never as a fallback of the hot path.
@@ -370,8 +370,9 @@ class SafCausalSelfAttention(nn.Module):
                 return ops.linear_act(y, cw, cb, residual=residual.to(act_dt))   # residual add in the GEMM epilogue
             out = ops.linear_rows(y, cw, cb, self._all_rows)
             return out if residual is None else residual + out
-        # training / fp32: live-only Q,K projection with exact-zero frozen rows in the weight gradient
-        v = self.v_proj(x).view(B, T, nh, hd).transpose(1, 2)
+        # training / fp32: live-only Q,K projection with exact-zero frozen rows in the weight gradient; v_proj and
+        # c_proj run on the library's own forward / dx / dW GEMMs too (all rows selected)
+        v = ops.linear_rows(x, self.v_proj.weight, self.v_proj.bias, self._all_rows).view(B, T, nh, hd).transpose(1, 2)
         if nuf == 0:
             qu = ku = v[:, :0]
         else:
@@ -405,7 +406,8 @@ class SafCausalSelfAttention(nn.Module):
             y = ops.fused_mixed_attn(qu, ku, v, patt, self._fz_mask_i32, self._hidx_i32, pidx,
                                      alpha=dec[0], rho=dec[1], z=dec[2], validate=False, sink_decay=self._sd)
         y = y.transpose(1, 2).reshape(B, T, nh * hd)
-        out = F.dropout(self.c_proj(y), self.dropout, self.training)     # resid_dropout (nanogpt/model.py:1169)
+        out = ops.linear_rows(y, self.c_proj.weight, self.c_proj.bias, self._all_rows)
+        out = F.dropout(out, self.dropout, self.training)                # resid_dropout (nanogpt/model.py:1169)
         return out if residual is None else residual + out
 
     def forward(self, x, rope=None, residual=None):

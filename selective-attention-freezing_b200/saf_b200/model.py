@@ -38,7 +38,13 @@ class SafGPT(nn.Module):
             x = block(x, rope=rope)
         return self.transformer.ln_f(x)
 
-    def forward(self, idx):
-        """Next-token logits at the last position, (B, 1, vocab)."""
+    def forward(self, idx, targets=None):
+        """GPT.forward of the reference (nanogpt/model.py:1401-1417): with targets, logits at every position and
+        the mean cross-entropy (ignore_index -1); without, next-token logits at the last position, (B, 1, vocab),
+        and None."""
         x = self.forward_hidden(idx)
-        return F.linear(x[:, -1:, :], self.lm_head.weight)
+        if targets is not None:
+            logits = self.lm_head(x)
+            loss = F.cross_entropy(logits.view(-1, logits.size(-1)), targets.view(-1), ignore_index=-1)
+            return logits, loss
+        return F.linear(x[:, -1:, :], self.lm_head.weight), None

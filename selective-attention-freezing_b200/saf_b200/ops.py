@@ -283,6 +283,12 @@ class _FusedMixedAttn(torch.autograd.Function):
         a, keep = SafMixedAttnArgs(), []
         _fill_mixed(a, q, k, v, out, lse, patt, alpha, rho, z, frozen, hidx, pidx, kvidx, sm_scale, rope,
                     sink_decay, keep)
+        if v.dtype == torch.bfloat16 and HD in (64, 128) and q is not None and q.size(1) > 0:
+            # tile queue of the persistent forward kernel: two zeroed ints owned by this call (torch's allocator
+            # hands the block out again only in stream order, and a CUDA graph capture gives it a private pool)
+            sched = torch.zeros(2, dtype=torch.int32, device=v.device)
+            keep.append(sched)
+            a.sched = sched.data_ptr()
         if _ATTN_EVENTS is not None:
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
@@ -666,8 +672,9 @@ class _RowSlicedLinearN(torch.autograd.Function):
             _call(x, lib.saf_indexed_linear_bwd_dx, C.byref(a), dout2.data_ptr(), dout2.stride(0), dx2.data_ptr(),
                                                 dx2.stride(0), None)
             dx = dx2.view(x.shape)
-        need_w = any(ctx.needs_input_grad[3 + i] for i in range(nw))
-        need_b = any(ctx.has_bias[i] and ctx.needs_input_grad[3 + nw + i] for i in range(nw))
+        # forward's arguments: x, rows, nw, rope, then the weights, then the biases
+        need_w = any(ctx.needs_input_grad[4 + i] for i in range(nw))
+        need_b = any(ctx.has_bias[i] and ctx.needs_input_grad[4 + nw + i] for i in range(nw))
         if need_w or need_b:
             # rows of no slab stay exactly zero (kernel/indexed_linear.py:112-115)
             dws = [torch.zeros_like(w) for w in weights]

@@ -113,7 +113,7 @@ def test_whole_model_last_position_logits():
         blk.main_block.freeze_heads_sink_decay(fz, a.tolist(), r.tolist())
     idx = torch.randint(0, V, (B, T), generator=torch.Generator().manual_seed(2), dtype=torch.int32)
     with torch.inference_mode():
-        logits = m(idx.cuda())
+        logits, _ = m(idx.cuda())
     assert logits.shape == (B, 1, V)
     sd = {k: v.float().cpu() for k, v in m.state_dict().items()}
     patt = torch.zeros(H, T, T)

@@ -200,3 +200,36 @@ def test_backward_products_many_tiles_bf16():
     dead = [h for h in range(H) if h not in live]
     dr = head_rows(dead, hd).to(dev)
     assert dev_in[1].grad[dr].abs().max().item() == 0.0 and dev_in[2].grad[dr].abs().max().item() == 0.0
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["fp32", "bf16"])
+@pytest.mark.parametrize("bias", [False, True])
+def test_linear_rows_single_weight_gradients(bias, dtype):
+    """linear_rows (one weight) with its three gradients against the reference's own autograd Function: dx, the
+    weight gradient with exact zeros in the rows that were not selected, the bias gradient likewise
+    (kernel/indexed_linear.py:28-55)."""
+    from kernel import linear_rows
+    dev = "cuda"
+    g = torch.Generator().manual_seed(31)
+    x = torch.randn(3, 70, 256, generator=g)
+    w = torch.randn(256, 256, generator=g) * 0.05
+    b = torch.randn(256, generator=g) * 0.1 if bias else None
+    rows = (torch.tensor([0, 2, 3])[:, None] * 64 + torch.arange(64)).reshape(-1)
+    ins = [t.to(dtype) for t in (x, w)] + ([b.to(dtype)] if bias else [])
+    ref = [t.float().clone().requires_grad_(True) for t in ins]
+    y_ref = O.linear_rows(ref[0], ref[1], ref[2] if bias else None, rows)
+    gy = torch.randn(y_ref.shape, generator=g)
+    (y_ref * gy).sum().backward()
+    got = [t.clone().to(dev).requires_grad_(True) for t in ins]
+    y = linear_rows(got[0], got[1], got[2] if bias else None, rows.to(dev))
+    (y.float() * gy.to(dev)).sum().backward()
+    tol = 2e-5 if dtype == torch.float32 else 2e-2
+    assert O.rel_l2(y.float().cpu(), y_ref.detach()) <= tol
+    for name, a, r in zip(("dx", "dw", "db"), got, ref):
+        assert a.grad is not None, f"{name} was not produced"
+        assert O.rel_l2(a.grad.float().cpu(), r.grad) <= tol, name
+    unselected = torch.ones(256, dtype=torch.bool)
+    unselected[rows] = False
+    assert got[1].grad[unselected.to(dev)].abs().max().item() == 0.0
+    if bias:
+        assert got[2].grad[unselected.to(dev)].abs().max().item() == 0.0
