@@ -196,6 +196,11 @@ def run_reference(args, w):
 
 
 def workload_name(key, w):
+    if w.get("n_kv") is not None:
+        return (f"{key}: Qwen2.5-1.5B-shaped SAF-25% grouped-query attention+projection stack, {w['n_layer']} layers x "
+                f"(indexed Q(live)/K/V GEMM + RoPE base {w['rope_base']:.0e}, kvidx mixed attention, o_proj), "
+                f"{w['n_head']} query / {w['n_kv']} KV heads x {w['head_dim']}, hidden {w['hidden']}, {w['n_frozen']} "
+                f"sink+decay frozen query heads per layer, T={w['T']}, B={w['B']} per GPU")
     return (f"{key}: GPT-2 124M SAF-25% attention+projection stack, {w['n_layer']} layers x "
             f"(indexed QKV GEMM + RoPE, mixed attention, c_proj), {w['n_head']} heads x {w['head_dim']}, "
             f"{w['n_frozen']} sink+decay frozen heads per layer, T={w['T']}, B={w['B']} per GPU")
@@ -206,6 +211,42 @@ def bench_config(key, w, scope):
              "model": "; whole blocks: + LayerNorms, residuals, 4x MLP with GELU; token ids in, last-position logits out"}
     return {"workload": workload_name(key, w) + extra[scope],
             "l2": "per-layer working set (x 100 MB, qkv 250 MB, attention out 100 MB) exceeds the 126 MB L2"}
+
+
+def parity_block_gqa(layer, rope, w, x_one):
+    """Layer 0 of a grouped-query stack on one sequence against the CPU oracle's restatement of the reference's
+    Qwen3 hybrid attention layer, 64 sampled query rows.  Runs after the timed regions."""
+    from oracle import saf_oracle as O
+    T, H, hd = w["T"], w["n_head"], w["head_dim"]
+    with torch.inference_mode():
+        y = layer(x_one, rope)
+    torch.cuda.synchronize()
+    rows = torch.tensor(sorted(set([0, 1, 127, 128, 255, 256, T // 2, T - 129, T - 128, T - 2, T - 1]
+                                   + torch.linspace(0, T - 1, 53).long().tolist())))
+    wf = {n: t.detach().float().cpu() for n, t in layer.named_parameters()}
+    qrows = (torch.tensor(layer._live)[:, None] * hd + torch.arange(hd)).reshape(-1)
+    x1 = x_one.float().cpu()
+    has_bias = "q_proj.bias" in wf
+    xb = torch.cat([x1, torch.ones(1, T, 1)], -1) if has_bias else x1
+
+    def with_bias(wn, bn, sel=None):
+        wt = wf[wn] if sel is None else wf[wn][sel]
+        if not has_bias:
+            return wt
+        b = wf[bn] if sel is None else wf[bn][sel]
+        return torch.cat([wt, b[:, None]], 1)
+    torch.set_num_threads(os.cpu_count() or 1)
+    oc, os_ = O.rope_cache(hd, T, base=w["rope_base"])
+    with torch.no_grad():
+        ref = O.gqa_attention_layer(xb, with_bias("q_proj.weight", "q_proj.bias", qrows),
+                                    with_bias("k_proj.weight", "k_proj.bias"), with_bias("v_proj.weight", "v_proj.bias"),
+                                    wf["o_proj.weight"], layer.frozen_mask_i32.cpu(), layer.hidx_i32.cpu(),
+                                    layer.pidx_i32.cpu(), layer.kvidx_i32.cpu(), None, oc, os_, layer.scaling, rows=rows,
+                                    sink_decay=(layer.sd_alpha.double().cpu(), layer.sd_rho.double().cpu()))
+    got = y[:, rows.to(y.device)].float().cpu()
+    return {"max_abs": O.max_abs(got, ref), "rel_l2": O.rel_l2(got, ref), "rows": int(rows.numel()),
+            "against": "fp32 CPU oracle of the reference's grouped-query attention layer, layer 0, 1 sequence, all heads",
+            "bar": "max_abs <= 2e-2 and rel_l2 <= 1e-2"}
 
 
 def parity_block(layer, rope, w, x_one):
@@ -380,6 +421,18 @@ def main():
         last_host = torch.empty(B, model.config.vocab_size, dtype=torch.bfloat16).pin_memory()
         run = lambda xin: model(xin)[0][:, 0, :]          # (B, vocab)
         result_of = lambda out: out
+    elif w.get("n_kv") is not None:
+        # grouped-query workload: Qwen-shaped attention modules (q_proj read for live heads only, K/V for the raw KV
+        # heads, kvidx attention, o_proj) -- with --scope block the RMSNorms and the gated MLP around them
+        from saf_b200 import gqa
+        if args.scope == "model":
+            raise SystemExit("--scope model is built for the GPT-2-shaped workloads only")
+        layers, rope, w = gqa.build_gqa_stack(args.workload, dev, blocks=(args.scope == "block"))
+        B, T, C = w["B"], w["T"], w["hidden"]
+        x_host = torch.randn(B, T, C, generator=g).bfloat16().pin_memory()
+        last_host = torch.empty(B, C, dtype=torch.bfloat16).pin_memory()
+        run = lambda xin: gqa.gqa_stack_forward(layers, rope, xin)
+        result_of = lambda out: out[:, -1, :]
     else:
         layers, rope, w = synthetic.build_attention_stack(args.workload, dev, blocks=(args.scope == "block"))
         B, T, C = w["B"], w["T"], w["n_head"] * w["head_dim"]
@@ -468,8 +521,9 @@ def main():
         e2e_ms = e0.elapsed_time(e1)
 
         # per-layer split (outside the timed regions): each piece launched alone on layer 0's tensors
-        attn0 = layers[0] if args.scope == "stack" else layers[0].main_block
-        if rank != 0:
+        is_gqa = w.get("n_kv") is not None
+        attn0 = None if is_gqa else (layers[0] if args.scope == "stack" else layers[0].main_block)
+        if rank != 0 or is_gqa:
             split = None
         elif args.scope == "model":
             split = synthetic.per_layer_split(attn0, model.rope(T, dev), model.transformer.wte(x_dev))
@@ -482,13 +536,19 @@ def main():
     parallel.finalize()
     if rank != 0:
         return
-    parity = parity_block(layers[0], rope, w, x_dev[:1]) if args.scope == "stack" else None
+    parity = None
+    if args.scope == "stack":
+        parity = (parity_block_gqa if is_gqa else parity_block)(layers[0], rope, w, x_dev[:1])
 
     ms_per_step = total_ms / steps
     value = tokens / (ms_per_step * 1e-3)
     e2e_value = tokens / (e2e_ms / steps * 1e-3)
     peak_tf, peak_burst_tf, peak_hbm, peak_kind = measured_peaks()
-    fl = synthetic.hot_stack_flops(w)
+    if is_gqa:
+        from saf_b200 import gqa
+        fl = gqa.gqa_stack_flops(w, blocks=(args.scope != "stack"))
+    else:
+        fl = synthetic.hot_stack_flops(w)
     live_flops_per_launch = fl["live"] / w["n_layer"] * B
     attn_mean_ms = statistics.mean(attn_ms)
     achieved = live_flops_per_launch / (attn_mean_ms * 1e-3) / 1e12
@@ -515,7 +575,7 @@ def main():
         "per_layer_ms": split,
         "parity": parity,
     }
-    if world == 1 and not args.no_cpu_baseline:
+    if world == 1 and not args.no_cpu_baseline and not is_gqa:
         tok_s, t_layer, cores, sample = cpu_reference_sample(w, 2, 1)
         line["cpu_baseline"] = {"value": tok_s, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample}
     print(json.dumps(line), flush=True)

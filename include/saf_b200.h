@@ -198,11 +198,14 @@ typedef struct SafIndexedLinearArgs {
   /* epilogue of the rest of the transformer block around the attention path (forward only, bf16 tensor-core
    * path): out = [residual +] act(x W^T + b).  Replaces the separate GELU and residual-add kernels of
    * MLP.forward / Block.forward (nanogpt/model.py:1202-1207, 1237-1240). */
-  int32_t act;                /* SAF_ACT_NONE or SAF_ACT_GELU (exact erf form, nn.GELU()) */
+  int32_t act;                /* SAF_ACT_NONE, SAF_ACT_GELU (exact erf form, nn.GELU()) or SAF_ACT_SWIGLU:
+                                 slabs come in (gate, up) pairs of 64 rows and the output, of width
+                                 n_slabs*slab/2, is silu(gate) * up -- the gated MLP of the Qwen-shaped
+                                 blocks (slab 64, no bias, no rotation, bf16 tensor-core path only)     */
   const void* residual;       /* (M, n_slabs*slab) same dtype, row stride ldr, or null    */
   int64_t ldr;
 } SafIndexedLinearArgs;
-enum { SAF_ACT_NONE = 0, SAF_ACT_GELU = 1 };
+enum { SAF_ACT_NONE = 0, SAF_ACT_GELU = 1, SAF_ACT_SWIGLU = 2 };
 
 int saf_indexed_linear_fwd(const SafIndexedLinearArgs* args, void* stream);
 
@@ -237,6 +240,11 @@ int saf_rope_slabs(void* x, int64_t ld, int32_t M, int32_t n_slabs, int32_t slab
  * ------------------------------------------------------------------------- */
 int saf_layernorm_fwd(const void* x, int64_t ldx, const void* weight, const void* bias, void* out, int64_t ldo,
                       int32_t M, int32_t C, float eps, int32_t dtype, void* stream);
+/* RMSNorm over the last dimension, y = x / sqrt(mean(x^2) + eps) * weight: the norm of the Qwen-shaped blocks
+ * around the grouped-query attention (the reference leaves it to the Hugging Face model its adapter wraps,
+ * qwen/nanogpt/hybrid_prior_attention.py:522-523).  Same layout rules as saf_layernorm_fwd. */
+int saf_rmsnorm_fwd(const void* x, int64_t ldx, const void* weight, void* out, int64_t ldo, int32_t M, int32_t C,
+                    float eps, int32_t dtype, void* stream);
 
 /* ---------------------------------------------------------------------------
  * Freeze-time helper: z[h,i] = logsumexp_{j<=i}(alpha[h,j] + rho[h,i-j]).

@@ -339,7 +339,8 @@ static int validate_linear(const SafIndexedLinearArgs* a) {
                 (int)sizeof(SafIndexedLinearArgs));
   if (a->dtype != SAF_F32 && a->dtype != SAF_BF16) return fail(SAF_ERR_UNSUPPORTED, "indexed linear takes fp32 or bf16");
   if (a->M < 0 || a->C <= 0 || a->n_slabs < 0 || a->slab <= 0) return fail(SAF_ERR_INVALID, "bad dimensions");
-  if (a->act != SAF_ACT_NONE && a->act != SAF_ACT_GELU) return fail(SAF_ERR_INVALID, "unknown activation %d", a->act);
+  if (a->act != SAF_ACT_NONE && a->act != SAF_ACT_GELU && a->act != SAF_ACT_SWIGLU)
+    return fail(SAF_ERR_INVALID, "unknown activation %d", a->act);
   if (a->n_weights < 1 || a->n_weights > SAF_MAX_WEIGHTS) return fail(SAF_ERR_INVALID, "n_weights %d", a->n_weights);
   if (a->M == 0 || a->n_slabs == 0) return SAF_OK;
   if (!a->x || !a->slab_weight || !a->slab_row0) return fail(SAF_ERR_INVALID, "null x / slab tables");
@@ -413,7 +414,16 @@ int saf_layernorm_fwd(const void* x, int64_t ldx, const void* weight, const void
   if (dtype != SAF_F32 && dtype != SAF_BF16) return fail(SAF_ERR_UNSUPPORTED, "layernorm takes fp32 or bf16");
   if (M == 0) return SAF_OK;
   if (!x || !weight || !out) return fail(SAF_ERR_INVALID, "null pointer");
-  return launch_layernorm(x, ldx, weight, bias, out, ldo, M, C, eps, dtype, (cudaStream_t)stream);
+  return launch_layernorm(x, ldx, weight, bias, out, ldo, M, C, eps, dtype, 0, (cudaStream_t)stream);
+}
+
+int saf_rmsnorm_fwd(const void* x, int64_t ldx, const void* weight, void* out, int64_t ldo, int32_t M, int32_t C,
+                    float eps, int32_t dtype, void* stream) {
+  if (M < 0 || C <= 0) return fail(SAF_ERR_INVALID, "bad dimensions");
+  if (dtype != SAF_F32 && dtype != SAF_BF16) return fail(SAF_ERR_UNSUPPORTED, "rmsnorm takes fp32 or bf16");
+  if (M == 0) return SAF_OK;
+  if (!x || !weight || !out) return fail(SAF_ERR_INVALID, "null pointer");
+  return launch_layernorm(x, ldx, weight, nullptr, out, ldo, M, C, eps, dtype, 1, (cudaStream_t)stream);
 }
 
 int saf_decomposed_logz(const float* alpha, const float* rho, float* z, int32_t H, int32_t S, void* stream) {

@@ -1,5 +1,8 @@
 // LayerNorm of the transformer block around the attention path (LayerNorm.forward, nanogpt/model.py:45-54):
 // y = (x - mean) / sqrt(var + eps) * weight (+ bias), statistics in fp32, biased variance as F.layer_norm.
+// rms = 1 gives the RMSNorm of the Qwen-shaped blocks instead (the norm the reference's grouped-query adapter
+// leaves to the Hugging Face model, qwen/nanogpt/hybrid_prior_attention.py:522-523): no mean, no bias,
+// y = x / sqrt(mean(x^2) + eps) * weight.
 // HBM-bound: one warp per row, 16-byte loads, the row stays in registers between the two passes.
 #include "saf_internal.h"
 
@@ -22,7 +25,7 @@ __global__ void __launch_bounds__(LN_WARPS * 32) layernorm_bf16_kernel(const __n
                                                                        const __nv_bfloat16* __restrict__ w,
                                                                        const __nv_bfloat16* __restrict__ b,
                                                                        __nv_bfloat16* __restrict__ out, int64_t ldo, int M,
-                                                                       int C, float eps) {
+                                                                       int C, float eps, int rms) {
   const int row = blockIdx.x * LN_WARPS + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (row >= M) return;
   const int n_chunks = C >> 3;                     // 8 elements each
@@ -40,7 +43,7 @@ __global__ void __launch_bounds__(LN_WARPS * 32) layernorm_bf16_kernel(const __n
   }
 #pragma unroll
   for (int off = 16; off; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
-  const float mean = s / (float)C;
+  const float mean = rms ? 0.f : s / (float)C;
   float q = 0.f;
 #pragma unroll
   for (int k = 0; k < LN_MAX_CHUNKS; ++k) {
@@ -86,7 +89,7 @@ template <typename T>
 __global__ void __launch_bounds__(LN_WARPS * 32) layernorm_generic_kernel(const T* __restrict__ x, int64_t ldx,
                                                                           const T* __restrict__ w, const T* __restrict__ b,
                                                                           T* __restrict__ out, int64_t ldo, int M, int C,
-                                                                          float eps) {
+                                                                          float eps, int rms) {
   const int row = blockIdx.x * LN_WARPS + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (row >= M) return;
   const T* xr = x + (int64_t)row * ldx;
@@ -94,7 +97,7 @@ __global__ void __launch_bounds__(LN_WARPS * 32) layernorm_generic_kernel(const 
   for (int c = lane; c < C; c += 32) s += to_f<T>(xr[c]);
 #pragma unroll
   for (int off = 16; off; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
-  const float mean = s / (float)C;
+  const float mean = rms ? 0.f : s / (float)C;
   float q = 0.f;
   for (int c = lane; c < C; c += 32) {
     const float d = to_f<T>(xr[c]) - mean;
@@ -116,7 +119,7 @@ bool ln_al16(const void* p) { return ((uintptr_t)p & 15) == 0; }
 }  // namespace
 
 int launch_layernorm(const void* x, int64_t ldx, const void* w, const void* b, void* out, int64_t ldo, int M, int C,
-                     float eps, int dtype, cudaStream_t st) {
+                     float eps, int dtype, int rms, cudaStream_t st) {
   const unsigned grid = (unsigned)((M + LN_WARPS - 1) / LN_WARPS);
   if (dtype == SAF_BF16) {
     const bool vec = C % 8 == 0 && C <= 256 * LN_MAX_CHUNKS && ldx % 8 == 0 && ldo % 8 == 0 && ln_al16(x) && ln_al16(w) &&
@@ -124,15 +127,15 @@ int launch_layernorm(const void* x, int64_t ldx, const void* w, const void* b, v
     if (vec)
       layernorm_bf16_kernel<<<grid, LN_WARPS * 32, 0, st>>>(
           reinterpret_cast<const __nv_bfloat16*>(x), ldx, reinterpret_cast<const __nv_bfloat16*>(w),
-          reinterpret_cast<const __nv_bfloat16*>(b), reinterpret_cast<__nv_bfloat16*>(out), ldo, M, C, eps);
+          reinterpret_cast<const __nv_bfloat16*>(b), reinterpret_cast<__nv_bfloat16*>(out), ldo, M, C, eps, rms);
     else
       layernorm_generic_kernel<__nv_bfloat16><<<grid, LN_WARPS * 32, 0, st>>>(
           reinterpret_cast<const __nv_bfloat16*>(x), ldx, reinterpret_cast<const __nv_bfloat16*>(w),
-          reinterpret_cast<const __nv_bfloat16*>(b), reinterpret_cast<__nv_bfloat16*>(out), ldo, M, C, eps);
+          reinterpret_cast<const __nv_bfloat16*>(b), reinterpret_cast<__nv_bfloat16*>(out), ldo, M, C, eps, rms);
   } else {
     layernorm_generic_kernel<float><<<grid, LN_WARPS * 32, 0, st>>>(
         reinterpret_cast<const float*>(x), ldx, reinterpret_cast<const float*>(w), reinterpret_cast<const float*>(b),
-        reinterpret_cast<float*>(out), ldo, M, C, eps);
+        reinterpret_cast<float*>(out), ldo, M, C, eps, rms);
   }
   count_launch();
   return check_launch("layernorm_kernel");

@@ -78,10 +78,13 @@ struct Cfg {
   static constexpr int SMEM_FLASH = 1024 + Q_BYTES + RING_BYTES + 4096;
   // the dense-pattern role of the same launch needs its own ring
   static constexpr int SMEM_BYTES = SMEM_FLASH > DpCfg<HD>::SMEM_BYTES ? SMEM_FLASH : DpCfg<HD>::SMEM_BYTES;
-  // persistent kernel: Q, rings, two 16 KB output staging buffers, barriers
-  static constexpr int SMEM_PERSIST_OWN = 1024 + Q_BYTES + RING_BYTES + 2 * 128 * 128 + 1024;
+  // persistent kernel: Q, rings, barriers; at head_dim 64 two 16 KB output staging buffers as well (at head_dim
+  // 128 Q and the rings leave no room: the epilogue stages a tile in its own Q buffer)
+  static constexpr bool STAGE_IN_Q = (HD == 128);
+  static constexpr int O_STAGING = STAGE_IN_Q ? 0 : 2 * 128 * 128;
+  static constexpr int SMEM_PERSIST_OWN = 1024 + Q_BYTES + RING_BYTES + O_STAGING + 1024;
   static constexpr int SMEM_PERSIST = SMEM_PERSIST_OWN > DpCfg<HD>::SMEM_BYTES ? SMEM_PERSIST_OWN : DpCfg<HD>::SMEM_BYTES;
-  static_assert(SMEM_PERSIST_OWN <= 232448, "persistent kernel exceeds the 227 KB of shared memory per CTA");
+  static_assert(SMEM_PERSIST_OWN + 4096 <= 232448, "persistent kernel exceeds the 227 KB of shared memory per CTA");
   static constexpr int TMEM_COLS = 512;
   static constexpr int NBUF = (HD == 64) ? 3 : 2;      // score buffers
   static constexpr int O_COL = NBUF * 128;
@@ -801,8 +804,8 @@ flash_fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __gr
   uint8_t* sQ = smem;
   uint8_t* sK = smem + C::Q_BYTES;
   uint8_t* sV = sK + C::KSTAGE * C::TILE_BYTES;
-  uint8_t* sO = sK + C::RING_BYTES;                       // 2 x O_STAGE_BYTES
-  PersistBars* bars = reinterpret_cast<PersistBars*>(sO + 2 * O_STAGE_BYTES);
+  uint8_t* sO = sK + C::RING_BYTES;                       // 2 x O_STAGE_BYTES (head_dim 64 only)
+  PersistBars* bars = reinterpret_cast<PersistBars*>(sO + C::O_STAGING);
   const int tid = threadIdx.x, warp = tid >> 5;
 
   if (tid == 0) {
@@ -976,7 +979,7 @@ flash_fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __gr
             }
             umma_commit(&bars->s_full[buf]);
             if (t == 1 || !g.act1) umma_commit(&bars->k_empty[ks_]);   // last reader of K_j
-            if (j == (t ? g.nkv1 : g.nkv0) - 1) umma_commit(&bars->q_free[t]);   // last reader of Q_t
+            if (!C::STAGE_IN_Q && j == (t ? g.nkv1 : g.nkv0) - 1) umma_commit(&bars->q_free[t]);   // last reader of Q_t
           }
           __syncwarp();
         }
@@ -1158,15 +1161,13 @@ flash_fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __gr
         }
         tc_fence_after();
         const float inv = 1.f / l;
-        uint8_t* stage = sO + t * O_STAGE_BYTES;
         const int trow = g.row0 + t * FM;
+        if constexpr (C::STAGE_IN_Q) {
+          // head_dim 128: the tile's own Q buffer is the staging area (its last score product retired before the
+          // last P V did); Q_t of the next item may land once the store has read it
+          uint8_t* stage = sQ + t * C::TILE_BYTES;
 #pragma unroll
-        for (int hh = 0; hh < HD / 64; ++hh) {
-          // the staging buffer is free once the store that last read it (previous half or previous item) is done
-          if (r == 0) tma_store_wait_read();
-          named_bar_sync(1 + t, 128);
-#pragma unroll
-          for (int c0 = hh * 64; c0 < hh * 64 + 64; c0 += 32) {
+          for (int c0 = 0; c0 < HD; c0 += 32) {
             uint32_t o[32];
             tmem_ld32(tO + c0, o);
             tmem_ld_wait();
@@ -1174,7 +1175,7 @@ flash_fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __gr
               tc_fence_before();
               mbar_arrive(&bars->o_free[t]);
             }
-            uint8_t* dst = stage + r * 128;
+            uint8_t* dst = stage + (c0 >> 6) * 16384 + r * 128;
             const int cbase = (c0 & 63) >> 3;
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
@@ -1189,8 +1190,46 @@ flash_fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __gr
           fence_proxy_async_smem();
           named_bar_sync(1 + t, 128);
           if (r == 0) {
-            tma_store_4d(&mapO, stage, hh * 64, trow, g.h, g.b);
+#pragma unroll
+            for (int hh = 0; hh < HD / 64; ++hh) tma_store_4d(&mapO, stage + hh * 16384, hh * 64, trow, g.h, g.b);
             tma_store_commit();
+            tma_store_wait_read();
+            mbar_arrive(&bars->q_free[t]);
+          }
+        } else {
+          uint8_t* stage = sO + t * O_STAGE_BYTES;
+#pragma unroll
+          for (int hh = 0; hh < HD / 64; ++hh) {
+            // the staging buffer is free once the store that last read it (previous item) is done
+            if (r == 0) tma_store_wait_read();
+            named_bar_sync(1 + t, 128);
+#pragma unroll
+            for (int c0 = hh * 64; c0 < hh * 64 + 64; c0 += 32) {
+              uint32_t o[32];
+              tmem_ld32(tO + c0, o);
+              tmem_ld_wait();
+              if (c0 + 32 >= HD) {   // O_t is in registers: the next item may overwrite it
+                tc_fence_before();
+                mbar_arrive(&bars->o_free[t]);
+              }
+              uint8_t* dst = stage + r * 128;
+              const int cbase = (c0 & 63) >> 3;
+#pragma unroll
+              for (int c = 0; c < 4; ++c) {
+                uint4 q;
+                q.x = pack_bf16(__uint_as_float(o[c * 8 + 0]) * inv, __uint_as_float(o[c * 8 + 1]) * inv);
+                q.y = pack_bf16(__uint_as_float(o[c * 8 + 2]) * inv, __uint_as_float(o[c * 8 + 3]) * inv);
+                q.z = pack_bf16(__uint_as_float(o[c * 8 + 4]) * inv, __uint_as_float(o[c * 8 + 5]) * inv);
+                q.w = pack_bf16(__uint_as_float(o[c * 8 + 6]) * inv, __uint_as_float(o[c * 8 + 7]) * inv);
+                *reinterpret_cast<uint4*>(dst + (((cbase + c) ^ (r & 7)) << 4)) = q;
+              }
+            }
+            fence_proxy_async_smem();
+            named_bar_sync(1 + t, 128);
+            if (r == 0) {
+              tma_store_4d(&mapO, stage, hh * 64, trow, g.h, g.b);
+              tma_store_commit();
+            }
           }
         }
         if (p.lse && trow + r < p.T)
@@ -1227,10 +1266,10 @@ int launch_typed(const SafMixedAttnArgs& a, uint32_t want, cudaStream_t st) {
   int rc;
   const int Hkv = a.HKV > 0 ? a.HKV : 0;
   const bool any_live = a.U > 0 && a.q.ptr && a.k.ptr;     // an all-frozen layer has no q/k: the maps are never used
-  if ((rc = make_map4(&mq, any_live ? a.q : a.v, a.B, any_live ? a.U : (Hkv ? Hkv : a.H), a.T, HD))) return rc;
-  if ((rc = make_map4(&mk, any_live ? a.k : a.v, a.B, any_live ? (Hkv ? Hkv : a.U) : (Hkv ? Hkv : a.H), a.T, HD))) return rc;
-  if ((rc = make_map4(&mv, a.v, a.B, Hkv ? Hkv : a.H, a.T, HD))) return rc;
-  if ((rc = make_map4(&mo, a.out, a.B, a.H, a.T, HD))) return rc;
+  if ((rc = make_map4(&mq, any_live ? a.q : a.v, a.B, any_live ? a.U : (Hkv ? Hkv : a.H), a.T, a.HD))) return rc;
+  if ((rc = make_map4(&mk, any_live ? a.k : a.v, a.B, any_live ? (Hkv ? Hkv : a.U) : (Hkv ? Hkv : a.H), a.T, a.HD))) return rc;
+  if ((rc = make_map4(&mv, a.v, a.B, Hkv ? Hkv : a.H, a.T, a.HD))) return rc;
+  if ((rc = make_map4(&mo, a.out, a.B, a.H, a.T, a.HD))) return rc;
   FlashParams p;
   memset(&p, 0, sizeof(p));
   p.B = a.B; p.H = a.H; p.T = a.T; p.HKV = a.HKV; p.force_state = a.force_state;
@@ -1329,7 +1368,10 @@ extern "C" int saf_debug_ftrace(long long* host) {
 
 int launch_flash_fwd_sm100(const SafMixedAttnArgs& a, uint32_t want, uint32_t* handled, cudaStream_t st) {
   *handled = 0;
-  if (a.dtype != SAF_BF16 || (a.HD != 64 && a.HD != 128) || a.rope) return SAF_ERR_UNSUPPORTED;
+  // head_dim 96 (the reference's 1B recipe, 16 heads x 96) rides the 128-column kernel: the tensor maps carry the
+  // real width, so the TMA loads fill columns 96..127 of every Q, K and V tile with zeros (they add nothing to
+  // Q K^T and give zero output columns) and the stores clip them; a quarter of the MMA work is padding.
+  if (a.dtype != SAF_BF16 || (a.HD != 64 && a.HD != 96 && a.HD != 128) || a.rope) return SAF_ERR_UNSUPPORTED;
   if (a.sm_scale <= 0.f) return SAF_ERR_UNSUPPORTED;
   const bool q_ok = a.U > 0 && a.q.ptr && a.k.ptr;
   if (q_ok && (!tma_ok(a.q) || !tma_ok(a.k))) return SAF_ERR_UNSUPPORTED;
@@ -1340,7 +1382,7 @@ int launch_flash_fwd_sm100(const SafMixedAttnArgs& a, uint32_t want, uint32_t* h
   if (q_ok) can |= 1u << SAF_LIVE;
   if (a.patt.ptr) can |= 1u << SAF_DENSE;
   if (a.alpha.ptr && a.rho.ptr && a.z.ptr) can |= 1u << SAF_DECOMP;
-  if (a.sd_alpha && a.sd_rho) can |= 1u << SAF_SINK_DECAY;
+  if (a.sd_alpha && a.sd_rho && a.HD != 96) can |= 1u << SAF_SINK_DECAY;   // the co-scheduled scan walks 64-column slices
   can &= want;
   uint32_t present = can;
   if (a.force_state >= 0) present = 1u << a.force_state;

@@ -30,13 +30,17 @@ constexpr int B_BYTES = GN * GK * 2;            // 32 KB
 constexpr int SUB_BYTES = 64 * GK * 2;          // 8 KB: one 64-row block of weights
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;  // 48 KB
 constexpr int OUT_BYTES = 2 * GM * 64 * 2;      // two 16 KB staging blocks for the TMA stores
-constexpr int MAX_SUB = 160;                    // 64-row blocks of output features (N <= 10240)
+constexpr int MAX_SUB = 288;                    // 64-row blocks of output features (N <= 18432)
 constexpr int GEMM_THREADS = 192;   // TMA warp, MMA warp, one epilogue warpgroup
 
 struct SubTable {
   int32_t row0[MAX_SUB];
   uint8_t weight[MAX_SUB];
   uint8_t rope[MAX_SUB];     // 0: none, 1: this 64-block is the first half of a rotated slab... see kernel
+  // slabs that are a multiple of 32 but not of 64 rows (head_dim 96): a 64-column block is two runs of 32 weight
+  // rows, each with its own source (first run in row0 / weight, second run here)
+  int32_t row0b[MAX_SUB];
+  uint8_t weightb[MAX_SUB];
 };
 
 struct GemmParams {
@@ -49,6 +53,7 @@ struct GemmParams {
   int act;                       // SAF_ACT_*
   const __nv_bfloat16* residual; // added to the output, or null
   int64_t ldr;
+  int halves;                    // weight blocks arrive as two 32-row TMA boxes (see SubTable)
 };
 
 // exact-form GELU, 0.5 x (1 + erf(x / sqrt 2)), with erf from Abramowitz-Stegun 7.1.26 (|error| < 1.5e-7):
@@ -65,6 +70,14 @@ __device__ __forceinline__ float gelu_erf(float x) {
   poly = fmaf(poly, t, 0.5f * 0.254829592f);
   const float q = poly * t * e;                 // Phi(-|x|)
   return x * (x >= 0.f ? 1.f - q : q);          // x Phi(x)
+}
+
+// SiLU gate: g * sigmoid(g) * u, sigmoid through one exponential and one approximate reciprocal
+__device__ __forceinline__ float silu_mul(float g, float u) {
+  float e, r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(g * -1.4426950408889634f));
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.f + e));
+  return g * r * u;
 }
 
 struct SmemLayout {
@@ -129,6 +142,8 @@ indexed_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_const
           for (int u = 0; u < nsub; ++u) {
             const int sb = tn * SUBS + u;
             tma_load_2d(b + u * SUB_BYTES, wm[tb.weight[sb]], &sl->full[s], kb * GK, tb.row0[sb]);
+            if (p.halves)   // the maps' boxes are 32 rows: the second run lands behind the first (4 swizzle atoms on)
+              tma_load_2d(b + u * SUB_BYTES + SUB_BYTES / 2, wm[tb.weightb[sb]], &sl->full[s], kb * GK, tb.row0b[sb]);
           }
         }
       }
@@ -199,8 +214,12 @@ indexed_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_const
       }
       tc_fence_after();
       const uint32_t tsrc = tmem + ((uint32_t)(quad * 32) << 16) + buf * GN;
+      const bool swiglu = p.act == SAF_ACT_SWIGLU;
       for (int u = 0; u < nsub; ++u) {
-        // staging block (u & 1) is free once the store issued two blocks ago has read it
+        // gated MLP: blocks come in (gate, up) pairs; the even block of a pair produces the 64 output columns
+        if (swiglu && (u & 1)) continue;
+        const int ob = swiglu ? (u >> 1) & 1 : (u & 1);     // staging block of this output block
+        // the staging block is free once the store issued two output blocks ago has read it
         if (etid == 0) tma_store_wait_read1();
         named_bar_sync(1, 128);
         const int sb = tn * SUBS + u;
@@ -220,7 +239,19 @@ indexed_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_const
             v[32 + j] = __uint_as_float(r1[j]);
           }
         }
-        if (p.bias[w]) {
+        if (p.halves) {
+          const int wb = tb.weightb[sb];
+          if (p.bias[w]) {
+            const __nv_bfloat16* bp = reinterpret_cast<const __nv_bfloat16*>(p.bias[w]) + tb.row0[sb];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] += __bfloat162float(bp[j]);
+          }
+          if (p.bias[wb]) {
+            const __nv_bfloat16* bp = reinterpret_cast<const __nv_bfloat16*>(p.bias[wb]) + tb.row0b[sb];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[32 + j] += __bfloat162float(bp[j]);
+          }
+        } else if (p.bias[w]) {
           const __nv_bfloat16* bp = reinterpret_cast<const __nv_bfloat16*>(p.bias[w]) + tb.row0[sb];
 #pragma unroll
           for (int j = 0; j < 64; ++j) v[j] += __bfloat162float(bp[j]);
@@ -229,8 +260,20 @@ indexed_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_const
 #pragma unroll
           for (int j = 0; j < 64; ++j) v[j] = gelu_erf(v[j]);
         }
+        if (swiglu) {   // v holds the gate block; the up block is the next 64 accumulator columns
+          uint32_t q0[32], q1[32];
+          tmem_ld32(tsrc + (u + 1) * 64, q0);
+          tmem_ld32(tsrc + (u + 1) * 64 + 32, q1);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            v[j] = silu_mul(v[j], __uint_as_float(q0[j]));
+            v[32 + j] = silu_mul(v[32 + j], __uint_as_float(q1[j]));
+          }
+        }
+        const int out_col = swiglu ? (tn * GN + u * 64) / 2 : tn * GN + u * 64;
         if (p.residual && m < p.M) {   // this row's 64 residual values: one 128-byte line
-          const uint4* rr = reinterpret_cast<const uint4*>(p.residual + (int64_t)m * p.ldr + tn * GN + u * 64);
+          const uint4* rr = reinterpret_cast<const uint4*>(p.residual + (int64_t)m * p.ldr + out_col);
 #pragma unroll
           for (int c8 = 0; c8 < 8; ++c8) {
             const uint4 q = rr[c8];
@@ -286,7 +329,7 @@ indexed_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_const
           }
         }
         // bf16 pack -> swizzled staging: 16-byte chunk c of row r lands at chunk (c ^ (r & 7))
-        uint8_t* dst = out_stage + (u & 1) * (OUT_BYTES / 2) + row * 128;
+        uint8_t* dst = out_stage + ob * (OUT_BYTES / 2) + row * 128;
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
           uint4 q;
@@ -299,7 +342,7 @@ indexed_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_const
         fence_proxy_async_smem();
         named_bar_sync(1, 128);
         if (etid == 0) {
-          tma_store_2d(&mapO, out_stage + (u & 1) * (OUT_BYTES / 2), tn * GN + u * 64, tm * GM);
+          tma_store_2d(&mapO, out_stage + ob * (OUT_BYTES / 2), out_col, tm * GM);
           tma_store_commit();
         }
       }
@@ -321,12 +364,22 @@ bool aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
 
 int launch_gemm_sm100(const SafIndexedLinearArgs& a, cudaStream_t st) {
   if (a.dtype != SAF_BF16) return SAF_ERR_UNSUPPORTED;
-  if (a.slab != 64 && a.slab != 128) return SAF_ERR_UNSUPPORTED;
+  // slabs of 64 or 128 rows are whole 64-row weight blocks; other multiples of 32 (head_dim 96) are served as runs
+  // of 32 rows, two per block, when the total width still fills whole 64-column blocks.  The rotation is fused in
+  // the epilogue for the first kind only; for the second it runs as a second launch over the output.
+  const bool halves = a.slab != 64 && a.slab != 128;
+  if (halves && (a.slab % 32 || (a.n_slabs * a.slab) % 64 || a.act != SAF_ACT_NONE || a.residual)) return SAF_ERR_UNSUPPORTED;
   const int N = a.n_slabs * a.slab;
   if (N / 64 > MAX_SUB) return SAF_ERR_UNSUPPORTED;
   if (a.C % 8 || a.ldx % 8 || a.ldo % 8 || !aligned16(a.x) || !aligned16(a.out)) return SAF_ERR_UNSUPPORTED;
   if ((a.rope_cos && !aligned16(a.rope_cos)) || (a.rope_sin && !aligned16(a.rope_sin))) return SAF_ERR_UNSUPPORTED;
   if (a.residual && (!aligned16(a.residual) || a.ldr % 8)) return SAF_ERR_UNSUPPORTED;
+  if (a.act == SAF_ACT_SWIGLU) {
+    // (gate, up) pairs of 64-row blocks, no bias, no rotation; every tile holds whole pairs (4 blocks per tile)
+    if (a.slab != 64 || a.n_slabs % 2 || a.slab_rope) return SAF_ERR_UNSUPPORTED;
+    for (int w = 0; w < a.n_weights; ++w)
+      if (a.biases[w]) return SAF_ERR_UNSUPPORTED;
+  }
   for (int w = 0; w < a.n_weights; ++w) {
     if (!a.weights[w]) continue;
     if (a.ldw[w] % 8 || (a.cdw[w] != 0 && a.cdw[w] != 1) || !aligned16(a.weights[w])) return SAF_ERR_UNSUPPORTED;
@@ -345,24 +398,41 @@ int launch_gemm_sm100(const SafIndexedLinearArgs& a, cudaStream_t st) {
     const int ww = (w < a.n_weights && a.weights[w]) ? w : 0;
     uint64_t dims[2] = {(uint64_t)a.C, (uint64_t)a.rows_w[ww]};
     uint64_t strides[2] = {0, (uint64_t)a.ldw[ww] * 2};
-    uint32_t box[2] = {GK, 64};
+    uint32_t box[2] = {GK, halves ? 32u : 64u};
     if ((rc = make_tensor_map_bf16(&mw[w], a.weights[ww], 2, dims, strides, box, true))) return rc;
   }
   {
-    uint64_t dims[2] = {(uint64_t)N, (uint64_t)a.M};
+    // gated MLP: the output holds one column per (gate, up) pair
+    uint64_t dims[2] = {(uint64_t)(a.act == SAF_ACT_SWIGLU ? N / 2 : N), (uint64_t)a.M};
     uint64_t strides[2] = {0, (uint64_t)a.ldo * 2};
     uint32_t box[2] = {64, GM};
     if ((rc = make_tensor_map_bf16(&mo, a.out, 2, dims, strides, box, false))) return rc;
   }
   SubTable tb;
   memset(&tb, 0, sizeof(tb));
-  const int per = a.slab / 64;
-  for (int g = 0; g < a.n_slabs; ++g)
-    for (int u = 0; u < per; ++u) {
-      tb.row0[g * per + u] = a.slab_row0[g] + u * 64;
-      tb.weight[g * per + u] = (uint8_t)a.slab_weight[g];
-      tb.rope[g * per + u] = (uint8_t)(a.slab_rope ? (a.slab_rope[g] != 0) : 0);
+  bool rope_after = false;
+  if (halves) {
+    for (int hb = 0; hb < N / 32; ++hb) {          // 32-column runs of the output, two per block
+      const int g = (hb * 32) / a.slab, r = (hb * 32) % a.slab;
+      if (hb & 1) {
+        tb.row0b[hb >> 1] = a.slab_row0[g] + r;
+        tb.weightb[hb >> 1] = (uint8_t)a.slab_weight[g];
+      } else {
+        tb.row0[hb >> 1] = a.slab_row0[g] + r;
+        tb.weight[hb >> 1] = (uint8_t)a.slab_weight[g];
+      }
     }
+    if (a.slab_rope)
+      for (int g = 0; g < a.n_slabs; ++g) rope_after |= a.slab_rope[g] != 0;
+  } else {
+    const int per = a.slab / 64;
+    for (int g = 0; g < a.n_slabs; ++g)
+      for (int u = 0; u < per; ++u) {
+        tb.row0[g * per + u] = a.slab_row0[g] + u * 64;
+        tb.weight[g * per + u] = (uint8_t)a.slab_weight[g];
+        tb.rope[g * per + u] = (uint8_t)(a.slab_rope ? (a.slab_rope[g] != 0) : 0);
+      }
+  }
   GemmParams p;
   memset(&p, 0, sizeof(p));
   p.M = a.M; p.N = N; p.K = a.C; p.T = a.T; p.slab = a.slab;
@@ -375,6 +445,7 @@ int launch_gemm_sm100(const SafIndexedLinearArgs& a, cudaStream_t st) {
   p.act = a.act;
   p.residual = reinterpret_cast<const __nv_bfloat16*>(a.residual);
   p.ldr = a.ldr;
+  p.halves = halves ? 1 : 0;
 
   const int sm_count = device_sm_count();
   const size_t smem = 1024 + STAGES * STAGE_BYTES + OUT_BYTES + sizeof(SmemLayout);
@@ -383,7 +454,10 @@ int launch_gemm_sm100(const SafIndexedLinearArgs& a, cudaStream_t st) {
   const int grid = std::min(sm_count, p.tiles_m * p.tiles_n);
   indexed_gemm_kernel<<<grid, GEMM_THREADS, smem, st>>>(mx, mw[0], mw[1], mw[2], mw[3], mo, p, tb);
   count_launch();
-  return check_launch("indexed_gemm_kernel");
+  if ((rc = check_launch("indexed_gemm_kernel"))) return rc;
+  if (rope_after)
+    return launch_rope_slabs(a.out, a.ldo, a.M, a.n_slabs, a.slab, a.T, a.slab_rope, a.rope_cos, a.rope_sin, a.dtype, 0, st);
+  return SAF_OK;
 }
 
 }  // namespace saf

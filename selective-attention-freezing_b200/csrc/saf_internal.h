@@ -99,7 +99,7 @@ int launch_gemm_bwd_dw_sm100(const SafIndexedLinearArgs& a, const void* dout, in
 int launch_rope_slabs(void* x, int64_t ld, int M, int n_slabs, int slab, int T, const int32_t* slab_rope,
                       const float* cosT, const float* sinT, int dtype, int inverse, cudaStream_t st);
 int launch_layernorm(const void* x, int64_t ldx, const void* w, const void* b, void* out, int64_t ldo, int M, int C,
-                     float eps, int dtype, cudaStream_t st);
+                     float eps, int dtype, int rms, cudaStream_t st);
 int launch_logz(const float* alpha, const float* rho, float* z, int H, int S, int rows, cudaStream_t st);   // rows >= `rows` get 0
 int launch_pattern_grad(const SafPatternGradArgs& a, cudaStream_t st);
 int launch_attn_stats_sm100(const SafAttnStatsArgs& a, cudaStream_t st);

@@ -89,13 +89,13 @@ class SafAttnStatsArgs(C.Structure):
     ]
 
 
-ACT_NONE, ACT_GELU = 0, 1
+ACT_NONE, ACT_GELU, ACT_SWIGLU = 0, 1, 2
 
 EXPORTS = (
     "saf_abi_version", "saf_last_error", "saf_launch_count", "saf_device_supported",
     "saf_mixed_attn_fwd", "saf_mixed_attn_bwd", "saf_mixed_attn_bwd_static", "saf_frozen_pv_fwd", "saf_frozen_pv_bwd",
     "saf_indexed_linear_fwd", "saf_indexed_linear_bwd_dx", "saf_indexed_linear_bwd_dw",
-    "saf_decomposed_logz", "saf_rope_slabs", "saf_layernorm_fwd",
+    "saf_decomposed_logz", "saf_rope_slabs", "saf_layernorm_fwd", "saf_rmsnorm_fwd",
     "saf_pattern_normalisers", "saf_pattern_param_grad", "saf_attention_moments",
     "saf_selftest_wait_timeout", "saf_selftest_per_device_once",
 )
@@ -143,6 +143,9 @@ def _load():
     lib.saf_layernorm_fwd.argtypes = [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64,
                                       C.c_int32, C.c_int32, C.c_float, C.c_int32, C.c_void_p]
     lib.saf_layernorm_fwd.restype = C.c_int
+    lib.saf_rmsnorm_fwd.argtypes = [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int32,
+                                    C.c_float, C.c_int32, C.c_void_p]
+    lib.saf_rmsnorm_fwd.restype = C.c_int
     lib.saf_selftest_wait_timeout.argtypes = [C.c_void_p, C.c_int64, C.c_void_p]
     lib.saf_selftest_wait_timeout.restype = C.c_int
     lib.saf_selftest_per_device_once.restype = C.c_int

@@ -270,11 +270,15 @@ class _FusedMixedAttn(torch.autograd.Function):
     """Mirror of kernel/fused_attn.py:626-647."""
 
     @staticmethod
-    def forward(ctx, q, k, v, patt, alpha, rho, z, frozen, hidx, pidx, kvidx, sm_scale, rope, sink_decay):
+    def forward(ctx, q, k, v, patt, alpha, rho, z, frozen, hidx, pidx, kvidx, sm_scale, rope, sink_decay,
+                token_major_out=False):
         gqa = kvidx is not None
         B, Hv, T, HD = v.shape
         H = frozen.numel()
-        if gqa:
+        if gqa and token_major_out:
+            # (B, H, T, hd) view of a (B, T, H, hd) buffer: out.transpose(1, 2).reshape(B, T, H * hd) is then free
+            out = torch.empty((B, T, H, HD), device=v.device, dtype=v.dtype).transpose(1, 2)
+        elif gqa:
             out = torch.empty((B, H, T, HD), device=v.device, dtype=v.dtype)  # qwen/kernel/fused_attn.py:586
         else:
             out = torch.empty_like(v)  # keeps v's strides (kernel/fused_attn.py:575)
@@ -283,7 +287,7 @@ class _FusedMixedAttn(torch.autograd.Function):
         a, keep = SafMixedAttnArgs(), []
         _fill_mixed(a, q, k, v, out, lse, patt, alpha, rho, z, frozen, hidx, pidx, kvidx, sm_scale, rope,
                     sink_decay, keep)
-        if v.dtype == torch.bfloat16 and HD in (64, 128) and q is not None and q.size(1) > 0:
+        if v.dtype == torch.bfloat16 and HD in (64, 96, 128) and q is not None and q.size(1) > 0:
             # tile queue of the persistent forward kernel: two zeroed ints owned by this call (torch's allocator
             # hands the block out again only in stream order, and a CUDA graph capture gives it a private pool)
             sched = torch.zeros(2, dtype=torch.int32, device=v.device)
@@ -326,7 +330,7 @@ class _FusedMixedAttn(torch.autograd.Function):
                     sink_decay, keep)
         g.dout, g.dq, g.dk, g.dv, g.delta = _st(do), _st(dq), _st(dk), _st(dv), _st(delta)
         _call(v, lib.saf_mixed_attn_bwd, C.byref(g))
-        return (dq, dk, dv) + (None,) * 11
+        return (dq, dk, dv) + (None,) * 12
 
 
 class _RotatedCopy(torch.autograd.Function):
@@ -363,7 +367,8 @@ class _RotatedCopy(torch.autograd.Function):
 
 def fused_mixed_attn(q, k, v, patt, frozen, hidx=None, pidx=None,
                      sm_scale=None, alpha=None, rho=None, z=None,
-                     rho_band=None, validate=True, kvidx=None, *, rope=None, sink_decay=None):
+                     rho_band=None, validate=True, kvidx=None, *, rope=None, sink_decay=None,
+                     token_major_out=False):
     """Causal attention over all heads at once; frozen heads use a fixed pattern.
 
     Same positional/keyword contract as the reference (kernel/fused_attn.py:650-734;
@@ -377,6 +382,8 @@ def fused_mixed_attn(q, k, v, patt, frozen, hidx=None, pidx=None,
         into private copies ahead of the tensor-core kernels (bf16, head_dim 64 / 128).
       sink_decay=(a, r): fp32 (H,) tensors; heads with state 3 use the structured
         pattern a[j=0] + (1-a) r^(i-j)/Z_i through an O(T) scan.
+      token_major_out=True (with kvidx): the (B, H, T, hd) result is a view of a (B, T, H, hd) buffer instead of the
+        reference's contiguous tensor, so the caller's transpose(1, 2).reshape(B, T, H * hd) copies nothing.
     alpha / rho that require grad receive their exact gradients (z is then recomputed from them).
     """
     _require_cuda(v, "v")
@@ -440,14 +447,14 @@ def fused_mixed_attn(q, k, v, patt, frozen, hidx=None, pidx=None,
             assert states is None or 2 not in states, "decomposed-frozen heads require alpha/rho/z"
         if sink_decay is None:
             assert states is None or 3 not in states, "sink-decay heads require sink_decay=(a, r)"
-    if (rope is not None and q.dtype == torch.bfloat16 and v.size(-1) in (64, 128) and q.size(1) > 0
+    if (rope is not None and q.dtype == torch.bfloat16 and v.size(-1) in (64, 96, 128) and q.size(1) > 0
             and rope[0].dtype == torch.float32 and rope[0].is_contiguous() and rope[1].is_contiguous()):
         # tensor-core kernels: rotate q, k once into private copies (see _RotatedCopy) and run without in-kernel RoPE
         q = _RotatedCopy.apply(q, rope[0], rope[1])
         k = _RotatedCopy.apply(k, rope[0], rope[1])
         rope = None
     out = _FusedMixedAttn.apply(q, k, v, patt, alpha, rho, z, frozen, hidx, pidx, kvidx, sm_scale, rope,
-                                sink_decay)
+                                sink_decay, token_major_out)
     if train_patterns:
         out = _tp.PatternGradient.apply(out, v, alpha_p, rho_p, z, frozen)
     return out
@@ -758,24 +765,33 @@ def linear_permuted_cols(y, weight, bias, cols):
     return _ColPermutedLinear.apply(y, weight, bias, cols)
 
 
-def qkv_projection(x, wq, wk, wv, live_heads, head_dim, rope=None, T=None, biases=None):
+def qkv_projection(x, wq, wk, wv, live_heads, head_dim, rope=None, T=None, biases=None, grouped=False):
     """One GEMM for [Q(live heads) | K(live heads) | V(all heads)], weights read in place,
     RoPE applied to the Q and K slabs in the GEMM epilogue when `rope=(cos, sin)` is given.
 
     Inference-side fusion of what the reference does with a cached gathered weight,
     F.linear and separate RoPE kernels (nanogpt/model.py:981-990, 1007-1008).
-    Returns (M, (2U + H) * head_dim); no autograd (use linear_rows2 when training)."""
+    grouped=True is the grouped-query layout: wk and wv hold the HKV raw KV heads, every one of them is projected
+    (several query heads share one, so none can be dropped, qwen/nanogpt/hybrid_prior_attention.py:551-557) and
+    the result is [Q(live heads) | K(HKV heads) | V(HKV heads)].
+    Returns (M, (2U + H) * head_dim) [grouped: (U + 2 HKV) * head_dim]; no autograd (use linear_rows2 when training)."""
     _check_lin(x, wq, wk, wv)
     x2 = _as_2d(x)
     H = wv.shape[0] // head_dim
     U = len(live_heads)
-    sw = [0] * U + [1] * U + [2] * H
-    sr = [h * head_dim for h in live_heads] * 2 + [h * head_dim for h in range(H)]
-    srope = ([1] * (2 * U) + [0] * H) if rope is not None else None
+    if grouped:
+        HK = wk.shape[0] // head_dim
+        sw = [0] * U + [1] * HK + [2] * H
+        sr = [h * head_dim for h in live_heads] + [h * head_dim for h in range(HK)] + [h * head_dim for h in range(H)]
+        srope = ([1] * (U + HK) + [0] * H) if rope is not None else None
+    else:
+        sw = [0] * U + [1] * U + [2] * H
+        sr = [h * head_dim for h in live_heads] * 2 + [h * head_dim for h in range(H)]
+        srope = ([1] * (2 * U) + [0] * H) if rope is not None else None
     keep = []
     a = _lin_args(x2, [wq, wk, wv], biases, head_dim, sw, sr, keep, rope=rope,
                   T=(T if T is not None else x.shape[-2]), slab_rope=srope)
-    out = torch.empty((x2.shape[0], (2 * U + H) * head_dim), device=x.device, dtype=x.dtype)
+    out = torch.empty((x2.shape[0], len(sw) * head_dim), device=x.device, dtype=x.dtype)
     a.out, a.ldo = out.data_ptr(), out.stride(0)
     _call(x, lib.saf_indexed_linear_fwd, C.byref(a))
     return out
@@ -797,7 +813,48 @@ def layer_norm(x, weight, bias=None, eps=1e-5):
     return out.view(x.shape)
 
 
+def rms_norm(x, weight, eps=1e-6):
+    """x / sqrt(mean(x^2) + eps) * weight over the last dimension (the RMSNorm of Qwen-shaped blocks).
+    No autograd (prefill path)."""
+    _require_cuda(x, "x")
+    x2 = _as_2d(x)
+    w = weight if weight.dtype == x.dtype else weight.to(x.dtype)
+    out = torch.empty_like(x2)
+    _call(x, lib.saf_rmsnorm_fwd, x2.data_ptr(), x2.stride(0), w.data_ptr(), out.data_ptr(), out.stride(0),
+          x2.shape[0], x2.shape[1], float(eps), _dt(x2))
+    return out.view(x.shape)
+
+
 _ALL_ROWS64 = {}
+_GATE_UP_ROWS = {}
+
+
+def linear_swiglu(x, w_gate, w_up):
+    """silu(x @ w_gate^T) * (x @ w_up^T) in ONE GEMM launch: 64-row blocks of the two weights alternate in the
+    tile's B operand, and the epilogue multiplies each gate block with its up block before the store -- the
+    gated MLP of the Qwen-shaped blocks without the (M, 2 * hidden) intermediate.  bf16, hidden a multiple of
+    128, no bias, no autograd."""
+    _check_lin(x, w_gate, w_up)
+    if x.dtype != torch.bfloat16:
+        raise TypeError("linear_swiglu runs on the bf16 tensor-core path only")
+    N = w_gate.shape[0]
+    if w_up.shape != w_gate.shape or N % 128:
+        raise ValueError("gate and up weights must share a shape with a multiple of 128 rows")
+    x2 = _as_2d(x)
+    tab = _GATE_UP_ROWS.get(N)
+    if tab is None:
+        sw, sr = [], []
+        for r0 in range(0, N, 64):
+            sw += [0, 1]
+            sr += [r0, r0]
+        tab = _GATE_UP_ROWS[N] = (sw, sr)
+    keep = []
+    a = _lin_args(x2, [w_gate, w_up], None, 64, tab[0], tab[1], keep)
+    out = torch.empty((x2.shape[0], N), device=x.device, dtype=x.dtype)
+    a.out, a.ldo = out.data_ptr(), out.stride(0)
+    a.act = _cabi.ACT_SWIGLU
+    _call(x, lib.saf_indexed_linear_fwd, C.byref(a))
+    return out.view(*x.shape[:-1], N)
 
 
 def linear_act(x, weight, bias=None, act=None, residual=None):
