@@ -39,6 +39,16 @@ sys.path.insert(0, os.path.join(ROOT, "selective-attention-freezing_b200"))
 METRIC = "prefill tokens/s, SAF-25% 124M @16K ctx (attention+projection stack)"
 
 
+def metric_name(key, w):
+    """The headline metric for the workload it is quoted on; the same unit for the others, named for what they are."""
+    if key == "c2":
+        return METRIC
+    if w.get("n_kv") is not None:
+        return f"prefill tokens/s, SAF-25% Qwen2.5-1.5B-shaped GQA @{w['T'] // 1024}K ctx (attention+projection stack)"
+    return (f"prefill tokens/s, SAF-25% {w['n_layer']} x [{w['n_head']} heads x {w['head_dim']}] @{w['T'] // 1024}K ctx "
+            f"(attention+projection stack)")
+
+
 def load_workloads():
     """The workload table, read by path so that the CPU reference arm does not import the package (and with it
     the CUDA library)."""
@@ -184,7 +194,7 @@ def run_reference(args, w):
               f"reference's attention layer (dense stored patterns for frozen heads); {steps} timed steps after 1 "
               f"warm-up step (asked for {args.steps}/{args.warmup}; cut to fit {budget_s:.0f} s)")
     line = {
-        "impl": "reference", "metric": METRIC, "value": tok_s, "unit": "tokens/s", "n_gpus": args.gpus,
+        "impl": "reference", "metric": metric_name(args.workload, w), "value": tok_s, "unit": "tokens/s", "n_gpus": args.gpus,
         "steps": steps, "warmup": 1, "ms_per_step": t_step * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": bench_config(args.workload, w, "stack"),
@@ -554,7 +564,7 @@ def main():
     achieved = live_flops_per_launch / (attn_mean_ms * 1e-3) / 1e12
     stack_flops = (fl["live"] + fl["qkv"] + fl["oproj"] + (fl["mlp"] if args.scope != "stack" else 0)) * B
     line = {
-        "metric": METRIC.replace("attention+projection stack", {"stack": "attention+projection stack", "block": "whole transformer blocks", "model": "whole model: embedding, blocks, final LayerNorm, last-position logits"}[args.scope]),
+        "metric": metric_name(args.workload, w).replace("attention+projection stack", {"stack": "attention+projection stack", "block": "whole transformer blocks", "model": "whole model: embedding, blocks, final LayerNorm, last-position logits"}[args.scope]),
         "value": value, "unit": "tokens/s", "n_gpus": world, "steps": steps, "warmup": warmup,
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic",

@@ -756,6 +756,7 @@ struct DeltaParams {
   int64_t delta_s[3];
   const int32_t* frozen;
   int B, H, T, force_state;
+  int hd;                       // real head width (<= the kernel's HD)
 };
 
 template <int HD>
@@ -768,7 +769,7 @@ __global__ void __launch_bounds__(256) flash_bwd_delta_kernel(const __grid_const
   const int row = blockIdx.x * ROWS + threadIdx.x / TPR;
   const int c = (threadIdx.x % TPR) * 8;
   float s = 0.f;
-  if (row < p.T) {
+  if (row < p.T && c < p.hd) {   // p.hd < HD: head_dim 96 on the 128-column kernels
     const uint4 a = *reinterpret_cast<const uint4*>(p.o + (int64_t)b * p.o_s[0] + (int64_t)h * p.o_s[1] + (int64_t)row * p.o_s[2] + c);
     const uint4 d = *reinterpret_cast<const uint4*>(p.dout + (int64_t)b * p.do_s[0] + (int64_t)h * p.do_s[1] + (int64_t)row * p.do_s[2] + c);
     const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, dw[4] = {d.x, d.y, d.z, d.w};
@@ -812,13 +813,13 @@ int bwd_launch_typed(const SafMixedAttnBwdArgs& g, bool live, bool* dense_done, 
   const SafTensor& tdk = live ? g.dk : g.dv;
   const SafTensor& tv = live ? a.v : g.dv;               // frozen_pv passes no forward tensors
   const int Uq = live ? a.U : a.H;
-  if ((rc = bwd_map4(&mq, tq, a.B, Uq, a.T, HD))) return rc;
-  if ((rc = bwd_map4(&mk, tk, a.B, Uq, a.T, HD))) return rc;
-  if ((rc = bwd_map4(&mv, tv, a.B, a.H, a.T, HD))) return rc;
-  if ((rc = bwd_map4(&mdo, g.dout, a.B, a.H, a.T, HD))) return rc;
-  if ((rc = bwd_map4(&mdq, tdq, a.B, Uq, a.T, HD))) return rc;
-  if ((rc = bwd_map4(&mdk, tdk, a.B, Uq, a.T, HD))) return rc;
-  if ((rc = bwd_map4(&mdv, g.dv, a.B, a.H, a.T, HD))) return rc;
+  if ((rc = bwd_map4(&mq, tq, a.B, Uq, a.T, a.HD))) return rc;
+  if ((rc = bwd_map4(&mk, tk, a.B, Uq, a.T, a.HD))) return rc;
+  if ((rc = bwd_map4(&mv, tv, a.B, a.H, a.T, a.HD))) return rc;
+  if ((rc = bwd_map4(&mdo, g.dout, a.B, a.H, a.T, a.HD))) return rc;
+  if ((rc = bwd_map4(&mdq, tdq, a.B, Uq, a.T, a.HD))) return rc;
+  if ((rc = bwd_map4(&mdk, tdk, a.B, Uq, a.T, a.HD))) return rc;
+  if ((rc = bwd_map4(&mdv, g.dv, a.B, a.H, a.T, a.HD))) return rc;
 
   DeltaParams d;
   d.o = reinterpret_cast<const __nv_bfloat16*>(a.out.ptr);
@@ -831,6 +832,7 @@ int bwd_launch_typed(const SafMixedAttnBwdArgs& g, bool live, bool* dense_done, 
   d.delta = reinterpret_cast<float*>(g.delta.ptr);
   d.frozen = a.frozen;
   d.B = a.B; d.H = a.H; d.T = a.T; d.force_state = a.force_state;
+  d.hd = a.HD;
   constexpr int ROWS = 256 / (HD / 8);
   if (live) {
     flash_bwd_delta_kernel<HD><<<dim3((a.T + ROWS - 1) / ROWS, a.B * a.H), 256, 0, st>>>(d);
@@ -852,7 +854,7 @@ int bwd_launch_typed(const SafMixedAttnBwdArgs& g, bool live, bool* dense_done, 
     p.delta_s[i] = g.delta.stride[i];
   }
   p.status = a.status;
-  if (a.sd_alpha && a.sd_rho) {
+  if (a.sd_alpha && a.sd_rho) {   // (the scan clips its 64-column slices to the real width)
     ScanArgs& sc = p.scan;
     sc.in = g.dout.ptr;
     sc.out = g.dv.ptr;
@@ -919,7 +921,9 @@ extern "C" int saf_debug_trace(long long* host) {
 int launch_flash_bwd_sm100(const SafMixedAttnBwdArgs& g, uint32_t* handled, cudaStream_t st) {
   *handled = 0;
   const SafMixedAttnArgs& a = g.fwd;
-  if (a.dtype != SAF_BF16 || (a.HD != 64 && a.HD != 128) || a.rope || a.HKV > 0) return SAF_ERR_UNSUPPORTED;
+  // head_dim 96 rides the 128-column kernels: the tensor maps carry the real width, loads fill the missing columns
+  // with zeros and stores clip them
+  if (a.dtype != SAF_BF16 || (a.HD != 64 && a.HD != 96 && a.HD != 128) || a.rope || a.HKV > 0) return SAF_ERR_UNSUPPORTED;
   if (!bwd_tma_ok(g.dout) || !bwd_tma_ok(g.dv)) return SAF_ERR_UNSUPPORTED;
   if (!saf_device_supported()) return SAF_ERR_UNSUPPORTED;
   // live heads need the full set of tensors; without them only the frozen-head roles are launched
@@ -932,6 +936,7 @@ int launch_flash_bwd_sm100(const SafMixedAttnBwdArgs& g, uint32_t* handled, cuda
   }
   if (live_present && !live) return SAF_ERR_UNSUPPORTED;   // live heads this launch cannot serve: leave everything
   live = live && live_present;
+  if (a.HD == 96 && !live && !(a.sd_alpha && a.sd_rho)) return SAF_ERR_UNSUPPORTED;   // no role of this launch applies
   bool dense_done = false, decomp_done = false;
   const int rc = (a.HD == 64) ? bwd_launch_typed<64>(g, live, &dense_done, &decomp_done, st)
                               : bwd_launch_typed<128>(g, live, &dense_done, &decomp_done, st);

@@ -1382,7 +1382,7 @@ int launch_flash_fwd_sm100(const SafMixedAttnArgs& a, uint32_t want, uint32_t* h
   if (q_ok) can |= 1u << SAF_LIVE;
   if (a.patt.ptr) can |= 1u << SAF_DENSE;
   if (a.alpha.ptr && a.rho.ptr && a.z.ptr) can |= 1u << SAF_DECOMP;
-  if (a.sd_alpha && a.sd_rho && a.HD != 96) can |= 1u << SAF_SINK_DECAY;   // the co-scheduled scan walks 64-column slices
+  if (a.sd_alpha && a.sd_rho) can |= 1u << SAF_SINK_DECAY;   // (the scan clips its 64-column slices to the real width)
   can &= want;
   uint32_t present = can;
   if (a.force_state >= 0) present = 1u << a.force_state;

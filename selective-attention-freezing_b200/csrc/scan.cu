@@ -14,6 +14,8 @@
 // combined across the 4 row groups of a warp with shuffles and across the 8
 // warps through shared memory.  The backward (dV = P^T dY) is the same scan run
 // over reversed rows on (1-a) dY_i / Z_i, plus a * sum_i dY_i added to row 0.
+#include <algorithm>
+
 #include "saf_internal.h"
 #include "scan_body.cuh"
 
@@ -44,9 +46,15 @@ template <typename T>
 bool scan_chunked(const ScanArgs& s, cudaStream_t st, int* rc) {
   constexpr int STASH_ROWS = 256 / (SCAN_COLS * (int)sizeof(T));   // rows of an output slice that hold 64 fp32 words
   if (!s.vec_ok || s.HD % SCAN_COLS || s.T < 4096) return false;
-  // as many chunks as the carry pass takes (64), in whole 256-row block steps
-  int chunk = ((s.T + 63) / 64 + SCAN_ROWS - 1) / SCAN_ROWS * SCAN_ROWS;
+  // Chunks are as long as the machine allows: a chunk CTA prefetches its next 256-row block while it scans the
+  // current one, so long chunks keep loads in flight, but the launch still needs about three waves of CTAs (two
+  // per SM) to fill the GPU.  At most 64 chunks (what the carry pass takes), in whole 256-row block steps.
+  const int heads = s.force_state >= 0 ? s.H : (s.n_active > 0 ? s.n_active : s.H);
+  const int n_seq = std::max(1, s.B * heads * (s.HD / SCAN_COLS));
+  const int want = std::max(1, std::min(64, (6 * device_sm_count() + n_seq - 1) / n_seq));
+  int chunk = ((s.T + want - 1) / want + SCAN_ROWS - 1) / SCAN_ROWS * SCAN_ROWS;
   const int n_chunks = (s.T + chunk - 1) / chunk;
+  if (n_chunks < 2) return false;                                   // one chunk: the one-pass kernel does it
   if (s.T - (n_chunks - 1) * chunk < STASH_ROWS) return false;     // the last chunk must hold its stash
   dim3 grid(s.B * s.H, n_chunks, s.HD / SCAN_COLS);
   sink_decay_chunk_kernel<T, 1><<<grid, SCAN_NT, 0, st>>>(s, chunk);
@@ -94,6 +102,8 @@ int launch_scan_fwd(const SafMixedAttnArgs& a, cudaStream_t st) {
   s.B = a.B; s.H = a.H; s.T = a.T; s.HD = a.HD; s.force_state = a.force_state; s.HKV = a.HKV;
   const int es = dtype_size(a.dtype);
   s.vec_ok = vec_ok(a.v.ptr, a.v.stride, es) && vec_ok(a.out.ptr, a.out.stride, es);
+  if (a.frozen_host && a.force_state < 0)
+    for (int h = 0; h < a.H; ++h) s.n_active += a.frozen_host[h] == SAF_SINK_DECAY;
   return scan_dispatch(s, a.dtype, false, st);
 }
 

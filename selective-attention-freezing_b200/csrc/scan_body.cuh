@@ -75,6 +75,7 @@ struct ScanArgs {
   const float* sd_rho;
   int B, H, T, HD, force_state, HKV;
   int vec_ok;
+  int n_active;        // host hint: heads that are in the structured state (0 = unknown, all H are assumed)
 };
 
 // 256-thread barrier that leaves barrier 0 (and any other warps of the CTA) alone

@@ -11,5 +11,7 @@ WORKLOADS = {
                hidden=1536, mlp=8960, qkv_bias=True),
     "tiny_gqa": dict(n_layer=2, n_head=6, n_kv=2, head_dim=64, n_frozen=2, T=384, B=2, rope_base=1000000.0,
                      hidden=256, mlp=512, qkv_bias=True),
+    # the reference's own ~1B recipe (nanogpt/config/train_gpt_1b_rope.py): 32 layers, 16 heads x 96
+    "r1b": dict(n_layer=32, n_head=16, head_dim=96, n_frozen=4, T=8192, B=2, rope_base=10000.0),
     "tiny": dict(n_layer=2, n_head=4, head_dim=64, n_frozen=1, T=512, B=2, rope_base=10000.0),
 }

@@ -54,9 +54,13 @@ def test_linear_rows2(shape, bias, dtype):
         dr = head_rows(dead, hd).to(dev)
         assert dev_in[1].grad[dr].abs().max().item() == 0.0
         assert dev_in[2].grad[dr].abs().max().item() == 0.0
-    # single-weight variant, bit-identical to the matching half of the fused call
+    # single-weight variant: bit-identical to the matching half of the fused call when both run the same kernel
+    # (head widths that are whole 64-row weight blocks); other widths may take different kernels for the two calls
     y1 = linear_rows(dev_in[0].detach(), dev_in[1].detach(), None if b1 is None else dev_in[3].detach(), rows.to(dev))
-    assert torch.equal(y1, y[..., : y.shape[-1] // 2])
+    if hd % 64 == 0 or dtype == torch.float32:
+        assert torch.equal(y1, y[..., : y.shape[-1] // 2])
+    else:
+        assert errs(y1, y[..., : y.shape[-1] // 2])[1] <= 1e-2
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["fp32", "bf16"])
@@ -111,8 +115,10 @@ def test_decomposed_logz_kernel():
 @pytest.mark.parametrize("cfg", [(2, 9000, 768, 12, 64, [0, 1, 3, 4, 6, 7, 9, 10, 11], False),
                                  (2, 1000, 768, 12, 64, [0, 1, 3, 4, 6, 7, 9, 10, 11], True),
                                  (1, 700, 512, 4, 128, [0, 2, 3], False),
-                                 (3, 129, 256, 4, 64, [], False)],
-                         ids=["c2shape", "bias", "hd128", "allfrozen"])
+                                 (3, 129, 256, 4, 64, [], False),
+                                 (1, 1500, 1536, 16, 96, [0, 1, 2, 3, 5, 6, 7, 9, 10, 11, 13, 14], False),
+                                 (2, 333, 384, 4, 96, [1, 3], True)],
+                         ids=["c2shape", "bias", "hd128", "allfrozen", "hd96", "hd96bias"])
 def test_qkv_projection_with_rope_epilogue(cfg):
     """[Q(live) | K(live) | V(all)] in one tensor-core GEMM with the rotation in the epilogue equals
     projection followed by the reference's apply_rotary_pos_emb (nanogpt/model.py:63-68)."""
