@@ -154,6 +154,19 @@ def launch_count():
 # ---------------------------------------------------------------------------
 # host helpers kept from the reference's import surface (pure index algebra)
 # ---------------------------------------------------------------------------
+def _toeplitz_windows(rho, width, cols=None):
+    """W of shape (H, width, S) with W[h, w, u] = rho[h, u - w] (-inf where u < w): row w is rho shifted right
+    by w.  Built without index arithmetic: rho is padded with `width - 1` leading -inf values, reversed, and its
+    length-S sliding windows (a strided view, `unfold`) are read back to front.  cols = (u0, u1) materialises
+    only those columns."""
+    H, S = rho.shape
+    u0, u1 = (0, S) if cols is None else cols
+    pad = rho.new_full((H, width - 1), float("-inf"))
+    rev = torch.cat([pad, rho], dim=1).flip(1)               # rev[k] = padded[S + width - 2 - k]
+    win = rev.unfold(1, S, 1)                                 # (H, width, S) view: win[h, i, u] = rev[h, i + u]
+    return win[:, :, S - u1:S - u0].flip(2)                   # [h, i, u - u0] = padded[width - 1 - i + u] = rho[u - i]
+
+
 def make_rho_band(rho):
     """(H, S) -> (H, 64, S) with band[h, r, u] = rho[h, r - u + (S - 64)], -inf outside
     (kernel/fused_attn.py:65-80).  The CUDA kernels index rho directly and do not
@@ -161,23 +174,19 @@ def make_rho_band(rho):
     H, S = rho.shape
     assert S % BAND_ROWS == 0, \
         f"decomposed prior buffer length {S} must be a multiple of {BAND_ROWS}"
-    r = torch.arange(BAND_ROWS, device=rho.device)[:, None]
-    u = torch.arange(S, device=rho.device)[None, :]
-    src = r - u + (S - BAND_ROWS)
-    inside = (src >= 0) & (src < S)
-    band = rho[:, src.clamp(0, S - 1)]
-    return band.masked_fill(~inside, float("-inf")).contiguous()
+    # band row r, read right to left, is rho shifted by (63 - r): reverse the columns of the shifted copies
+    shifted = _toeplitz_windows(rho, BAND_ROWS)               # [h, w, u] = rho[h, u - w]
+    return shifted.flip(1).flip(2).contiguous()               # [h, r, u] = rho[h, (S - 1 - u) - (63 - r)]
 
 
 def decomp_logits(alpha, rho, rows=None):
     """L[h,i,j] = alpha[h,j] + rho[h,i-j], -inf above the diagonal (kernel/fused_attn.py:83-98)."""
     H, S = alpha.shape
     r0, r1 = (0, S) if rows is None else rows
-    i = torch.arange(r0, r1, device=alpha.device)
-    j = torch.arange(S, device=alpha.device)
-    dist = i[:, None] - j[None, :]
-    lg = alpha[:, None, :] + rho[:, dist.clamp(min=0)]
-    return lg.masked_fill(dist < 0, float("-inf"))
+    # column j of the Toeplitz matrix rho[i - j] is rho shifted down by j; the -inf padding of the shifted copies
+    # is the causal mask
+    shifted = _toeplitz_windows(rho, S, cols=(r0, r1))        # [h, j, i - r0] = rho[h, i - j]
+    return alpha[:, None, :] + shifted.transpose(1, 2)
 
 
 @torch.no_grad()
