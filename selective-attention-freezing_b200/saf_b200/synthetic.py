@@ -36,18 +36,20 @@ def build_attention_layer(w, li, g, seed=1337):
     with torch.no_grad():
         for lin in (m.q_proj, m.k_proj, m.v_proj, m.c_proj):
             lin.weight.copy_(torch.randn(C, C, generator=g) * 0.02)
-    fz = frozen_heads_for_layer(w["n_head"], w["n_frozen"], seed, li)
+    fz = w.get("frozen_heads") or frozen_heads_for_layer(w["n_head"], w["n_frozen"], seed, li)
     a, r = sink_decay_params(len(fz), seed + 1000 + li)
     m.freeze_heads_sink_decay(fz, a.tolist(), r.tolist())
     return m
 
 
-def build_attention_stack(name, device, dtype=torch.bfloat16, seed=1337, blocks=False, n_layer=None):
+def build_attention_stack(name, device, dtype=None, seed=1337, blocks=False, n_layer=None):
     """The attention+projection stack of a GPT-2-style model: one SafCausalSelfAttention per layer with
     random-init N(0, 0.02^2) weights, 25 % of the heads of every layer frozen on seeded sink+decay patterns.
     blocks=True wraps every layer in its transformer block (LayerNorms, residuals, MLP with 4x expansion);
     n_layer builds only the first layers (same weights as the full stack's)."""
     w = WORKLOADS[name]
+    if dtype is None:
+        dtype = getattr(torch, w.get("dtype", "bfloat16"))
     if w.get("n_kv") is not None:
         raise ValueError("workload %r is grouped-query: build it with saf_b200.gqa.build_gqa_stack" % name)
     C = w["n_head"] * w["head_dim"]

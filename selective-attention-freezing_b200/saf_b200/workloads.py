@@ -3,6 +3,9 @@ the CUDA library -- the CPU reference arm of the benchmark -- can read it by pat
 
 WORKLOADS = {
     # name: layers, heads, head_dim, frozen heads per layer, sequence, batch per GPU
+    # c0: the single fp32 layer the reference can run on a CPU (heads 2, 5, 8 frozen)
+    "c0": dict(n_layer=1, n_head=12, head_dim=64, n_frozen=3, T=1024, B=2, rope_base=10000.0, dtype="float32",
+               frozen_heads=[2, 5, 8]),
     "c1": dict(n_layer=12, n_head=12, head_dim=64, n_frozen=3, T=4096, B=16, rope_base=10000.0),
     "c2": dict(n_layer=12, n_head=12, head_dim=64, n_frozen=3, T=16384, B=4, rope_base=10000.0),
     "c3": dict(n_layer=24, n_head=16, head_dim=128, n_frozen=4, T=8192, B=2, rope_base=10000.0),
