@@ -62,7 +62,11 @@ __device__ __forceinline__ void store8(T* p, int64_t sd, bool vec, int ncol, con
 __device__ __forceinline__ float inv_z(float r, float log_r, int n) {
   if (r >= 1.f) return 1.f / (float)n;
   if (r <= 0.f) return 1.f;
-  return (1.f - r) / (-expm1f((float)n * log_r));
+  // r^n below half an fp32 ulp of 1: Z has converged to 1 / (1 - r) (true for all but the first rows of a long
+  // sequence, and the test is uniform over almost every warp: the exponential and the division are skipped)
+  const float t = (float)n * log_r;
+  if (t < -17.5f) return 1.f - r;
+  return (1.f - r) / (-expm1f(t));
 }
 
 struct ScanArgs {
