@@ -7,5 +7,5 @@ the attention-module hook, `kernel` (sibling package) the drop-in import surface
 """
 from . import _cabi  # noqa: F401  (raises if the CUDA library is not built)
 from .ops import (fused_mixed_attn, frozen_pv, linear_rows, linear_rows2, linear_permuted_cols,  # noqa: F401
-                  qkv_projection, decomposed_logz, decomp_logits, make_rho_band, fused_attn_usable,
+                  qkv_projection, decomposed_logz, decomposed_logz_fft, decomp_logits, make_rho_band, fused_attn_usable,
                   frozen_pv_usable, launch_count, BAND_ROWS)

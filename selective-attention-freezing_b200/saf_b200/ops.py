@@ -211,6 +211,29 @@ def decomposed_logz(alpha, rho, chunk=None):
     return z
 
 
+def decomposed_logz_fft(alpha, rho):
+    """The same row normalisers, z[h,i] = log sum_{j<=i} exp(alpha[h,j]) exp(rho[h,i-j]), as the first T entries of a
+    linear convolution computed with FFTs in O(T log T) (nanogpt/dynamic_freeze.py:330-361).  Differentiable in
+    alpha and rho (the reference's prior fitter optimises through it); any device.  Both factors are shifted by
+    their detached row maxima and the transform runs in fp64: one global shift cannot keep an early prefix, whose
+    terms may sit far below a late maximum, above fp32 round-off of the transform.  Like the reference's, it resolves
+    prefixes down to about 1e-13 of the largest term; beyond that spread use decomposed_logz."""
+    if alpha.ndim != 2 or alpha.shape != rho.shape:
+        raise ValueError("alpha and rho must have matching (N, T) shapes")
+    T = alpha.shape[1]
+    wide = torch.float64
+    a_max = alpha.detach().to(wide).amax(dim=-1, keepdim=True)
+    r_max = rho.detach().to(wide).amax(dim=-1, keepdim=True)
+    ea = torch.exp(alpha.to(wide) - a_max)
+    er = torch.exp(rho.to(wide) - r_max)
+    n = 1
+    while n < 2 * T - 1:                       # zero padding makes the circular product a linear one
+        n *= 2
+    conv = torch.fft.irfft(torch.fft.rfft(ea, n=n) * torch.fft.rfft(er, n=n), n=n)[..., :T]
+    z = torch.log(conv.clamp_min(torch.finfo(wide).tiny)) + a_max + r_max
+    return z.to(alpha.dtype)
+
+
 def fused_attn_usable(q):
     """True when the CUDA library can serve this tensor (kernel/fused_attn.py:61-62)."""
     return bool(q.is_cuda)

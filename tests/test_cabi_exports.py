@@ -154,3 +154,23 @@ def test_static_backward_validates_before_it_applies_its_limit():
     for t in (g.fwd.v, g.fwd.out, g.fwd.q, g.fwd.k):
         t.stride[3] = 1
     assert _cabi.lib.saf_mixed_attn_bwd_static(C.byref(g), None) == _cabi.SAF_ERR_LIMIT
+
+
+def test_fft_normalisers_match_the_direct_ones_and_differentiate():
+    """decomposed_logz_fft (the reference's O(T log T) normaliser, nanogpt/dynamic_freeze.py:330-361) equals the
+    direct logsumexp the oracle is pinned on (for logit spreads the transform's fp64 round-off can resolve) and its
+    gradient equals the dense one's."""
+    import torch
+    from oracle import saf_oracle as O
+    from saf_b200 import decomposed_logz_fft
+    g = torch.Generator().manual_seed(8)
+    for scale in (0.8, 3.0):
+        alpha = torch.randn(3, 192, generator=g) * scale
+        rho = torch.randn(3, 192, generator=g) * scale - 0.02 * torch.arange(192)
+        z = decomposed_logz_fft(alpha, rho)
+        assert O.max_abs(z, O.decomposed_logz(alpha, rho)) <= 2e-5 * max(1.0, scale)
+    a1, r1 = alpha.clone().requires_grad_(True), rho.clone().requires_grad_(True)
+    decomposed_logz_fft(a1, r1).sum().backward()
+    a2, r2 = alpha.clone().requires_grad_(True), rho.clone().requires_grad_(True)
+    O.decomp_logits(a2, r2).logsumexp(-1).sum().backward()
+    assert O.max_abs(a1.grad, a2.grad) <= 1e-4 and O.max_abs(r1.grad, r2.grad) <= 1e-4
