@@ -122,7 +122,6 @@ struct FlashBars {
   uint64_t k_full[4], k_empty[4], v_full[4], v_empty[4];
   uint64_t s_full[3];     // score buffer written by the score MMAs
   uint64_t p_full[3];     // P written by the softmax warpgroup (128 arrivals)
-  uint64_t p_half[3];     // its first 64 key columns written (128 arrivals; only with SAF_P_HALVES)
   uint64_t buf_free[3];   // PV product that read P from this buffer has finished
   uint32_t tmem_base;
   float dec_alpha[2][128];   // decomposed heads: alpha of the current key tile, per query tile
@@ -157,19 +156,6 @@ __device__ __forceinline__ float2 exp2_poly2(float2 x) {
   r.y = __int_as_float(__float_as_int(p.y) + (__float_as_int(t.y) << 23));
   return r;
 }
-
-// bf16x2 pack on the integer pipe: round half up by adding 0x8000 to the fp32 bit patterns, then take the two
-// high halves with one byte permute (values here are finite and non-negative)
-__device__ __forceinline__ uint32_t pack_bf16_int(float lo, float hi) {
-  uint32_t r;
-  asm("prmt.b32 %0, %1, %2, 0x7632;" : "=r"(r) : "r"(__float_as_uint(lo) + 0x8000u), "r"(__float_as_uint(hi) + 0x8000u));
-  return r;
-}
-#ifdef SAF_INT_PACK
-#define PACK_P(lo, hi) pack_bf16_int(lo, hi)
-#else
-#define PACK_P(lo, hi) pack_bf16(lo, hi)
-#endif
 
 template <int N>
 __device__ __forceinline__ void reg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
@@ -249,7 +235,6 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
     for (int i = 0; i < 3; ++i) {
       mbar_init(&bars->s_full[i], 1);
       mbar_init(&bars->p_full[i], 128);
-      mbar_init(&bars->p_half[i], 128);
       mbar_init(&bars->buf_free[i], 1);
     }
     fence_mbar_init();
@@ -374,23 +359,6 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
           }
           const uint32_t va = vbase + vs_ * C::TILE_BYTES;
           const uint32_t dO = tmem + C::O_COL + t * HD, aP = tmem + buf * FN;
-#ifdef SAF_P_HALVES
-          if (live) {
-            // live heads hand P over in two halves of 64 keys: the first four MMAs start while the softmax warps
-            // are still producing the second half
-            if (!mbar_wait(&bars->p_half[buf], bph)) {
-              dev_set_error(p.status, SAF_DEV_TIMEOUT_MMA, 32);
-              break;
-            }
-            tc_fence_after();
-            if (leader) {
-#pragma unroll
-              for (int ks = 0; ks < FN / 32; ++ks)
-                umma_ts(dO, aP + ks * 8, umma_smem_desc_sw128(va + ks * 2048, 16384, 1024), idesc_o, (j > 0) || (ks > 0));
-            }
-            __syncwarp();
-          }
-#endif
           if (!mbar_wait(&bars->p_full[buf], bph)) {
             dev_set_error(p.status, SAF_DEV_TIMEOUT_MMA, 26);
             break;
@@ -398,15 +366,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
           tc_fence_after();
           if (t == 0) FTRACE(3, j);
           if (leader) {
-#ifdef SAF_P_HALVES
-            const int ks0 = live ? FN / 32 : 0;
-#else
-            const int ks0 = 0;
-#endif
 #pragma unroll
             for (int ks = 0; ks < FN / 16; ++ks)
-              if (ks >= ks0)
-                umma_ts(dO, aP + ks * 8, umma_smem_desc_sw128(va + ks * 2048, 16384, 1024), idesc_o, (j > 0) || (ks > 0));
+              umma_ts(dO, aP + ks * 8, umma_smem_desc_sw128(va + ks * 2048, 16384, 1024), idesc_o, (j > 0) || (ks > 0));
             umma_commit(&bars->buf_free[buf]);
             if (t == 1 || !act1) umma_commit(&bars->v_empty[vs_]);   // last reader of V_j
           }
@@ -563,28 +525,17 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
           for (int i = 0; i < 16; ++i) {
             const float2 x = __ffma2_rn(make_float2(__uint_as_float(s[q][2 * i]), __uint_as_float(s[q][2 * i + 1])), sc2, nm2);
             float2 e;
-#ifdef SAF_WHATIF_NOEXP
-            e = x;
-#else
             if (i < SAF_POLY_EXP_PER_16 / 2) {
               e = exp2_poly2(x);
             } else {
               e.x = ex2(x.x);
               e.y = ex2(x.y);
             }
-#endif
             if (i & 1) acc1 = __fadd2_rn(acc1, e);
             else acc0 = __fadd2_rn(acc0, e);
-            pk[i] = PACK_P(e.x, e.y);
+            pk[i] = pack_bf16(e.x, e.y);
           }
           tmem_st16(tS + q * 16, pk);
-#ifdef SAF_P_HALVES
-          if (q == 1) {   // keys 0..63 of P are complete: the output issuer may start on them
-            tmem_st_wait();
-            tc_fence_before();
-            mbar_arrive(&bars->p_half[buf]);
-          }
-#endif
         }
         acc0 = __fadd2_rn(acc0, acc1);
         return acc0.x + acc0.y;
@@ -624,28 +575,6 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
         }
         return true;
       };
-#if defined(SAF_SPECULATIVE_MAX) && !defined(SAF_P_HALVES)
-      if (j > 0) {
-        // The reference maximum rarely moves by more than the rescale threshold, so P is produced against the
-        // old one while the row maximum is still being reduced (the two instruction streams are independent);
-        // in the rare case that the maximum did jump, O is rescaled and P produced again.
-        float acc = emit_p(m_ref);
-        const float mx = row_max();
-        const bool need = mx > m_ref + RESCALE_THRESHOLD;
-        if (__any_sync(0xffffffffu, need)) {
-          tmem_st_wait();
-          if (!rescale_o(need, mx)) {
-            ok = false;
-            break;
-          }
-          acc = emit_p(m_ref);
-        }
-        l += acc;
-      } else {
-        m_ref = row_max();
-        l += emit_p(m_ref);
-      }
-#else
       const float mx = row_max();
       if (j == 0) {
         m_ref = mx;
@@ -657,7 +586,6 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
         }
       }
       l += emit_p(m_ref);
-#endif
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(&bars->p_full[buf]);

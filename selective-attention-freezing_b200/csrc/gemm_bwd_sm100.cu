@@ -31,6 +31,11 @@ enum { MODE_DX = 0, MODE_DW = 1 };
 struct BlockTable {
   int32_t row0[BMAX_SUB];
   uint8_t weight[BMAX_SUB];
+  // slabs that are a multiple of 32 but not of 64 rows (head_dim 96): a 64-row block is two runs of 32 weight
+  // rows, each with its own source (first run in row0 / weight, second run here); the weight maps then carry
+  // 32-row boxes
+  int32_t row0b[BMAX_SUB];
+  uint8_t weightb[BMAX_SUB];
 };
 
 struct BwdGemmParams {
@@ -39,6 +44,7 @@ struct BwdGemmParams {
   int n_blocks;              // selected 64-row blocks
   const void* bias;          // DX only: bf16 over the J output columns, or null
   int* status;
+  int halves;                // see BlockTable
 };
 
 struct BSmem {
@@ -103,8 +109,11 @@ indexed_gemm_bwd_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_c
           if (MODE == MODE_DX) {
             mbar_expect_tx(&sl->full[s], BA_BYTES + nsub * ATOM);
             tma_load_2d(a, &mapA, &sl->full[s], kb * BK, tm * BM);               // dout[m tile, block kb]
-            for (int u = 0; u < nsub; ++u)
+            for (int u = 0; u < nsub; ++u) {
               tma_load_2d(b + u * ATOM, wm[tb.weight[kb]], &sl->full[s], tn * BN + u * 64, tb.row0[kb]);
+              if (p.halves)
+                tma_load_2d(b + u * ATOM + ATOM / 2, wm[tb.weightb[kb]], &sl->full[s], tn * BN + u * 64, tb.row0b[kb]);
+            }
           } else {
             mbar_expect_tx(&sl->full[s], (nrow + nsub) * ATOM);
             for (int u = 0; u < nrow; ++u)
@@ -208,6 +217,7 @@ indexed_gemm_bwd_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_c
             for (int hb = 0; hb < nrow; ++hb) {
               const int sb = tm * 2 + hb;
               tma_store_2d(wm[tb.weight[sb]], src + hb * ATOM, tn * BN + u * 64, tb.row0[sb]);
+              if (p.halves) tma_store_2d(wm[tb.weightb[sb]], src + hb * ATOM + ATOM / 2, tn * BN + u * 64, tb.row0b[sb]);
             }
           }
           tma_store_commit();
@@ -234,8 +244,8 @@ int map2(CUtensorMap* m, const void* base, uint64_t cols, uint64_t rows, int64_t
 }
 
 bool common_ok(const SafIndexedLinearArgs& a, const void* dout, int64_t lddo) {
-  if (a.dtype != SAF_BF16 || a.slab % 64 || a.n_slabs <= 0 || a.M <= 0) return false;
-  if (a.n_slabs * (a.slab / 64) > BMAX_SUB) return false;
+  if (a.dtype != SAF_BF16 || a.slab % 32 || (a.n_slabs * a.slab) % 64 || a.n_slabs <= 0 || a.M <= 0) return false;
+  if (a.n_slabs * a.slab / 64 > BMAX_SUB) return false;
   if (a.C % 8 || lddo % 8 || !al16(dout)) return false;
   for (int w = 0; w < a.n_weights; ++w) {
     if (!a.weights[w]) return false;
@@ -244,8 +254,23 @@ bool common_ok(const SafIndexedLinearArgs& a, const void* dout, int64_t lddo) {
   return saf_device_supported() != 0;
 }
 
+bool is_halves(const SafIndexedLinearArgs& a) { return a.slab % 64 != 0; }
+
 void fill_blocks(const SafIndexedLinearArgs& a, BlockTable* tb) {
   memset(tb, 0, sizeof(*tb));
+  if (is_halves(a)) {
+    for (int hb = 0; hb < a.n_slabs * a.slab / 32; ++hb) {       // 32-row runs, two per block
+      const int g = (hb * 32) / a.slab, r = (hb * 32) % a.slab;
+      if (hb & 1) {
+        tb->row0b[hb >> 1] = a.slab_row0[g] + r;
+        tb->weightb[hb >> 1] = (uint8_t)a.slab_weight[g];
+      } else {
+        tb->row0[hb >> 1] = a.slab_row0[g] + r;
+        tb->weight[hb >> 1] = (uint8_t)a.slab_weight[g];
+      }
+    }
+    return;
+  }
   const int per = a.slab / 64;
   for (int g = 0; g < a.n_slabs; ++g)
     for (int u = 0; u < per; ++u) {
@@ -279,13 +304,14 @@ int launch_gemm_bwd_dx_sm100(const SafIndexedLinearArgs& a, const void* dout, in
   if ((rc = map2(&ma, dout, (uint64_t)N, (uint64_t)a.M, lddo, 128))) return rc;
   for (int w = 0; w < 4; ++w) {
     const int ww = w < a.n_weights ? w : 0;
-    if ((rc = map2(&mw[w], a.weights[ww], (uint64_t)a.C, (uint64_t)a.rows_w[ww], a.ldw[ww], 64))) return rc;
+    if ((rc = map2(&mw[w], a.weights[ww], (uint64_t)a.C, (uint64_t)a.rows_w[ww], a.ldw[ww], is_halves(a) ? 32 : 64))) return rc;
   }
   if ((rc = map2(&mo, dx, (uint64_t)a.C, (uint64_t)a.M, lddx, 128))) return rc;
   BlockTable tb;
   fill_blocks(a, &tb);
   BwdGemmParams p;
   memset(&p, 0, sizeof(p));
+  p.halves = is_halves(a) ? 1 : 0;
   p.I = a.M; p.J = a.C; p.KB = N / 64; p.n_blocks = N / 64;
   p.tiles_m = (a.M + BM - 1) / BM;
   p.tiles_n = (a.C + BN - 1) / BN;
@@ -306,12 +332,13 @@ int launch_gemm_bwd_dw_sm100(const SafIndexedLinearArgs& a, const void* dout, in
   if ((rc = map2(&mb, a.x, (uint64_t)a.C, (uint64_t)a.M, a.ldx, 64))) return rc;
   for (int w = 0; w < 4; ++w) {
     const int ww = w < a.n_weights ? w : 0;
-    if ((rc = map2(&mw[w], a.weights[ww], (uint64_t)a.C, (uint64_t)a.rows_w[ww], a.ldw[ww], 64))) return rc;
+    if ((rc = map2(&mw[w], a.weights[ww], (uint64_t)a.C, (uint64_t)a.rows_w[ww], a.ldw[ww], is_halves(a) ? 32 : 64))) return rc;
   }
   BlockTable tb;
   fill_blocks(a, &tb);
   BwdGemmParams p;
   memset(&p, 0, sizeof(p));
+  p.halves = is_halves(a) ? 1 : 0;
   p.I = N; p.J = a.C; p.KB = (a.M + BK - 1) / BK; p.n_blocks = N / 64;
   p.tiles_m = (p.n_blocks + 1) / 2;
   p.tiles_n = (a.C + BN - 1) / BN;

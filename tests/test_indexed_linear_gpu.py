@@ -147,6 +147,7 @@ def test_qkv_projection_with_rope_epilogue(cfg):
 
 @pytest.mark.parametrize("cfg", [(2, 300, 256, 4, 64, [0, 2, 3], torch.float32), (2, 300, 256, 4, 64, [0, 2, 3], torch.bfloat16),
                                  (1, 1100, 1024, 8, 128, [0, 1, 2, 4, 5, 7], torch.bfloat16),
+                                 (1, 700, 768, 8, 96, [0, 1, 2, 4, 5, 7], torch.bfloat16),
                                  (2, 40, 96, 3, 32, [0, 2], torch.float32)],
                          ids=lambda c: f"T{c[1]}C{c[2]}hd{c[4]}{'bf16' if c[6] == torch.bfloat16 else 'fp32'}")
 def test_linear_rows2_with_fused_rope(cfg):
