@@ -136,6 +136,8 @@ __device__ __forceinline__ void sink_decay_scan_cta(const ScanArgs& a, int b, in
 #pragma unroll
   for (int c = 0; c < 8; ++c) v0[c] = 0.f;
   if (!BWD && ncol > 0) load8<T>(ib, a.si[3], vec, ncol, v0);
+#pragma unroll
+  for (int c = 0; c < 8; ++c) v0[c] *= alpha;            // the sink term a * v_0 of every output row
   float carry[8], csum[8];
 #pragma unroll
   for (int c = 0; c < 8; ++c) carry[c] = csum[c] = 0.f;
@@ -254,7 +256,7 @@ __device__ __forceinline__ void sink_decay_scan_cta(const ScanArgs& a, int b, in
       if (!BWD) {
         const float w = (1.f - alpha) * inv_z(r, log_r, i + 1);
 #pragma unroll
-        for (int c = 0; c < 8; ++c) o[c] = fmaf(alpha, v0[c], w * fmaf(rp, cin[c], x[j][c]));
+        for (int c = 0; c < 8; ++c) o[c] = fmaf(w, fmaf(rp, cin[c], x[j][c]), v0[c]);
       } else {
 #pragma unroll
         for (int c = 0; c < 8; ++c) o[c] = fmaf(rp, cin[c], x[j][c]);

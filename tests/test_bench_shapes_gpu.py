@@ -214,3 +214,50 @@ def test_layer_of_the_benchmark_stack(name, B):
         torch.backends.cuda.matmul.allow_tf32 = prev
     a, r = errs(y, full)
     assert a <= FWD_ABS and r <= FWD_REL, f"all rows: max-abs {a} rel-l2 {r}"
+
+
+@pytest.mark.parametrize("with_dense", [False, True], ids=["structured", "structured+dense"])
+def test_head_dim_96_recipe_shape_forward_and_backward(with_dense):
+    """16 heads x 96 at T=8192 (the reference's own ~1B recipe, nanogpt/config/train_gpt_1b_rope.py): the 128-column
+    tensor-core kernels with zero-filled tiles, forward and all three input gradients.  With a dense-stored head
+    the call takes the one-shot kernel (pattern tiles produced by the softmax warps), without it the persistent one."""
+    from kernel import fused_mixed_attn
+    dev, B, T, hd, H = "cuda", 1, 8192, 96, 16
+    states = [0] * H
+    states[2], states[11] = 3, 3
+    patt = pidx = None
+    if with_dense:
+        states[7] = 1
+        g = torch.Generator().manual_seed(79)
+        p = torch.rand(1, T, T, generator=g).tril_()
+        p /= p.sum(-1, keepdim=True)
+        patt = p.bfloat16()
+        pidx = torch.zeros(H, dtype=torch.int32)
+    live, hidx = head_maps(H, states)
+    q, k, v = op_inputs(B, len(live), H, len(live), T, hd, 9696, dev)
+    a, r = O.sink_decay_params(H, 6337)
+    sd = (a.float().double(), r.float().double())
+    qd, kd, vd = [t.to(dev).requires_grad_(True) for t in (q, k, v)]
+    y = fused_mixed_attn(qd, kd, vd, None if patt is None else patt.to(dev),
+                         torch.tensor(states, dtype=torch.int32, device=dev), hidx.to(dev),
+                         None if pidx is None else pidx.to(dev), sink_decay=(sd[0].float().to(dev), sd[1].float().to(dev)))
+    gw = torch.Generator().manual_seed(7)
+    w = torch.randn(B, H, T, hd, generator=gw).bfloat16()
+    y.backward(w.to(dev))
+    torch.cuda.synchronize()
+    kw = dict(sink_decay=sd)
+    if with_dense:
+        kw.update(patt=patt.float(), pidx=pidx)
+    check_forward(y.detach(), q, k, v, states, hidx, T, **kw)
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        rq, rk, rv = [t.to(dev).float().requires_grad_(True) for t in (q, k, v)]
+        y_ref = O.mixed_attn(rq, rk, rv, None if patt is None else patt.float().to(dev), states, hidx=hidx, pidx=pidx,
+                             sink_decay=sd)
+        y_ref.backward(w.to(dev).float())
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = prev
+    for name, got, want in (("dq", qd.grad, rq.grad), ("dk", kd.grad, rk.grad), ("dv", vd.grad, rv.grad)):
+        a_, r_ = errs(got, want)
+        assert a_ <= BWD_ABS and r_ <= BWD_REL, f"{name}: max-abs {a_} rel-l2 {r_}"
