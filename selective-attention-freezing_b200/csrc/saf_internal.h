@@ -81,6 +81,8 @@ int launch_generic_fwd(const SafMixedAttnArgs& a, uint32_t states_mask, cudaStre
 int launch_generic_bwd(const SafMixedAttnBwdArgs& a, uint32_t states_mask, cudaStream_t st);
 int launch_scan_fwd(const SafMixedAttnArgs& a, cudaStream_t st);                       // state 3 heads
 int launch_scan_bwd(const SafMixedAttnBwdArgs& a, cudaStream_t st);                    // state 3 heads: dv
+// state 3 heads, forward, on the tensor core (bf16, head_dim a multiple of 64, long T); SAF_ERR_UNSUPPORTED otherwise
+int launch_scan_fwd_mma(const SafMixedAttnArgs& a, cudaStream_t st);
 // tcgen05 fast path; returns SAF_ERR_UNSUPPORTED when the call does not qualify
 // `want`: states still to be served; the launch covers the subset it can and reports it
 int launch_flash_fwd_sm100(const SafMixedAttnArgs& a, uint32_t want, uint32_t* handled_states, cudaStream_t st);

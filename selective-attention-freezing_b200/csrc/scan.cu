@@ -88,6 +88,10 @@ int scan_dispatch(const ScanArgs& s, int dtype, bool bwd, cudaStream_t st) {
 
 int launch_scan_fwd(const SafMixedAttnArgs& a, cudaStream_t st) {
   if (!a.sd_alpha || !a.sd_rho) return fail(SAF_ERR_INVALID, "sink-decay heads need sd_alpha and sd_rho");
+  {   // long bf16 sequences: blocks of 128 rows as Toeplitz products on the tensor core
+    const int rc = launch_scan_fwd_mma(a, st);
+    if (rc != SAF_ERR_UNSUPPORTED) return rc;
+  }
   ScanArgs s{};
   s.in = a.v.ptr;
   s.out = a.out.ptr;

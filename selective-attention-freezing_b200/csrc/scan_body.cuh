@@ -66,6 +66,9 @@ __device__ __forceinline__ float inv_z(float r, float log_r, int n) {
   // sequence, and the test is uniform over almost every warp: the exponential and the division are skipped)
   const float t = (float)n * log_r;
   if (t < -17.5f) return 1.f - r;
+  // r^n at most 1/2: 1 - r^n has no cancellation, so the hardware exponential (2 ulp) and reciprocal (1 ulp) keep
+  // the quotient within a few fp32 ulp
+  if (t < -0.6931472f) return __fdividef(1.f - r, 1.f - exp2f(t * 1.4426950408889634f));
   return (1.f - r) / (-expm1f(t));
 }
 
