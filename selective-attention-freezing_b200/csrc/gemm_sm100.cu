@@ -16,6 +16,9 @@
 //               -> TMA store (two staging blocks in flight).  The row's cos/sin values are fetched once
 //               per tile, before the accumulator is waited for, so their latency hides behind the MMAs.
 // All waits are bounded; a wait that runs out sets *status and the CTA drains.
+#include <algorithm>
+#include <atomic>
+
 #include "saf_internal.h"
 #include "sm100_prims.cuh"
 
@@ -24,11 +27,19 @@ namespace {
 
 constexpr int GM = 128, GN = 256, GK = 64;   // 128x256 tiles: 96 B/clk/SM of operand traffic at full MMA rate
 constexpr int SUBS = GN / 64;                // 64-column blocks per tile
-constexpr int STAGES = 4;
 constexpr int A_BYTES = GM * GK * 2;            // 16 KB
-constexpr int B_BYTES = GN * GK * 2;            // 32 KB
 constexpr int SUB_BYTES = 64 * GK * 2;          // 8 KB: one 64-row block of weights
-constexpr int STAGE_BYTES = A_BYTES + B_BYTES;  // 48 KB
+constexpr int MAX_STAGES = 6;
+// PAIR: two CTAs of a cluster share one 256 x 256 tile through tcgen05 cta_group::2.  Each CTA loads its 128 rows of x
+// and HALF of the weight tile (two 64-row blocks), so the operand traffic per SM drops from 96 to 64 bytes per clock at
+// the full MMA rate -- what one SM can pull from L2 -- and a stage shrinks to 32 KB (6 stages instead of 4).
+template <bool PAIR>
+struct GCfg {
+  static constexpr int STAGES = PAIR ? 6 : 4;
+  static constexpr int B_SUBS = PAIR ? 2 : SUBS;                       // weight blocks a CTA loads per stage
+  static constexpr int STAGE_BYTES = A_BYTES + B_SUBS * SUB_BYTES;     // 32 KB / 48 KB
+  static constexpr int ROWS = PAIR ? 2 * GM : GM;                      // rows of a tile
+};
 constexpr int OUT_BYTES = 2 * GM * 64 * 2;      // two 16 KB staging blocks for the TMA stores
 constexpr int MAX_SUB = 288;                    // 64-row blocks of output features (N <= 18432)
 constexpr int GEMM_THREADS = 192;   // TMA warp, MMA warp, one epilogue warpgroup
@@ -81,10 +92,11 @@ __device__ __forceinline__ float silu_mul(float g, float u) {
 }
 
 struct SmemLayout {
-  uint64_t full[STAGES], empty[STAGES], acc_full[2], acc_empty[2];
+  uint64_t full[MAX_STAGES], empty[MAX_STAGES], acc_full[2], acc_empty[2];
   uint32_t tmem_base;
 };
 
+template <bool PAIR>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 indexed_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant__ CUtensorMap mapW0,
                     const __grid_constant__ CUtensorMap mapW1, const __grid_constant__ CUtensorMap mapW2,
@@ -92,30 +104,44 @@ indexed_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_const
                     const __grid_constant__ GemmParams p, const __grid_constant__ SubTable tb) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  using C = GCfg<PAIR>;
+  constexpr int STAGES = C::STAGES, STAGE_BYTES = C::STAGE_BYTES;
   uint8_t* stage_base = smem;
   uint8_t* out_stage = smem + STAGES * STAGE_BYTES;
   SmemLayout* sl = reinterpret_cast<SmemLayout*>(out_stage + OUT_BYTES);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int KB = (p.K + GK - 1) / GK;
   const int total_tiles = p.tiles_m * p.tiles_n;
+  // each CTA walks a contiguous run of tiles (column tile fastest): consecutive tiles share their rows, so the
+  // row's cos / sin values stay in registers and the x tile stays hot in L2
+  const int rank = PAIR ? (int)cluster_ctarank() : 0;                 // which 128 rows of the tile are this CTA's
+  const int unit = PAIR ? blockIdx.x >> 1 : blockIdx.x, n_units = PAIR ? gridDim.x >> 1 : gridDim.x;
+  const int tile_lo = (int)((int64_t)unit * total_tiles / n_units);
+  const int tile_hi = (int)((int64_t)(unit + 1) * total_tiles / n_units);
 
   if (tid == 0) {
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(&sl->full[s], 1);
+      mbar_init(&sl->full[s], PAIR ? 2 : 1);            // pair: one producer per CTA, both on the even CTA's barrier
       mbar_init(&sl->empty[s], 1);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&sl->acc_full[b], 1);
-      mbar_init(&sl->acc_empty[b], 4);      // one arrival per epilogue warp
+      mbar_init(&sl->acc_empty[b], PAIR ? 8 : 4);       // one arrival per epilogue warp (of both CTAs)
     }
     fence_mbar_init();
   }
   if (warp == 1) {
-    tmem_alloc(&sl->tmem_base, 512);
-    tmem_relinquish();
+    if constexpr (PAIR) {
+      tmem_alloc_pair(&sl->tmem_base, 512);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(&sl->tmem_base, 512);
+      tmem_relinquish();
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if constexpr (PAIR) cluster_sync_all();                 // the peer's barriers exist before anything arrives on them
   tc_fence_after();
   const uint32_t tmem = sl->tmem_base;
 
@@ -125,7 +151,7 @@ indexed_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_const
       tma_prefetch_desc(&mapX);
       uint32_t it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      for (int tile = tile_lo; tile < tile_hi && ok; ++tile) {
         const int tm = tile / p.tiles_n, tn = tile - tm * p.tiles_n;
         const int nsub = min(SUBS, (p.N - tn * GN) / 64);
         for (int kb = 0; kb < KB; ++kb, ++it) {
@@ -137,25 +163,41 @@ indexed_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_const
           }
           uint8_t* a = stage_base + s * STAGE_BYTES;
           uint8_t* b = a + A_BYTES;
-          mbar_expect_tx(&sl->full[s], A_BYTES + nsub * SUB_BYTES);
-          tma_load_2d(a, &mapX, &sl->full[s], kb * GK, tm * GM);
-          for (int u = 0; u < nsub; ++u) {
-            const int sb = tn * SUBS + u;
-            tma_load_2d(b + u * SUB_BYTES, wm[tb.weight[sb]], &sl->full[s], kb * GK, tb.row0[sb]);
-            if (p.halves)   // the maps' boxes are 32 rows: the second run lands behind the first (4 swizzle atoms on)
-              tma_load_2d(b + u * SUB_BYTES + SUB_BYTES / 2, wm[tb.weightb[sb]], &sl->full[s], kb * GK, tb.row0b[sb]);
+          if constexpr (PAIR) {
+            // this CTA's 128 rows of x and its two of the tile's four weight blocks; every byte is counted on the
+            // even CTA's barrier, which its MMA warp waits on
+            const int mine = max(0, min(C::B_SUBS, nsub - rank * C::B_SUBS));
+            const uint32_t bar = cluster_addr_of(&sl->full[s], 0);
+            mbar_expect_tx_cluster(bar, A_BYTES + mine * SUB_BYTES);
+            tma_load_2d_pair(a, &mapX, bar, kb * GK, tm * C::ROWS + rank * GM);
+            for (int u = 0; u < mine; ++u) {
+              const int sb = tn * SUBS + rank * C::B_SUBS + u;
+              tma_load_2d_pair(b + u * SUB_BYTES, wm[tb.weight[sb]], bar, kb * GK, tb.row0[sb]);
+              if (p.halves)
+                tma_load_2d_pair(b + u * SUB_BYTES + SUB_BYTES / 2, wm[tb.weightb[sb]], bar, kb * GK, tb.row0b[sb]);
+            }
+          } else {
+            mbar_expect_tx(&sl->full[s], A_BYTES + nsub * SUB_BYTES);
+            tma_load_2d(a, &mapX, &sl->full[s], kb * GK, tm * GM);
+            for (int u = 0; u < nsub; ++u) {
+              const int sb = tn * SUBS + u;
+              tma_load_2d(b + u * SUB_BYTES, wm[tb.weight[sb]], &sl->full[s], kb * GK, tb.row0[sb]);
+              if (p.halves)   // the maps' boxes are 32 rows: the second run lands behind the first (4 swizzle atoms on)
+                tma_load_2d(b + u * SUB_BYTES + SUB_BYTES / 2, wm[tb.weightb[sb]], &sl->full[s], kb * GK, tb.row0b[sb]);
+            }
           }
         }
       }
     }
-  } else if (warp == 1) {
-    // the whole warp walks the schedule (uniform addresses); one elected lane issues
+  } else if (warp == 1 && rank == 0) {
+    // the whole warp walks the schedule (uniform addresses); one elected lane issues.  In a pair only the even
+    // CTA issues: its instructions read both CTAs' stages and write both CTAs' accumulators.
     const bool leader = elect_one();
-    const uint32_t idesc = umma_idesc_bf16(GM, GN, 0, 0);
+    const uint32_t idesc = umma_idesc_bf16(C::ROWS, GN, 0, 0);
     const uint32_t sbase = smem_u32(stage_base);
     uint32_t it = 0, lt = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++lt) {
+    for (int tile = tile_lo; tile < tile_hi && ok; ++tile, ++lt) {
       const int buf = lt & 1;
       if (!mbar_wait(&sl->acc_empty[buf], ((lt >> 1) & 1) ^ 1)) {
         dev_set_error(p.status, SAF_DEV_TIMEOUT_MMA, 11);
@@ -175,31 +217,39 @@ indexed_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_const
         const uint32_t b = a + A_BYTES;
         if (leader) {
 #pragma unroll
-          for (int k4 = 0; k4 < GK / 16; ++k4)
-            umma_ss(d, umma_smem_desc_sw128(a + k4 * 32, 16, 1024), umma_smem_desc_sw128(b + k4 * 32, 16, 1024), idesc,
-                    (kb | k4) != 0);
-          umma_commit(&sl->empty[s]);
+          for (int k4 = 0; k4 < GK / 16; ++k4) {
+            const uint64_t ad = umma_smem_desc_sw128(a + k4 * 32, 16, 1024), bd = umma_smem_desc_sw128(b + k4 * 32, 16, 1024);
+            if constexpr (PAIR) umma_ss_pair(d, ad, bd, idesc, (kb | k4) != 0);
+            else umma_ss(d, ad, bd, idesc, (kb | k4) != 0);
+          }
+          if constexpr (PAIR) umma_commit_pair(&sl->empty[s]);      // frees the stage in both CTAs
+          else umma_commit(&sl->empty[s]);
         }
         __syncwarp();
       }
-      if (ok && leader) umma_commit(&sl->acc_full[buf]);
+      if (ok && leader) {
+        if constexpr (PAIR) umma_commit_pair(&sl->acc_full[buf]);
+        else umma_commit(&sl->acc_full[buf]);
+      }
       __syncwarp();
     }
-  } else {
+  } else if (warp >= 2) {
     // epilogue warps 2..5 -> TMEM lane quadrant (warp % 4)
     const int quad = warp & 3;
     const int row = quad * 32 + lane;           // row inside the tile
     const int etid = tid - 64;                  // 0..127
     uint32_t lt = 0;
-    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++lt) {
+    int tm_held = -1;                           // row tile whose cos / sin values the registers hold
+    float4 cs4[8], sn4[8];
+    for (int tile = tile_lo; tile < tile_hi; ++tile, ++lt) {
       const int tm = tile / p.tiles_n, tn = tile - tm * p.tiles_n;
       const int nsub = min(SUBS, (p.N - tn * GN) / 64);
       const int buf = lt & 1;
-      const int m = tm * GM + row;
+      const int m = tm * C::ROWS + rank * GM + row;
       const int t = (p.T > 0) ? (m % p.T) : 0;
       // head_dim 64: this row's 32 cos and 32 sin values, shared by every rotated block of the tile
-      float4 cs4[8], sn4[8];
-      if (p.slab == 64 && p.cosT) {
+      if (p.slab == 64 && p.cosT && tm != tm_held) {
+        tm_held = tm;
         const float4* cr4 = reinterpret_cast<const float4*>(p.cosT + (int64_t)t * 64);
         const float4* sr4 = reinterpret_cast<const float4*>(p.sinT + (int64_t)t * 64);
 #pragma unroll
@@ -342,20 +392,28 @@ indexed_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_const
         fence_proxy_async_smem();
         named_bar_sync(1, 128);
         if (etid == 0) {
-          tma_store_2d(&mapO, out_stage + ob * (OUT_BYTES / 2), out_col, tm * GM);
+          tma_store_2d(&mapO, out_stage + ob * (OUT_BYTES / 2), out_col, tm * C::ROWS + rank * GM);
           tma_store_commit();
         }
       }
       // accumulator buffer can be overwritten by the MMA warp
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&sl->acc_empty[buf]);
+      if (lane == 0) {
+        if constexpr (PAIR) mbar_arrive_cluster(cluster_addr_of(&sl->acc_empty[buf], 0));   // the even CTA's MMA warp waits
+        else mbar_arrive(&sl->acc_empty[buf]);
+      }
     }
     if (etid == 0) tma_store_wait_all();
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem, 512);
+  if constexpr (PAIR) {
+    cluster_sync_all();               // nothing of the peer's is touched after this point
+    if (warp == 1) tmem_dealloc_pair(tmem, 512);
+  } else {
+    if (warp == 1) tmem_dealloc(tmem, 512);
+  }
 }
 
 bool aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
@@ -448,13 +506,59 @@ int launch_gemm_sm100(const SafIndexedLinearArgs& a, cudaStream_t st) {
   p.halves = halves ? 1 : 0;
 
   const int sm_count = device_sm_count();
-  const size_t smem = 1024 + STAGES * STAGE_BYTES + OUT_BYTES + sizeof(SmemLayout);
-  static PerDeviceOnce smem_once;
-  if ((rc = ensure_dyn_smem(indexed_gemm_kernel, (int)smem, smem_once))) return rc;
-  const int grid = std::min(sm_count, p.tiles_m * p.tiles_n);
-  indexed_gemm_kernel<<<grid, GEMM_THREADS, smem, st>>>(mx, mw[0], mw[1], mw[2], mw[3], mo, p, tb);
-  count_launch();
-  if ((rc = check_launch("indexed_gemm_kernel"))) return rc;
+  // CTA pairs on 256-row tiles when the product is large enough to fill the machine with them
+  const char* pair_env = getenv("SAF_B200_GEMM_PAIR");
+  const bool pair_off = !(pair_env && pair_env[0] == '1' && pair_env[1] == 0);   // opt-in until measured
+  if (!pair_off && a.M >= 2 * GM * 32 && N >= GN) {
+    constexpr size_t smem_p = 1024 + GCfg<true>::STAGES * GCfg<true>::STAGE_BYTES + OUT_BYTES + sizeof(SmemLayout);
+    static_assert(smem_p <= 227 * 1024, "pair kernel shared memory");
+    static PerDeviceOnce smem_once_p;
+    if ((rc = ensure_dyn_smem(indexed_gemm_kernel<true>, (int)smem_p, smem_once_p))) return rc;
+    p.tiles_m = (a.M + 2 * GM - 1) / (2 * GM);
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.blockDim = dim3(GEMM_THREADS);
+    cfg.dynamicSmemBytes = smem_p;
+    cfg.stream = st;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    // pairs that can be resident at once (an SM without a free neighbour in its GPC stays out)
+    static std::atomic<int> pairs_cache[SAF_MAX_DEVICES];
+    const int dev = current_device();
+    int pairs = (dev >= 0 && dev < SAF_MAX_DEVICES) ? pairs_cache[dev].load(std::memory_order_acquire) : 0;
+    if (pairs <= 0) {
+      cfg.gridDim = dim3(sm_count & ~1);
+      int n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, indexed_gemm_kernel<true>, &cfg) != cudaSuccess || n <= 0) {
+        cudaGetLastError();
+        n = sm_count / 2;
+      }
+      pairs = n;
+      if (dev >= 0 && dev < SAF_MAX_DEVICES) pairs_cache[dev].store(pairs, std::memory_order_release);
+    }
+    pairs = std::min(pairs, p.tiles_m * p.tiles_n);
+    cfg.gridDim = dim3(2 * pairs);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, indexed_gemm_kernel<true>, mx, mw[0], mw[1], mw[2], mw[3], mo, p, tb);
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      return fail(SAF_ERR_CUDA, "indexed_gemm_kernel<pair> launch: %s", cudaGetErrorString(e));
+    }
+    count_launch();
+    if ((rc = check_launch("indexed_gemm_kernel<pair>"))) return rc;
+  } else {
+    constexpr size_t smem = 1024 + GCfg<false>::STAGES * GCfg<false>::STAGE_BYTES + OUT_BYTES + sizeof(SmemLayout);
+    static PerDeviceOnce smem_once;
+    if ((rc = ensure_dyn_smem(indexed_gemm_kernel<false>, (int)smem, smem_once))) return rc;
+    const int grid = std::min(sm_count, p.tiles_m * p.tiles_n);
+    indexed_gemm_kernel<false><<<grid, GEMM_THREADS, smem, st>>>(mx, mw[0], mw[1], mw[2], mw[3], mo, p, tb);
+    count_launch();
+    if ((rc = check_launch("indexed_gemm_kernel"))) return rc;
+  }
   if (rope_after)
     return launch_rope_slabs(a.out, a.ldo, a.M, a.n_slabs, a.slab, a.T, a.slab_rope, a.rope_cos, a.rope_sin, a.dtype, 0, st);
   return SAF_OK;

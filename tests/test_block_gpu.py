@@ -27,7 +27,8 @@ def test_layer_norm(shape, dtype):
     assert (a <= 2e-5 * max(1.0, ref.abs().max().item())) if dtype == torch.float32 else (a <= 3e-2 and r <= 5e-3), f"{a} {r}"
 
 
-@pytest.mark.parametrize("shape", [(2, 300, 256, False), (1, 1000, 768, True), (2, 130, 1024, False)],
+@pytest.mark.parametrize("shape", [(2, 300, 256, False), (1, 1000, 768, True), (2, 130, 1024, False),
+                                   (3, 2900, 256, True)],     # 8700 rows: the CTA-pair tiles, ragged last pair
                          ids=lambda s: f"M{s[0] * s[1]}C{s[2]}")
 def test_mlp_with_fused_gelu_and_residual(shape):
     from saf_b200 import ops

@@ -117,8 +117,13 @@ def test_decomposed_logz_kernel():
                                  (1, 700, 512, 4, 128, [0, 2, 3], False),
                                  (3, 129, 256, 4, 64, [], False),
                                  (1, 1500, 1536, 16, 96, [0, 1, 2, 3, 5, 6, 7, 9, 10, 11, 13, 14], False),
-                                 (2, 333, 384, 4, 96, [1, 3], True)],
-                         ids=["c2shape", "bias", "hd128", "allfrozen", "hd96", "hd96bias"])
+                                 (2, 333, 384, 4, 96, [1, 3], True),
+                                 # 8192 rows and more: CTA-pair tiles (ragged last pair, bias, 128- and 96-wide heads)
+                                 (3, 3000, 768, 12, 64, [0, 1, 3, 4, 6, 7, 9, 10, 11], True),
+                                 (2, 4100, 512, 4, 128, [0, 2, 3], False),
+                                 (6, 1500, 768, 8, 96, [0, 1, 2, 3, 5, 6], True)],
+                         ids=["c2shape", "bias", "hd128", "allfrozen", "hd96", "hd96bias", "pair-bias", "pair-hd128",
+                              "pair-hd96"])
 def test_qkv_projection_with_rope_epilogue(cfg):
     """[Q(live) | K(live) | V(all)] in one tensor-core GEMM with the rotation in the epilogue equals
     projection followed by the reference's apply_rotary_pos_emb (nanogpt/model.py:63-68)."""

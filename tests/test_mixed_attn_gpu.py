@@ -243,6 +243,27 @@ def test_validate_messages():
         fused_mixed_attn(q, q, v, torch.zeros(3, 8, 8, device=dev), frozen.long(), hidx)
 
 
+@pytest.mark.parametrize("T", [1500, 4224])
+def test_gqa_all_heads_structured_take_the_tensor_core_scan(T):
+    """Every query head in state 3 with kvidx: the call is the scan alone (one chunk and several chunks per head),
+    each head reading the values of its KV head."""
+    from kernel import fused_mixed_attn
+    dev = "cuda"
+    B, H, HKV, hd = 2, 6, 2, 128
+    g = torch.Generator().manual_seed(T)
+    states = [3] * H
+    kv = torch.tensor([0, 0, 0, 1, 1, 1], dtype=torch.int32)
+    q = torch.zeros(B, 0, T, hd).bfloat16()
+    v = torch.randn(B, HKV, T, hd, generator=g).bfloat16()
+    sd_a, sd_r = O.sink_decay_params(H, seed=T)
+    y_ref = torch.stack([torch.stack([O.sink_decay_scan(v[b, kv[h]], sd_a[h].item(), sd_r[h].item())
+                                      for h in range(H)]) for b in range(B)])
+    y = fused_mixed_attn(q.to(dev), v.to(dev), v.to(dev), None, torch.tensor(states, dtype=torch.int32, device=dev),
+                         kvidx=kv.to(dev), sink_decay=(sd_a.float().to(dev), sd_r.float().to(dev)))
+    a, r = errs(y, y_ref)
+    assert a <= BF16_FWD_ABS and r <= BF16_FWD_REL, (a, r)
+
+
 def test_gqa_forward_and_backward_error():
     """kvidx variant (qwen/kernel/fused_attn.py:667-768): forward only."""
     from kernel import fused_mixed_attn
