@@ -121,7 +121,7 @@ indexed_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_const
 
   if (tid == 0) {
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(&sl->full[s], PAIR ? 2 : 1);            // pair: one producer per CTA, both on the even CTA's barrier
+      mbar_init(&sl->full[s], 1);
       mbar_init(&sl->empty[s], 1);
     }
     for (int b = 0; b < 2; ++b) {
@@ -164,11 +164,13 @@ indexed_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_const
           uint8_t* a = stage_base + s * STAGE_BYTES;
           uint8_t* b = a + A_BYTES;
           if constexpr (PAIR) {
-            // this CTA's 128 rows of x and its two of the tile's four weight blocks; every byte is counted on the
-            // even CTA's barrier, which its MMA warp waits on
+            // this CTA's 128 rows of x and its two of the tile's four weight blocks.  Every byte of both CTAs is
+            // counted on the even CTA's barrier, which its MMA warp waits on: the even CTA's producer announces the
+            // pair's bytes there (a local arrive), the odd CTA's producer only issues its loads -- they cannot land
+            // before the barrier's previous phase is over, because its own empty barrier opens after that.
             const int mine = max(0, min(C::B_SUBS, nsub - rank * C::B_SUBS));
             const uint32_t bar = cluster_addr_of(&sl->full[s], 0);
-            mbar_expect_tx_cluster(bar, A_BYTES + mine * SUB_BYTES);
+            if (rank == 0) mbar_expect_tx(&sl->full[s], 2 * A_BYTES + nsub * SUB_BYTES);
             tma_load_2d_pair(a, &mapX, bar, kb * GK, tm * C::ROWS + rank * GM);
             for (int u = 0; u < mine; ++u) {
               const int sb = tn * SUBS + rank * C::B_SUBS + u;
@@ -508,7 +510,7 @@ int launch_gemm_sm100(const SafIndexedLinearArgs& a, cudaStream_t st) {
   const int sm_count = device_sm_count();
   // CTA pairs on 256-row tiles when the product is large enough to fill the machine with them
   const char* pair_env = getenv("SAF_B200_GEMM_PAIR");
-  const bool pair_off = !(pair_env && pair_env[0] == '1' && pair_env[1] == 0);   // opt-in until measured
+  const bool pair_off = pair_env && pair_env[0] == '0' && pair_env[1] == 0;
   if (!pair_off && a.M >= 2 * GM * 32 && N >= GN) {
     constexpr size_t smem_p = 1024 + GCfg<true>::STAGES * GCfg<true>::STAGE_BYTES + OUT_BYTES + sizeof(SmemLayout);
     static_assert(smem_p <= 227 * 1024, "pair kernel shared memory");

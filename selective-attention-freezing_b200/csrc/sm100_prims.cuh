@@ -298,12 +298,11 @@ __device__ __forceinline__ uint32_t cluster_addr_of(const void* p, uint32_t rank
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_u32(p)), "r"(rank));
   return r;
 }
+// Arrive on a barrier of the pair (default semantics: release at CTA scope).  It hands over TMEM or shared-memory
+// ownership that tcgen05 fences or the async proxy order; it does not publish generic-proxy writes to the peer, so it
+// does not pay for a cluster-wide release (about 1500 cycles per arrive).
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx_cluster(uint32_t cluster_addr, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.release.cluster.shared::cluster.b64 _, [%0], %1;" ::"r"(cluster_addr), "r"(bytes)
-               : "memory");
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 // TMA tile load of a CTA pair: lands in this CTA's shared memory, completes on a barrier that may live in the peer
 __device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* m, uint32_t bar_cluster_addr, int c0, int c1) {
