@@ -26,6 +26,7 @@ namespace saf {
 
 struct DpParams {
   int B, H, T, n_pairs, groups, force_state, HKV;
+  int split_from;            // forward: row pairs mp >= split_from run as two CTAs, one per 128-row tile
   const int32_t* frozen;
   const int32_t* pidx;
   const int32_t* kvidx;
@@ -87,6 +88,16 @@ inline int dense_pv_prepare(const SafMixedAttnArgs& a, bool dense, bool decomp, 
   p->status = a.status;
   p->dense_ok = dense ? 1 : 0;
   p->dec_ok = decomp ? 1 : 0;
+  // A row pair m walks 4m + 4 key steps for two tiles: the CTAs of a long sequence differ in length by the factor
+  // n_pairs, and the longest alone takes 1.5x the average load of an SM when a few heads fill the machine.  The top
+  // eighth (quarter at head_dim 128) of the row pairs is therefore cut into its two tiles.  A one-tile CTA costs about
+  // 0.7 of a pair's step, not 0.5 (V is read by both), so cutting more loses more than the balance gains: measured
+  // 0.294 -> 0.267 ms at c2 (3 heads, T=16384), 0.135 -> 0.112 ms at the c3 shape.
+  // Stored patterns only: the generated (decomposed) form builds both tiles with fixed warp groups.
+  {
+    const int eighths = a.HD == 128 ? 6 : 7;
+    p->split_from = (decomp || p->n_pairs < 8) ? p->n_pairs : p->n_pairs * eighths / 8;
+  }
   if (decomp) {
     p->alpha = a.alpha.ptr; p->rho = a.rho.ptr; p->z = a.z.ptr;
     for (int i = 0; i < 2; ++i) {
@@ -114,7 +125,9 @@ inline bool dense_pv_decomp_eligible(const SafMixedAttnArgs& a) {
   if (!a.alpha.ptr || !a.rho.ptr || !a.z.ptr || a.SD < a.T) return false;
   return tma_ok(a.v) && tma_ok(a.out);
 }
-inline unsigned dense_pv_slots(const DpParams& p) { return (unsigned)(p.n_pairs * p.H * p.groups); }
+inline unsigned dense_pv_slots(const DpParams& p) {
+  return (unsigned)((p.n_pairs + (p.n_pairs - p.split_from)) * p.H * p.groups);
+}
 
 // backward of dense-stored heads, dV = tril(P)^T dO: same role with the pattern read as a transposed (MN-major)
 // A operand in 64-query steps.  Maps: pattern in 64 x 64 boxes, dO in 64-row boxes, dV in 128-row boxes.
@@ -173,6 +186,7 @@ inline int dense_dv_prepare(const SafMixedAttnBwdArgs& g, bool dense, bool decom
   memset(p, 0, sizeof(*p));
   p->B = a.B; p->H = a.H; p->T = a.T; p->force_state = a.force_state; p->HKV = 0;
   p->n_pairs = (a.T + 255) / 256;
+  p->split_from = p->n_pairs;      // the backward role keeps whole key-tile pairs
   p->groups = (a.B + 256 / a.HD - 1) / (256 / a.HD);
   p->frozen = a.frozen; p->pidx = a.pidx; p->kvidx = nullptr;
   p->status = a.status;
@@ -220,9 +234,18 @@ template <int HD>
 __device__ __forceinline__ void dense_pv_cta(const CUtensorMap& mapP, const CUtensorMap& mapV, const CUtensorMap& mapO,
                                              const DpParams& p, int slot, uint8_t* smem) {
   using C = DpCfg<HD>;
-  // CTA -> (head, batch group, row pair); heaviest row pairs first
+  // CTA -> (head, batch group, row pair [, tile]); heaviest first.  Row pairs from split_from up come as two slots,
+  // tile 1 (one key step more) before tile 0.
   const int per_mp = p.H * p.groups;
-  const int mp = p.n_pairs - 1 - slot / per_mp;
+  const int n_split = p.n_pairs - p.split_from;
+  int mp, only_t = -1;                                      // only_t: the one tile this CTA computes, -1 = both
+  if (slot < 2 * n_split * per_mp) {
+    const int q = slot / per_mp;
+    mp = p.n_pairs - 1 - (q >> 1);
+    only_t = 1 - (q & 1);
+  } else {
+    mp = p.split_from - 1 - (slot - 2 * n_split * per_mp) / per_mp;
+  }
   const int rem = slot % per_mp;
   const int h = rem / p.groups, grp = rem % p.groups;
   const int state = p.force_state >= 0 ? p.force_state : p.frozen[h];
@@ -233,12 +256,13 @@ __device__ __forceinline__ void dense_pv_cta(const CUtensorMap& mapP, const CUte
   const int b0 = grp * C::NB;
   const int nb = min(C::NB, p.B - b0);
   const int row0 = mp * 256;
-  const bool act1 = row0 + 128 < p.T;
+  const bool act1 = row0 + 128 < p.T && only_t != 0;
+  if (only_t == 1 && !act1) return;                        // the sequence ends inside tile 0
   const int n_half = (p.T + 63) / 64;
-  const int nk0 = min(4 * mp + 2, n_half);                 // 64-key steps of tile 0
+  const int nk0 = only_t == 1 ? 0 : min(4 * mp + 2, n_half);   // 64-key steps of tile 0
   const int nkh = act1 ? min(4 * mp + 4, n_half) : nk0;    // and of the CTA
   // steps whose pattern tile holds above-diagonal entries: the two steps that cover a tile's own 128 keys
-  auto diag_of = [&](int kh, int t) { return kh >= 4 * mp + 2 * t && kh < 4 * mp + 2 * t + 2; };
+  auto diag_of = [&](int kh, int t) { return (t == 0 ? nk0 > 0 : act1) && kh >= 4 * mp + 2 * t && kh < 4 * mp + 2 * t + 2; };
 
   DpBars* bars = reinterpret_cast<DpBars*>(smem + DP_NST * C::STAGE);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -455,6 +479,7 @@ __device__ __forceinline__ void dense_pv_cta(const CUtensorMap& mapP, const CUte
     int n_st = 0;
     for (int t = 0; t < 2; ++t) {
       if (t == 1 && !act1) break;
+      if (t == 0 && nk0 == 0) continue;                   // this CTA computes tile 1 only
       for (int bi = 0; bi < nb; ++bi, ++n_st) {
         uint8_t* stage = smem + (n_st & 1) * (128 * HD * 2);
         if (etid == 0) tma_store_wait_read1();
