@@ -14,7 +14,9 @@
 //   warp 1      MMA issuer: tcgen05.mma 128x256x16, bf16 -> fp32 in TMEM, 2 accumulator buffers (512 columns)
 //   warps 2..5  epilogue, 64 columns at a time: TMEM -> registers (bias, RoPE) -> bf16 -> swizzled smem
 //               -> TMA store (two staging blocks in flight).  The row's cos/sin values are fetched once
-//               per tile, before the accumulator is waited for, so their latency hides behind the MMAs.
+//               per row of tiles, before the accumulator is waited for, so their latency hides behind the MMAs.
+// Large products run the same kernel as CTA PAIRS (template parameter PAIR, a cluster of two): one 256x256 tile per
+// pair through tcgen05.mma.cta_group::2, each CTA loading its 128 rows of x and half of the weight tile (see GCfg).
 // All waits are bounded; a wait that runs out sets *status and the CTA drains.
 #include <algorithm>
 #include <atomic>

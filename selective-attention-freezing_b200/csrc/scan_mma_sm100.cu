@@ -7,13 +7,15 @@
 // block inherits enters as  s_i = s_loc_i + r^(i_loc+1) carry.  So the scan of a long sequence becomes a stream of
 // 128 x 128 x 64 tcgen05 products fed by a TMA ring, and the only sequential piece left is a 64-float carry
 // handed from one block's epilogue to the next.  The CUDA-core scan this replaces (csrc/scan_body.cuh) spends
-// about 800 instructions per thread per 256-row block and is bound by instruction issue at 0.19 of the HBM
-// copy rate; here a block costs 16 MMAs and ~250 epilogue instructions per row.
+// about 800 instructions per thread per 256-row block and is bound by instruction issue at 0.20 of the HBM
+// copy rate; here a block costs 16 MMAs and ~300 epilogue instructions per row (0.5 of the copy rate at B = 32).
 // The reference has no counterpart: it holds such a pattern as a dense T x T buffer and multiplies it
 // (kernel/fused_attn.py:125-143, kernel/frozen_attn.py:51-89).
 //
 // L is split into a bf16 head and a bf16 remainder (two MMAs accumulate into the same fp32 TMEM tile), so the
-// product is as exact as the fp32 register scan to ~2^-17; V is bf16 as stored.
+// product is as exact as the fp32 register scan to ~2^-17; V is bf16 as stored.  Both parts live in TMEM (128 columns,
+// written once per CTA), so the MMAs take their A operand from TMEM and shared memory holds nothing but V tiles and
+// output staging.
 //
 // Launch structure (forward, bf16, head_dim a multiple of 64):
 //   pass 1  sink_decay_state_kernel     every chunk: its end state from a zero carry -- a weighted column sum,
@@ -22,14 +24,15 @@
 //   pass 3  sink_decay_apply_mma_kernel every chunk: blocks of 128 rows through the tensor core  (V again, writes Y)
 // A chunk hands its 64 fp32 state words to the next pass in the first rows of its own output slice, which pass 3
 // overwrites only after it has read them (the same stash as the CUDA-core passes): no scratch memory.
-// One chunk per head (enough heads to fill the GPU): pass 3 alone with a zero carry.
+// One chunk per head (enough heads to fill the GPU): pass 3 alone with a zero carry, V read once.
 //
-//   pass 3 CTA, 320 threads:  warp 0 TMA producer (V tiles 128 rows x 64 columns, 5-stage ring = 80 KB in flight)
-//                             warp 1 MMA issuer (4 TMEM accumulators of 64 columns)
-//                             warps 2-5 / 6-9 epilogue of the even / odd blocks, thread = row: TMEM -> carry /
-//                             normaliser / sink term -> bf16 -> swizzled staging -> TMA store.  The thread of row 127
-//                             publishes the block's end state before anything else, so the serial chain from block
-//                             to block is 64 fused multiply-adds long and the two warpgroups overlap otherwise.
+//   pass 3 CTA, 320 threads:  warp 0 TMA producer (V tiles 128 rows x 64 columns, 11-stage ring = 176 KB in flight)
+//                             warp 1 MMA issuer (4 TMEM accumulators of 64 columns, A = the Toeplitz operand in TMEM)
+//                             warps 2-5 / 6-9 epilogue of the even / odd blocks, thread = row: TMEM -> + carry (in
+//                             place) -> normaliser / sink term -> bf16 -> swizzled staging -> TMA store.  The thread
+//                             of row 127 publishes the block's end state before anything else, so the serial chain
+//                             from block to block is 64 fused multiply-adds long and the two warpgroups overlap
+//                             otherwise.
 // Every wait is bounded.
 #include <algorithm>
 
@@ -55,7 +58,7 @@ struct MsBars {
   alignas(16) float av0[64];
 };
 constexpr int MS_SMEM = 1024 + (MS_STAGES + MS_OUT) * MS_TILE + 2048;
-static_assert(sizeof(MsBars) <= 2048 && MS_SMEM <= 227 * 1024, "shared memory budget");
+static_assert(sizeof(MsBars) <= 2048 && MS_SMEM <= 227 * 1024, "shared memory limit");
 
 #ifdef SAF_SCAN_TRACE
 __device__ long long g_strace[12][64];

@@ -245,3 +245,21 @@ def test_linear_rows_single_weight_gradients(bias, dtype):
     assert got[1].grad[unselected.to(dev)].abs().max().item() == 0.0
     if bias:
         assert got[2].grad[unselected.to(dev)].abs().max().item() == 0.0
+
+
+@pytest.mark.parametrize("blocks", [1, 3, 5, 7], ids=lambda k: f"{k}x64cols")
+def test_cta_pair_gemm_with_partial_column_tiles(blocks):
+    """8192 rows and more take the CTA-pair kernel (256 x 256 tiles, each CTA loads half of the weight tile): output
+    widths of 64, 192, 320 and 448 columns leave the last column tile with 1 or 3 of its 4 blocks, so one CTA of the
+    pair loads fewer weight blocks than the other (or none); C = 200 ends inside a K step; bias and a ragged last pair."""
+    from kernel import linear_rows
+    M, C = 8192 + 70, 200
+    g = torch.Generator().manual_seed(blocks)
+    x = torch.randn(M, C, generator=g).bfloat16()
+    w = (torch.randn(1024, C, generator=g) * 0.05).bfloat16()
+    b = (torch.randn(1024, generator=g) * 0.1).bfloat16()
+    rows = torch.arange(128, 128 + 64 * blocks)
+    ref = O.linear_rows(x.float(), w.float(), b.float(), rows)
+    y = linear_rows(x.cuda(), w.cuda(), b.cuda(), rows.cuda())
+    a, r = errs(y, ref)
+    assert r <= 5e-3 and a <= 2e-2 * max(1.0, ref.abs().max().item()), f"{a} {r}"
