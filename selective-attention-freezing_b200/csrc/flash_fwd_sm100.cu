@@ -33,6 +33,7 @@
 #include "saf_internal.h"
 #include "dense_pv_body.cuh"
 #include "scan_body.cuh"
+#include "scan_mma_body.cuh"
 #include "sm100_prims.cuh"
 #include <stdlib.h>
 #include <string.h>
@@ -89,6 +90,11 @@ struct Cfg {
   static constexpr int NBUF = (HD == 64) ? 3 : 2;      // score buffers
   static constexpr int O_COL = NBUF * 128;
 };
+
+// ring depth of the tensor-core scan when it runs in a scan slot of these launches: what their shared memory holds
+constexpr int SCAN_ROLE_STAGES = 8;
+static_assert(ms_smem_bytes(SCAN_ROLE_STAGES) <= Cfg<64>::SMEM_BYTES && ms_smem_bytes(SCAN_ROLE_STAGES) <= Cfg<64>::SMEM_PERSIST,
+              "the scan role must fit the launches' dynamic shared memory");
 
 struct FlashParams {
   int B, H, T, HKV, force_state, n_pairs;
@@ -180,8 +186,24 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
   if ((int)blockIdx.x < bh_count) {
     const int b = blockIdx.x / p.H, h = blockIdx.x % p.H;
     const int state = p.force_state >= 0 ? p.force_state : p.frozen[h];
-    if (state == SAF_SINK_DECAY && p.has_scan && threadIdx.x < SCAN_NT)
-      for (int col0 = 0; col0 < HD; col0 += SCAN_COLS) sink_decay_scan_cta<__nv_bfloat16, false>(p.scan, b, h, col0);
+    if (state == SAF_SINK_DECAY && p.has_scan) {
+      if constexpr (HD == 64) {
+        // one 64-column slice: the whole sequence as 128-row Toeplitz products on the tensor core (about a third of
+        // the time of the register scan, so the SM joins the live tiles that much earlier)
+        if (p.T >= 4 * MB) {
+          extern __shared__ uint8_t scan_smem_raw[];
+          MsParams mp;
+          mp.a = p.scan;
+          mp.chunk = (p.T + MB - 1) / MB * MB;
+          mp.use_stash = 0;
+          mp.status = p.status;
+          sink_decay_apply_mma_cta<SCAN_ROLE_STAGES>(mapV, mapO, mp, b, h, 0, 0, scan_smem_raw);
+          return;
+        }
+      }
+      if (threadIdx.x < SCAN_NT)
+        for (int col0 = 0; col0 < HD; col0 += SCAN_COLS) sink_decay_scan_cta<__nv_bfloat16, false>(p.scan, b, h, col0);
+    }
     return;
   }
   // ---- dense-stored frozen heads: TMA-staged lower-triangular GEMM, pattern tiles shared by batch rows ---
@@ -716,8 +738,24 @@ flash_fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __gr
   if ((int)blockIdx.x < bh_count) {          // scan slots, as in flash_fwd_kernel
     const int b = blockIdx.x / p.H, h = blockIdx.x % p.H;
     const int state = p.force_state >= 0 ? p.force_state : p.frozen[h];
-    if (state == SAF_SINK_DECAY && p.has_scan && threadIdx.x < SCAN_NT)
-      for (int col0 = 0; col0 < HD; col0 += SCAN_COLS) sink_decay_scan_cta<__nv_bfloat16, false>(p.scan, b, h, col0);
+    if (state == SAF_SINK_DECAY && p.has_scan) {
+      if constexpr (HD == 64) {
+        // one 64-column slice: the whole sequence as 128-row Toeplitz products on the tensor core (about a third of
+        // the time of the register scan, so the SM joins the live tiles that much earlier)
+        if (p.T >= 4 * MB) {
+          extern __shared__ uint8_t scan_smem_raw[];
+          MsParams mp;
+          mp.a = p.scan;
+          mp.chunk = (p.T + MB - 1) / MB * MB;
+          mp.use_stash = 0;
+          mp.status = p.status;
+          sink_decay_apply_mma_cta<SCAN_ROLE_STAGES>(mapV, mapO, mp, b, h, 0, 0, scan_smem_raw);
+          return;
+        }
+      }
+      if (threadIdx.x < SCAN_NT)
+        for (int col0 = 0; col0 < HD; col0 += SCAN_COLS) sink_decay_scan_cta<__nv_bfloat16, false>(p.scan, b, h, col0);
+    }
     return;
   }
   if ((int)blockIdx.x < bh_count + p.dense_slots) {   // dense-pattern role
