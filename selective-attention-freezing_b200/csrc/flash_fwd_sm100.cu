@@ -93,7 +93,8 @@ struct Cfg {
 
 // ring depth of the tensor-core scan when it runs in a scan slot of these launches: what their shared memory holds
 constexpr int SCAN_ROLE_STAGES = 8;
-static_assert(ms_smem_bytes(SCAN_ROLE_STAGES) <= Cfg<64>::SMEM_BYTES && ms_smem_bytes(SCAN_ROLE_STAGES) <= Cfg<64>::SMEM_PERSIST,
+static_assert(ms_smem_bytes(SCAN_ROLE_STAGES) <= Cfg<64>::SMEM_BYTES && ms_smem_bytes(SCAN_ROLE_STAGES) <= Cfg<64>::SMEM_PERSIST &&
+                  ms_smem_bytes(SCAN_ROLE_STAGES) <= Cfg<128>::SMEM_BYTES && ms_smem_bytes(SCAN_ROLE_STAGES) <= Cfg<128>::SMEM_PERSIST,
               "the scan role must fit the launches' dynamic shared memory");
 
 struct FlashParams {
@@ -187,17 +188,17 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
     const int b = blockIdx.x / p.H, h = blockIdx.x % p.H;
     const int state = p.force_state >= 0 ? p.force_state : p.frozen[h];
     if (state == SAF_SINK_DECAY && p.has_scan) {
-      if constexpr (HD == 64) {
-        // one 64-column slice: the whole sequence as 128-row Toeplitz products on the tensor core (about a third of
-        // the time of the register scan, so the SM joins the live tiles that much earlier)
-        if (p.T >= 4 * MB) {
+      {
+        // the whole sequence as 128-row Toeplitz products on the tensor core, one 64-column slice after the other
+        // (about a third of the time of the register scan, so the SM joins the live tiles that much earlier)
+        if (p.T >= 4 * MB && p.scan.HD == HD) {
           extern __shared__ uint8_t scan_smem_raw[];
           MsParams mp;
           mp.a = p.scan;
           mp.chunk = (p.T + MB - 1) / MB * MB;
           mp.use_stash = 0;
           mp.status = p.status;
-          sink_decay_apply_mma_cta<SCAN_ROLE_STAGES>(mapV, mapO, mp, b, h, 0, 0, scan_smem_raw);
+          sink_decay_apply_mma_cta<SCAN_ROLE_STAGES>(mapV, mapO, mp, b, h, 0, 0, HD / 64, scan_smem_raw);
           return;
         }
       }
@@ -739,17 +740,17 @@ flash_fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __gr
     const int b = blockIdx.x / p.H, h = blockIdx.x % p.H;
     const int state = p.force_state >= 0 ? p.force_state : p.frozen[h];
     if (state == SAF_SINK_DECAY && p.has_scan) {
-      if constexpr (HD == 64) {
-        // one 64-column slice: the whole sequence as 128-row Toeplitz products on the tensor core (about a third of
-        // the time of the register scan, so the SM joins the live tiles that much earlier)
-        if (p.T >= 4 * MB) {
+      {
+        // the whole sequence as 128-row Toeplitz products on the tensor core, one 64-column slice after the other
+        // (about a third of the time of the register scan, so the SM joins the live tiles that much earlier)
+        if (p.T >= 4 * MB && p.scan.HD == HD) {
           extern __shared__ uint8_t scan_smem_raw[];
           MsParams mp;
           mp.a = p.scan;
           mp.chunk = (p.T + MB - 1) / MB * MB;
           mp.use_stash = 0;
           mp.status = p.status;
-          sink_decay_apply_mma_cta<SCAN_ROLE_STAGES>(mapV, mapO, mp, b, h, 0, 0, scan_smem_raw);
+          sink_decay_apply_mma_cta<SCAN_ROLE_STAGES>(mapV, mapO, mp, b, h, 0, 0, HD / 64, scan_smem_raw);
           return;
         }
       }

@@ -20,7 +20,7 @@ struct MsBars {
   uint64_t full[MS_MAX_STAGES], empty[MS_MAX_STAGES], acc_full[MS_ACC], acc_empty[MS_ACC], carry_ready[4], l_ready;
   uint32_t tmem_base;
   alignas(16) float carry[4][64];      // carry[n & 3]: the state block n inherits
-  alignas(16) float av0[64];
+  alignas(16) float av0[2][64];        // sink term a * v_0 of each column slice
 };
 // dynamic shared memory of a CTA with a ring of `stages` V tiles
 constexpr int ms_smem_bytes(int stages) { return 1024 + (stages + MS_OUT) * MS_TILE + 2048; }
@@ -40,19 +40,21 @@ struct MsParams {
   int* status;
 };
 
-// Body of one CTA: rows [chunk_idx * p.chunk, ...) of head (b, h), columns [64 slice, 64 slice + 64), through the tensor
-// core.  Every thread of the CTA must call it (it holds CTA-wide barriers); the first ten warps work, further warps only
+// Body of one CTA: rows [chunk_idx * p.chunk, ...) of head (b, h), columns [64 slice, 64 (slice + n_slices)), through
+// the tensor core.  With n_slices = 2 (zero carry only) the CTA walks the rows once per 64-column slice, back to back
+// through the same rings: the running block index goes on, the carry restarts at zero at the slice boundary.  Every thread of the CTA must call it (it holds CTA-wide barriers); the first ten warps work, further warps only
 // take part in those barriers.  STAGES V tiles are in flight; `smem_raw` is the CTA's dynamic shared memory, at least
 // ms_smem_bytes(STAGES) bytes.
 template <int STAGES>
 __device__ __forceinline__ void sink_decay_apply_mma_cta(const CUtensorMap& mapV, const CUtensorMap& mapY, const MsParams& p,
-                                                         int b, int h, int chunk_idx, int slice, uint8_t* smem_raw) {
+                                                         int b, int h, int chunk_idx, int slice, int n_slices, uint8_t* smem_raw) {
   static_assert(STAGES >= 2 && STAGES <= MS_MAX_STAGES, "ring depth");
   constexpr int MS_STAGES = STAGES;
   const ScanArgs& a = p.a;
   const int col0 = slice * SCAN_COLS;
   const int p_lo = chunk_idx * p.chunk, p_hi = min(a.T, p_lo + p.chunk);
-  const int n_blocks = (p_hi - p_lo + MB - 1) / MB;
+  const int blocks_per_slice = (p_hi - p_lo + MB - 1) / MB;
+  const int n_blocks = blocks_per_slice * n_slices;                 // running block n = (slice n / bps, block n % bps)
   const int hin = a.HKV > 0 ? (a.kvidx ? a.kvidx[h] : 0) : h;
 #ifdef SAF_SCAN_TRACE
   const bool trace_on = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
@@ -97,7 +99,8 @@ __device__ __forceinline__ void sink_decay_apply_mma_cta(const CUtensorMap& mapV
         }
         STRACE(0, n);
         mbar_expect_tx(&bars->full[s], MS_TILE);
-        tma_load_4d(sV + s * MS_TILE, &mapV, &bars->full[s], col0, p_lo + n * MB, hin, b);
+        tma_load_4d(sV + s * MS_TILE, &mapV, &bars->full[s], col0 + (n / blocks_per_slice) * SCAN_COLS,
+                    p_lo + (n % blocks_per_slice) * MB, hin, b);
       }
     }
   } else if (warp == 1) {
@@ -146,10 +149,12 @@ __device__ __forceinline__ void sink_decay_apply_mma_cta(const CUtensorMap& mapV
     // incoming carry (read before any output row of this chunk is stored) and v_0 for the sink term: the loads are in
     // flight while the Toeplitz operand is built
     float carry_in = 0.f, v_first = 0.f;
-    if (wg == 0 && et < 64) {
+    if (et < 64 * (wg == 0 ? 1 : n_slices - 1)) {          // warpgroup 0: slice 0 (and the stash); warpgroup 1: slice 1
+      const int sl = wg;
       const __nv_bfloat16* ob0 = reinterpret_cast<const __nv_bfloat16*>(a.out) + (int64_t)b * a.so[0] + (int64_t)h * a.so[1] + (int64_t)col0;
-      if (p.use_stash) carry_in = *scan_stash<__nv_bfloat16>(const_cast<__nv_bfloat16*>(ob0), a.so[2], p_lo, et);
-      const __nv_bfloat16* v0 = reinterpret_cast<const __nv_bfloat16*>(a.in) + (int64_t)b * a.si[0] + (int64_t)hin * a.si[1] + (int64_t)(col0 + et);
+      if (p.use_stash && wg == 0) carry_in = *scan_stash<__nv_bfloat16>(const_cast<__nv_bfloat16*>(ob0), a.so[2], p_lo, et);
+      const __nv_bfloat16* v0 = reinterpret_cast<const __nv_bfloat16*>(a.in) + (int64_t)b * a.si[0] + (int64_t)hin * a.si[1] +
+                                (int64_t)(col0 + sl * SCAN_COLS + et);
       v_first = __bfloat162float(*v0);
     }
     // Toeplitz operand in TMEM, row `lrow`, column k = the bf16 pair (L[2k], L[2k+1]): its bf16 head from warpgroup 0
@@ -178,9 +183,9 @@ __device__ __forceinline__ void sink_decay_apply_mma_cta(const CUtensorMap& mapV
       tmem_st_wait();
       tc_fence_before();
     }
-    if (wg == 0 && et < 64) {
-      bars->carry[0][et] = carry_in;
-      bars->av0[et] = alpha * v_first;
+    if (et < 64 * (wg == 0 ? 1 : n_slices - 1)) {
+      if (wg == 0) bars->carry[0][et] = carry_in;
+      bars->av0[wg][et] = alpha * v_first;
     }
     mbar_arrive(&bars->l_ready);
     named_bar_sync(3, 256);                                 // carry[0] and av0 are in place for both warpgroups
@@ -188,11 +193,12 @@ __device__ __forceinline__ void sink_decay_apply_mma_cta(const CUtensorMap& mapV
     float pw = r;                                           // r^(lrow + 1)
     for (int i = 0; i < lrow; ++i) pw *= r;
     const uint32_t tsrc = tlane;
-    const float4* a4 = reinterpret_cast<const float4*>(bars->av0);
     for (int n = wg; n < n_blocks; n += 2) {
       const int buf = n % MS_ACC, slot = n & 3;
+      const int sl = n / blocks_per_slice, blk = n - sl * blocks_per_slice;
+      const float4* a4 = reinterpret_cast<const float4*>(bars->av0[sl]);
       // the row's weight (1 - a) / Z_i waits for nothing
-      const float w = (1.f - alpha) * inv_z(r, log_r, p_lo + n * MB + lrow + 1);
+      const float w = (1.f - alpha) * inv_z(r, log_r, p_lo + blk * MB + lrow + 1);
       bool ok = mbar_wait(&bars->acc_full[buf], (n / MS_ACC) & 1);
       uint32_t s0[32], s1[32];
       if (et == 0) STRACE(4, n);
@@ -228,10 +234,13 @@ __device__ __forceinline__ void sink_decay_apply_mma_cta(const CUtensorMap& mapV
         // the state at the end of the block goes out first: the other warpgroup's next block waits for it alone
         if (lrow == MB - 1) {
           uint4* n4 = reinterpret_cast<uint4*>(bars->carry[(n + 1) & 3]);
+          const uint32_t keep = blk + 1 == blocks_per_slice ? 0u : 0xffffffffu;   // a new column slice starts from zero
 #pragma unroll
-          for (int q = 0; q < 8; ++q) n4[q] = make_uint4(s0[q * 4], s0[q * 4 + 1], s0[q * 4 + 2], s0[q * 4 + 3]);
+          for (int q = 0; q < 8; ++q)
+            n4[q] = make_uint4(s0[q * 4] & keep, s0[q * 4 + 1] & keep, s0[q * 4 + 2] & keep, s0[q * 4 + 3] & keep);
 #pragma unroll
-          for (int q = 0; q < 8; ++q) n4[8 + q] = make_uint4(s1[q * 4], s1[q * 4 + 1], s1[q * 4 + 2], s1[q * 4 + 3]);
+          for (int q = 0; q < 8; ++q)
+            n4[8 + q] = make_uint4(s1[q * 4] & keep, s1[q * 4 + 1] & keep, s1[q * 4 + 2] & keep, s1[q * 4 + 3] & keep);
           mbar_arrive(&bars->carry_ready[(n + 1) & 3]);
           STRACE(7, n);
         }
@@ -268,7 +277,7 @@ __device__ __forceinline__ void sink_decay_apply_mma_cta(const CUtensorMap& mapV
       if (et == 0) STRACE(9, n);
       named_bar_sync(1 + wg, 128);
       if (et == 0) {
-        tma_store_4d(&mapY, sY + wg * MS_TILE, col0, p_lo + n * MB, h, b);
+        tma_store_4d(&mapY, sY + wg * MS_TILE, col0 + sl * SCAN_COLS, p_lo + blk * MB, h, b);
         tma_store_commit();
         STRACE(10, n);
       }

@@ -105,7 +105,7 @@ sink_decay_apply_mma_kernel(const __grid_constant__ CUtensorMap mapV, const __gr
   const int state = a.force_state >= 0 ? a.force_state : a.frozen[h];
   if (state != SAF_SINK_DECAY) return;
   extern __shared__ uint8_t ms_smem_raw[];
-  sink_decay_apply_mma_cta<MS_STAGES>(mapV, mapY, p, b, h, blockIdx.y, blockIdx.z, ms_smem_raw);
+  sink_decay_apply_mma_cta<MS_STAGES>(mapV, mapY, p, b, h, blockIdx.y, blockIdx.z, 1, ms_smem_raw);
 }
 
 }  // namespace
