@@ -170,12 +170,14 @@ indexed_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_const
             // counted on the even CTA's barrier, which its MMA warp waits on: the even CTA's producer announces the
             // pair's bytes there (a local arrive), the odd CTA's producer only issues its loads -- they cannot land
             // before the barrier's previous phase is over, because its own empty barrier opens after that.
-            const int mine = max(0, min(C::B_SUBS, nsub - rank * C::B_SUBS));
+            // (a last column tile of two blocks is computed as a 256 x 128 product: one block per CTA)
+            const int per = nsub == 2 ? 1 : C::B_SUBS;
+            const int mine = max(0, min(per, nsub - rank * per));
             const uint32_t bar = cluster_addr_of(&sl->full[s], 0);
             if (rank == 0) mbar_expect_tx(&sl->full[s], 2 * A_BYTES + nsub * SUB_BYTES);
             tma_load_2d_pair(a, &mapX, bar, kb * GK, tm * C::ROWS + rank * GM);
             for (int u = 0; u < mine; ++u) {
-              const int sb = tn * SUBS + rank * C::B_SUBS + u;
+              const int sb = tn * SUBS + rank * per + u;
               tma_load_2d_pair(b + u * SUB_BYTES, wm[tb.weight[sb]], bar, kb * GK, tb.row0[sb]);
               if (p.halves)
                 tma_load_2d_pair(b + u * SUB_BYTES + SUB_BYTES / 2, wm[tb.weightb[sb]], bar, kb * GK, tb.row0b[sb]);
@@ -197,7 +199,8 @@ indexed_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_const
     // the whole warp walks the schedule (uniform addresses); one elected lane issues.  In a pair only the even
     // CTA issues: its instructions read both CTAs' stages and write both CTAs' accumulators.
     const bool leader = elect_one();
-    const uint32_t idesc = umma_idesc_bf16(C::ROWS, GN, 0, 0);
+    const uint32_t idesc_full = umma_idesc_bf16(C::ROWS, GN, 0, 0);
+    const uint32_t idesc_half = umma_idesc_bf16(C::ROWS, GN / 2, 0, 0);   // pair: a last column tile of two blocks
     const uint32_t sbase = smem_u32(stage_base);
     uint32_t it = 0, lt = 0;
     bool ok = true;
@@ -209,6 +212,8 @@ indexed_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_const
       }
       tc_fence_after();
       const uint32_t d = tmem + buf * GN;
+      const int tn_ = tile % p.tiles_n;
+      const uint32_t idesc = (PAIR && (p.N - tn_ * GN) / 64 == 2) ? idesc_half : idesc_full;
       for (int kb = 0; kb < KB; ++kb, ++it) {
         const int s = it % STAGES;
         if (!mbar_wait(&sl->full[s], (it / STAGES) & 1)) {
