@@ -167,6 +167,7 @@ indexed_gemm_bwd_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_c
     const int row = quad * 32 + lane;
     const int etid = tid - 64;
     uint32_t lt = 0;
+    uint32_t n_out = 0;                         // output blocks stored so far (staging block = parity)
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++lt) {
       const int tm = tile / p.tiles_n, tn = tile - tm * p.tiles_n;
       const int nsub = min(4, (p.J - tn * BN + 63) / 64);
@@ -179,6 +180,8 @@ indexed_gemm_bwd_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_c
       tc_fence_after();
       const uint32_t tsrc = tmem + ((uint32_t)(quad * 32) << 16) + buf * BN;
       for (int u = 0; u < nsub; ++u) {
+        // the two staging blocks take turns over all stores of the CTA (nsub may be odd)
+        const int ob = (n_out++) & 1;
         if (etid == 0) tma_store_wait_read1();
         named_bar_sync(1, 128);
         uint32_t r0[32], r1[32];
@@ -197,7 +200,7 @@ indexed_gemm_bwd_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_c
           for (int j = 0; j < 64; ++j)
             if (tn * BN + u * 64 + j < p.J) v[j] += __bfloat162float(bp[j]);
         }
-        uint8_t* dst = out_stage + (u & 1) * (BOUT_BYTES / 2) + row * 128;
+        uint8_t* dst = out_stage + ob * (BOUT_BYTES / 2) + row * 128;
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
           uint4 q;
@@ -210,7 +213,7 @@ indexed_gemm_bwd_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_c
         fence_proxy_async_smem();
         named_bar_sync(1, 128);
         if (etid == 0) {
-          const uint8_t* src = out_stage + (u & 1) * (BOUT_BYTES / 2);
+          const uint8_t* src = out_stage + ob * (BOUT_BYTES / 2);
           if (MODE == MODE_DX) {
             tma_store_2d(&mapO, src, tn * BN + u * 64, tm * BM);
           } else {

@@ -248,6 +248,7 @@ indexed_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_const
     const int row = quad * 32 + lane;           // row inside the tile
     const int etid = tid - 64;                  // 0..127
     uint32_t lt = 0;
+    uint32_t n_out = 0;                         // output blocks stored so far (staging block = parity)
     int tm_held = -1;                           // row tile whose cos / sin values the registers hold
     float4 cs4[8], sn4[8];
     for (int tile = tile_lo; tile < tile_hi; ++tile, ++lt) {
@@ -277,8 +278,10 @@ indexed_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_const
       for (int u = 0; u < nsub; ++u) {
         // gated MLP: blocks come in (gate, up) pairs; the even block of a pair produces the 64 output columns
         if (swiglu && (u & 1)) continue;
-        const int ob = swiglu ? (u >> 1) & 1 : (u & 1);     // staging block of this output block
-        // the staging block is free once the store issued two output blocks ago has read it
+        // the two staging blocks take turns over ALL stores of the CTA (a column tile may hold an odd number of
+        // output blocks: alternating by u alone would reuse the block whose store was issued last);
+        // the one whose turn it is is free once the store issued two output blocks ago has read it
+        const int ob = (n_out++) & 1;
         if (etid == 0) tma_store_wait_read1();
         named_bar_sync(1, 128);
         const int sb = tn * SUBS + u;

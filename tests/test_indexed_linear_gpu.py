@@ -263,3 +263,35 @@ def test_cta_pair_gemm_with_partial_column_tiles(blocks):
     y = linear_rows(x.cuda(), w.cuda(), b.cuda(), rows.cuda())
     a, r = errs(y, ref)
     assert r <= 5e-3 and a <= 2e-2 * max(1.0, ref.abs().max().item()), f"{a} {r}"
+
+
+@pytest.mark.parametrize("cfg", [(16384, 120, 21), (20972, 184, 21), (3000, 120, 21)], ids=lambda c: f"M{c[0]}C{c[1]}b{c[2]}")
+def test_column_tiles_with_an_odd_number_of_blocks(cfg):
+    """A last column tile of 1 or 3 output blocks between full tiles: the epilogue's two staging buffers must keep
+    taking turns across tiles (they once alternated by the block's index inside its tile, and the block stored last
+    was overwritten while the TMA store was still reading it: whole 128-row tiles of the last block came out wrong,
+    a few per call).  Forward (both kernel forms), dx and dW (C = 320 gives their output an odd block count too)."""
+    from kernel import linear_rows
+    M, C, nb = cfg
+    g = torch.Generator().manual_seed(8)
+    rows = torch.arange(64 * nb) + 64
+    x = torch.randn(M, C, generator=g).bfloat16().cuda()
+    w = (torch.randn(64 * (nb + 4), C, generator=g) * 0.05).bfloat16().cuda()
+    ref = torch.nn.functional.linear(x.float(), w.float()[rows.cuda()])
+    for _ in range(3):                       # the overwrite was a race: give it more than one chance
+        y = linear_rows(x, w, None, rows.cuda()).float()
+        rel = ((y - ref).norm() / ref.norm()).item()
+        assert rel <= 5e-3 and (y - ref).abs().max().item() <= 0.1, rel
+    # backward products with 5 output blocks per row tile (C = 320)
+    C2 = 320
+    x2 = torch.randn(4096, C2, generator=g).bfloat16()
+    w2 = (torch.randn(64 * (nb + 4), C2, generator=g) * 0.05).bfloat16()
+    xr, wr = x2.float().requires_grad_(True), w2.float().requires_grad_(True)
+    yr = torch.nn.functional.linear(xr, wr[rows])
+    wgt = torch.randn(yr.shape, generator=g).bfloat16().float()
+    (yr * wgt).sum().backward()
+    xd, wd = x2.cuda().requires_grad_(True), w2.cuda().requires_grad_(True)
+    (linear_rows(xd, wd, None, rows.cuda()).float() * wgt.cuda()).sum().backward()
+    for name, d, r_ in (("dx", xd.grad, xr.grad), ("dw", wd.grad, wr.grad)):
+        a, r = errs(d, r_)
+        assert r <= 1.5e-2, f"{name} rel-l2 {r}"
