@@ -639,7 +639,7 @@ def main():
         "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": x_host.numel() * x_host.element_size(),
                 "d2h_bytes_per_step": last_host.numel() * last_host.element_size()},
         "gpu_launches": launches,
-        "roofline": {"bound": "tensor", "kernel": "flash_fwd_kernel (live heads on tcgen05 + co-scheduled frozen-head scan, one launch per layer)",
+        "roofline": {"bound": "tensor", "kernel": "flash_fwd_persistent_kernel (live heads on tcgen05 from a tile queue + co-scheduled frozen-head scan, one launch per layer)",
                      "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s", "frac": achieved / peak_tf,
                      "peak_kind": f"{peak_kind} sustained dense bf16 (kernel timed inside a long step)",
                      "frac_of_burst_peak": achieved / peak_burst_tf, "traffic": attention_traffic_bytes(args.workload),
