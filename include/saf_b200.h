@@ -307,7 +307,19 @@ int saf_pattern_param_grad(const SafPatternGradArgs* args, void* stream);
  * lse is the (B, U, T) fp32 row log-sum-exp of the same q, k in the log2 domain, as
  * saf_mixed_attn_fwd writes it.  bf16 q, k with head_dim 64 / 128 (tensor-core kernel);
  * anything else returns SAF_ERR_UNSUPPORTED.
+ *
+ * quantity == SAF_STATS_LOGITS measures the raw scores instead, lg = q k^T * sm_scale
+ * over the whole square (nothing masked), as the priors that sample logits want them
+ * (`_last_logits`, nanogpt/model.py:828-831; dynamic_freeze.py:721-737):
+ *   mean        (U, T, T) fp32, Chan-merged batch mean as above (lg.mean(0))
+ *   cell_m2     optional (U, T, T) fp32: _centered_batch_moments (:62-81) +
+ *               _merge_moments (:84-93) per cell,
+ *               m2 += sum_b (lg_b - batch_mean)^2 + (batch_mean - mean)^2 * count_prev * B / (count_prev + B)
+ * lse, head_m2 and neg_entropy are not used then and may be null.  A caller built against
+ * the struct without the last two fields (struct_size up to `status`) gets probabilities.
  * ------------------------------------------------------------------------- */
+#define SAF_STATS_PROBS 0
+#define SAF_STATS_LOGITS 1
 typedef struct SafAttnStatsArgs {
   int32_t struct_size; /* sizeof(SafAttnStatsArgs), checked */
   int32_t dtype;       /* SafDType of q, k */
@@ -320,6 +332,8 @@ typedef struct SafAttnStatsArgs {
   double* head_m2;
   double* neg_entropy;
   int32_t* status;     /* optional device int32, as in SafMixedAttnArgs */
+  int32_t quantity;    /* SAF_STATS_PROBS or SAF_STATS_LOGITS */
+  float* cell_m2;      /* SAF_STATS_LOGITS: optional (U, T, T) fp32 centred squares per cell, 16-byte aligned */
 } SafAttnStatsArgs;
 
 int saf_attention_moments(const SafAttnStatsArgs* args, void* stream);

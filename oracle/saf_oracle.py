@@ -430,6 +430,26 @@ def merge_reduced_moments(count, mean, head_m2, bn, bm, bm2):
     return total, mean + delta * (bn / total), head_m2 + bm2 + delta.square().sum(dim=(-1, -2)) * (count * bn / total)
 
 
+def raw_logits(q, k, sm_scale=None):
+    """What the eager capture retains as `_last_logits` (nanogpt/model.py:828-831): q k^T / sqrt(hd), nothing masked."""
+    return torch.matmul(q, k.transpose(-1, -2)) * (sm_scale if sm_scale is not None else 1.0 / math.sqrt(q.shape[-1]))
+
+
+def centered_batch_moments(values):
+    """_centered_batch_moments (nanogpt/dynamic_freeze.py:62-81): count, mean and centred squares over samples, per cell."""
+    bm = values.mean(0)
+    return int(values.shape[0]), bm.double(), (values - bm).square().sum(0).double()
+
+
+def merge_moments(count, mean, m2, bn, bm, bm2):
+    """_merge_moments (nanogpt/dynamic_freeze.py:84-93): Chan's merge per cell."""
+    if count == 0:
+        return bn, bm.clone(), bm2.clone()
+    total = count + bn
+    delta = bm - mean
+    return total, mean + delta * (bn / total), m2 + bm2 + delta.square() * (count * bn / total)
+
+
 def negative_entropy_sum(att, eps=1e-12):
     """_negative_entropy_sum (:146-173): sum of p log p over samples, rows and columns per head, rows renormalised."""
     pr = att.float()

@@ -1,5 +1,6 @@
 // extern "C" entry points: argument validation, dispatch, error text.
 #include <stdarg.h>
+#include <stddef.h>
 #include <string.h>
 
 #include <atomic>
@@ -462,13 +463,20 @@ int saf_pattern_param_grad(const SafPatternGradArgs* a, void* stream) {
 
 int saf_attention_moments(const SafAttnStatsArgs* a, void* stream) {
   if (!a) return fail(SAF_ERR_INVALID, "null args");
-  if (a->struct_size != (int32_t)sizeof(SafAttnStatsArgs))
+  // the struct grew by `quantity` and `cell_m2`: a caller that stops at `status` measures probabilities
+  constexpr int32_t OLD_SIZE = (int32_t)offsetof(SafAttnStatsArgs, quantity);
+  if (a->struct_size != (int32_t)sizeof(SafAttnStatsArgs) && a->struct_size != OLD_SIZE)
     return fail(SAF_ERR_INVALID, "SafAttnStatsArgs size mismatch (%d vs %d)", a->struct_size, (int)sizeof(SafAttnStatsArgs));
-  if (a->B < 0 || a->U < 0 || a->T < 0 || a->HD <= 0 || a->count_prev < 0) return fail(SAF_ERR_INVALID, "bad dimension");
-  if (a->B == 0 || a->U == 0 || a->T == 0) return SAF_OK;
-  if (!a->q.ptr || !a->k.ptr || !a->lse.ptr || !a->mean || !a->head_m2 || !a->neg_entropy)
-    return fail(SAF_ERR_INVALID, "null pointer");
-  return launch_attn_stats_sm100(*a, (cudaStream_t)stream);
+  SafAttnStatsArgs x;
+  memset(&x, 0, sizeof(x));
+  memcpy(&x, a, (size_t)a->struct_size);
+  if (x.B < 0 || x.U < 0 || x.T < 0 || x.HD <= 0 || x.count_prev < 0) return fail(SAF_ERR_INVALID, "bad dimension");
+  if (x.quantity != SAF_STATS_PROBS && x.quantity != SAF_STATS_LOGITS) return fail(SAF_ERR_INVALID, "unknown quantity %d", x.quantity);
+  if (x.B == 0 || x.U == 0 || x.T == 0) return SAF_OK;
+  if (!x.q.ptr || !x.k.ptr || !x.mean) return fail(SAF_ERR_INVALID, "null pointer");
+  if (x.quantity == SAF_STATS_PROBS && (!x.lse.ptr || !x.head_m2 || !x.neg_entropy)) return fail(SAF_ERR_INVALID, "null pointer");
+  if (x.quantity == SAF_STATS_PROBS && x.cell_m2) return fail(SAF_ERR_INVALID, "cell_m2 goes with SAF_STATS_LOGITS");
+  return launch_attn_stats_sm100(x, (cudaStream_t)stream);
 }
 
 }  // extern "C"

@@ -11,6 +11,11 @@
 //   warps 0-15: four warpgroups x 32 key columns, thread = query row (TMEM lane)
 //   warp 16: TMA producer ([Q_b tile | K_b tile] ring), warp 17: MMA issuer
 // Every wait is bounded; on expiry the kernel records a code in *status and falls through.
+//
+// LOGITS: the same walk over the raw scores q k^T * sm_scale of the whole square (nothing masked, tiles above the
+// diagonal included), for the priors that sample logits (`_last_logits`, nanogpt/model.py:828-831, reduced at
+// nanogpt/dynamic_freeze.py:721-737 with _centered_batch_moments / _merge_moments, :62-93): running mean per cell and,
+// when asked for, the centred squares per cell; no per-head scalars.
 #include "saf_internal.h"
 #include "sm100_prims.cuh"
 
@@ -24,6 +29,8 @@ constexpr float AS_LN2 = 0.6931471805599453f;
 struct AsParams {
   int B, U, T, n_tiles;
   float scale_log2;
+  float scale;                 // LOGITS: sm_scale itself
+  float* cell_m2;              // LOGITS: (U, T, T) or null
   const float* lse;
   int64_t lse_s[3];
   float* mean;                 // (U, T, T)
@@ -77,7 +84,7 @@ __device__ __forceinline__ AsTile as_decode(const AsParams& p, int t) {
   return x;
 }
 
-template <int HD>
+template <int HD, bool LOGITS>
 __global__ void __launch_bounds__(AS_THREADS, 1)
 attn_stats_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
                   const __grid_constant__ AsParams p) {
@@ -120,7 +127,7 @@ attn_stats_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
       bool ok = true;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         const AsTile x = as_decode(p, t);
-        if (x.jt > x.it) continue;
+        if (!LOGITS && x.jt > x.it) continue;
         for (int b = 0; b < p.B; ++b, ++g) {
           const int s = g % C::NS;
           if (!mbar_wait(&sh->empty[s], ((g / C::NS) & 1) ^ 1)) {
@@ -143,7 +150,7 @@ attn_stats_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
     bool ok = true;
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
       const AsTile x = as_decode(p, t);
-      if (x.jt > x.it) continue;
+      if (!LOGITS && x.jt > x.it) continue;
       for (int b = 0; b < p.B; ++b, ++g) {
         const int s = g % C::NS, k = g & 1;
         if (!mbar_wait(&sh->full[s], (g / C::NS) & 1) || !mbar_wait(&sh->s_empty[k], ((g >> 1) & 1) ^ 1)) {
@@ -203,7 +210,7 @@ attn_stats_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
       const AsTile x = as_decode(p, t);
       float* mean_u = p.mean + (int64_t)x.u * p.T * p.T;
-      if (x.jt > x.it) {
+      if (!LOGITS && x.jt > x.it) {
         // above the diagonal every probability is zero: the first batch writes the zeros, later ones leave them
         if (p.count_prev == 0) {
           for (int e = tid; e < 128 * 128; e += AS_COMPUTE) {
@@ -213,7 +220,7 @@ attn_stats_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
         }
         continue;
       }
-      if (x.u != cur_u) {
+      if (!LOGITS && x.u != cur_u) {
         if (cur_u >= 0) flush_head();
         cur_u = x.u;
       }
@@ -221,7 +228,7 @@ attn_stats_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
       const bool row_ok = gi < p.T;
       const int gj0 = x.jt * 128 + cb;
       const bool diag = (x.it == x.jt);
-      const float* lse_u = p.lse + (int64_t)x.u * p.lse_s[1] + (int64_t)gi * p.lse_s[2];
+      const float* lse_u = LOGITS ? nullptr : p.lse + (int64_t)x.u * p.lse_s[1] + (int64_t)gi * p.lse_s[2];
       // The running batch mean of the tile lives in the padded staging tile (each thread owns 32 cells of its row
       // until the tile is finished), the centred squares in registers: that leaves room to fetch a sample's 32
       // scores in one TMEM load and to hand the buffer back before the arithmetic.
@@ -230,12 +237,12 @@ attn_stats_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
       for (int c = 0; c < 32; ++c) m2[c] = 0.f;
       float* srow = stage + r * C::STAGE_LD + cb;
       float ent = 0.f;                                // sum p log2 p of this thread's cells
-      float nl = row_ok ? lse_u[0] : INFINITY;        // +inf: rows past T hold zeros
+      float nl = LOGITS ? 0.f : (row_ok ? lse_u[0] : INFINITY);        // +inf: rows past T hold zeros
       named_bar_sync(2, AS_COMPUTE);                  // the previous tile's rows have left the staging tile
       for (int b = 0; b < p.B; ++b, ++g) {
         const int k = g & 1;
         const float L = nl;
-        if (b + 1 < p.B && row_ok) nl = lse_u[(int64_t)(b + 1) * p.lse_s[0]];
+        if (!LOGITS && b + 1 < p.B && row_ok) nl = lse_u[(int64_t)(b + 1) * p.lse_s[0]];
         if (!mbar_wait(&sh->s_full[k], (g >> 1) & 1)) {
           dev_set_error(p.status, SAF_DEV_TIMEOUT_SOFTMAX, 82);
           ok = false;
@@ -257,10 +264,15 @@ attn_stats_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             const int c = c4 * 4 + e;
-            float xl = fmaf(__uint_as_float(d[c]), sc, -L);             // log2 of the probability
-            if (diag && gj0 + c > gi) xl = -INFINITY;                   // causal mask inside the diagonal tile
-            const float pe = as_ex2(xl);
-            ent = fmaf(pe, fmaxf(xl, -200.f), ent);                     // p = 0 there, so the clamp only avoids 0 * inf
+            float pe;
+            if constexpr (LOGITS) {
+              pe = __uint_as_float(d[c]) * p.scale;                     // the raw score
+            } else {
+              float xl = fmaf(__uint_as_float(d[c]), sc, -L);           // log2 of the probability
+              if (diag && gj0 + c > gi) xl = -INFINITY;                 // causal mask inside the diagonal tile
+              pe = as_ex2(xl);
+              ent = fmaf(pe, fmaxf(xl, -200.f), ent);                   // p = 0 there, so the clamp only avoids 0 * inf
+            }
             // Welford update of the cell's mean and centred sum of squares over the batch
             const float dlt = pe - mm[e];
             mm[e] = fmaf(dlt, inv, mm[e]);
@@ -273,19 +285,28 @@ attn_stats_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
       // ---- merge the tile into the running mean (Chan).  A thread holds 32 cells of one row; written from there the
       // rows of a warp would be 32 separate 16-byte pieces per instruction, so every warp now takes whole 512-byte
       // rows out of the staging tile.
+      if constexpr (!LOGITS) {
 #pragma unroll
-      for (int c4 = 0; c4 < 8; ++c4)
-        m2sum += (double)(m2[c4 * 4] + m2[c4 * 4 + 1]) + (double)(m2[c4 * 4 + 2] + m2[c4 * 4 + 3]);
+        for (int c4 = 0; c4 < 8; ++c4)
+          m2sum += (double)(m2[c4 * 4] + m2[c4 * 4 + 1]) + (double)(m2[c4 * 4 + 2] + m2[c4 * 4 + 3]);
+      }
       // the old rows are requested before the barrier (the accumulators are dead by now), so their latency and the
       // wait for the slowest warp overlap
       double corr = 0.0;
       const int gjl = x.jt * 128 + lane * 4;
       float4 o[8], pv[8];
+      float dl2[LOGITS ? 8 : 1][4];                   // LOGITS: (batch mean - running mean)^2 of this thread's cells
+      if constexpr (LOGITS) {
+#pragma unroll
+        for (int rr = 0; rr < 8; ++rr)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) dl2[rr][e] = 0.f;
+      }
 #pragma unroll
       for (int rr = 0; rr < 8; ++rr) {
         pv[rr] = make_float4(0.f, 0.f, 0.f, 0.f);
         const int grow = x.it * 128 + warp * 8 + rr;
-        if (vec && p.count_prev > 0 && grow < p.T && gjl < p.T)
+        if (!LOGITS && vec && p.count_prev > 0 && grow < p.T && gjl < p.T)   // (LOGITS keeps more state: loaded where used)
           pv[rr] = *reinterpret_cast<const float4*>(mean_u + (int64_t)grow * p.T + gjl);
       }
       named_bar_sync(2, AS_COMPUTE);
@@ -300,12 +321,14 @@ attn_stats_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
         float ov[4] = {o[rr].x, o[rr].y, o[rr].z, o[rr].w};
         if (vec) {
           if (p.count_prev > 0) {
+            if constexpr (LOGITS) pv[rr] = *reinterpret_cast<const float4*>(dst);
             const float pr[4] = {pv[rr].x, pv[rr].y, pv[rr].z, pv[rr].w};
             float cs = 0.f;
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
               const float dlt = ov[e] - pr[e];
               cs = fmaf(dlt, dlt, cs);
+              if constexpr (LOGITS) dl2[rr][e] = dlt * dlt;
               ov[e] = fmaf(dlt, w, pr[e]);
             }
             corr += (double)cs;
@@ -320,23 +343,61 @@ attn_stats_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
               const float pr = dst[e];
               const float dlt = v - pr;
               corr += (double)(dlt * dlt);
+              if constexpr (LOGITS) dl2[rr][e] = dlt * dlt;
               v = fmaf(dlt, w, pr);
             }
             dst[e] = v;
           }
         }
       }
-      m2sum += corr * ((double)p.count_prev * (double)p.B / total);
-      esum += (double)ent * (double)AS_LN2;          // natural log, as the reference's xlogy
+      if constexpr (LOGITS) {
+        if (p.cell_m2) {
+          // the centred squares take the same way out: registers -> staging tile -> whole rows, merged per cell
+          const float cw = (float)((double)p.count_prev * (double)p.B / total);
+          float* m2_u = p.cell_m2 + (int64_t)x.u * p.T * p.T;
+          named_bar_sync(2, AS_COMPUTE);              // every warp has taken its mean rows out of the staging tile
+#pragma unroll
+          for (int c4 = 0; c4 < 8; ++c4)
+            *reinterpret_cast<float4*>(srow + c4 * 4) = make_float4(m2[c4 * 4], m2[c4 * 4 + 1], m2[c4 * 4 + 2], m2[c4 * 4 + 3]);
+          named_bar_sync(2, AS_COMPUTE);
+#pragma unroll
+          for (int rr = 0; rr < 8; ++rr) {
+            const int grow = x.it * 128 + warp * 8 + rr;
+            if (grow >= p.T || gjl >= p.T) continue;
+            const float4 b2 = *reinterpret_cast<const float4*>(stage + (warp * 8 + rr) * C::STAGE_LD + lane * 4);
+            float* dst = m2_u + (int64_t)grow * p.T + gjl;
+            float ov[4] = {b2.x, b2.y, b2.z, b2.w};
+            if (vec) {
+              if (p.count_prev > 0) {
+                const float4 old = *reinterpret_cast<const float4*>(dst);
+                ov[0] += fmaf(dl2[rr][0], cw, old.x);
+                ov[1] += fmaf(dl2[rr][1], cw, old.y);
+                ov[2] += fmaf(dl2[rr][2], cw, old.z);
+                ov[3] += fmaf(dl2[rr][3], cw, old.w);
+              }
+              *reinterpret_cast<float4*>(dst) = make_float4(ov[0], ov[1], ov[2], ov[3]);
+            } else {
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                if (gjl + e >= p.T) continue;
+                dst[e] = p.count_prev > 0 ? ov[e] + fmaf(dl2[rr][e], cw, dst[e]) : ov[e];
+              }
+            }
+          }
+        }
+      } else {
+        m2sum += corr * ((double)p.count_prev * (double)p.B / total);
+        esum += (double)ent * (double)AS_LN2;          // natural log, as the reference's xlogy
+      }
     }
-    if (ok && cur_u >= 0) flush_head();
+    if (!LOGITS && ok && cur_u >= 0) flush_head();
   }
   tc_fence_before();
   __syncthreads();
   if (warp == W_MMA) tmem_dealloc(tmem, C::TMEM_COLS);
 }
 
-template <int HD>
+template <int HD, bool LOGITS>
 int as_launch(const SafAttnStatsArgs& a, cudaStream_t st) {
   CUtensorMap mq, mk;
   int rc;
@@ -346,20 +407,22 @@ int as_launch(const SafAttnStatsArgs& a, cudaStream_t st) {
   p.B = a.B; p.U = a.U; p.T = a.T;
   p.n_tiles = (a.T + 127) / 128;
   p.scale_log2 = a.sm_scale * 1.4426950408889634f;
-  p.lse = reinterpret_cast<const float*>(a.lse.ptr);
-  for (int i = 0; i < 3; ++i) p.lse_s[i] = a.lse.stride[i];
+  p.scale = a.sm_scale;
+  p.cell_m2 = LOGITS ? a.cell_m2 : nullptr;
+  p.lse = LOGITS ? nullptr : reinterpret_cast<const float*>(a.lse.ptr);
+  for (int i = 0; i < 3; ++i) p.lse_s[i] = LOGITS ? 0 : a.lse.stride[i];
   p.mean = a.mean;
   p.count_prev = a.count_prev;
   p.head_m2 = a.head_m2;
   p.neg_entropy = a.neg_entropy;
   p.status = a.status;
   static PerDeviceOnce smem_once;
-  if (int rc2 = ensure_dyn_smem(attn_stats_kernel<HD>, AsCfg<HD>::SMEM_BYTES, smem_once)) return rc2;
+  if (int rc2 = ensure_dyn_smem(attn_stats_kernel<HD, LOGITS>, AsCfg<HD>::SMEM_BYTES, smem_once)) return rc2;
   const int64_t tiles = (int64_t)a.U * p.n_tiles * p.n_tiles;
   if (tiles > 0x7fffffff) return fail(SAF_ERR_LIMIT, "attention statistics: too many tiles");
   const int sm_count = device_sm_count();
   const int grid = (int)(tiles < sm_count ? tiles : sm_count);      // one persistent CTA per SM
-  attn_stats_kernel<HD><<<(unsigned)grid, AS_THREADS, AsCfg<HD>::SMEM_BYTES, st>>>(mq, mk, p);
+  attn_stats_kernel<HD, LOGITS><<<(unsigned)grid, AS_THREADS, AsCfg<HD>::SMEM_BYTES, st>>>(mq, mk, p);
   count_launch();
   return check_launch("attn_stats_kernel");
 }
@@ -372,7 +435,9 @@ int launch_attn_stats_sm100(const SafAttnStatsArgs& a, cudaStream_t st) {
     return fail(SAF_ERR_UNSUPPORTED, "attention statistics: q, k need 16-byte aligned rows and unit last stride");
   if ((uintptr_t)a.mean & 15) return fail(SAF_ERR_INVALID, "attention statistics: mean must be 16-byte aligned");
   if (!saf_device_supported()) return fail(SAF_ERR_UNSUPPORTED, "attention statistics need an sm_100 device");
-  return a.HD == 64 ? as_launch<64>(a, st) : as_launch<128>(a, st);
+  if ((uintptr_t)a.cell_m2 & 15) return fail(SAF_ERR_INVALID, "attention statistics: cell_m2 must be 16-byte aligned");
+  if (a.quantity == SAF_STATS_LOGITS) return a.HD == 64 ? as_launch<64, true>(a, st) : as_launch<128, true>(a, st);
+  return a.HD == 64 ? as_launch<64, false>(a, st) : as_launch<128, false>(a, st);
 }
 
 }  // namespace saf

@@ -86,9 +86,11 @@ class SafAttnStatsArgs(C.Structure):
         ("q", SafTensor), ("k", SafTensor), ("lse", SafTensor),
         ("mean", C.c_void_p), ("count_prev", C.c_int64), ("head_m2", C.c_void_p), ("neg_entropy", C.c_void_p),
         ("status", C.c_void_p),
+        ("quantity", C.c_int32), ("cell_m2", C.c_void_p),
     ]
 
 
+STATS_PROBS, STATS_LOGITS = 0, 1
 ACT_NONE, ACT_GELU, ACT_SWIGLU = 0, 1, 2
 
 EXPORTS = (

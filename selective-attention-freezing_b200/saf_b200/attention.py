@@ -118,25 +118,39 @@ class SafCausalSelfAttention(nn.Module):
             self.register_buffer("dyn_pattern", None)
         self._capture = False
         self._last_attn = None
+        self._last_logits = None
+        self._capture_logits = True
         self._retain_attention = True
         self._stats = None
+        self._logit_stats = None
         self._fz_dirty = True
 
     # ---- freeze state ---------------------------------------------------------------------
     def set_capture(self, flag, capture_logits=True, retain_attention=True):
         """nanogpt/model.py:690-703."""
         self._capture = bool(flag)
+        self._capture_logits = bool(capture_logits)
         self._retain_attention = bool(retain_attention)
         if not flag:
             self._last_attn = None
+            self._last_logits = None
 
-    def set_statistics(self, accumulator):
+    def set_statistics(self, accumulator, logit_accumulator=None):
         """Measurement without the capture: while an accumulator is set (a `saf_b200.capture.AttentionMoments` over
         this layer's live heads, in their compact order), every fused forward merges the attention statistics of
         its live heads into it from the rotated q, k -- what the controller derives from `_last_attn` after
         `set_capture(True)` (nanogpt/dynamic_freeze.py:664-745) -- and the fast path keeps running.  None switches
-        it off.  Frozen heads are not measured: their attention is the stored pattern."""
+        it off.  Frozen heads are not measured: their attention is the stored pattern.  `logit_accumulator` (a
+        `saf_b200.capture.LogitMoments`) does the same for the raw scores of the live heads, what
+        `set_capture(True, capture_logits=True)` retains as `_last_logits` (nanogpt/dynamic_freeze.py:721-737)."""
         self._stats = accumulator
+        self._logit_stats = logit_accumulator
+
+    def _measure(self, qu, ku):
+        if self._stats is not None:
+            self._stats.update(qu, ku)
+        if self._logit_stats is not None:
+            self._logit_stats.update(qu, ku)
 
     def sd_params(self):
         """(H, 2) fp32 view of the structured heads' (sink weight, decay)."""
@@ -319,9 +333,11 @@ class SafCausalSelfAttention(nn.Module):
     def _attend_dynamic(self, q, k, v):
         """Eager definition (nanogpt/model.py:824-844)."""
         B, nh, T, hd = q.shape
-        att = (q @ k.transpose(-2, -1)) * (1.0 / math.sqrt(hd))
+        scores = (q @ k.transpose(-2, -1)) * (1.0 / math.sqrt(hd))
+        if self._capture and self._capture_logits:
+            self._last_logits = scores.detach()          # raw, unmasked: for the priors that sample logits
         causal = torch.tril(torch.ones(T, T, dtype=torch.bool, device=q.device))
-        att = F.softmax(att.masked_fill(~causal, float("-inf")), dim=-1)
+        att = F.softmax(scores.masked_fill(~causal, float("-inf")), dim=-1)
         if self._n_frozen:
             fp = self._frozen_patterns(T).to(att.dtype).unsqueeze(0)
             att = torch.where(self.dyn_frozen.view(1, nh, 1, 1), fp.expand_as(att), att)
@@ -359,8 +375,8 @@ class SafCausalSelfAttention(nn.Module):
             qu = qkv[:, :, :nuf].transpose(1, 2)
             ku = qkv[:, :, nuf:2 * nuf].transpose(1, 2)
             v = qkv[:, :, 2 * nuf:].transpose(1, 2)
-            if self._stats is not None and nuf:
-                self._stats.update(qu, ku)
+            if nuf:
+                self._measure(qu, ku)
             y = ops.fused_mixed_attn(qu, ku, v, patt, self._fz_mask_i32, self._hidx_i32, pidx,
                                      alpha=dec[0], rho=dec[1], z=dec[2], validate=False, sink_decay=self._sd)
             y = y.transpose(1, 2).reshape(B, T, nh * hd)
@@ -381,8 +397,7 @@ class SafCausalSelfAttention(nn.Module):
             qk = ops.linear_rows2(x, self.q_proj.weight, self.k_proj.weight, self.q_proj.bias, self.k_proj.bias,
                                   self._uf_cols, rope=rp, head_dim=hd).view(B, T, 2, nuf, hd)
             qu, ku = qk[:, :, 0].transpose(1, 2), qk[:, :, 1].transpose(1, 2)
-            if self._stats is not None:
-                self._stats.update(qu.detach(), ku.detach())
+            self._measure(qu.detach(), ku.detach())
         if self.dropout > 0.0 and self.training and nuf:
             # The fused kernels implement no attention dropout.  As in the reference, which leaves its fused path
             # in this case and lets the SDPA half of its split path apply the dropout (nanogpt/model.py:971-974,

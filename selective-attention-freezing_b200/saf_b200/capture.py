@@ -7,6 +7,10 @@ matrix, the centred sum of squares summed over cells (`_centered_batch_reduced_m
 heads of one layer and updates them from q, k alone: one flash forward for the row log-sum-exp, then
 `saf_attention_moments`, which recomputes each probability tile on the tensor cores and merges it into the running
 mean in place.  Frozen heads need no measurement: their "attention" is the stored pattern (zero variance).
+
+Priors that sample logits also want per-cell statistics of the raw scores (`_last_logits`, nanogpt/model.py:828-831;
+merged at nanogpt/dynamic_freeze.py:721-737): `LogitMoments` keeps their running mean and, on request, centred squares,
+from the same kernel run on q k^T * sm_scale over the whole square.
 """
 import ctypes as C
 import math
@@ -14,7 +18,7 @@ import math
 import torch
 
 from . import ops
-from ._cabi import SafAttnStatsArgs, SafMixedAttnArgs, lib
+from ._cabi import STATS_LOGITS, SafAttnStatsArgs, SafMixedAttnArgs, lib
 
 
 def _row_lse(q, k, sm_scale):
@@ -90,3 +94,49 @@ class AttentionMoments:
             pr = pr / pr.sum(-1, keepdim=True).clamp_min(1e-12)
             mean_term += torch.xlogy(pr, pr).sum(dim=(1, 2)).double()
         return (sample_term - mean_term / T).clamp_min(0).float()
+
+
+@torch.no_grad()
+def logit_moments(q, k, mean, count_prev, cell_m2=None, sm_scale=None):
+    """Merge one batch of raw scores lg = q k^T * sm_scale (B, U, T, T, nothing masked) into running per-cell
+    statistics, in place: mean (U, T, T) fp32 becomes the Chan merge of `lg.mean(0)`; cell_m2 (U, T, T) fp32, when
+    given, that of `_centered_batch_moments(lg)` under `_merge_moments` (nanogpt/dynamic_freeze.py:62-93).
+    Returns the new count."""
+    ops._require_cuda(q, "q")
+    B, U, T, HD = q.shape
+    assert k.shape == q.shape, "q and k must have the same (B, U, T, hd) shape"
+    assert mean.shape == (U, T, T) and mean.dtype == torch.float32 and mean.is_contiguous()
+    if cell_m2 is not None:
+        assert cell_m2.shape == (U, T, T) and cell_m2.dtype == torch.float32 and cell_m2.is_contiguous()
+    a = SafAttnStatsArgs()
+    a.struct_size = C.sizeof(SafAttnStatsArgs)
+    a.dtype = ops._dt(q)
+    a.B, a.U, a.T, a.HD = B, U, T, HD
+    a.sm_scale = float(sm_scale if sm_scale is not None else 1.0 / math.sqrt(HD))
+    a.q, a.k = ops._st(q), ops._st(k)
+    a.mean = mean.data_ptr()
+    a.count_prev = int(count_prev)
+    a.status = ops._status_ptr(q.device)
+    a.quantity = STATS_LOGITS
+    a.cell_m2 = cell_m2.data_ptr() if cell_m2 is not None else None
+    ops._call(q, lib.saf_attention_moments, C.byref(a))
+    return int(count_prev) + B
+
+
+class LogitMoments:
+    """Running per-cell statistics of the raw scores of one layer's heads (`logit_mean` / `logit_m2` of `_measure`)."""
+
+    def __init__(self, n_heads, T, device, with_var=False):
+        self.count = 0
+        self.T = T
+        self.mean = torch.empty((n_heads, T, T), device=device, dtype=torch.float32)   # written by the first update
+        self.m2 = torch.empty((n_heads, T, T), device=device, dtype=torch.float32) if with_var else None
+
+    def update(self, q, k, sm_scale=None):
+        self.count = logit_moments(q, k, self.mean, self.count, self.m2, sm_scale)
+        return self
+
+    def std(self):
+        """`(logit_m2 / max(n - 1, 1)).clamp_min(0).sqrt()` (nanogpt/dynamic_freeze.py:787-790)."""
+        assert self.m2 is not None, "built without with_var"
+        return (self.m2 / max(self.count - 1, 1)).clamp_min(0).sqrt()

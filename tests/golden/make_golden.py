@@ -14,7 +14,8 @@ reference's behaviour travels.  What is recorded:
   * block level: the reference's LayerNorm and MLP modules (nanogpt/model.py:45-54, 1193-1207) on seeded inputs;
   * learnable patterns: dense_reference of supplement/trainable_patterns.py:7-13 with its autograd gradients;
   * controller statistics: _centered_batch_reduced_moments, _merge_reduced_moments, _negative_entropy_sum and
-    _mean_forward_kl_from_entropy of nanogpt/dynamic_freeze.py:96-193 on two seeded batches of softmax attention.
+    _mean_forward_kl_from_entropy of nanogpt/dynamic_freeze.py:96-193 on two seeded batches of softmax attention;
+    _centered_batch_moments and _merge_moments (:62-93) on the raw logits of the same batches.
 """
 import importlib.util
 import os
@@ -211,6 +212,16 @@ def main(ref_root):
         out[f"st_q{bi}"], out[f"st_k{bi}"] = qs.numpy(), ks.numpy()
         out[f"st_mean{bi}"], out[f"st_m2_{bi}"], out[f"st_negent{bi}"] = mean.numpy().copy(), m2.numpy().copy(), negent.numpy().copy()
     out["st_kl"] = DF._mean_forward_kl_from_entropy(negent, mean.float(), count).numpy()
+
+    # ---- per-cell statistics of the raw logits (the tensor model.py:828-831 retains as `_last_logits`), reduced with
+    # the reference's _centered_batch_moments / _merge_moments as _measure does (nanogpt/dynamic_freeze.py:721-727) ----
+    lcount, lmean, lm2 = 0, None, None
+    for bi in range(2):
+        qs, ks = torch.from_numpy(out[f"st_q{bi}"]), torch.from_numpy(out[f"st_k{bi}"])
+        lg = (qs @ ks.transpose(-2, -1)) * (1.0 / Ds ** 0.5)
+        lbn, lbm, lb2 = DF._centered_batch_moments(lg)
+        lcount, lmean, lm2 = DF._merge_moments(lcount, lmean, lm2, lbn, lbm, lb2)
+        out[f"lg_mean{bi}"], out[f"lg_m2_{bi}"] = lmean.numpy().copy(), lm2.numpy().copy()
 
     path = os.path.join(HERE, "reference_vectors.npz")
     np.savez_compressed(path, **out)

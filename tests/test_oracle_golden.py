@@ -179,6 +179,19 @@ def test_controller_statistics():
     assert O.max_abs(O.mean_forward_kl(negent, mean.float(), count), g("st_kl")) <= 1e-5
 
 
+def test_logit_statistics():
+    """Per-cell moments of the raw logits, merged over two batches, equal the reference's _centered_batch_moments /
+    _merge_moments (nanogpt/dynamic_freeze.py:62-93, used at :721-727)."""
+    count, mean, m2 = 0, None, None
+    for bi in range(2):
+        lg = O.raw_logits(g(f"st_q{bi}"), g(f"st_k{bi}"))
+        bn, bm, b2 = O.centered_batch_moments(lg)
+        count, mean, m2 = O.merge_moments(count, mean, m2, bn, bm, b2)
+        assert O.max_abs(mean, g(f"lg_mean{bi}")) <= 1e-6
+        assert O.max_abs(m2, g(f"lg_m2_{bi}")) <= 1e-5
+    assert count == 6
+
+
 # ---- grouped-query variant: vectors from the reference's own Qwen3 hybrid attention module (split torch path) ----
 GQ = np.load(os.path.join(os.path.dirname(__file__), "golden", "gqa_vectors.npz"))
 
