@@ -361,6 +361,25 @@ int saf_selftest_wait_timeout(int32_t* status, int64_t limit_ns, void* stream);
 /* Host-only check of the per-device bookkeeping (dynamic shared memory limits and SM counts are remembered per
  * device ordinal, never per process): 0 when it behaves, else the number of the failing step.  No CUDA call. */
 int saf_selftest_per_device_once(void);
+/* Hardware characterisation behind the kernels' tiling: one CTA per SM issues reps groups of tcgen05.mma
+ * instructions (bf16, M = 128, K = 16; eight per group unless stated) back to back and the first CTA writes the
+ * elapsed SM cycles to *cycles (device int64).  form & 255 selects what is issued:
+ *   0-7    one product, one operand form: 0 smem/smem K-major N 128, 1 TMEM / smem MN-major N 128, 2 TMEM / smem
+ *          MN-major N 64, 3 smem/smem MN-major N 256, 4 smem/smem K-major N 256, 5 TMEM / smem K-major N 128,
+ *          6 smem/smem K-major N 64, 7 smem K-major / smem MN-major N 128
+ *   8-11   forms 0 / 1 with operand addresses that change per group (ring stages): descriptors built per
+ *          instruction (8, 9) or advanced by an add (10, 11)
+ *   12-15  a new product every group: two accumulators in turn with / without a commit per group (12 / 13),
+ *          smem-operand and TMEM-operand products in turn (14), one accumulator with commits (15)
+ *   16-18  the products of a forward key step at head_dim 64 in turn: all from TMEM operands, 4 + 4 instructions
+ *          of N 64 (16); scores from shared memory (4 of N 128) and P V from TMEM (8 of N 64), alternating (17) or
+ *          as score, score, P V, P V (18)
+ *   19-21  form 14 with one thing changed: the TMEM-operand product as two halves of N 64 (19), with a K-major B
+ *          operand (20), with its A operand in consecutive columns (21)
+ * form + 256 fills the operands with random bf16 values instead of zeros; + 512 / 1024 / 2048 adds neighbour
+ * load while the instructions run: eight warps on tensor memory, eight warps on the arithmetic pipes, bulk
+ * copies landing in shared memory.  Every wait is bounded (status as in SafMixedAttnArgs, may be null). */
+int saf_selftest_mma_rate(int form, int reps, long long* cycles, int32_t* status, void* stream);
 
 #ifdef __cplusplus
 }

@@ -19,9 +19,9 @@
 // CTA = 384 threads: warps 0-3 and 4-7 are two compute warpgroups that split the 128 columns of a tile in
 // halves (TMEM lane = row = thread; both groups cover all 128 lanes), warp 8 TMA producer, warp 9 MMA
 // issuer (whole warp walks the schedule, one elected lane issues), warps 10-11 complete the third
-// warpgroup for the register reallocation.  The bf16 operand a compute warpgroup writes lands in the
-// first half of ITS OWN 64 score columns (half 0: columns 0-31, half 1: columns 64-95), so the other
-// group's unread scores are never overwritten; the TS MMA takes each 16-row k-step from its own address.
+// warpgroup for the register reallocation.  The bf16 operand the compute warpgroups write lands in the
+// first 64 columns of the tile they read (see operand_columns_read); the TS MMA takes K step ks from
+// columns 8 ks.
 // The sm_scale factor of dS is applied once to the finished dK / dQ accumulators.
 // Every wait is bounded; on expiry the kernel records a code in *status and falls through.
 #include "saf_internal.h"
@@ -41,8 +41,11 @@ constexpr float LOG2E_B = 1.4426950408889634f;
 // timing probe (only in specially built libraries): clock64 stamps of one CTA's pipeline events
 __device__ long long g_trace[2][8][64];   // [kernel][event][tile]
 #define TRACE(kern, evt, tile) do { if (trace_on && (tile) < 64) g_trace[kern][evt][tile] = clock64(); } while (0)
+__device__ long long g_wtrace[8][2][64];  // dK/dV kernel, per compute warp: [warp][P^T / dS^T handed over][tile]
+#define WTRACE(evt, tile) do { if (wtrace_on && (tile) < 64) g_wtrace[warp][evt][tile] = clock64(); } while (0)
 #else
 #define TRACE(kern, evt, tile) do { } while (0)
+#define WTRACE(evt, tile) do { } while (0)
 #endif
 
 template <int HD>
@@ -136,6 +139,26 @@ __device__ __forceinline__ void exp4(float (&o)[4], const uint32_t (&s)[4], floa
     o[2] = ex2b(x2); o[3] = ex2b(x3);
   }
 }
+// The bf16 operand the two compute warpgroups write for the next product lies in the first 64 columns of the fp32 tile
+// they have just read: group 0 (columns 0-63 of the tile) writes columns 0-31, group 1 (columns 64-127) writes columns
+// 32-63, which group 0 reads.  So group 1 stores only once group 0 has its values in registers: group 0 signals
+// after its tcgen05.wait::ld, group 1 waits (named barrier `id`, 256 threads, one-way).  In consecutive columns
+// the operand costs the tensor pipe 64 cycles per K step; split over the halves' own columns (0-31 and 64-95) a
+// product that follows a shared-memory-operand product took 90 (`saf_selftest_mma_rate` forms 14 / 21).
+// Group 0 signals as soon as its loads have landed, group 1 waits only in front of its first store, after the
+// arithmetic of its first 32 columns: by then the signal has long been given, also by group 0's slowest warp.
+__device__ __forceinline__ void operand_columns_read(int half, int id) {
+  if (half == 0) {
+    tc_fence_before();
+    named_bar_arrive(id, 256);
+  }
+}
+__device__ __forceinline__ void operand_columns_wait(int half, int id) {
+  if (half != 0) {
+    named_bar_sync(id, 256);
+    tc_fence_after();
+  }
+}
 // two fp32 -> packed bf16x2
 __device__ __forceinline__ uint32_t bpack(float lo, float hi) {
 #ifdef SAF_BWD_PACK_INT
@@ -157,22 +180,28 @@ __device__ __forceinline__ void bload_tile(uint8_t* dst, const CUtensorMap* m, u
   for (int hh = 0; hh < HD / 64; ++hh) tma_load_4d(dst + hh * 16384, m, bar, hh * 64, row, head, b);
 }
 
+// The issuing lane shares its scheduler with two compute warps that keep it busy, so every instruction between two
+// tcgen05.mma costs it tens of cycles: the two descriptors of a product are built once and each K step adds its
+// byte offset to their low words.
+//
 // D[128 x 128] = A[128 x HD] B[128 x HD]^T, both operands K-major tiles in shared memory
 template <int HD>
 __device__ __forceinline__ void issue_ss(uint32_t d, uint32_t a_smem, uint32_t b_smem, uint32_t idesc) {
+  const uint64_t da = umma_smem_desc_sw128(a_smem, 16, 1024), db = umma_smem_desc_sw128(b_smem, 16, 1024);
 #pragma unroll
   for (int ks = 0; ks < HD / 16; ++ks) {
     const uint32_t off = (ks >> 2) * 16384 + (ks & 3) * 32;
-    umma_ss(d, umma_smem_desc_sw128(a_smem + off, 16, 1024), umma_smem_desc_sw128(b_smem + off, 16, 1024), idesc, ks > 0);
+    umma_ss(d, umma_desc_advance(da, off), umma_desc_advance(db, off), idesc, ks > 0);
   }
 }
-// D[128 x HD] (+)= A[128 x 128] B[128 x HD]; A = bf16 in TMEM in the split layout described above,
+// D[128 x HD] (+)= A[128 x 128] B[128 x HD]; A = bf16 in the first 64 columns of its region in TMEM,
 // B = a [128 rows x HD] tile read MN-major
+template <int HD>
 __device__ __forceinline__ void issue_ts(uint32_t d, uint32_t a_tmem, uint32_t b_smem, uint32_t idesc, bool accumulate) {
+  const uint64_t db = umma_smem_desc_sw128(b_smem, 16384, 1024);
 #pragma unroll
   for (int ks = 0; ks < 8; ++ks)
-    umma_ts(d, a_tmem + (ks >> 2) * 64 + (ks & 3) * 8, umma_smem_desc_sw128(b_smem + ks * 2048, 16384, 1024), idesc,
-            accumulate || ks > 0);
+    umma_ts(d, a_tmem + ks * 8, umma_desc_advance(db, ks * 2048), idesc, accumulate || ks > 0);
 }
 
 // 32 fp32 accumulator columns [c0, c0+32) of row r -> bf16 -> 128-byte-swizzled staging tile
@@ -285,6 +314,7 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
   constexpr uint32_t COL_S = 0, COL_DP = 128, COL_DV = 256, COL_DK = 256 + HD;
 #ifdef SAF_BWD_TRACE
   const bool trace_on = (b == 0 && h == 0 && jt == 0) && (tid == 0 || tid == 9 * 32);
+  const bool wtrace_on = (b == 0 && h == 0 && jt == 0) && (tid & 31) == 0 && tid < 256;
 #endif
 
   if (warp >= 8) {
@@ -350,10 +380,11 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         tc_fence_after();
         TRACE(0, 4, i);   // issuer saw p_full
         if (leader) {
-          issue_ts(tmem + COL_DV, tmem + COL_S, adO, idesc_o, i > 0);
+          issue_ts<HD>(tmem + COL_DV, tmem + COL_S, adO, idesc_o, i > 0);
           umma_commit(&bars->v_empty[sd]);                // dO_i is not read again
         }
         __syncwarp();
+        TRACE(0, 6, i);   // dV issued
         const int s2 = (i + 1) % C::NQ, sd2 = (i + 1) % C::ND;
         const uint32_t aQ2 = aR + s2 * C::TILE_BYTES, adO2 = aRd + sd2 * C::TILE_BYTES;
         if (i + 1 < n) {
@@ -367,6 +398,7 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
             umma_commit(&bars->s_full[0]);
           }
           __syncwarp();
+          TRACE(0, 7, i);   // next S^T issued
         }
         if (!mbar_wait(&bars->ds_full, i & 1)) {
           dev_set_error(p.status, SAF_DEV_TIMEOUT_MMA, 45);
@@ -375,7 +407,7 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         tc_fence_after();
         TRACE(0, 5, i);   // issuer saw ds_full
         if (leader) {
-          issue_ts(tmem + COL_DK, tmem + COL_DP, aQ, idesc_o, i > 0);
+          issue_ts<HD>(tmem + COL_DK, tmem + COL_DP, aQ, idesc_o, i > 0);
           umma_commit(&bars->ring_empty[s]);              // Q_i is not read again
         }
         __syncwarp();
@@ -434,6 +466,7 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         tmem_ld32(tS + cb, s[0]);
         tmem_ld32(tS + cb + 32, s[1]);
         tmem_ld_wait();
+        operand_columns_read(half, 2);
 #pragma unroll
         for (int ch = 0; ch < 2; ++ch) {
           const float4* L4 = reinterpret_cast<const float4*>(&vec->lse[cb + ch * 32]);
@@ -455,13 +488,15 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
           uint32_t pk[16];
 #pragma unroll
           for (int x = 0; x < 16; ++x) pk[x] = bpack(pf[ch * 32 + 2 * x], pf[ch * 32 + 2 * x + 1]);
-          tmem_st16(tS + cb + ch * 16, pk);
+          if (ch == 0) operand_columns_wait(half, 2);
+          tmem_st16(tS + half * 32 + ch * 16, pk);
         }
       }
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(&bars->p_full);
       TRACE(0, 1, i);   // P^T handed over
+      WTRACE(0, i);
       // ---- dS^T
       if (!mbar_wait(&bars->dp_full, i & 1)) {
         dev_set_error(p.status, SAF_DEV_TIMEOUT_SOFTMAX, 47);
@@ -475,6 +510,7 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         tmem_ld32(tdP + cb, d[0]);
         tmem_ld32(tdP + cb + 32, d[1]);
         tmem_ld_wait();
+        operand_columns_read(half, 3);
 #pragma unroll
         for (int ch = 0; ch < 2; ++ch) {
           const float4* D4 = reinterpret_cast<const float4*>(&vec->dl[cb + ch * 32]);
@@ -489,13 +525,15 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
             pk[2 * x] = bpack(d0, d1);
             pk[2 * x + 1] = bpack(d2, d3);
           }
-          tmem_st16(tdP + cb + ch * 16, pk);
+          if (ch == 0) operand_columns_wait(half, 3);
+          tmem_st16(tdP + half * 32 + ch * 16, pk);
         }
       }
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(&bars->ds_full);
       TRACE(0, 3, i);   // dS^T handed over
+      WTRACE(1, i);
     }
     // ---- epilogue: dV_j, dK_j -> bf16 -> swizzled staging (the K / V tiles are no longer read) -> TMA store
     if (ok && !mbar_wait(&bars->acc_full, 0)) {
@@ -638,7 +676,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_const
         tc_fence_after();
         TRACE(1, 5, j);
         if (leader) {
-          issue_ts(tmem + COL_DQ, tmem + COL_DP, aK + s * C::TILE_BYTES, idesc_o, j > 0);
+          issue_ts<HD>(tmem + COL_DQ, tmem + COL_DP, aK + s * C::TILE_BYTES, idesc_o, j > 0);
           umma_commit(&bars->ring_empty[s]);          // K_j is not read again
         }
         __syncwarp();
@@ -702,17 +740,22 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_const
       }
       tc_fence_after();
       TRACE(1, 2, j);
-#pragma unroll
-      for (int ch = 0; ch < 2; ++ch) {
-        uint32_t d[32];
-        tmem_ld32(tdP + cb + ch * 32, d);
+      {
+        uint32_t d[2][32];
+        tmem_ld32(tdP + cb, d[0]);
+        tmem_ld32(tdP + cb + 32, d[1]);
         tmem_ld_wait();
-        uint32_t pk[16];
+        operand_columns_read(half, 2);
 #pragma unroll
-        for (int x = 0; x < 16; ++x)
-          pk[x] = bpack(pf[ch * 32 + 2 * x] * (__uint_as_float(d[2 * x]) - dl_r),
-                        pf[ch * 32 + 2 * x + 1] * (__uint_as_float(d[2 * x + 1]) - dl_r));
-        tmem_st16(tdP + cb + ch * 16, pk);
+        for (int ch = 0; ch < 2; ++ch) {
+          uint32_t pk[16];
+#pragma unroll
+          for (int x = 0; x < 16; ++x)
+            pk[x] = bpack(pf[ch * 32 + 2 * x] * (__uint_as_float(d[ch][2 * x]) - dl_r),
+                          pf[ch * 32 + 2 * x + 1] * (__uint_as_float(d[ch][2 * x + 1]) - dl_r));
+          if (ch == 0) operand_columns_wait(half, 2);
+          tmem_st16(tdP + half * 32 + ch * 16, pk);
+        }
       }
       tmem_st_wait();
       tc_fence_before();
@@ -913,6 +956,9 @@ int bwd_launch_typed(const SafMixedAttnBwdArgs& g, bool live, bool* dense_done, 
 #ifdef SAF_BWD_TRACE
 extern "C" int saf_debug_trace(long long* host) {
   return (int)cudaMemcpyFromSymbol(host, g_trace, sizeof(g_trace));
+}
+extern "C" int saf_debug_wtrace(long long* host) {
+  return (int)cudaMemcpyFromSymbol(host, g_wtrace, sizeof(g_wtrace));
 }
 #endif
 

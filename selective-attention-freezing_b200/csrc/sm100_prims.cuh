@@ -203,6 +203,13 @@ __device__ __forceinline__ uint64_t umma_smem_desc_sw128(uint32_t smem_addr, uin
          (1ull << 46) | (2ull << 61);
 }
 
+// The descriptor of the same tile `bytes` further on (a multiple of 16; the start address stays inside its 14-bit
+// field): one 32-bit add instead of building the descriptor from the address again.
+__device__ __forceinline__ uint64_t umma_desc_advance(uint64_t desc, uint32_t bytes) {
+  const uint32_t lo = (uint32_t)desc + (bytes >> 4);
+  return (desc & 0xffffffff00000000ull) | lo;
+}
+
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
@@ -269,6 +276,10 @@ __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
 // named barrier that also ORs a predicate over its threads: every thread gets the same answer, so a
 // decision such as "somebody's wait ran out" is taken by the whole group and nobody is left behind at a
 // later barrier
+// one-way: the caller only signals; `nthreads` counts the arriving and the waiting threads of the barrier together
+__device__ __forceinline__ void named_bar_arrive(int id, int nthreads) {
+  asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
 __device__ __forceinline__ bool named_bar_or(int id, int nthreads, bool pred) {
   uint32_t r;
   asm volatile(

@@ -99,7 +99,7 @@ EXPORTS = (
     "saf_indexed_linear_fwd", "saf_indexed_linear_bwd_dx", "saf_indexed_linear_bwd_dw",
     "saf_decomposed_logz", "saf_rope_slabs", "saf_layernorm_fwd", "saf_rmsnorm_fwd",
     "saf_pattern_normalisers", "saf_pattern_param_grad", "saf_attention_moments",
-    "saf_selftest_wait_timeout", "saf_selftest_per_device_once",
+    "saf_selftest_wait_timeout", "saf_selftest_per_device_once", "saf_selftest_mma_rate",
 )
 
 
@@ -150,6 +150,8 @@ def _load():
     lib.saf_rmsnorm_fwd.restype = C.c_int
     lib.saf_selftest_wait_timeout.argtypes = [C.c_void_p, C.c_int64, C.c_void_p]
     lib.saf_selftest_wait_timeout.restype = C.c_int
+    lib.saf_selftest_mma_rate.argtypes = [C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]
+    lib.saf_selftest_mma_rate.restype = C.c_int
     lib.saf_selftest_per_device_once.restype = C.c_int
     if lib.saf_abi_version() != 2:
         raise ImportError("libsaf_b200.so ABI version %d, expected 2: rebuild" % lib.saf_abi_version())

@@ -121,6 +121,8 @@ def main():
                     help="after the runs, print the per-step clock stamps a library built with -DSAF_FWD_TRACE / "
                          "-DSAF_BWD_TRACE recorded for one CTA (heaviest tile of batch 0, head 0; head 0 must be live)")
     args = ap.parse_args()
+    if "mma_rate" in args.ops.split(","):
+        return print_mma_rate()
     w = dict(synthetic.WORKLOADS[args.workload])
     if args.B:
         w["B"] = args.B
@@ -351,6 +353,51 @@ def main():
                           "tflops": round(fl / ms / 1e9, 1), "launches": n, **extra}), flush=True)
 
 
+MMA_FORMS = ("A smem K-major, B smem K-major, N 128", "A TMEM, B smem MN-major, N 128", "A TMEM, B smem MN-major, N 64",
+             "A smem MN-major, B smem MN-major, N 256", "A smem K-major, B smem K-major, N 256",
+             "A TMEM, B smem K-major, N 128", "A smem K-major, B smem K-major, N 64",
+             "A smem K-major, B smem MN-major, N 128",
+             "ring stages, descriptors built per instruction: A smem, B smem K-major, N 128",
+             "ring stages, descriptors built per instruction: A TMEM, B smem MN-major, N 128",
+             "ring stages, descriptors advanced by an add: A smem, B smem K-major, N 128",
+             "ring stages, descriptors advanced by an add: A TMEM, B smem MN-major, N 128",
+             "a new product every 8 instructions, two accumulators in turn, commit after each: smem operands, N 128",
+             "a new product every 8 instructions, two accumulators in turn, no commits: smem operands, N 128",
+             "a new product every 8 instructions, smem- and TMEM-operand products in turn, commit after each: N 128",
+             "a new product every 8 instructions, one accumulator, commit after each: smem operands, N 128",
+             "forward key step hd 64, all operands from TMEM: 4 score + 4 P V instructions of N 64 in turn, N 64",
+             "forward key step hd 64: 4 score instructions N 128 from smem, 8 P V instructions N 64 from TMEM, in turn, N 96",
+             "forward key step hd 64: as before, issued score, score, P V, P V, N 96",
+             "smem- and TMEM-operand products in turn, the TMEM-operand one as two halves of N 64 (12 per group), N 128",
+             "smem- and TMEM-operand products in turn, the TMEM-operand one with a K-major B operand, N 128",
+             "smem- and TMEM-operand products in turn, the TMEM operand in consecutive columns, N 128")
+
+
+def print_mma_rate(reps=2048):
+    """Cycles per tcgen05.mma instruction (bf16, M 128, K 16) for the operand forms the kernels use
+    (`saf_selftest_mma_rate`): alone on the SM, and with the neighbours a kernel gives the issuer -- warps on tensor
+    memory, warps on the arithmetic pipes, bulk copies landing in shared memory.  The kernels' clock-stamp traces are
+    read against these."""
+    dev = torch.device("cuda")
+    cyc = torch.zeros(1, dtype=torch.int64, device=dev)
+    st = torch.cuda.current_stream().cuda_stream
+
+    def pace(code):
+        for r in (8, reps, reps):                             # short warm-up launch first
+            ops.check(ops.lib.saf_selftest_mma_rate(code, r, cyc.data_ptr(), ops._status_ptr(dev), st))
+        ops.device_status(dev)
+        per_group = 4.0 if code & 255 == 16 else 6.0 if code & 255 in (17, 18) else 12.0 if code & 255 == 19 else 8.0
+        return round(cyc.item() / (per_group * reps), 1)
+
+    loads = (("alone", 0), ("tensor_memory_traffic", 512), ("arithmetic", 1024), ("bulk_copies", 2048), ("all_three", 3584))
+    for form, name in enumerate(MMA_FORMS):
+        row = {"op": "mma_rate", "form": name, "ideal_at_4096_mac_per_clk": 128 * int(name.rsplit(" ", 1)[1]) * 16 / 4096,
+               "alone_zero_operands": pace(form)}
+        for what, flag in loads:
+            row[what] = pace(form + 256 + flag)               # random operands
+        print(json.dumps(row))
+
+
 def print_trace():
     """Steady-state cycle counts of one CTA's pipeline from the trace arrays of a special build."""
     import ctypes
@@ -381,6 +428,22 @@ def print_trace():
                               "scores_visible_to_first_handover": mean(lambda j: t[first][j] - t[0][j]),
                               "dP_visible_to_dS_handed_over": mean(lambda j: t[3][j] - t[2][j]),
                               "dS_handed_over_to_next_scores_visible": mean(lambda j: t[0][j + 1] - t[3][j])}))
+            if kern == 0 and t[6][8]:
+                # issuer side of the dK/dV kernel: how long the 8 + 8 instructions of dV(i) and S^T(i+1) take to issue
+                print(json.dumps({"trace": name + ", issuer, cycles after the scores of the tile became visible",
+                                  "saw_P": mean(lambda j: t[4][j] - t[0][j]), "dV_issued": mean(lambda j: t[6][j] - t[0][j]),
+                                  "next_scores_issued": mean(lambda j: t[7][j] - t[0][j]),
+                                  "saw_dS": mean(lambda j: t[5][j] - t[0][j])}))
+    if hasattr(lib, "saf_debug_wtrace"):
+        wb = (ctypes.c_longlong * (8 * 2 * 64))()
+        lib.saf_debug_wtrace.argtypes = [ctypes.c_void_p]
+        lib.saf_debug_wtrace(wb)
+        buf0 = (ctypes.c_longlong * (2 * 8 * 64))()
+        lib.saf_debug_trace(buf0)
+        n = range(8, 40)
+        for evt, what in ((0, "P^T"), (1, "dS^T")):
+            print(json.dumps({"trace": "flash_bwd_dkdv, %s handed over per compute warp, cycles after scores visible" % what,
+                              "warps": [round(sum(wb[(w * 2 + evt) * 64 + j] - buf0[j] for j in n) / len(n)) for w in range(8)]}))
 
 
 if __name__ == "__main__":

@@ -56,3 +56,28 @@ class SafArgsProbe:
         a = _cabi.SafMixedAttnArgs()
         ops._fill_mixed(a, v, v, v, v, None, None, None, None, None, frozen, None, None, None, 0.125, None, None, [])
         return a
+
+
+def test_mma_rate_probe_reports_the_tensor_pipe_pace():
+    """The characterisation probe: a K = 16 step of a 128 x 128 product cannot beat 128 * 128 * 16 / 4096 = 64 cycles
+    (nominal dense bf16 rate) and, alone on the SM, stays near it; N = 64 from a TMEM operand halves it."""
+    from saf_b200 import _cabi, ops
+    dev = torch.device("cuda")
+    stream = C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+    cyc = torch.zeros(1, dtype=torch.int64, device=dev)
+    reps = 128
+    got = {}
+    for form in (0, 1, 2):
+        assert _cabi.lib.saf_selftest_mma_rate(form, reps, cyc.data_ptr(), ops._status_ptr(dev), stream) == 0
+        assert ops.device_status(dev) == 0
+        got[form] = cyc.item() / (8.0 * reps)
+    assert 60 <= got[0] <= 90 and 60 <= got[1] <= 90, got
+    assert 30 <= got[2] <= 50, got
+    # with the neighbour warps on tensor memory and arithmetic and bulk copies landing in shared memory the
+    # instructions still retire (slower), and nothing runs into a limit
+    assert _cabi.lib.saf_selftest_mma_rate(0 + 512 + 1024 + 2048, reps, cyc.data_ptr(), ops._status_ptr(dev), stream) == 0
+    assert ops.device_status(dev) == 0
+    assert got[0] - 1 <= cyc.item() / (8.0 * reps) <= 400
+    assert _cabi.lib.saf_selftest_mma_rate(-1, reps, cyc.data_ptr(), None, stream) == _cabi.SAF_ERR_INVALID
+    assert _cabi.lib.saf_selftest_mma_rate(200, reps, cyc.data_ptr(), None, stream) == _cabi.SAF_ERR_INVALID
+    assert _cabi.lib.saf_selftest_mma_rate(0, 0, cyc.data_ptr(), None, stream) == _cabi.SAF_ERR_INVALID
