@@ -347,11 +347,13 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
           const uint32_t qa = qaddr0 + t * C::TILE_BYTES, ka = kbase + ks_ * C::TILE_BYTES;
           const uint32_t d = tmem + buf * FN;
           if (leader) {
+            // (descriptors built once per product, advanced per K step: the issuing lane competes for its scheduler
+            // with two softmax warps, so every instruction it saves reaches the tensor pipe sooner)
+            const uint64_t dq = umma_smem_desc_sw128(qa, 16, 1024), dk = umma_smem_desc_sw128(ka, 16, 1024);
 #pragma unroll
             for (int ks = 0; ks < HD / 16; ++ks) {
               const uint32_t off = (ks >> 2) * 16384 + (ks & 3) * 32;
-              umma_ss(d, umma_smem_desc_sw128(qa + off, 16, 1024), umma_smem_desc_sw128(ka + off, 16, 1024), idesc_s,
-                      ks > 0);
+              umma_ss(d, umma_desc_advance(dq, off), umma_desc_advance(dk, off), idesc_s, ks > 0);
             }
             umma_commit(&bars->s_full[buf]);
             if (t == 1 || !act1) umma_commit(&bars->k_empty[ks_]);   // last reader of K_j
@@ -389,9 +391,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
           tc_fence_after();
           if (t == 0) FTRACE(3, j);
           if (leader) {
+            const uint64_t dv = umma_smem_desc_sw128(va, 16384, 1024);
 #pragma unroll
             for (int ks = 0; ks < FN / 16; ++ks)
-              umma_ts(dO, aP + ks * 8, umma_smem_desc_sw128(va + ks * 2048, 16384, 1024), idesc_o, (j > 0) || (ks > 0));
+              umma_ts(dO, aP + ks * 8, umma_desc_advance(dv, ks * 2048), idesc_o, (j > 0) || (ks > 0));
             umma_commit(&bars->buf_free[buf]);
             if (t == 1 || !act1) umma_commit(&bars->v_empty[vs_]);   // last reader of V_j
           }
@@ -938,11 +941,13 @@ flash_fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __gr
           const uint32_t qa = qaddr0 + t * C::TILE_BYTES, ka = kbase + ks_ * C::TILE_BYTES;
           const uint32_t d = tmem + buf * FN;
           if (leader) {
+            // (descriptors built once per product, advanced per K step: the issuing lane competes for its scheduler
+            // with two softmax warps, so every instruction it saves reaches the tensor pipe sooner)
+            const uint64_t dq = umma_smem_desc_sw128(qa, 16, 1024), dk = umma_smem_desc_sw128(ka, 16, 1024);
 #pragma unroll
             for (int ks = 0; ks < HD / 16; ++ks) {
               const uint32_t off = (ks >> 2) * 16384 + (ks & 3) * 32;
-              umma_ss(d, umma_smem_desc_sw128(qa + off, 16, 1024), umma_smem_desc_sw128(ka + off, 16, 1024), idesc_s,
-                      ks > 0);
+              umma_ss(d, umma_desc_advance(dq, off), umma_desc_advance(dk, off), idesc_s, ks > 0);
             }
             umma_commit(&bars->s_full[buf]);
             if (t == 1 || !g.act1) umma_commit(&bars->k_empty[ks_]);   // last reader of K_j
@@ -997,9 +1002,10 @@ flash_fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __gr
           const uint32_t va = vbase + vs_ * C::TILE_BYTES;
           const uint32_t dO = tmem + C::O_COL + t * HD, aP = tmem + buf * FN;
           if (leader) {
+            const uint64_t dv = umma_smem_desc_sw128(va, 16384, 1024);
 #pragma unroll
             for (int ks = 0; ks < FN / 16; ++ks)
-              umma_ts(dO, aP + ks * 8, umma_smem_desc_sw128(va + ks * 2048, 16384, 1024), idesc_o, (j > 0) || (ks > 0));
+              umma_ts(dO, aP + ks * 8, umma_desc_advance(dv, ks * 2048), idesc_o, (j > 0) || (ks > 0));
             umma_commit(&bars->buf_free[buf]);
             if (t == 1 || !g.act1) umma_commit(&bars->v_empty[vs_]);   // last reader of V_j
           }

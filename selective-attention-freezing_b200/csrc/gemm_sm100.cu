@@ -225,9 +225,10 @@ indexed_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_const
         const uint32_t a = sbase + s * STAGE_BYTES;
         const uint32_t b = a + A_BYTES;
         if (leader) {
+          const uint64_t ad0 = umma_smem_desc_sw128(a, 16, 1024), bd0 = umma_smem_desc_sw128(b, 16, 1024);
 #pragma unroll
           for (int k4 = 0; k4 < GK / 16; ++k4) {
-            const uint64_t ad = umma_smem_desc_sw128(a + k4 * 32, 16, 1024), bd = umma_smem_desc_sw128(b + k4 * 32, 16, 1024);
+            const uint64_t ad = umma_desc_advance(ad0, k4 * 32), bd = umma_desc_advance(bd0, k4 * 32);
             if constexpr (PAIR) umma_ss_pair(d, ad, bd, idesc, (kb | k4) != 0);
             else umma_ss(d, ad, bd, idesc, (kb | k4) != 0);
           }
