@@ -353,24 +353,33 @@ def main():
                           "tflops": round(fl / ms / 1e9, 1), "launches": n, **extra}), flush=True)
 
 
-MMA_FORMS = ("A smem K-major, B smem K-major, N 128", "A TMEM, B smem MN-major, N 128", "A TMEM, B smem MN-major, N 64",
-             "A smem MN-major, B smem MN-major, N 256", "A smem K-major, B smem K-major, N 256",
-             "A TMEM, B smem K-major, N 128", "A smem K-major, B smem K-major, N 64",
-             "A smem K-major, B smem MN-major, N 128",
-             "ring stages, descriptors built per instruction: A smem, B smem K-major, N 128",
-             "ring stages, descriptors built per instruction: A TMEM, B smem MN-major, N 128",
-             "ring stages, descriptors advanced by an add: A smem, B smem K-major, N 128",
-             "ring stages, descriptors advanced by an add: A TMEM, B smem MN-major, N 128",
-             "a new product every 8 instructions, two accumulators in turn, commit after each: smem operands, N 128",
-             "a new product every 8 instructions, two accumulators in turn, no commits: smem operands, N 128",
-             "a new product every 8 instructions, smem- and TMEM-operand products in turn, commit after each: N 128",
-             "a new product every 8 instructions, one accumulator, commit after each: smem operands, N 128",
-             "forward key step hd 64, all operands from TMEM: 4 score + 4 P V instructions of N 64 in turn, N 64",
-             "forward key step hd 64: 4 score instructions N 128 from smem, 8 P V instructions N 64 from TMEM, in turn, N 96",
-             "forward key step hd 64: as before, issued score, score, P V, P V, N 96",
-             "smem- and TMEM-operand products in turn, the TMEM-operand one as two halves of N 64 (12 per group), N 128",
-             "smem- and TMEM-operand products in turn, the TMEM-operand one with a K-major B operand, N 128",
-             "smem- and TMEM-operand products in turn, the TMEM operand in consecutive columns, N 128")
+# (what is issued, tensor-pipe cycles per instruction at 4096 multiply-adds per clock, instructions per group)
+MMA_FORMS = (
+    ("A smem K-major, B smem K-major, N 128", 64.0, 8),
+    ("A TMEM, B smem MN-major, N 128", 64.0, 8),
+    ("A TMEM, B smem MN-major, N 64", 32.0, 8),
+    ("A smem MN-major, B smem MN-major, N 256", 128.0, 8),
+    ("A smem K-major, B smem K-major, N 256", 128.0, 8),
+    ("A TMEM, B smem K-major, N 128", 64.0, 8),
+    ("A smem K-major, B smem K-major, N 64", 32.0, 8),
+    ("A smem K-major, B smem MN-major, N 128", 64.0, 8),
+    ("ring stages, descriptors built per instruction: A smem, B smem K-major, N 128", 64.0, 8),
+    ("ring stages, descriptors built per instruction: A TMEM, B smem MN-major, N 128", 64.0, 8),
+    ("ring stages, descriptors advanced by an add: A smem, B smem K-major, N 128", 64.0, 8),
+    ("ring stages, descriptors advanced by an add: A TMEM, B smem MN-major, N 128", 64.0, 8),
+    ("a new product every 8 instructions, two accumulators in turn, commit after each: smem operands, N 128", 64.0, 8),
+    ("a new product every 8 instructions, two accumulators in turn, no commits: smem operands, N 128", 64.0, 8),
+    ("smem-operand and TMEM-operand products in turn (TMEM operand in columns 0-31 and 64-95 of its region), N 128", 64.0, 8),
+    ("a new product every 8 instructions, one accumulator, commit after each: smem operands, N 128", 64.0, 8),
+    ("forward key step hd 64, all operands from TMEM: 4 score + 4 P V instructions of N 64 in turn", 32.0, 4),
+    ("forward key step hd 64: 4 score instructions N 128 from smem, 8 P V instructions N 64 from TMEM, in turn",
+     512.0 / 12, 6),
+    ("forward key step hd 64: the same, issued score, score, P V, P V", 512.0 / 12, 6),
+    ("smem- and TMEM-operand products in turn, the TMEM-operand one as two halves of N 64 (8 + 16 instructions)",
+     1024.0 / 24, 12),
+    ("smem- and TMEM-operand products in turn, the TMEM-operand one with a K-major B operand, N 128", 64.0, 8),
+    ("smem- and TMEM-operand products in turn, the TMEM operand in consecutive columns, N 128", 64.0, 8),
+)
 
 
 def print_mma_rate(reps=2048):
@@ -386,12 +395,11 @@ def print_mma_rate(reps=2048):
         for r in (8, reps, reps):                             # short warm-up launch first
             ops.check(ops.lib.saf_selftest_mma_rate(code, r, cyc.data_ptr(), ops._status_ptr(dev), st))
         ops.device_status(dev)
-        per_group = 4.0 if code & 255 == 16 else 6.0 if code & 255 in (17, 18) else 12.0 if code & 255 == 19 else 8.0
-        return round(cyc.item() / (per_group * reps), 1)
+        return round(cyc.item() / (float(MMA_FORMS[code & 255][2]) * reps), 1)
 
     loads = (("alone", 0), ("tensor_memory_traffic", 512), ("arithmetic", 1024), ("bulk_copies", 2048), ("all_three", 3584))
-    for form, name in enumerate(MMA_FORMS):
-        row = {"op": "mma_rate", "form": name, "ideal_at_4096_mac_per_clk": 128 * int(name.rsplit(" ", 1)[1]) * 16 / 4096,
+    for form, (name, ideal, _) in enumerate(MMA_FORMS):
+        row = {"op": "mma_rate", "form": name, "tensor_pipe_cycles_per_instruction": round(ideal, 1),
                "alone_zero_operands": pace(form)}
         for what, flag in loads:
             row[what] = pace(form + 256 + flag)               # random operands
