@@ -444,18 +444,31 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
       return row < p.T ? dl_g[(int64_t)row * p.delta_s[2]] : 0.f;
     };
     float nxt = fetch(jt);
+    // A warp whose wait ran out (decided for the whole warp) stops working but keeps taking part, one-way, in the
+    // named barriers of every remaining tile -- two arrivals on barrier 1, one each on 2 and 3 per tile, as a working
+    // warp gives -- so the other warps never block on it; they run into their own limits because P^T / dS^T stay
+    // incomplete, and all meet again at the epilogue's barrier.
     bool ok = true;
     for (int i = 0; i < n; ++i) {
+      if (!ok) {
+        named_bar_arrive(1, 256);
+        named_bar_arrive(1, 256);
+        named_bar_arrive(2, 256);
+        named_bar_arrive(3, 256);
+        continue;
+      }
       named_bar_sync(1, 256);                 // the previous tile's readers are done with the vectors
       if (tid < 128) vec->lse[r] = nxt;
       else vec->dl[r] = nxt;
       named_bar_sync(1, 256);
       if (i + 1 < n) nxt = fetch(jt + i + 1);
       // ---- P^T
-      if (!mbar_wait(&bars->s_full[0], i & 1)) {
+      if (!__all_sync(0xffffffffu, mbar_wait(&bars->s_full[0], i & 1))) {
         dev_set_error(p.status, SAF_DEV_TIMEOUT_SOFTMAX, 46);
         ok = false;
-        break;
+        named_bar_arrive(2, 256);
+        named_bar_arrive(3, 256);
+        continue;
       }
       tc_fence_after();
       TRACE(0, 0, i);   // scores visible
@@ -498,10 +511,11 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
       TRACE(0, 1, i);   // P^T handed over
       WTRACE(0, i);
       // ---- dS^T
-      if (!mbar_wait(&bars->dp_full, i & 1)) {
+      if (!__all_sync(0xffffffffu, mbar_wait(&bars->dp_full, i & 1))) {
         dev_set_error(p.status, SAF_DEV_TIMEOUT_SOFTMAX, 47);
         ok = false;
-        break;
+        named_bar_arrive(3, 256);
+        continue;
       }
       tc_fence_after();
       TRACE(0, 2, i);   // dP^T visible
@@ -701,13 +715,19 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_const
       lse_r = p.lse[(int64_t)b * p.lse_s[0] + (int64_t)h * p.lse_s[1] + (int64_t)row * p.lse_s[2]];
       dl_r = p.delta[(int64_t)b * p.delta_s[0] + (int64_t)h * p.delta_s[1] + (int64_t)row * p.delta_s[2]];
     }
+    // (a warp whose wait ran out keeps giving its one arrival per tile on named barrier 2, as in the dK/dV kernel)
     bool ok = true;
     for (int j = 0; j < n; ++j) {
+      if (!ok) {
+        named_bar_arrive(2, 256);
+        continue;
+      }
       const uint32_t tS = tmem + lane_base + COL_S + (j & 1) * 128;
-      if (!mbar_wait(&bars->s_full[j & 1], (j >> 1) & 1)) {
+      if (!__all_sync(0xffffffffu, mbar_wait(&bars->s_full[j & 1], (j >> 1) & 1))) {
         dev_set_error(p.status, SAF_DEV_TIMEOUT_SOFTMAX, 54);
         ok = false;
-        break;
+        named_bar_arrive(2, 256);
+        continue;
       }
       tc_fence_after();
       TRACE(1, 0, j);
@@ -733,10 +753,11 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_const
             if (cb + ch * 32 + x > r) pf[ch * 32 + x] = 0.f;
         }
       }
-      if (!mbar_wait(&bars->dp_full, j & 1)) {
+      if (!__all_sync(0xffffffffu, mbar_wait(&bars->dp_full, j & 1))) {
         dev_set_error(p.status, SAF_DEV_TIMEOUT_SOFTMAX, 55);
         ok = false;
-        break;
+        named_bar_arrive(2, 256);
+        continue;
       }
       tc_fence_after();
       TRACE(1, 2, j);
