@@ -155,8 +155,8 @@ __device__ __forceinline__ void mr_issue_group(uint32_t tmem, uint32_t tmem_a, u
 // to itself:
 //   1  eight other warps keep reading the accumulator and writing packed operands in tensor memory (tcgen05.ld / st)
 //   2  eight other warps keep the FMA and special-function pipes busy (two of them share the issuer's scheduler)
-//   4  one thread keeps 32 KB bulk copies from global into shared memory in flight (what TMA loads do to the
-//      shared-memory write port)
+//   4  one thread keeps pairs of 32 KB bulk copies from global into shared memory in flight (what TMA loads do to
+//      the shared-memory write port)
 constexpr int MR_THREADS = 320;          // warps 0-7 neighbours, warp 8 issuer, warp 9 copy thread
 constexpr int MR_COPY_BYTES = 32 * 1024;
 __device__ uint4 g_mr_src[MR_COPY_BYTES / 16];
@@ -266,10 +266,12 @@ mma_rate_kernel(int reps, int random_operands, int load, long long* cycles, int*
     __syncwarp();
   } else if (warp == 9) {
     if ((load & 4) && (tid & 31) == 0) {
-      // copies into [96 KB, 128 KB) of the buffer, which no operand form reads; at most 4096 of them
+      // two 32 KB copies per round (the size of a Q and a dO tile) into [96 KB, 160 KB) of the buffer, which no
+      // operand form reads; at most 4096 rounds
       for (int n = 0; n < 4096 && !sh->done; ++n) {
-        mbar_expect_tx(&sh->copy_bar, MR_COPY_BYTES);
+        mbar_expect_tx(&sh->copy_bar, 2 * MR_COPY_BYTES);
         mr_bulk_g2s(smem + 96 * 1024, g_mr_src, MR_COPY_BYTES, &sh->copy_bar);
+        mr_bulk_g2s(smem + 128 * 1024, g_mr_src, MR_COPY_BYTES, &sh->copy_bar);
         if (!mbar_wait(&sh->copy_bar, n & 1)) {
           dev_set_error(status, SAF_DEV_TIMEOUT_SELFTEST, 97);
           break;
