@@ -174,3 +174,29 @@ def test_fft_normalisers_match_the_direct_ones_and_differentiate():
     a2, r2 = alpha.clone().requires_grad_(True), rho.clone().requires_grad_(True)
     O.decomp_logits(a2, r2).logsumexp(-1).sum().backward()
     assert O.max_abs(a1.grad, a2.grad) <= 1e-4 and O.max_abs(r1.grad, r2.grad) <= 1e-4
+
+
+def test_statistics_entry_accepts_the_shorter_struct_and_refuses_unknown_quantities():
+    """SafAttnStatsArgs grew by `quantity` and `cell_m2`: a caller that stops at `status` (the struct as it was)
+    is still served, any other size and any unknown quantity are INVALID; empty problems return before a launch."""
+    import ctypes as C
+    from saf_b200 import _cabi
+    a = _cabi.SafAttnStatsArgs()
+    full = C.sizeof(_cabi.SafAttnStatsArgs)
+    short = _cabi.SafAttnStatsArgs.quantity.offset
+    assert short < full
+    a.B, a.U, a.T, a.HD = 0, 2, 128, 64            # empty batch: nothing to launch
+    for size in (full, short):
+        a.struct_size = size
+        assert _cabi.lib.saf_attention_moments(C.byref(a), None) == 0
+    a.struct_size = full - 4
+    assert _cabi.lib.saf_attention_moments(C.byref(a), None) == _cabi.SAF_ERR_INVALID
+    a.struct_size = full
+    a.quantity = 7
+    assert _cabi.lib.saf_attention_moments(C.byref(a), None) == _cabi.SAF_ERR_INVALID
+    a.quantity = _cabi.STATS_LOGITS
+    assert _cabi.lib.saf_attention_moments(C.byref(a), None) == 0
+    # the probe validates its arguments before it looks for a device
+    assert _cabi.lib.saf_selftest_mma_rate(0, 16, None, None, None) == _cabi.SAF_ERR_INVALID
+    assert _cabi.lib.saf_selftest_mma_rate(0, 0, C.c_void_p(8), None, None) == _cabi.SAF_ERR_INVALID
+    assert _cabi.lib.saf_selftest_mma_rate(5000, 16, C.c_void_p(8), None, None) == _cabi.SAF_ERR_INVALID
